@@ -1,0 +1,1007 @@
+// The C ABI: context / stream / buffer / event objects, the checked prepare +
+// launch surface, the runtime adapter and the bounded wait.  Mirrors
+// fe2o3-core (crates/fe2o3-core/src/{context,stream,memory,event}.rs), the
+// generated host adapters (crates/fe2o3-host/src/generated_*.rs) and the
+// executable lifecycle adapter (crates/fe2o3-host/src/hsa_executable_lifecycle.rs).
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <atomic>
+#include <chrono>
+#include <new>
+#include <thread>
+
+#include "gemm_tc.h"
+
+// ---- launchers implemented by the kernel sources -----------------------------
+typedef int32_t (*LaunchFn)(fe2o3_ctx *, cudaStream_t, const void *, fe2o3_geometry *, bool);
+int32_t launch_masked_reduce_u32(fe2o3_ctx *, cudaStream_t, const void *, fe2o3_geometry *, bool);
+int32_t launch_masked_reduce_u32_packed(fe2o3_ctx *, cudaStream_t, const void *, fe2o3_geometry *, bool);
+int32_t launch_wave_lds_v1(fe2o3_ctx *, cudaStream_t, const void *, fe2o3_geometry *, bool);
+int32_t launch_wave64_collectives_v1(fe2o3_ctx *, cudaStream_t, const void *, fe2o3_geometry *, bool);
+int32_t launch_wave64_collectives_segmented(fe2o3_ctx *, cudaStream_t, const void *, fe2o3_geometry *, bool);
+int32_t launch_lds_reduce_i32(fe2o3_ctx *, cudaStream_t, const void *, fe2o3_geometry *, bool);
+int32_t launch_scoped_atomic_add(fe2o3_ctx *, cudaStream_t, const void *, fe2o3_geometry *, bool);
+int32_t launch_row_softmax(fe2o3_ctx *, cudaStream_t, const void *, fe2o3_geometry *, bool);
+int32_t launch_moe_gate(fe2o3_ctx *, cudaStream_t, const void *, fe2o3_geometry *, bool);
+int32_t launch_moe_top2(fe2o3_ctx *, cudaStream_t, const void *, fe2o3_geometry *, bool);
+int32_t launch_moe_route_weights(fe2o3_ctx *, cudaStream_t, const void *, fe2o3_geometry *, bool);
+int32_t launch_moe_combine(fe2o3_ctx *, cudaStream_t, const void *, fe2o3_geometry *, bool);
+int32_t launch_moe_compact(cudaStream_t, uint64_t x, uint64_t perm, uint64_t compact_x, uint32_t rows,
+                           uint32_t d_model, uint32_t tokens);
+int32_t launch_gemm_exact(cudaStream_t, uint32_t dtype, bool epilogue, uint64_t a, uint64_t b, uint64_t c, uint32_t M,
+                          uint32_t N, uint32_t K, uint32_t lda, uint32_t ldb, uint32_t ldc, float alpha, float beta,
+                          fe2o3_geometry *, bool);
+int32_t launch_attention_simt(fe2o3_ctx *, cudaStream_t, const fe2o3_flash_attention_v1_args *, fe2o3_geometry *, bool);
+
+struct AttnTcPlan;
+bool attention_tc_supported(const fe2o3_flash_attention_v1_args *);
+int32_t attention_tc_plan(fe2o3_ctx *, const fe2o3_flash_attention_v1_args *, AttnTcPlan **);
+int32_t attention_tc_launch(const AttnTcPlan *, cudaStream_t);
+void attention_tc_geometry(const AttnTcPlan *, fe2o3_geometry *);
+void attention_tc_free(AttnTcPlan *);
+
+// ---- error bookkeeping ---------------------------------------------------------
+static thread_local char g_error[512] = "";
+static std::atomic<uint64_t> g_launches{0};
+
+void fe2o3_set_error(const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof g_error, fmt, ap);
+    va_end(ap);
+}
+void fe2o3_count_launch(uint32_t n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+int32_t fe2o3_cuda_status(cudaError_t e, const char *what) {
+    if (e == cudaSuccess) return FE2O3_OK;
+    fe2o3_set_error("%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
+    if (e == cudaErrorNoDevice || e == cudaErrorInsufficientDriver) return FE2O3_ERR_NO_DEVICE;
+    return (int32_t)e;
+}
+
+struct fe2o3_buf {
+    fe2o3_ctx *ctx;
+    void *ptr;
+    uint64_t elements;
+    uint32_t element_bytes;
+    bool quarantined;
+};
+struct fe2o3_event {
+    fe2o3_ctx *ctx;
+    cudaEvent_t e;
+};
+
+enum OpId : uint32_t {
+    OP_SCALAR_GEMM, OP_TILED_GEMM, OP_TILED_GEMM_GENERAL, OP_FLASH_ATTENTION, OP_ROW_SOFTMAX, OP_MOE_TOP2,
+    OP_MOE_GATE, OP_MOE_ROUTE_WEIGHTS, OP_MOE_EXPERT_FFN, OP_MOE_COMBINE, OP_MASKED_REDUCE, OP_MASKED_REDUCE_PACKED,
+    OP_WAVE_LDS, OP_WAVE64_COLLECTIVES, OP_WAVE64_SEGMENTED, OP_LDS_REDUCE_I32, OP_SCOPED_ATOMIC_ADD, OP_COUNT
+};
+
+struct OpInfo {
+    const char *symbol;  // the reference kernel function name this entry replaces
+    uint64_t kernarg_bytes;
+    LaunchFn simple;     // non-null for ops with a single uniform launcher
+};
+
+static const OpInfo kOps[OP_COUNT] = {
+    {"scalar_gemm_v1", sizeof(fe2o3_scalar_gemm_v1_args), nullptr},
+    {"tiled_gemm_lds_slice1", sizeof(fe2o3_tiled_gemm_v1_args), nullptr},
+    {"tiled_gemm_general_v1", sizeof(fe2o3_tiled_gemm_general_v1_args), nullptr},
+    {"flash_attention_v1", sizeof(fe2o3_flash_attention_v1_args), nullptr},
+    {"row_softmax_v1", sizeof(fe2o3_row_softmax_v1_args), launch_row_softmax},
+    {"moe_top2_v1", sizeof(fe2o3_moe_top2_v1_args), launch_moe_top2},
+    {"moe_gate_v1", sizeof(fe2o3_moe_gate_v1_args), launch_moe_gate},
+    {"moe_route_weights_v1", sizeof(fe2o3_moe_route_weights_v1_args), launch_moe_route_weights},
+    {"moe_expert_ffn_v1", sizeof(fe2o3_moe_expert_ffn_v1_args), nullptr},
+    {"moe_expert_combine_v1", sizeof(fe2o3_moe_expert_combine_v1_args), launch_moe_combine},
+    {"masked_reduce_sum_u32", sizeof(fe2o3_masked_reduce_u32_args), launch_masked_reduce_u32},
+    {"masked_reduce_sum_u32_packed", sizeof(fe2o3_masked_reduce_u32_packed_args), launch_masked_reduce_u32_packed},
+    {"gfx942_wave_lds_v1_hw", sizeof(fe2o3_wave_lds_v1_args), launch_wave_lds_v1},
+    {"wave64_collectives_v1", sizeof(fe2o3_wave64_collectives_v1_args), launch_wave64_collectives_v1},
+    {"wave64_collectives_segmented", sizeof(fe2o3_wave64_collectives_segmented_args), launch_wave64_collectives_segmented},
+    {"lds_publish_read_reduce_i32_v1", sizeof(fe2o3_lds_publish_read_reduce_i32_v1_args), launch_lds_reduce_i32},
+    {"scoped_atomic_add_u32_v1", sizeof(fe2o3_scoped_atomic_add_u32_v1_args), launch_scoped_atomic_add},
+};
+
+struct fe2o3_prepared {
+    fe2o3_ctx *ctx;
+    uint32_t op;
+    alignas(8) uint8_t kernarg[192];
+    uint32_t schedule;   // GEMM: resolved schedule
+    GemmTcPlan gemm[2];  // tcgen05 plans (FFN uses both)
+    AttnTcPlan *attn;
+    fe2o3_geometry geo;
+};
+
+struct fe2o3_executable {
+    fe2o3_ctx *ctx;
+};
+
+// ---- region checks ---------------------------------------------------------------
+namespace {
+
+struct Region {
+    const char *role;
+    fe2o3_slice s;
+    uint64_t expected;
+    uint32_t elem_bytes;
+    bool output;
+};
+
+bool mul_overflow(uint64_t a, uint64_t b, uint64_t *r) { return __builtin_mul_overflow(a, b, r); }
+
+int32_t check_regions(const Region *r, int n) {
+    uint64_t lo[16], hi[16];
+    for (int i = 0; i < n; ++i) {
+        if (r[i].s.len != r[i].expected) {
+            fe2o3_set_error("Length{role=%s, expected=%llu, actual=%llu}", r[i].role,
+                            (unsigned long long)r[i].expected, (unsigned long long)r[i].s.len);
+            return FE2O3_ERR_LENGTH;
+        }
+        uint64_t bytes;
+        if (mul_overflow(r[i].s.len, r[i].elem_bytes, &bytes) || r[i].s.ptr + bytes < r[i].s.ptr) {
+            fe2o3_set_error("RegionOverflow{role=%s}", r[i].role);
+            return FE2O3_ERR_INVALID_REGION;
+        }
+        if (r[i].s.len != 0 && r[i].s.ptr == 0) {
+            fe2o3_set_error("NullAddress{role=%s}", r[i].role);
+            return FE2O3_ERR_NULL_ADDRESS;
+        }
+        if (r[i].s.ptr % r[i].elem_bytes != 0) {
+            fe2o3_set_error("Alignment{role=%s}", r[i].role);
+            return FE2O3_ERR_ALIGNMENT;
+        }
+        lo[i] = r[i].s.ptr;
+        hi[i] = r[i].s.ptr + bytes;
+    }
+    for (int o = 0; o < n; ++o) {
+        if (!r[o].output || lo[o] == hi[o]) continue;
+        for (int i = 0; i < n; ++i) {
+            if (i == o || lo[i] == hi[i]) continue;
+            if (r[i].output && i < o) continue;  // output pairs are checked once
+            if (lo[i] < hi[o] && lo[o] < hi[i]) {
+                fe2o3_set_error("OutputAliasesInput{output=%s, input=%s}", r[o].role, r[i].role);
+                return FE2O3_ERR_OUTPUT_ALIASES_INPUT;
+            }
+        }
+    }
+    return FE2O3_OK;
+}
+
+// storage extent of a strided matrix: (rows-1)*ld + cols, or 0 when empty
+bool extent(uint64_t rows, uint64_t cols, uint64_t ld, uint64_t *out) {
+    if (rows == 0 || cols == 0) { *out = 0; return true; }
+    uint64_t t;
+    if (mul_overflow(rows - 1, ld, &t) || t + cols < t) return false;
+    *out = t + cols;
+    return true;
+}
+
+int32_t unsupported(const char *why) {
+    fe2o3_set_error("UnsupportedShape: %s", why);
+    return FE2O3_ERR_UNSUPPORTED_SHAPE;
+}
+
+int32_t check_ctx_device(fe2o3_ctx *ctx, const Region *r, int n) {
+    for (int i = 0; i < n; ++i) {
+        if (r[i].s.len == 0) continue;
+        cudaPointerAttributes attr;
+        cudaError_t e = cudaPointerGetAttributes(&attr, reinterpret_cast<const void *>(r[i].s.ptr));
+        if (e != cudaSuccess) { cudaGetLastError(); continue; }
+        if ((attr.type == cudaMemoryTypeDevice) && attr.device != ctx->device) {
+            fe2o3_set_error("WrongContext{role=%s, device=%d, context_device=%d}", r[i].role, attr.device, ctx->device);
+            return FE2O3_ERR_DEVICE_MISMATCH;
+        }
+        if (attr.type == cudaMemoryTypeUnregistered || attr.type == cudaMemoryTypeHost) {
+            fe2o3_set_error("WrongContext{role=%s}: not device memory", r[i].role);
+            return FE2O3_ERR_DEVICE_MISMATCH;
+        }
+    }
+    return FE2O3_OK;
+}
+
+#define RGN(role_, slice_, expected_, bytes_, out_) Region{role_, slice_, (uint64_t)(expected_), bytes_, out_}
+
+// Per-op region tables.  Returns the number of regions, fills `r`.
+int regions_for(uint32_t op, const void *args, Region *r, int32_t *status) {
+    *status = FE2O3_OK;
+    switch (op) {
+        case OP_SCALAR_GEMM:
+        case OP_TILED_GEMM: {
+            const fe2o3_scalar_gemm_v1_args *a = static_cast<const fe2o3_scalar_gemm_v1_args *>(args);
+            const uint32_t eb = op == OP_SCALAR_GEMM ? 4 : 2;
+            if (op == OP_TILED_GEMM && ((a->m % 16) || (a->n % 16) || (a->k % 16))) {
+                *status = unsupported("tiled_gemm_v1 admits M, N, K multiples of 16 (tails rejected)");
+                return 0;
+            }
+            r[0] = RGN("A", a->a, (uint64_t)a->m * a->k, eb, false);
+            r[1] = RGN("B", a->b, (uint64_t)a->k * a->n, eb, false);
+            r[2] = RGN("C", a->c, (uint64_t)a->m * a->n, 4, true);
+            return 3;
+        }
+        case OP_TILED_GEMM_GENERAL: {
+            const fe2o3_tiled_gemm_general_v1_args *a = static_cast<const fe2o3_tiled_gemm_general_v1_args *>(args);
+            if (a->lda < a->k || a->ldb < a->n || a->ldc < a->n) {
+                *status = unsupported("StrideTooSmall: lda >= k, ldb >= n, ldc >= n required");
+                return 0;
+            }
+            uint64_t ea, ebx, ec;
+            if (!extent(a->m, a->k, a->lda, &ea) || !extent(a->k, a->n, a->ldb, &ebx) ||
+                !extent(a->m, a->n, a->ldc, &ec)) {
+                fe2o3_set_error("ExtentOverflow");
+                *status = FE2O3_ERR_SIZE_OVERFLOW;
+                return 0;
+            }
+            r[0] = RGN("A", a->a, ea, 2, false);
+            r[1] = RGN("B", a->b, ebx, 2, false);
+            r[2] = RGN("C", a->c, ec, 4, true);
+            return 3;
+        }
+        case OP_FLASH_ATTENTION: {
+            const fe2o3_flash_attention_v1_args *a = static_cast<const fe2o3_flash_attention_v1_args *>(args);
+            if (a->input_dtype > FE2O3_DTYPE_BF16 || a->dim == 0 || a->dim > 256 || a->seq == 0 ||
+                !(a->scale == a->scale)) {
+                *status = unsupported("flash_attention_v1 needs f32/bf16 inputs, 1 <= dim <= 256, seq >= 1");
+                return 0;
+            }
+            const uint64_t n = (uint64_t)a->batch * a->heads * a->seq * a->dim;
+            const uint32_t eb = a->input_dtype == FE2O3_DTYPE_F32 ? 4 : 2;
+            r[0] = RGN("Query", a->q, n, eb, false);
+            r[1] = RGN("Key", a->k, n, eb, false);
+            r[2] = RGN("Value", a->v, n, eb, false);
+            r[3] = RGN("Output", a->output, n, 4, true);
+            return 4;
+        }
+        case OP_ROW_SOFTMAX: {
+            const fe2o3_row_softmax_v1_args *a = static_cast<const fe2o3_row_softmax_v1_args *>(args);
+            if (a->cols == 0) { *status = unsupported("EmptyRow"); return 0; }
+            if (a->cols > 4096) { *status = unsupported("RowTooLarge: at most 4096 columns"); return 0; }
+            const uint64_t n = (uint64_t)a->rows * a->cols;
+            r[0] = RGN("Input", a->input, n, 4, false);
+            r[1] = RGN("Output", a->output, n, 4, true);
+            if (a->mask.ptr == 0 && a->mask.len == 0) return 2;
+            r[2] = RGN("Mask", a->mask, n, 1, false);
+            return 3;
+        }
+        case OP_MOE_TOP2: {
+            const fe2o3_moe_top2_v1_args *a = static_cast<const fe2o3_moe_top2_v1_args *>(args);
+            if (a->experts < 2 || a->experts > 32) { *status = unsupported("2 <= experts <= 32"); return 0; }
+            if (a->tokens > 0x7fffffffu) { *status = unsupported("route ids must fit u32"); return 0; }
+            const uint64_t R = 2ull * a->tokens;
+            r[0] = RGN("Logits", a->logits, (uint64_t)a->tokens * a->experts, 4, false);
+            r[1] = RGN("Top2Experts", a->top2_experts, R, 4, true);
+            r[2] = RGN("RequestedCounts", a->requested_counts, a->experts, 4, true);
+            r[3] = RGN("AdmittedCounts", a->admitted_counts, a->experts, 4, true);
+            r[4] = RGN("ExpertOffsets", a->expert_offsets, a->experts + 1, 4, true);
+            r[5] = RGN("RouteSlots", a->route_slots, R, 4, true);
+            r[6] = RGN("Permutation", a->permutation, R, 4, true);
+            r[7] = RGN("Inverse", a->inverse, R, 4, true);
+            return 8;
+        }
+        case OP_MOE_GATE: {
+            const fe2o3_moe_gate_v1_args *a = static_cast<const fe2o3_moe_gate_v1_args *>(args);
+            if (a->experts < 1 || a->experts > 256) { *status = unsupported("1 <= experts <= 256"); return 0; }
+            r[0] = RGN("X", a->x, (uint64_t)a->tokens * a->d_model, 2, false);
+            r[1] = RGN("Wg", a->wg, (uint64_t)a->d_model * a->experts, 2, false);
+            r[2] = RGN("Logits", a->logits, (uint64_t)a->tokens * a->experts, 4, true);
+            return 3;
+        }
+        case OP_MOE_ROUTE_WEIGHTS: {
+            const fe2o3_moe_route_weights_v1_args *a = static_cast<const fe2o3_moe_route_weights_v1_args *>(args);
+            r[0] = RGN("Logits", a->logits, (uint64_t)a->tokens * a->experts, 4, false);
+            r[1] = RGN("Top2Experts", a->top2_experts, 2ull * a->tokens, 4, false);
+            r[2] = RGN("RouteWeights", a->route_weights, 2ull * a->tokens, 4, true);
+            return 3;
+        }
+        case OP_MOE_EXPERT_FFN: {
+            const fe2o3_moe_expert_ffn_v1_args *a = static_cast<const fe2o3_moe_expert_ffn_v1_args *>(args);
+            if (a->d_model == 0 || a->d_ff == 0 || (a->d_model % 8) || (a->d_ff % 8) || a->experts < 1 ||
+                a->experts > 32) {
+                *status = unsupported("d_model and d_ff must be positive multiples of 8; 1 <= experts <= 32");
+                return 0;
+            }
+            if (a->compact_output.len % a->d_model) { *status = unsupported("compact_output is not whole rows"); return 0; }
+            const uint64_t rows = a->compact_output.len / a->d_model;
+            r[0] = RGN("X", a->x, (uint64_t)a->tokens * a->d_model, 2, false);
+            r[1] = RGN("W1", a->w1, (uint64_t)a->experts * a->d_model * a->d_ff, 2, false);
+            r[2] = RGN("W2", a->w2, (uint64_t)a->experts * a->d_ff * a->d_model, 2, false);
+            r[3] = RGN("Permutation", a->permutation, rows, 4, false);
+            r[4] = RGN("ExpertOffsets", a->expert_offsets, a->experts + 1, 4, false);
+            r[5] = RGN("CompactX", a->compact_x, rows * a->d_model, 2, true);
+            r[6] = RGN("Hidden", a->hidden, rows * a->d_ff, 2, true);
+            r[7] = RGN("CompactOutput", a->compact_output, rows * a->d_model, 4, true);
+            return 8;
+        }
+        case OP_MOE_COMBINE: {
+            const fe2o3_moe_expert_combine_v1_args *a = static_cast<const fe2o3_moe_expert_combine_v1_args *>(args);
+            if (a->width == 0 || a->compact_output.len % a->width) {
+                *status = unsupported("compact_output is not whole rows");
+                return 0;
+            }
+            r[0] = RGN("CompactOutput", a->compact_output, a->compact_output.len, 4, false);
+            r[1] = RGN("Inverse", a->inverse, 2ull * a->tokens, 4, false);
+            r[2] = RGN("RouteWeights", a->route_weights, 2ull * a->tokens, 4, false);
+            r[3] = RGN("CombinedOutput", a->combined_output, (uint64_t)a->tokens * a->width, 4, true);
+            return 4;
+        }
+        case OP_MASKED_REDUCE: {
+            const fe2o3_masked_reduce_u32_args *a = static_cast<const fe2o3_masked_reduce_u32_args *>(args);
+            r[0] = RGN("Values", a->values, a->values.len, 4, false);
+            r[1] = RGN("Active", a->active, a->values.len, 4, false);
+            r[2] = RGN("Output", a->output, 1, 4, true);
+            return 3;
+        }
+        case OP_MASKED_REDUCE_PACKED: {
+            const fe2o3_masked_reduce_u32_packed_args *a = static_cast<const fe2o3_masked_reduce_u32_packed_args *>(args);
+            r[0] = RGN("Values", a->values, a->values.len, 4, false);
+            r[1] = RGN("Mask", a->mask, (a->values.len + 63) / 64, 8, false);
+            r[2] = RGN("Output", a->output, 1, 4, true);
+            return 3;
+        }
+        case OP_WAVE_LDS: {
+            const fe2o3_wave_lds_v1_args *a = static_cast<const fe2o3_wave_lds_v1_args *>(args);
+            if (a->values.len % 256) { *status = unsupported("length must be a multiple of the 256-lane workgroup"); return 0; }
+            r[0] = RGN("Values", a->values, a->values.len, 4, false);
+            r[1] = RGN("Active", a->active, a->values.len, 4, false);
+            r[2] = RGN("WaveOut", a->wave_out, a->values.len, 4, true);
+            r[3] = RGN("WorkgroupOut", a->workgroup_out, a->values.len, 4, true);
+            return 4;
+        }
+        case OP_WAVE64_COLLECTIVES: {
+            const fe2o3_wave64_collectives_v1_args *a = static_cast<const fe2o3_wave64_collectives_v1_args *>(args);
+            r[0] = RGN("Input", a->input, 64, 4, false);
+            r[1] = RGN("Reduction", a->reduction_output, 64, 4, true);
+            r[2] = RGN("Inclusive", a->inclusive_output, 64, 4, true);
+            r[3] = RGN("Exclusive", a->exclusive_output, 64, 4, true);
+            return 4;
+        }
+        case OP_WAVE64_SEGMENTED: {
+            const fe2o3_wave64_collectives_segmented_args *a = static_cast<const fe2o3_wave64_collectives_segmented_args *>(args);
+            const uint64_t n = a->masks.len * 64;
+            r[0] = RGN("Input", a->input, n, 4, false);
+            r[1] = RGN("Masks", a->masks, a->masks.len, 8, false);
+            r[2] = RGN("Reduction", a->reduction_output, n, 4, true);
+            r[3] = RGN("Inclusive", a->inclusive_output, n, 4, true);
+            r[4] = RGN("Exclusive", a->exclusive_output, n, 4, true);
+            return 5;
+        }
+        case OP_LDS_REDUCE_I32: {
+            const fe2o3_lds_publish_read_reduce_i32_v1_args *a = static_cast<const fe2o3_lds_publish_read_reduce_i32_v1_args *>(args);
+            r[0] = RGN("Values", a->values, 64, 4, false);
+            r[1] = RGN("Output", a->output, 1, 4, true);
+            return 2;
+        }
+        case OP_SCOPED_ATOMIC_ADD: {
+            const fe2o3_scoped_atomic_add_u32_v1_args *a = static_cast<const fe2o3_scoped_atomic_add_u32_v1_args *>(args);
+            r[0] = RGN("Values", a->values, 64, 4, false);
+            r[1] = RGN("Eligible", a->eligible, 64, 4, false);
+            r[2] = RGN("Target", (fe2o3_slice{a->target, 1}), 1, 4, true);
+            return 3;
+        }
+    }
+    *status = FE2O3_ERR_INVALID_ARGUMENT;
+    return 0;
+}
+
+int32_t check_op(uint32_t op, const void *args) {
+    if (!args) { fe2o3_set_error("null argument block"); return FE2O3_ERR_INVALID_ARGUMENT; }
+    Region r[16];
+    int32_t st;
+    int n = regions_for(op, args, r, &st);
+    if (st != FE2O3_OK) return st;
+    return check_regions(r, n);
+}
+
+int32_t resolve_gemm(fe2o3_prepared *p, uint32_t schedule, uint32_t dtype, uint64_t a, uint64_t b, uint64_t c,
+                     uint32_t M, uint32_t N, uint32_t K, uint32_t lda, uint32_t ldb, uint32_t ldc, float alpha,
+                     float beta, bool epilogue) {
+    const bool tc_ok = dtype == FE2O3_DTYPE_BF16 && gemm_tc_supported(a, b, lda, ldb, K);
+    if (schedule == FE2O3_GEMM_SCHEDULE_TCGEN05 && !tc_ok)
+        return unsupported("tcgen05 schedule needs bf16 operands, K > 0, 16-byte aligned bases, lda and ldb multiples of 8");
+    if (schedule > FE2O3_GEMM_SCHEDULE_AUTO) { fe2o3_set_error("unknown schedule"); return FE2O3_ERR_INVALID_ARGUMENT; }
+    if (schedule == FE2O3_GEMM_SCHEDULE_AUTO)
+        schedule = (tc_ok && (uint64_t)M * N * K >= (1ull << 21)) ? FE2O3_GEMM_SCHEDULE_TCGEN05 : FE2O3_GEMM_SCHEDULE_EXACT_ORDER;
+    p->schedule = schedule;
+    if (schedule == FE2O3_GEMM_SCHEDULE_TCGEN05) {
+        int32_t st = gemm_tc_plan(p->ctx, &p->gemm[0], a, b, c, M, N, K, lda, ldb, ldc, alpha, beta, epilogue ? 1u : 0u,
+                                  nullptr, 0);
+        if (st != FE2O3_OK) return st;
+        gemm_tc_geometry(&p->gemm[0], &p->geo);
+        return FE2O3_OK;
+    }
+    return launch_gemm_exact(nullptr, dtype, epilogue, a, b, c, M, N, K, lda, ldb, ldc, alpha, beta, &p->geo, true);
+}
+
+int32_t prepare_common(fe2o3_ctx *ctx, uint32_t op, const void *args, fe2o3_prepared **out) {
+    if (!ctx || !out) { fe2o3_set_error("null context or output"); return FE2O3_ERR_INVALID_ARGUMENT; }
+    *out = nullptr;
+    int32_t st = check_op(op, args);
+    if (st != FE2O3_OK) return st;
+    Region r[16];
+    int n = regions_for(op, args, r, &st);
+    st = check_ctx_device(ctx, r, n);
+    if (st != FE2O3_OK) return st;
+    fe2o3_prepared *p = new (std::nothrow) fe2o3_prepared();
+    if (!p) return FE2O3_ERR_SIZE_OVERFLOW;
+    p->ctx = ctx;
+    p->op = op;
+    p->attn = nullptr;
+    p->schedule = 0;
+    memset(p->kernarg, 0, sizeof p->kernarg);
+    memcpy(p->kernarg, args, kOps[op].kernarg_bytes);
+    memset(&p->geo, 0, sizeof p->geo);
+    *out = p;
+    return FE2O3_OK;
+}
+
+int32_t finish_simple(fe2o3_prepared *p) {
+    return kOps[p->op].simple(p->ctx, nullptr, p->kernarg, &p->geo, true);
+}
+
+int32_t launch_prepared(fe2o3_prepared *p, cudaStream_t s) {
+    fe2o3_ctx *ctx = p->ctx;
+    switch (p->op) {
+        case OP_SCALAR_GEMM:
+        case OP_TILED_GEMM: {
+            const fe2o3_scalar_gemm_v1_args *a = reinterpret_cast<const fe2o3_scalar_gemm_v1_args *>(p->kernarg);
+            if (p->schedule == FE2O3_GEMM_SCHEDULE_TCGEN05) return gemm_tc_launch(&p->gemm[0], s);
+            return launch_gemm_exact(s, p->op == OP_SCALAR_GEMM ? FE2O3_DTYPE_F32 : FE2O3_DTYPE_BF16, false, a->a.ptr,
+                                     a->b.ptr, a->c.ptr, a->m, a->n, a->k, a->k, a->n, a->n, 1.f, 0.f, nullptr, false);
+        }
+        case OP_TILED_GEMM_GENERAL: {
+            const fe2o3_tiled_gemm_general_v1_args *a = reinterpret_cast<const fe2o3_tiled_gemm_general_v1_args *>(p->kernarg);
+            if (p->schedule == FE2O3_GEMM_SCHEDULE_TCGEN05) return gemm_tc_launch(&p->gemm[0], s);
+            return launch_gemm_exact(s, FE2O3_DTYPE_BF16, true, a->a.ptr, a->b.ptr, a->c.ptr, a->m, a->n, a->k, a->lda,
+                                     a->ldb, a->ldc, a->alpha, a->beta, nullptr, false);
+        }
+        case OP_FLASH_ATTENTION: {
+            if (p->attn) return attention_tc_launch(p->attn, s);
+            return launch_attention_simt(ctx, s, reinterpret_cast<const fe2o3_flash_attention_v1_args *>(p->kernarg),
+                                         nullptr, false);
+        }
+        case OP_MOE_EXPERT_FFN: {
+            const fe2o3_moe_expert_ffn_v1_args *a = reinterpret_cast<const fe2o3_moe_expert_ffn_v1_args *>(p->kernarg);
+            const uint32_t rows = (uint32_t)(a->compact_output.len / a->d_model);
+            int32_t st = launch_moe_compact(s, a->x.ptr, a->permutation.ptr, a->compact_x.ptr, rows, a->d_model, a->tokens);
+            if (st != FE2O3_OK) return st;
+            st = gemm_tc_launch(&p->gemm[0], s);
+            if (st != FE2O3_OK) return st;
+            return gemm_tc_launch(&p->gemm[1], s);
+        }
+        default:
+            return kOps[p->op].simple(ctx, s, p->kernarg, nullptr, false);
+    }
+}
+
+// Host deadline poll; never blocks past timeout_ms.
+int32_t bounded_wait(cudaStream_t s, uint32_t timeout_ms) {
+    cudaEvent_t ev;
+    FE2O3_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    cudaError_t e = cudaEventRecord(ev, s);
+    if (e != cudaSuccess) { cudaEventDestroy(ev); return fe2o3_cuda_status(e, "cudaEventRecord"); }
+    const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms);
+    int32_t result = FE2O3_OK;
+    for (;;) {
+        e = cudaEventQuery(ev);
+        if (e == cudaSuccess) break;
+        if (e != cudaErrorNotReady) { result = fe2o3_cuda_status(e, "cudaEventQuery"); break; }
+        if (std::chrono::steady_clock::now() >= deadline) {
+            fe2o3_set_error("AmbiguousCompletion: no completion within %u ms; buffers must stay alive", timeout_ms);
+            result = FE2O3_ERR_AMBIGUOUS_COMPLETION;
+            break;
+        }
+        std::this_thread::sleep_for(std::chrono::microseconds(50));
+    }
+    if (result != FE2O3_ERR_AMBIGUOUS_COMPLETION) cudaEventDestroy(ev);  // an unfinished event is leaked, not destroyed
+    return result;
+}
+
+int32_t take_status(fe2o3_ctx *ctx, cudaStream_t s, uint32_t *status) {
+    FE2O3_CUDA(cudaMemcpyAsync(ctx->host_status, ctx->status_word, 4, cudaMemcpyDeviceToHost, s));
+    FE2O3_CUDA(cudaStreamSynchronize(s));
+    const uint32_t v = *ctx->host_status;
+    if (status) *status = v;
+    if (v != 0) FE2O3_CUDA(cudaMemsetAsync(ctx->status_word, 0, 4, s));
+    return FE2O3_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+// ---- context ---------------------------------------------------------------------
+int32_t fe2o3_ctx_create(int32_t device, fe2o3_ctx **out) {
+    if (!out) return FE2O3_ERR_INVALID_ARGUMENT;
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) {
+        cudaGetLastError();
+        fe2o3_set_error("NoDevice: %s", e == cudaSuccess ? "no CUDA device" : cudaGetErrorString(e));
+        return FE2O3_ERR_NO_DEVICE;
+    }
+    if (device < 0 || device >= count) {
+        fe2o3_set_error("device %d out of range (count %d)", device, count);
+        return FE2O3_ERR_INVALID_ARGUMENT;
+    }
+    FE2O3_CUDA(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    FE2O3_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10) {
+        fe2o3_set_error("target check: device %d is sm_%d%d, this library is built for sm_100a only", device, prop.major,
+                        prop.minor);
+        return FE2O3_ERR_NOT_SM100;
+    }
+    fe2o3_ctx *ctx = new (std::nothrow) fe2o3_ctx();
+    if (!ctx) return FE2O3_ERR_SIZE_OVERFLOW;
+    ctx->device = device;
+    ctx->sm_count = prop.multiProcessorCount;
+    ctx->cc_major = prop.major;
+    ctx->cc_minor = prop.minor;
+    ctx->default_stream = nullptr;
+    ctx->reduce_scratch_elems = FE2O3_REDUCE_MAX_BLOCKS + 1;
+    uint32_t *dev = nullptr;
+    e = cudaMalloc(&dev, (ctx->reduce_scratch_elems + 1) * sizeof(uint32_t));
+    if (e != cudaSuccess) { delete ctx; return fe2o3_cuda_status(e, "cudaMalloc(context scratch)"); }
+    cudaMemset(dev, 0, (ctx->reduce_scratch_elems + 1) * sizeof(uint32_t));
+    ctx->reduce_scratch = dev;
+    ctx->status_word = dev + ctx->reduce_scratch_elems;
+    e = cudaMallocHost(&ctx->host_status, 64);
+    if (e != cudaSuccess) { cudaFree(dev); delete ctx; return fe2o3_cuda_status(e, "cudaMallocHost"); }
+    *out = ctx;
+    return FE2O3_OK;
+}
+
+int32_t fe2o3_ctx_destroy(fe2o3_ctx *ctx) {
+    if (!ctx) return FE2O3_OK;
+    cudaSetDevice(ctx->device);
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) {  // quiescent: safe to free; otherwise leak (completion is ambiguous)
+        cudaFree(ctx->reduce_scratch);
+        cudaFreeHost(ctx->host_status);
+    }
+    delete ctx;
+    return fe2o3_cuda_status(e, "cudaDeviceSynchronize");
+}
+
+int32_t fe2o3_ctx_bind_to_thread(fe2o3_ctx *ctx) {
+    if (!ctx) return FE2O3_ERR_INVALID_ARGUMENT;
+    FE2O3_CUDA(cudaSetDevice(ctx->device));
+    return FE2O3_OK;
+}
+
+int32_t fe2o3_ctx_device(const fe2o3_ctx *ctx, int32_t *device) {
+    if (!ctx || !device) return FE2O3_ERR_INVALID_ARGUMENT;
+    *device = ctx->device;
+    return FE2O3_OK;
+}
+
+int32_t fe2o3_ctx_observe_environment(fe2o3_ctx *ctx, fe2o3_device_properties *out) {
+    if (!ctx || !out) return FE2O3_ERR_INVALID_ARGUMENT;
+    cudaDeviceProp prop;
+    FE2O3_CUDA(cudaGetDeviceProperties(&prop, ctx->device));
+    memset(out, 0, sizeof *out);
+    strncpy(out->name, prop.name, sizeof out->name - 1);
+    out->total_global_bytes = prop.totalGlobalMem;
+    out->compute_major = prop.major;
+    out->compute_minor = prop.minor;
+    out->multiprocessors = prop.multiProcessorCount;
+    out->max_shared_bytes_per_block_optin = (uint32_t)prop.sharedMemPerBlockOptin;
+    out->l2_bytes = prop.l2CacheSize;
+    int v = 0;
+    cudaDeviceGetAttribute(&v, cudaDevAttrClockRate, ctx->device);
+    out->sm_clock_khz = v;
+    cudaDeviceGetAttribute(&v, cudaDevAttrMemoryClockRate, ctx->device);
+    out->mem_clock_khz = v;
+    out->warp_size = prop.warpSize;
+    return FE2O3_OK;
+}
+
+// ---- streams -----------------------------------------------------------------------
+static int32_t make_stream(fe2o3_ctx *ctx, cudaStream_t s, bool owned, fe2o3_stream **out) {
+    fe2o3_stream *st = new (std::nothrow) fe2o3_stream();
+    if (!st) return FE2O3_ERR_SIZE_OVERFLOW;
+    st->ctx = ctx;
+    st->s = s;
+    st->owned = owned;
+    *out = st;
+    return FE2O3_OK;
+}
+int32_t fe2o3_stream_default(fe2o3_ctx *ctx, fe2o3_stream **out) {
+    if (!ctx || !out) return FE2O3_ERR_INVALID_ARGUMENT;
+    return make_stream(ctx, ctx->default_stream, false, out);
+}
+int32_t fe2o3_stream_create(fe2o3_ctx *ctx, fe2o3_stream **out) {
+    if (!ctx || !out) return FE2O3_ERR_INVALID_ARGUMENT;
+    FE2O3_CUDA(cudaSetDevice(ctx->device));
+    cudaStream_t s;
+    FE2O3_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+    return make_stream(ctx, s, true, out);
+}
+int32_t fe2o3_stream_wrap(fe2o3_ctx *ctx, void *cuda_stream, fe2o3_stream **out) {
+    if (!ctx || !out) return FE2O3_ERR_INVALID_ARGUMENT;
+    return make_stream(ctx, static_cast<cudaStream_t>(cuda_stream), false, out);
+}
+int32_t fe2o3_stream_sync(fe2o3_stream *stream) {
+    if (!stream) return FE2O3_ERR_INVALID_ARGUMENT;
+    FE2O3_CUDA(cudaStreamSynchronize(stream->s));
+    return FE2O3_OK;
+}
+int32_t fe2o3_stream_native(fe2o3_stream *stream, void **cuda_stream) {
+    if (!stream || !cuda_stream) return FE2O3_ERR_INVALID_ARGUMENT;
+    *cuda_stream = stream->s;
+    return FE2O3_OK;
+}
+int32_t fe2o3_stream_destroy(fe2o3_stream *stream) {
+    if (!stream) return FE2O3_OK;
+    int32_t st = FE2O3_OK;
+    if (stream->owned) st = fe2o3_cuda_status(cudaStreamDestroy(stream->s), "cudaStreamDestroy");
+    delete stream;
+    return st;
+}
+
+// ---- buffers -------------------------------------------------------------------------
+int32_t fe2o3_buf_alloc_zeroed(fe2o3_stream *stream, uint64_t elements, uint32_t element_bytes, fe2o3_buf **out) {
+    if (!stream || !out || element_bytes == 0) return FE2O3_ERR_INVALID_ARGUMENT;
+    *out = nullptr;
+    uint64_t bytes;
+    if (mul_overflow(elements, element_bytes, &bytes)) {
+        fe2o3_set_error("SizeOverflow: %llu elements of %u bytes", (unsigned long long)elements, element_bytes);
+        return FE2O3_ERR_SIZE_OVERFLOW;
+    }
+    FE2O3_CUDA(cudaSetDevice(stream->ctx->device));
+    void *ptr = nullptr;
+    if (bytes) {
+        FE2O3_CUDA(cudaMalloc(&ptr, bytes));
+        cudaError_t e = cudaMemsetAsync(ptr, 0, bytes, stream->s);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(stream->s);
+        if (e != cudaSuccess) { cudaFree(ptr); return fe2o3_cuda_status(e, "zero-fill"); }
+    }
+    fe2o3_buf *b = new (std::nothrow) fe2o3_buf{stream->ctx, ptr, elements, element_bytes, false};
+    if (!b) { cudaFree(ptr); return FE2O3_ERR_SIZE_OVERFLOW; }
+    *out = b;
+    return FE2O3_OK;
+}
+
+int32_t fe2o3_buf_copy_from_host_async(fe2o3_stream *stream, fe2o3_buf *buf, const void *host, uint64_t elements) {
+    if (!stream || !buf || (!host && elements)) return FE2O3_ERR_INVALID_ARGUMENT;
+    if (stream->ctx != buf->ctx) { fe2o3_set_error("OperationDeviceMismatch"); return FE2O3_ERR_DEVICE_MISMATCH; }
+    if (elements > buf->elements) { fe2o3_set_error("copy exceeds buffer"); return FE2O3_ERR_INVALID_REGION; }
+    if (elements) FE2O3_CUDA(cudaMemcpyAsync(buf->ptr, host, elements * buf->element_bytes, cudaMemcpyHostToDevice, stream->s));
+    return FE2O3_OK;
+}
+int32_t fe2o3_buf_copy_to_host_async(fe2o3_stream *stream, const fe2o3_buf *buf, void *host, uint64_t elements) {
+    if (!stream || !buf || (!host && elements)) return FE2O3_ERR_INVALID_ARGUMENT;
+    if (stream->ctx != buf->ctx) { fe2o3_set_error("OperationDeviceMismatch"); return FE2O3_ERR_DEVICE_MISMATCH; }
+    if (elements > buf->elements) { fe2o3_set_error("copy exceeds buffer"); return FE2O3_ERR_INVALID_REGION; }
+    if (elements) FE2O3_CUDA(cudaMemcpyAsync(host, buf->ptr, elements * buf->element_bytes, cudaMemcpyDeviceToHost, stream->s));
+    return FE2O3_OK;
+}
+int32_t fe2o3_buf_from_host(fe2o3_stream *stream, const void *host, uint64_t elements, uint32_t element_bytes,
+                            fe2o3_buf **out) {
+    int32_t st = fe2o3_buf_alloc_zeroed(stream, elements, element_bytes, out);
+    if (st != FE2O3_OK) return st;
+    st = fe2o3_buf_copy_from_host_async(stream, *out, host, elements);
+    if (st == FE2O3_OK) st = fe2o3_cuda_status(cudaStreamSynchronize(stream->s), "cudaStreamSynchronize");
+    if (st != FE2O3_OK) { fe2o3_buf_free(*out); *out = nullptr; }
+    return st;
+}
+int32_t fe2o3_buf_to_host(fe2o3_stream *stream, const fe2o3_buf *buf, void *host, uint64_t elements) {
+    int32_t st = fe2o3_buf_copy_to_host_async(stream, buf, host, elements);
+    if (st != FE2O3_OK) return st;
+    return fe2o3_cuda_status(cudaStreamSynchronize(stream->s), "cudaStreamSynchronize");
+}
+int32_t fe2o3_buf_quarantine(fe2o3_buf *buf) {
+    if (!buf) return FE2O3_ERR_INVALID_ARGUMENT;
+    buf->quarantined = true;
+    return FE2O3_OK;
+}
+int32_t fe2o3_buf_free(fe2o3_buf *buf) {
+    if (!buf) return FE2O3_OK;
+    int32_t st = FE2O3_OK;
+    if (buf->ptr && !buf->quarantined) st = fe2o3_cuda_status(cudaFree(buf->ptr), "cudaFree");
+    delete buf;
+    return st;
+}
+uint64_t fe2o3_buf_ptr(const fe2o3_buf *buf) { return buf ? reinterpret_cast<uint64_t>(buf->ptr) : 0; }
+uint64_t fe2o3_buf_len(const fe2o3_buf *buf) { return buf ? buf->elements : 0; }
+int32_t fe2o3_buf_slice(const fe2o3_buf *buf, uint64_t start, uint64_t len, fe2o3_slice *out) {
+    if (!buf || !out) return FE2O3_ERR_INVALID_ARGUMENT;
+    if (start > buf->elements || len > buf->elements - start) {
+        fe2o3_set_error("InvalidRegion: [%llu, +%llu) of %llu", (unsigned long long)start, (unsigned long long)len,
+                        (unsigned long long)buf->elements);
+        return FE2O3_ERR_INVALID_REGION;
+    }
+    out->ptr = reinterpret_cast<uint64_t>(buf->ptr) + start * buf->element_bytes;
+    out->len = len;
+    return FE2O3_OK;
+}
+
+int32_t fe2o3_pinned_alloc(fe2o3_ctx *ctx, uint64_t bytes, void **out) {
+    if (!ctx || !out) return FE2O3_ERR_INVALID_ARGUMENT;
+    FE2O3_CUDA(cudaSetDevice(ctx->device));
+    FE2O3_CUDA(cudaMallocHost(out, bytes ? bytes : 1));
+    return FE2O3_OK;
+}
+int32_t fe2o3_pinned_free(fe2o3_ctx *ctx, void *ptr) {
+    (void)ctx;
+    if (ptr) FE2O3_CUDA(cudaFreeHost(ptr));
+    return FE2O3_OK;
+}
+
+// ---- events ----------------------------------------------------------------------------
+int32_t fe2o3_event_create(fe2o3_ctx *ctx, fe2o3_event **out) {
+    if (!ctx || !out) return FE2O3_ERR_INVALID_ARGUMENT;
+    FE2O3_CUDA(cudaSetDevice(ctx->device));
+    cudaEvent_t e;
+    FE2O3_CUDA(cudaEventCreate(&e));
+    *out = new (std::nothrow) fe2o3_event{ctx, e};
+    return *out ? FE2O3_OK : FE2O3_ERR_SIZE_OVERFLOW;
+}
+int32_t fe2o3_event_record(fe2o3_event *event, fe2o3_stream *stream) {
+    if (!event || !stream) return FE2O3_ERR_INVALID_ARGUMENT;
+    if (event->ctx != stream->ctx) { fe2o3_set_error("OperationDeviceMismatch"); return FE2O3_ERR_DEVICE_MISMATCH; }
+    FE2O3_CUDA(cudaEventRecord(event->e, stream->s));
+    return FE2O3_OK;
+}
+int32_t fe2o3_event_sync(fe2o3_event *event) {
+    if (!event) return FE2O3_ERR_INVALID_ARGUMENT;
+    FE2O3_CUDA(cudaEventSynchronize(event->e));
+    return FE2O3_OK;
+}
+int32_t fe2o3_event_query(fe2o3_event *event, int32_t *done) {
+    if (!event || !done) return FE2O3_ERR_INVALID_ARGUMENT;
+    cudaError_t e = cudaEventQuery(event->e);
+    if (e == cudaErrorNotReady) { *done = 0; return FE2O3_OK; }
+    *done = 1;
+    return fe2o3_cuda_status(e, "cudaEventQuery");
+}
+int32_t fe2o3_event_elapsed_ms(fe2o3_event *start, fe2o3_event *end, float *ms) {
+    if (!start || !end || !ms) return FE2O3_ERR_INVALID_ARGUMENT;
+    FE2O3_CUDA(cudaEventElapsedTime(ms, start->e, end->e));
+    return FE2O3_OK;
+}
+int32_t fe2o3_event_destroy(fe2o3_event *event) {
+    if (!event) return FE2O3_OK;
+    cudaError_t e = cudaEventDestroy(event->e);
+    delete event;
+    return fe2o3_cuda_status(e, "cudaEventDestroy");
+}
+
+int32_t fe2o3_peer_access_enable(fe2o3_ctx *ctx, int32_t peer_device) {
+    if (!ctx) return FE2O3_ERR_INVALID_ARGUMENT;
+    FE2O3_CUDA(cudaSetDevice(ctx->device));
+    int can = 0;
+    FE2O3_CUDA(cudaDeviceCanAccessPeer(&can, ctx->device, peer_device));
+    if (!can) { fe2o3_set_error("peer access %d -> %d unavailable", ctx->device, peer_device); return FE2O3_ERR_INVALID_ARGUMENT; }
+    cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
+    if (e == cudaErrorPeerAccessAlreadyEnabled) { cudaGetLastError(); return FE2O3_OK; }
+    return fe2o3_cuda_status(e, "cudaDeviceEnablePeerAccess");
+}
+
+const char *fe2o3_status_string(int32_t s) {
+    switch (s) {
+        case FE2O3_OK: return "Ok";
+        case FE2O3_ERR_NO_DEVICE: return "NoDevice";
+        case FE2O3_ERR_INVALID_ARGUMENT: return "InvalidArgument";
+        case FE2O3_ERR_SIZE_OVERFLOW: return "SizeOverflow";
+        case FE2O3_ERR_DEVICE_MISMATCH: return "OperationDeviceMismatch";
+        case FE2O3_ERR_LENGTH: return "Length";
+        case FE2O3_ERR_ALIGNMENT: return "Alignment";
+        case FE2O3_ERR_NULL_ADDRESS: return "NullAddress";
+        case FE2O3_ERR_INVALID_REGION: return "InvalidRegion";
+        case FE2O3_ERR_OUTPUT_ALIASES_INPUT: return "OutputAliasesInput";
+        case FE2O3_ERR_UNSUPPORTED_SHAPE: return "UnsupportedShape";
+        case FE2O3_ERR_AMBIGUOUS_COMPLETION: return "AmbiguousCompletion";
+        case FE2O3_ERR_KERNEL_STATUS: return "KernelStatus";
+        case FE2O3_ERR_UNKNOWN_SYMBOL: return "UnknownSymbol";
+        case FE2O3_ERR_NOT_SM100: return "NotSm100";
+        case FE2O3_ERR_NONFINITE: return "NonFinite";
+        case FE2O3_ERR_NO_DISPATCH: return "NoDispatch";
+        default: return s > 0 ? "CudaError" : "Unknown";
+    }
+}
+const char *fe2o3_last_error(void) { return g_error; }
+uint64_t fe2o3_launch_count(void) { return g_launches.load(); }
+
+// ---- checks --------------------------------------------------------------------------------
+#define DEFINE_CHECK(name, op) \
+    int32_t fe2o3_##name##_check(const fe2o3_##name##_args *args) { return check_op(op, args); }
+DEFINE_CHECK(scalar_gemm_v1, OP_SCALAR_GEMM)
+DEFINE_CHECK(tiled_gemm_v1, OP_TILED_GEMM)
+DEFINE_CHECK(tiled_gemm_general_v1, OP_TILED_GEMM_GENERAL)
+DEFINE_CHECK(flash_attention_v1, OP_FLASH_ATTENTION)
+DEFINE_CHECK(row_softmax_v1, OP_ROW_SOFTMAX)
+DEFINE_CHECK(moe_top2_v1, OP_MOE_TOP2)
+DEFINE_CHECK(moe_gate_v1, OP_MOE_GATE)
+DEFINE_CHECK(moe_route_weights_v1, OP_MOE_ROUTE_WEIGHTS)
+DEFINE_CHECK(moe_expert_ffn_v1, OP_MOE_EXPERT_FFN)
+DEFINE_CHECK(moe_expert_combine_v1, OP_MOE_COMBINE)
+DEFINE_CHECK(masked_reduce_u32, OP_MASKED_REDUCE)
+DEFINE_CHECK(masked_reduce_u32_packed, OP_MASKED_REDUCE_PACKED)
+DEFINE_CHECK(wave_lds_v1, OP_WAVE_LDS)
+DEFINE_CHECK(wave64_collectives_v1, OP_WAVE64_COLLECTIVES)
+DEFINE_CHECK(wave64_collectives_segmented, OP_WAVE64_SEGMENTED)
+DEFINE_CHECK(lds_publish_read_reduce_i32_v1, OP_LDS_REDUCE_I32)
+DEFINE_CHECK(scoped_atomic_add_u32_v1, OP_SCOPED_ATOMIC_ADD)
+
+// ---- prepare ---------------------------------------------------------------------------------
+#define DEFINE_SIMPLE_PREPARE(name, op)                                                                 \
+    int32_t fe2o3_##name##_prepare(fe2o3_ctx *ctx, const fe2o3_##name##_args *args, fe2o3_prepared **out) { \
+        int32_t st = prepare_common(ctx, op, args, out);                                                \
+        if (st != FE2O3_OK) return st;                                                                  \
+        return finish_simple(*out);                                                                     \
+    }
+DEFINE_SIMPLE_PREPARE(row_softmax_v1, OP_ROW_SOFTMAX)
+DEFINE_SIMPLE_PREPARE(moe_top2_v1, OP_MOE_TOP2)
+DEFINE_SIMPLE_PREPARE(moe_gate_v1, OP_MOE_GATE)
+DEFINE_SIMPLE_PREPARE(moe_route_weights_v1, OP_MOE_ROUTE_WEIGHTS)
+DEFINE_SIMPLE_PREPARE(moe_expert_combine_v1, OP_MOE_COMBINE)
+DEFINE_SIMPLE_PREPARE(masked_reduce_u32, OP_MASKED_REDUCE)
+DEFINE_SIMPLE_PREPARE(masked_reduce_u32_packed, OP_MASKED_REDUCE_PACKED)
+DEFINE_SIMPLE_PREPARE(wave_lds_v1, OP_WAVE_LDS)
+DEFINE_SIMPLE_PREPARE(wave64_collectives_v1, OP_WAVE64_COLLECTIVES)
+DEFINE_SIMPLE_PREPARE(wave64_collectives_segmented, OP_WAVE64_SEGMENTED)
+DEFINE_SIMPLE_PREPARE(lds_publish_read_reduce_i32_v1, OP_LDS_REDUCE_I32)
+DEFINE_SIMPLE_PREPARE(scoped_atomic_add_u32_v1, OP_SCOPED_ATOMIC_ADD)
+
+static int32_t fail_prepare(fe2o3_prepared **out, int32_t st) {
+    fe2o3_prepared_destroy(*out);
+    *out = nullptr;
+    return st;
+}
+
+int32_t fe2o3_scalar_gemm_v1_prepare(fe2o3_ctx *ctx, const fe2o3_scalar_gemm_v1_args *a, uint32_t schedule,
+                                     fe2o3_prepared **out) {
+    int32_t st = prepare_common(ctx, OP_SCALAR_GEMM, a, out);
+    if (st != FE2O3_OK) return st;
+    if ((uint64_t)a->m * a->n == 0) return fail_prepare(out, FE2O3_ERR_NO_DISPATCH);
+    st = resolve_gemm(*out, schedule, FE2O3_DTYPE_F32, a->a.ptr, a->b.ptr, a->c.ptr, a->m, a->n, a->k, a->k, a->n, a->n,
+                      1.f, 0.f, false);
+    return st == FE2O3_OK ? st : fail_prepare(out, st);
+}
+int32_t fe2o3_tiled_gemm_v1_prepare(fe2o3_ctx *ctx, const fe2o3_tiled_gemm_v1_args *a, uint32_t schedule,
+                                    fe2o3_prepared **out) {
+    int32_t st = prepare_common(ctx, OP_TILED_GEMM, a, out);
+    if (st != FE2O3_OK) return st;
+    if ((uint64_t)a->m * a->n == 0) return fail_prepare(out, FE2O3_ERR_NO_DISPATCH);
+    st = resolve_gemm(*out, schedule, FE2O3_DTYPE_BF16, a->a.ptr, a->b.ptr, a->c.ptr, a->m, a->n, a->k, a->k, a->n,
+                      a->n, 1.f, 0.f, false);
+    return st == FE2O3_OK ? st : fail_prepare(out, st);
+}
+int32_t fe2o3_tiled_gemm_general_v1_prepare(fe2o3_ctx *ctx, const fe2o3_tiled_gemm_general_v1_args *a,
+                                            uint32_t schedule, fe2o3_prepared **out) {
+    int32_t st = prepare_common(ctx, OP_TILED_GEMM_GENERAL, a, out);
+    if (st != FE2O3_OK) return st;
+    if ((uint64_t)a->m * a->n == 0) return fail_prepare(out, FE2O3_ERR_NO_DISPATCH);
+    st = resolve_gemm(*out, schedule, FE2O3_DTYPE_BF16, a->a.ptr, a->b.ptr, a->c.ptr, a->m, a->n, a->k, a->lda, a->ldb,
+                      a->ldc, a->alpha, a->beta, true);
+    return st == FE2O3_OK ? st : fail_prepare(out, st);
+}
+int32_t fe2o3_flash_attention_v1_prepare(fe2o3_ctx *ctx, const fe2o3_flash_attention_v1_args *a, fe2o3_prepared **out) {
+    int32_t st = prepare_common(ctx, OP_FLASH_ATTENTION, a, out);
+    if (st != FE2O3_OK) return st;
+    if (attention_tc_supported(a)) {
+        st = attention_tc_plan(ctx, a, &(*out)->attn);
+        if (st != FE2O3_OK) return fail_prepare(out, st);
+        attention_tc_geometry((*out)->attn, &(*out)->geo);
+        return FE2O3_OK;
+    }
+    return launch_attention_simt(ctx, nullptr, a, &(*out)->geo, true);
+}
+int32_t fe2o3_moe_expert_ffn_v1_prepare(fe2o3_ctx *ctx, const fe2o3_moe_expert_ffn_v1_args *a, fe2o3_prepared **out) {
+    int32_t st = prepare_common(ctx, OP_MOE_EXPERT_FFN, a, out);
+    if (st != FE2O3_OK) return st;
+    fe2o3_prepared *p = *out;
+    const uint32_t rows = (uint32_t)(a->compact_output.len / a->d_model);
+    const uint32_t *off = reinterpret_cast<const uint32_t *>(a->expert_offsets.ptr);
+    st = gemm_tc_plan(ctx, &p->gemm[0], a->compact_x.ptr, a->w1.ptr, a->hidden.ptr, rows, a->d_ff, a->d_model,
+                      a->d_model, a->d_ff, a->d_ff, 1.f, 0.f, 2u, off, a->experts);
+    if (st == FE2O3_OK)
+        st = gemm_tc_plan(ctx, &p->gemm[1], a->hidden.ptr, a->w2.ptr, a->compact_output.ptr, rows, a->d_model, a->d_ff,
+                          a->d_ff, a->d_model, a->d_model, 1.f, 0.f, 0u, off, a->experts);
+    if (st != FE2O3_OK) return fail_prepare(out, st);
+    gemm_tc_geometry(&p->gemm[0], &p->geo);
+    p->geo.launches = 3;
+    return FE2O3_OK;
+}
+
+// ---- launch ------------------------------------------------------------------------------------
+int32_t fe2o3_prepared_launch(fe2o3_prepared *p, fe2o3_stream *stream) {
+    if (!p || !stream) return FE2O3_ERR_INVALID_ARGUMENT;
+    if (stream->ctx != p->ctx) { fe2o3_set_error("WrongContext{role=stream}"); return FE2O3_ERR_DEVICE_MISMATCH; }
+    return launch_prepared(p, stream->s);
+}
+int32_t fe2o3_prepared_launch_and_wait(fe2o3_prepared *p, fe2o3_stream *stream, uint32_t timeout_ms,
+                                       uint32_t *kernel_status) {
+    if (kernel_status) *kernel_status = 0;
+    int32_t st = fe2o3_prepared_launch(p, stream);
+    if (st != FE2O3_OK) return st;
+    st = bounded_wait(stream->s, timeout_ms);
+    if (st != FE2O3_OK) return st;
+    uint32_t ks = 0;
+    st = take_status(p->ctx, stream->s, &ks);
+    if (st != FE2O3_OK) return st;
+    if (kernel_status) *kernel_status = ks;
+    if (ks != 0) {
+        fe2o3_set_error("kernel %s reported status word %u", kOps[p->op].symbol, ks);
+        return FE2O3_ERR_KERNEL_STATUS;
+    }
+    return FE2O3_OK;
+}
+int32_t fe2o3_prepared_geometry(const fe2o3_prepared *p, fe2o3_geometry *out) {
+    if (!p || !out) return FE2O3_ERR_INVALID_ARGUMENT;
+    *out = p->geo;
+    return FE2O3_OK;
+}
+int32_t fe2o3_prepared_kernarg(const fe2o3_prepared *p, void *out, uint64_t *bytes) {
+    if (!p || !bytes) return FE2O3_ERR_INVALID_ARGUMENT;
+    const uint64_t n = kOps[p->op].kernarg_bytes;
+    if (out && *bytes >= n) memcpy(out, p->kernarg, n);
+    const bool ok = *bytes >= n;
+    *bytes = n;
+    return ok || !out ? FE2O3_OK : FE2O3_ERR_LENGTH;
+}
+const char *fe2o3_prepared_symbol(const fe2o3_prepared *p) { return p ? kOps[p->op].symbol : ""; }
+int32_t fe2o3_prepared_destroy(fe2o3_prepared *p) {
+    if (!p) return FE2O3_OK;
+    if (p->attn) attention_tc_free(p->attn);
+    delete p;
+    return FE2O3_OK;
+}
+int32_t fe2o3_ctx_take_kernel_status(fe2o3_ctx *ctx, fe2o3_stream *stream, uint32_t *status) {
+    if (!ctx || !stream) return FE2O3_ERR_INVALID_ARGUMENT;
+    return take_status(ctx, stream->s, status);
+}
+
+// ---- runtime adapter ---------------------------------------------------------------------------
+int32_t fe2o3_load_executable(fe2o3_ctx *ctx, fe2o3_executable **out) {
+    if (!ctx || !out) return FE2O3_ERR_INVALID_ARGUMENT;
+    *out = new (std::nothrow) fe2o3_executable{ctx};
+    return *out ? FE2O3_OK : FE2O3_ERR_SIZE_OVERFLOW;
+}
+int32_t fe2o3_resolve_kernel(fe2o3_executable *exe, const char *symbol, uint32_t *kernel_id, uint64_t *kernarg_bytes) {
+    if (!exe || !symbol || !kernel_id) return FE2O3_ERR_INVALID_ARGUMENT;
+    for (uint32_t i = 0; i < OP_COUNT; ++i) {
+        if (strcmp(kOps[i].symbol, symbol) == 0) {
+            *kernel_id = i;
+            if (kernarg_bytes) *kernarg_bytes = kOps[i].kernarg_bytes;
+            return FE2O3_OK;
+        }
+    }
+    fe2o3_set_error("UnknownSymbol: %s", symbol);
+    return FE2O3_ERR_UNKNOWN_SYMBOL;
+}
+int32_t fe2o3_launch_and_wait(fe2o3_executable *exe, uint32_t kernel_id, const void *kernarg, uint64_t kernarg_bytes,
+                              fe2o3_stream *stream, uint32_t timeout_ms, uint32_t *kernel_status) {
+    if (!exe || !kernarg || !stream || kernel_id >= OP_COUNT) return FE2O3_ERR_INVALID_ARGUMENT;
+    if (kernarg_bytes != kOps[kernel_id].kernarg_bytes) {
+        fe2o3_set_error("Length{role=kernarg, expected=%llu, actual=%llu}",
+                        (unsigned long long)kOps[kernel_id].kernarg_bytes, (unsigned long long)kernarg_bytes);
+        return FE2O3_ERR_LENGTH;
+    }
+    fe2o3_prepared *p = nullptr;
+    int32_t st;
+    switch (kernel_id) {
+        case OP_SCALAR_GEMM: st = fe2o3_scalar_gemm_v1_prepare(exe->ctx, (const fe2o3_scalar_gemm_v1_args *)kernarg, FE2O3_GEMM_SCHEDULE_AUTO, &p); break;
+        case OP_TILED_GEMM: st = fe2o3_tiled_gemm_v1_prepare(exe->ctx, (const fe2o3_tiled_gemm_v1_args *)kernarg, FE2O3_GEMM_SCHEDULE_AUTO, &p); break;
+        case OP_TILED_GEMM_GENERAL: st = fe2o3_tiled_gemm_general_v1_prepare(exe->ctx, (const fe2o3_tiled_gemm_general_v1_args *)kernarg, FE2O3_GEMM_SCHEDULE_AUTO, &p); break;
+        case OP_FLASH_ATTENTION: st = fe2o3_flash_attention_v1_prepare(exe->ctx, (const fe2o3_flash_attention_v1_args *)kernarg, &p); break;
+        case OP_MOE_EXPERT_FFN: st = fe2o3_moe_expert_ffn_v1_prepare(exe->ctx, (const fe2o3_moe_expert_ffn_v1_args *)kernarg, &p); break;
+        default:
+            st = prepare_common(exe->ctx, kernel_id, kernarg, &p);
+            if (st == FE2O3_OK) st = finish_simple(p);
+    }
+    if (st == FE2O3_ERR_NO_DISPATCH) return FE2O3_OK;
+    if (st != FE2O3_OK) return st;
+    st = fe2o3_prepared_launch_and_wait(p, stream, timeout_ms, kernel_status);
+    fe2o3_prepared_destroy(p);
+    return st;
+}
+int32_t fe2o3_unload_executable(fe2o3_executable *exe) {
+    delete exe;
+    return FE2O3_OK;
+}
+
+}  // extern "C"

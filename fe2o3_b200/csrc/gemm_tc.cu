@@ -1,0 +1,387 @@
+// Tensor-core GEMM schedule for sm_100a: bf16 x bf16 -> f32 on tcgen05 with the
+// accumulator in TMEM, operands staged by TMA into 128-byte-swizzled shared
+// memory through an mbarrier ring.
+//
+// Replaces the MFMA + LDS schedule of examples/tiled_gemm_v1/src/kernel.rs:63-124
+// and examples/tiled_gemm_general_v1/src/kernel.rs:67-120 (one wave per 16x16
+// tile, single-buffered LDS, two barriers per K phase) and, in grouped mode,
+// the per-expert GEMM launches of examples/moe_expert_v1/src/pipeline.rs:181-187.
+//
+// Layout.  A is row-major [M][K] (K contiguous, "K-major"); B is row-major
+// [K][N] (N contiguous, "MN-major") exactly as the reference stores them, so no
+// transpose pass is needed: the instruction descriptor marks B as MN-major.
+// A CTA owns a 128 x BN output tile; one K block is 64 bf16 = 128 bytes.
+//   A stage: one TMA box {64 k, 128 rows}  -> 128 rows x 128 B, 8-row groups 1 KiB apart
+//   B stage: BN/64 TMA boxes {64 n, 64 k}   -> per box 64 k-rows x 128 B (8 KiB)
+// Persistent CTAs (one per SM) walk a static tile list; six warps:
+//   warp 0  TMA producer (one lane)        warp 1  MMA issuer (one lane) + TMEM owner
+//   warps 2-5  epilogue: TMEM -> registers -> global, one TMEM lane quadrant each
+// Two accumulator buffers in TMEM let the epilogue of tile i overlap the main
+// loop of tile i+1.  Every wait is bounded: on expiry the kernel records
+// FE2O3_KSTATUS_WAIT_EXPIRED, drains its own copies and returns.
+#include "gemm_tc.h"
+
+#include <mutex>
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;          // bf16 elements per K block (128 bytes)
+constexpr int UMMA_K = 16;
+constexpr int kStages = 4;
+constexpr int kThreads = 192;
+constexpr int kGroupM = 16;     // m-tiles per rasterisation band (keeps a wave's A and B panels in L2)
+
+template <int BN>
+struct SmemLayout {
+    static constexpr uint32_t kABytes = BM * BK * 2;
+    static constexpr uint32_t kBBytes = BN * BK * 2;
+    static constexpr uint32_t kStageBytes = kABytes + kBBytes;
+    static constexpr uint32_t kBarOffset = kStages * kStageBytes;
+    static constexpr uint32_t kTotal = kBarOffset + 256 + 1024;  // barriers + alignment slack
+};
+
+struct TileCoord {
+    uint32_t m0, n0, m_end, expert;
+    bool valid;
+};
+
+// Static tile order.  Plain: bands of kGroupM m-tiles, m fastest inside a band.
+// Grouped: expert-major; inside an expert m fastest.
+__device__ __forceinline__ TileCoord decode_tile(uint32_t id, const GemmParams &p, uint32_t n_tiles,
+                                                 const uint32_t *s_off) {
+    TileCoord t;
+    t.valid = false;
+    t.expert = 0;
+    if (p.experts == 0) {
+        const uint32_t m_tiles = (p.M + BM - 1) / BM;
+        if (id >= m_tiles * n_tiles) return t;
+        const uint32_t band = id / (kGroupM * n_tiles);
+        const uint32_t first_m = band * kGroupM;
+        const uint32_t band_m = min((uint32_t)kGroupM, m_tiles - first_m);
+        const uint32_t local = id - band * kGroupM * n_tiles;
+        t.m0 = (first_m + local % band_m) * BM;
+        t.n0 = (local / band_m);
+        t.m_end = p.M;
+        t.valid = true;
+        return t;
+    }
+    uint32_t base = 0;
+    for (uint32_t e = 0; e < p.experts; ++e) {
+        const uint32_t rows = s_off[e + 1] - s_off[e];
+        const uint32_t mt = (rows + BM - 1) / BM;
+        const uint32_t cnt = mt * n_tiles;
+        if (id < base + cnt) {
+            const uint32_t local = id - base;
+            t.m0 = s_off[e] + (local % mt) * BM;
+            t.n0 = local / mt;
+            t.m_end = s_off[e + 1];
+            t.expert = e;
+            t.valid = true;
+            return t;
+        }
+        base += cnt;
+    }
+    return t;
+}
+
+__device__ __forceinline__ float gelu_erf(float x) {
+    return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+    using L = SmemLayout<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    // 128-byte swizzle atoms are 1 KiB: align the tile region.
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + L::kBarOffset);
+    uint64_t *empty = full + kStages;
+    uint64_t *tmem_full = empty + kStages;
+    uint64_t *tmem_empty = tmem_full + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + 2);
+    __shared__ uint32_t s_off[33];
+    __shared__ int s_abort;
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t n_tiles = (p.N + BN - 1) / BN;
+    const uint32_t num_kb = (p.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        for (int i = 0; i < kStages; ++i) {
+            mbar_init(&full[i], 1);
+            mbar_init(&empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&tmem_full[i], 1);
+            mbar_init(&tmem_empty[i], 4);
+        }
+        mbar_fence_init();
+    }
+    if (p.experts) {
+        for (uint32_t i = threadIdx.x; i <= p.experts; i += blockDim.x) s_off[i] = p.expert_offsets[i];
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 2 * BN);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------ TMA producer
+        if (lane == 0) {
+            tma_prefetch_desc(&tmA);
+            tma_prefetch_desc(&tmB);
+            uint32_t stage = 0, phase = 0;
+            uint32_t armed[kStages];
+            bool ever[kStages];
+            for (int i = 0; i < kStages; ++i) { armed[i] = 0; ever[i] = false; }
+            bool ok = true;
+            for (uint32_t id = blockIdx.x; ok; id += gridDim.x) {
+                TileCoord t = decode_tile(id, p, n_tiles, s_off);
+                if (!t.valid) break;
+                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(&empty[stage], phase ^ 1)) { ok = false; break; }
+                    uint8_t *sa = smem + stage * L::kStageBytes;
+                    uint8_t *sb = sa + L::kABytes;
+                    mbar_arrive_expect_tx(&full[stage], L::kStageBytes);
+                    armed[stage] = phase;
+                    ever[stage] = true;
+                    tma_load_2d(sa, &tmA, &full[stage], (int32_t)(kb * BK), (int32_t)t.m0);
+#pragma unroll
+                    for (int j = 0; j < BN / 64; ++j) {
+                        if (p.experts)
+                            tma_load_3d(sb + j * 8192, &tmB, &full[stage], (int32_t)(t.n0 * BN + j * 64),
+                                        (int32_t)(kb * BK), (int32_t)t.expert);
+                        else
+                            tma_load_2d(sb + j * 8192, &tmB, &full[stage], (int32_t)(t.n0 * BN + j * 64),
+                                        (int32_t)(kb * BK));
+                    }
+                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                }
+            }
+            if (!ok) {
+                kstatus_set(p.status, FE2O3_KSTATUS_WAIT_EXPIRED);
+                atomicExch(&s_abort, 1);
+            }
+            // Drain: every copy this thread issued must have landed before the CTA exits.
+            for (int i = 0; i < kStages; ++i)
+                if (ever[i]) mbar_wait(&full[i], armed[i]);
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc(1u, BM, BN, 0u, 1u);
+            uint32_t stage = 0, phase = 0, it = 0;
+            bool ok = true;
+            for (uint32_t id = blockIdx.x; ok; id += gridDim.x, ++it) {
+                TileCoord t = decode_tile(id, p, n_tiles, s_off);
+                if (!t.valid) break;
+                const uint32_t buf = it & 1, acc_phase = (it >> 1) & 1;
+                if (!mbar_wait(&tmem_empty[buf], acc_phase ^ 1)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(&full[stage], phase)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + stage * L::kStageBytes);
+                    const uint32_t sb = sa + L::kABytes;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // A: K-major, advance 16 elements = 32 bytes inside the 128-byte row
+                        const uint64_t adesc = umma_smem_desc(sa + k * UMMA_K * 2, 16, 1024);
+                        // B: MN-major, advance 16 k-rows = 2 KiB; 64-column groups are 8 KiB apart
+                        const uint64_t bdesc = umma_smem_desc(sb + k * UMMA_K * 128, 8192, 1024);
+                        umma_f16(d_tmem, adesc, bdesc, idesc, (kb | (uint32_t)k) != 0u);
+                    }
+                    umma_commit(&empty[stage]);
+                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                umma_commit(&tmem_full[buf]);
+            }
+            if (!ok) {
+                kstatus_set(p.status, FE2O3_KSTATUS_WAIT_EXPIRED);
+                atomicExch(&s_abort, 1);
+            }
+        }
+    } else {
+        // ------------------------------------------------ epilogue warps
+        const uint32_t quad = warp & 3;  // TMEM lane quadrant this warp may read
+        uint32_t it = 0;
+        bool ok = true;
+        for (uint32_t id = blockIdx.x; ok; id += gridDim.x, ++it) {
+            TileCoord t = decode_tile(id, p, n_tiles, s_off);
+            if (!t.valid) break;
+            const uint32_t buf = it & 1, acc_phase = (it >> 1) & 1;
+            if (!mbar_wait(&tmem_full[buf], acc_phase)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t row = t.m0 + quad * 32 + lane;
+            const bool row_ok = row < t.m_end;
+            const uint32_t col_base = t.n0 * BN;
+#pragma unroll 1
+            for (int chunk = 0; chunk < BN / 32; ++chunk) {
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(tmem_base + buf * BN + chunk * 32 + ((quad * 32u) << 16), r);
+                tmem_ld_wait();
+                const uint32_t col = col_base + chunk * 32;
+                if (!row_ok || col >= p.N) continue;
+                if (p.epilogue == EPI_GELU_BF16) {
+                    uint16_t *dst = reinterpret_cast<uint16_t *>(p.c) + (uint64_t)row * p.ldc + col;
+                    if (col + 32 <= p.N && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const uint32_t lo = f32_to_bf16_bits(gelu_erf(__uint_as_float(r[q * 8 + 2 * j])));
+                                const uint32_t hi = f32_to_bf16_bits(gelu_erf(__uint_as_float(r[q * 8 + 2 * j + 1])));
+                                w[j] = lo | (hi << 16);
+                            }
+                            reinterpret_cast<uint4 *>(dst)[q] = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    } else {
+                        for (int j = 0; j < 32 && col + j < p.N; ++j)
+                            dst[j] = f32_to_bf16_bits(gelu_erf(__uint_as_float(r[j])));
+                    }
+                } else {
+                    float *dst = reinterpret_cast<float *>(p.c) + (uint64_t)row * p.ldc + col;
+                    const bool vec = col + 32 <= p.N && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0);
+                    if (p.epilogue == EPI_ALPHA_BETA) {
+                        for (int j = 0; j < 32 && col + j < p.N; ++j)
+                            dst[j] = __fadd_rn(__fmul_rn(p.alpha, __uint_as_float(r[j])), __fmul_rn(p.beta, dst[j]));
+                    } else if (vec) {
+#pragma unroll
+                        for (int q = 0; q < 8; ++q)
+                            reinterpret_cast<float4 *>(dst)[q] =
+                                make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                            __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+                    } else {
+                        for (int j = 0; j < 32 && col + j < p.N; ++j) dst[j] = __uint_as_float(r[j]);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+        }
+        if (!ok && lane == 0) {
+            kstatus_set(p.status, FE2O3_KSTATUS_WAIT_EXPIRED);
+            atomicExch(&s_abort, 1);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 2 * BN);
+    }
+}
+
+// ---- host side ------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+}  // namespace
+
+// Encodes a bf16 tensor map with 128-byte swizzle.  dims/strides innermost first;
+// strides in bytes for dimensions 1..rank-1.
+int32_t fe2o3_make_tmap_bf16(CUtensorMap *out, uint64_t base, uint32_t rank, const uint64_t *dims,
+                             const uint64_t *strides_bytes, const uint32_t *box) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) {
+        fe2o3_set_error("cuTensorMapEncodeTiled is not available from the driver");
+        return FE2O3_ERR_NO_DEVICE;
+    }
+    cuuint64_t d[5];
+    cuuint64_t st[4];
+    cuuint32_t b[5], es[5];
+    for (uint32_t i = 0; i < rank; ++i) { d[i] = dims[i]; b[i] = box[i]; es[i] = 1; }
+    for (uint32_t i = 0; i + 1 < rank; ++i) st[i] = strides_bytes[i];
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, reinterpret_cast<void *>(base), d, st, b, es,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        fe2o3_set_error("cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+        return FE2O3_ERR_INVALID_ARGUMENT;
+    }
+    return FE2O3_OK;
+}
+
+// The tensor-core schedule needs 16-byte aligned bases and leading dimensions
+// that are multiples of 8 elements (TMA strides are multiples of 16 bytes).
+bool gemm_tc_supported(uint64_t a, uint64_t b, uint32_t lda, uint32_t ldb, uint32_t K) {
+    return K > 0 && (a & 15u) == 0 && (b & 15u) == 0 && (lda % 8u) == 0 && (ldb % 8u) == 0;
+}
+
+// experts == 0: plain C[M][N] = A[M][K] * B[K][N].  experts > 0: grouped, A rows
+// partitioned by expert_offsets (device array), B = [experts][K][N], M = upper
+// bound on rows (the capacity of A and C).
+int32_t gemm_tc_plan(fe2o3_ctx *ctx, GemmTcPlan *plan, uint64_t a, uint64_t b, uint64_t c, uint32_t M, uint32_t N,
+                     uint32_t K, uint32_t lda, uint32_t ldb, uint32_t ldc, float alpha, float beta, uint32_t epilogue,
+                     const uint32_t *expert_offsets, uint32_t experts) {
+    plan->bn = (N > 128) ? 256 : 128;
+    uint64_t dA[2] = {K, M}, sA[1] = {(uint64_t)lda * 2};
+    uint32_t bA[2] = {BK, BM};
+    int32_t st = fe2o3_make_tmap_bf16(&plan->tmA, a, 2, dA, sA, bA);
+    if (st != FE2O3_OK) return st;
+    if (experts) {
+        uint64_t dB[3] = {N, K, experts}, sB[2] = {(uint64_t)ldb * 2, (uint64_t)ldb * 2 * K};
+        uint32_t bB[3] = {64, BK, 1};
+        st = fe2o3_make_tmap_bf16(&plan->tmB, b, 3, dB, sB, bB);
+    } else {
+        uint64_t dB[2] = {N, K}, sB[1] = {(uint64_t)ldb * 2};
+        uint32_t bB[2] = {64, BK};
+        st = fe2o3_make_tmap_bf16(&plan->tmB, b, 2, dB, sB, bB);
+    }
+    if (st != FE2O3_OK) return st;
+    plan->p = GemmParams{reinterpret_cast<void *>(c), M, N, K, ldc, alpha, beta, epilogue, expert_offsets, experts,
+                         ctx->status_word};
+    const uint32_t n_tiles = (N + plan->bn - 1) / plan->bn;
+    const uint64_t m_tiles = (uint64_t)(M + BM - 1) / BM + experts;  // grouped: each expert may add a ragged tile
+    uint64_t tiles = m_tiles * n_tiles;
+    plan->grid = (uint32_t)(tiles < (uint64_t)ctx->sm_count ? (tiles ? tiles : 1) : (uint64_t)ctx->sm_count);
+    plan->smem = plan->bn == 256 ? SmemLayout<256>::kTotal : SmemLayout<128>::kTotal;
+    return FE2O3_OK;
+}
+
+int32_t gemm_tc_launch(const GemmTcPlan *plan, cudaStream_t s) {
+    static std::once_flag once;
+    std::call_once(once, [] {
+        cudaFuncSetAttribute(gemm_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)SmemLayout<256>::kTotal);
+        cudaFuncSetAttribute(gemm_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)SmemLayout<128>::kTotal);
+    });
+    if (plan->p.M == 0 || plan->p.N == 0) return FE2O3_OK;
+    if (plan->bn == 256)
+        gemm_tc_kernel<256><<<plan->grid, kThreads, plan->smem, s>>>(plan->tmA, plan->tmB, plan->p);
+    else
+        gemm_tc_kernel<128><<<plan->grid, kThreads, plan->smem, s>>>(plan->tmA, plan->tmB, plan->p);
+    fe2o3_count_launch(1);
+    return fe2o3_cuda_status(cudaGetLastError(), "gemm_tc");
+}
+
+void gemm_tc_geometry(const GemmTcPlan *plan, fe2o3_geometry *geo) {
+    *geo = fe2o3_geometry{{plan->grid, 1, 1}, {kThreads, 1, 1}, plan->smem, 1};
+}

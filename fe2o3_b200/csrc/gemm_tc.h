@@ -1,0 +1,35 @@
+// Plan object shared by the tensor-core GEMM source and the ABI layer.
+#pragma once
+#include "common.cuh"
+
+enum GemmEpilogue : uint32_t { EPI_STORE = 0, EPI_ALPHA_BETA = 1, EPI_GELU_BF16 = 2 };
+
+struct GemmParams {
+    void *c;                 // f32 (EPI_STORE / EPI_ALPHA_BETA) or bf16 bits (EPI_GELU_BF16)
+    uint32_t M, N, K;
+    uint32_t ldc;
+    float alpha, beta;
+    uint32_t epilogue;
+    // grouped mode: rows of A/C are partitioned by expert_offsets[0..experts];
+    // B has one [K][N] matrix per expert (third TMA coordinate).
+    const uint32_t *expert_offsets;
+    uint32_t experts;        // 0 = plain GEMM
+    uint32_t *status;
+};
+
+struct GemmTcPlan {
+    CUtensorMap tmA, tmB;
+    GemmParams p;
+    uint32_t bn;
+    uint32_t grid;
+    uint32_t smem;
+};
+
+int32_t fe2o3_make_tmap_bf16(CUtensorMap *out, uint64_t base, uint32_t rank, const uint64_t *dims,
+                             const uint64_t *strides_bytes, const uint32_t *box);
+bool gemm_tc_supported(uint64_t a, uint64_t b, uint32_t lda, uint32_t ldb, uint32_t K);
+int32_t gemm_tc_plan(fe2o3_ctx *ctx, GemmTcPlan *plan, uint64_t a, uint64_t b, uint64_t c, uint32_t M, uint32_t N,
+                     uint32_t K, uint32_t lda, uint32_t ldb, uint32_t ldc, float alpha, float beta, uint32_t epilogue,
+                     const uint32_t *expert_offsets, uint32_t experts);
+int32_t gemm_tc_launch(const GemmTcPlan *plan, cudaStream_t s);
+void gemm_tc_geometry(const GemmTcPlan *plan, fe2o3_geometry *geo);

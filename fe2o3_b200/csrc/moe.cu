@@ -1,0 +1,311 @@
+// MoE routing-side kernels: gate logits, top-2 selection with stable slot
+// packing, route weights, activation compaction and the weighted combine.
+// The expert FFN itself is the grouped tensor-core GEMM in gemm_tc.cu.
+#include "common.cuh"
+
+namespace {
+
+constexpr uint32_t kDrop = 0xffffffffu;
+
+// ---- gate logits ------------------------------------------------------------
+// logits[t,e] = sum_k x[t,k]*wg[k,e]; bf16 widened exactly, f32 accumulator from
+// +0, increasing k, separate product and sum, so top-2 indices can be compared
+// bit-for-bit with the CPU recurrence.  blockDim = (E, TPB): thread (e, t)
+// owns one output; x and wg are staged through shared memory KC deep.
+constexpr int kGateKC = 128;
+
+__global__ void moe_gate_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict__ wg,
+                                float *__restrict__ logits, uint32_t tokens, uint32_t d_model, uint32_t experts) {
+    extern __shared__ float gate_smem[];
+    const uint32_t tpb = blockDim.y;
+    float *xs = gate_smem;                      // [tpb][kGateKC + 1]
+    float *ws = gate_smem + tpb * (kGateKC + 1);  // [kGateKC][experts]
+    const uint32_t e = threadIdx.x, tl = threadIdx.y;
+    const uint32_t t0 = blockIdx.x * tpb;
+    const uint32_t lin = tl * blockDim.x + e, nthr = blockDim.x * blockDim.y;
+    float acc = 0.0f;
+    for (uint32_t k0 = 0; k0 < d_model; k0 += kGateKC) {
+        const uint32_t kc = min((uint32_t)kGateKC, d_model - k0);
+        for (uint32_t i = lin; i < tpb * kGateKC; i += nthr) {
+            const uint32_t r = i / kGateKC, kk = i % kGateKC;
+            const uint32_t t = t0 + r;
+            xs[r * (kGateKC + 1) + kk] = (t < tokens && kk < kc) ? bf16_bits_to_f32(x[(uint64_t)t * d_model + k0 + kk]) : 0.0f;
+        }
+        for (uint32_t i = lin; i < kc * experts; i += nthr) ws[i] = bf16_bits_to_f32(wg[(uint64_t)k0 * experts + i]);
+        __syncthreads();
+        for (uint32_t kk = 0; kk < kc; ++kk)
+            acc = __fadd_rn(acc, __fmul_rn(xs[tl * (kGateKC + 1) + kk], ws[kk * experts + e]));
+        __syncthreads();
+    }
+    if (t0 + tl < tokens) logits[(uint64_t)(t0 + tl) * experts + e] = acc;
+}
+
+// ---- top-2 routing ------------------------------------------------------------
+// examples/moe_top2_v1/src/kernel.rs:25-59 (comparator and running top-2) and
+// :132-202 (counts, clamp, exclusive scan, stable slots, permutation, inverse),
+// widened from one lane to one 1024-thread block.  Thread i owns the contiguous
+// token chunk [i*tpt, (i+1)*tpt), so route-id order is (thread, local order)
+// and a per-expert exclusive scan over threads gives every route its stable
+// rank without atomics: the packing is deterministic.
+constexpr int kRouteThreads = 1024;
+
+__device__ __forceinline__ bool precedes(float cs, uint32_t ce, float is, uint32_t ie) {
+    return cs > is || (cs == is && ce < ie);
+}
+
+__global__ void __launch_bounds__(kRouteThreads)
+moe_top2_kernel(fe2o3_moe_top2_v1_args a, uint32_t *status) {
+    extern __shared__ uint32_t counts[];  // [experts][kRouteThreads]
+    __shared__ uint32_t s_offsets[65];
+    __shared__ uint32_t s_requested[64];
+    __shared__ int s_bad;
+    const uint32_t T = a.tokens, E = a.experts, cap = a.capacity;
+    const uint64_t R = 2ull * T;
+    const uint32_t tid = threadIdx.x;
+    if (a.logits.len != (uint64_t)T * E || a.top2_experts.len != R || a.requested_counts.len != E ||
+        a.admitted_counts.len != E || a.expert_offsets.len != E + 1 || a.route_slots.len != R ||
+        a.permutation.len != R || a.inverse.len != R || E < 2 || E > 32) {
+        if (tid == 0) kstatus_set(status, FE2O3_KSTATUS_LENGTH);
+        return;
+    }
+    const float *logits = reinterpret_cast<const float *>(a.logits.ptr);
+    uint32_t *top2 = reinterpret_cast<uint32_t *>(a.top2_experts.ptr);
+    uint32_t *requested = reinterpret_cast<uint32_t *>(a.requested_counts.ptr);
+    uint32_t *admitted = reinterpret_cast<uint32_t *>(a.admitted_counts.ptr);
+    uint32_t *offsets = reinterpret_cast<uint32_t *>(a.expert_offsets.ptr);
+    uint32_t *slots = reinterpret_cast<uint32_t *>(a.route_slots.ptr);
+    uint32_t *perm = reinterpret_cast<uint32_t *>(a.permutation.ptr);
+    uint32_t *inverse = reinterpret_cast<uint32_t *>(a.inverse.ptr);
+
+    // finite-logit admission before any output is written
+    if (tid == 0) s_bad = 0;
+    __syncthreads();
+    bool bad = false;
+    for (uint64_t i = tid; i < (uint64_t)T * E; i += kRouteThreads) bad |= !isfinite(logits[i]);
+    if (bad) atomicExch(&s_bad, 1);
+    __syncthreads();
+    if (s_bad) {
+        if (tid == 0) kstatus_set(status, FE2O3_KSTATUS_NONFINITE);
+        return;
+    }
+
+    const uint32_t tpt = (T + kRouteThreads - 1) / kRouteThreads;
+    const uint32_t t_begin = min(T, tid * tpt), t_end = min(T, t_begin + tpt);
+    for (uint32_t e = 0; e < E; ++e) counts[e * kRouteThreads + tid] = 0;
+    for (uint32_t t = t_begin; t < t_end; ++t) {
+        const float *row = logits + (uint64_t)t * E;
+        uint32_t best = kDrop, second = kDrop;
+        float bs = 0.f, ss = 0.f;
+        for (uint32_t e = 0; e < E; ++e) {
+            const float sc = row[e];
+            if (best == kDrop || precedes(sc, e, bs, best)) {
+                second = best; ss = bs;
+                best = e; bs = sc;
+            } else if (second == kDrop || precedes(sc, e, ss, second)) {
+                second = e; ss = sc;
+            }
+        }
+        top2[2ull * t] = best;
+        top2[2ull * t + 1] = second;
+        counts[best * kRouteThreads + tid] += 1;
+        counts[second * kRouteThreads + tid] += 1;
+    }
+    __syncthreads();
+    // exclusive scan over threads, one warp per expert (strided over experts)
+    const uint32_t warp = tid >> 5, lane = tid & 31;
+    for (uint32_t e = warp; e < E; e += kRouteThreads / 32) {
+        uint32_t running = 0;
+        for (uint32_t c = 0; c < kRouteThreads; c += 32) {
+            const uint32_t v = counts[e * kRouteThreads + c + lane];
+            uint32_t inc = v;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                uint32_t n = __shfl_up_sync(0xffffffffu, inc, off);
+                if ((int)lane >= off) inc += n;
+            }
+            counts[e * kRouteThreads + c + lane] = running + inc - v;
+            running += __shfl_sync(0xffffffffu, inc, 31);
+        }
+        if (lane == 0) s_requested[e] = running;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        s_offsets[0] = 0;
+        for (uint32_t e = 0; e < E; ++e) {
+            const uint32_t adm = s_requested[e] > cap ? cap : s_requested[e];
+            requested[e] = s_requested[e];
+            admitted[e] = adm;
+            s_offsets[e + 1] = s_offsets[e] + adm;
+        }
+        for (uint32_t e = 0; e <= E; ++e) offsets[e] = s_offsets[e];
+    }
+    __syncthreads();
+    for (uint64_t s = s_offsets[E] + tid; s < R; s += kRouteThreads) perm[s] = kDrop;
+    for (uint32_t t = t_begin; t < t_end; ++t) {
+#pragma unroll
+        for (int rank = 0; rank < 2; ++rank) {
+            const uint64_t r = 2ull * t + rank;
+            const uint32_t e = top2[r];
+            const uint32_t stable_rank = counts[e * kRouteThreads + tid]++;
+            uint32_t slot = kDrop;
+            if (stable_rank < cap) {
+                slot = s_offsets[e] + stable_rank;
+                perm[slot] = (uint32_t)r;
+            }
+            slots[r] = slot;
+            inverse[r] = slot;
+        }
+    }
+}
+
+// ---- route weights ------------------------------------------------------------
+// Softmax over the experts renormalised over the two winners equals a softmax
+// over the two winning logits: e1 = exp(l1 - l0) <= 1, w0 = 1/(1+e1) in
+// [1/2, 1], w1 = 1 - w0, which is exact, so w0 + w1 == 1.0f as
+// examples/moe_expert_v1/src/contract.rs:34 requires.
+__global__ void moe_route_weights_kernel(const float *__restrict__ logits, const uint32_t *__restrict__ top2,
+                                         float *__restrict__ weights, uint32_t tokens, uint32_t experts) {
+    const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= tokens) return;
+    const float l0 = logits[(uint64_t)t * experts + top2[2ull * t]];
+    const float l1 = logits[(uint64_t)t * experts + top2[2ull * t + 1]];
+    const float e1 = expf(l1 - l0);
+    const float w0 = __fdiv_rn(1.0f, __fadd_rn(1.0f, e1));
+    weights[2ull * t] = w0;
+    weights[2ull * t + 1] = __fsub_rn(1.0f, w0);
+}
+
+// ---- compaction ---------------------------------------------------------------
+// compact_x[slot,:] = x[permutation[slot] / 2, :] for accepted slots, zero rows
+// elsewhere (examples/moe_expert_v1/src/pipeline.rs:181-215 builds zero-padded
+// per-expert activation tiles the same way).  One block per slot, 16-byte copies.
+__global__ void __launch_bounds__(256)
+moe_compact_kernel(const uint4 *__restrict__ x, const uint32_t *__restrict__ perm, uint4 *__restrict__ compact_x,
+                   uint32_t vec_per_row, uint32_t tokens) {
+    const uint32_t slot = blockIdx.x;
+    const uint32_t route = perm[slot];
+    uint4 *dst = compact_x + (uint64_t)slot * vec_per_row;
+    if (route == kDrop || (route >> 1) >= tokens) {
+        for (uint32_t i = threadIdx.x; i < vec_per_row; i += blockDim.x) dst[i] = make_uint4(0, 0, 0, 0);
+        return;
+    }
+    const uint4 *src = x + (uint64_t)(route >> 1) * vec_per_row;
+    for (uint32_t i = threadIdx.x; i < vec_per_row; i += blockDim.x) dst[i] = __ldg(src + i);
+}
+
+// ---- combine --------------------------------------------------------------------
+// examples/moe_expert_v1/src/kernel.rs:104-157: out[t,c] = sum over rank 0,1 in
+// that order, from +0, of w[2t+rank] * compact[inverse[2t+rank], c]; dropped
+// routes contribute nothing; a token whose weights are non-finite, negative or
+// do not sum to exactly 1.0 is left unwritten and a status word is recorded.
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const float *__restrict__ compact, const uint32_t *__restrict__ inverse,
+                   const float *__restrict__ weights, float *__restrict__ out, uint32_t tokens, uint32_t width,
+                   uint64_t compact_rows, uint32_t *status) {
+    const uint32_t t = blockIdx.x;
+    if (t >= tokens) return;
+    const float w0 = weights[2ull * t], w1 = weights[2ull * t + 1];
+    if (!isfinite(w0) || !isfinite(w1) || w0 < 0.f || w1 < 0.f || __fadd_rn(w0, w1) != 1.0f) {
+        if (threadIdx.x == 0) kstatus_set(status, FE2O3_KSTATUS_WEIGHTS);
+        return;
+    }
+    const uint32_t s0 = inverse[2ull * t], s1 = inverse[2ull * t + 1];
+    if ((s0 != kDrop && s0 >= compact_rows) || (s1 != kDrop && s1 >= compact_rows)) {
+        if (threadIdx.x == 0) kstatus_set(status, FE2O3_KSTATUS_SLOT_RANGE);
+        return;
+    }
+    const bool vec = (width & 3u) == 0 && ((reinterpret_cast<uint64_t>(compact) | reinterpret_cast<uint64_t>(out)) & 15u) == 0;
+    if (vec) {
+        const uint32_t nv = width >> 2;
+        const float4 *r0 = s0 != kDrop ? reinterpret_cast<const float4 *>(compact + (uint64_t)s0 * width) : nullptr;
+        const float4 *r1 = s1 != kDrop ? reinterpret_cast<const float4 *>(compact + (uint64_t)s1 * width) : nullptr;
+        float4 *dst = reinterpret_cast<float4 *>(out + (uint64_t)t * width);
+        for (uint32_t i = threadIdx.x; i < nv; i += blockDim.x) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (r0) {
+                float4 v = __ldcs(r0 + i);
+                acc.x = __fadd_rn(acc.x, __fmul_rn(w0, v.x)); acc.y = __fadd_rn(acc.y, __fmul_rn(w0, v.y));
+                acc.z = __fadd_rn(acc.z, __fmul_rn(w0, v.z)); acc.w = __fadd_rn(acc.w, __fmul_rn(w0, v.w));
+            }
+            if (r1) {
+                float4 v = __ldcs(r1 + i);
+                acc.x = __fadd_rn(acc.x, __fmul_rn(w1, v.x)); acc.y = __fadd_rn(acc.y, __fmul_rn(w1, v.y));
+                acc.z = __fadd_rn(acc.z, __fmul_rn(w1, v.z)); acc.w = __fadd_rn(acc.w, __fmul_rn(w1, v.w));
+            }
+            __stcs(dst + i, acc);
+        }
+    } else {
+        for (uint32_t c = threadIdx.x; c < width; c += blockDim.x) {
+            float acc = 0.f;
+            if (s0 != kDrop) acc = __fadd_rn(acc, __fmul_rn(w0, compact[(uint64_t)s0 * width + c]));
+            if (s1 != kDrop) acc = __fadd_rn(acc, __fmul_rn(w1, compact[(uint64_t)s1 * width + c]));
+            out[(uint64_t)t * width + c] = acc;
+        }
+    }
+}
+
+}  // namespace
+
+int32_t launch_moe_gate(fe2o3_ctx *, cudaStream_t s, const void *args, fe2o3_geometry *geo, bool plan_only) {
+    const fe2o3_moe_gate_v1_args *a = static_cast<const fe2o3_moe_gate_v1_args *>(args);
+    const uint32_t E = a->experts;
+    const uint32_t tpb = E >= 256 ? 1 : 256 / E;
+    const uint32_t grid = ceil_div_u32(a->tokens, tpb);
+    const uint32_t smem = (tpb * (kGateKC + 1) + kGateKC * E) * sizeof(float);
+    if (geo) *geo = fe2o3_geometry{{grid, 1, 1}, {E, tpb, 1}, smem, 1};
+    if (plan_only || a->tokens == 0) return FE2O3_OK;
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(moe_gate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    moe_gate_kernel<<<grid, dim3(E, tpb, 1), smem, s>>>(reinterpret_cast<const uint16_t *>(a->x.ptr),
+                                                        reinterpret_cast<const uint16_t *>(a->wg.ptr),
+                                                        reinterpret_cast<float *>(a->logits.ptr), a->tokens,
+                                                        a->d_model, E);
+    fe2o3_count_launch(1);
+    return fe2o3_cuda_status(cudaGetLastError(), "moe_gate_v1");
+}
+
+int32_t launch_moe_top2(fe2o3_ctx *ctx, cudaStream_t s, const void *args, fe2o3_geometry *geo, bool plan_only) {
+    const fe2o3_moe_top2_v1_args *a = static_cast<const fe2o3_moe_top2_v1_args *>(args);
+    const uint32_t smem = a->experts * kRouteThreads * sizeof(uint32_t);
+    if (geo) *geo = fe2o3_geometry{{1, 1, 1}, {kRouteThreads, 1, 1}, smem, 1};
+    if (plan_only) return FE2O3_OK;
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(moe_top2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    moe_top2_kernel<<<1, kRouteThreads, smem, s>>>(*a, ctx->status_word);
+    fe2o3_count_launch(1);
+    return fe2o3_cuda_status(cudaGetLastError(), "moe_top2_v1");
+}
+
+int32_t launch_moe_route_weights(fe2o3_ctx *, cudaStream_t s, const void *args, fe2o3_geometry *geo, bool plan_only) {
+    const fe2o3_moe_route_weights_v1_args *a = static_cast<const fe2o3_moe_route_weights_v1_args *>(args);
+    const uint32_t grid = ceil_div_u32(a->tokens, 256);
+    if (geo) *geo = fe2o3_geometry{{grid, 1, 1}, {256, 1, 1}, 0, 1};
+    if (plan_only || a->tokens == 0) return FE2O3_OK;
+    moe_route_weights_kernel<<<grid, 256, 0, s>>>(reinterpret_cast<const float *>(a->logits.ptr),
+                                                  reinterpret_cast<const uint32_t *>(a->top2_experts.ptr),
+                                                  reinterpret_cast<float *>(a->route_weights.ptr), a->tokens,
+                                                  a->experts);
+    fe2o3_count_launch(1);
+    return fe2o3_cuda_status(cudaGetLastError(), "moe_route_weights_v1");
+}
+
+int32_t launch_moe_compact(cudaStream_t s, uint64_t x, uint64_t perm, uint64_t compact_x, uint32_t rows,
+                           uint32_t d_model, uint32_t tokens) {
+    if (rows == 0) return FE2O3_OK;
+    moe_compact_kernel<<<rows, 256, 0, s>>>(reinterpret_cast<const uint4 *>(x), reinterpret_cast<const uint32_t *>(perm),
+                                            reinterpret_cast<uint4 *>(compact_x), d_model / 8, tokens);
+    fe2o3_count_launch(1);
+    return fe2o3_cuda_status(cudaGetLastError(), "moe_compact");
+}
+
+int32_t launch_moe_combine(fe2o3_ctx *ctx, cudaStream_t s, const void *args, fe2o3_geometry *geo, bool plan_only) {
+    const fe2o3_moe_expert_combine_v1_args *a = static_cast<const fe2o3_moe_expert_combine_v1_args *>(args);
+    if (geo) *geo = fe2o3_geometry{{a->tokens, 1, 1}, {256, 1, 1}, 0, 1};
+    if (plan_only || a->tokens == 0) return FE2O3_OK;
+    moe_combine_kernel<<<a->tokens, 256, 0, s>>>(
+        reinterpret_cast<const float *>(a->compact_output.ptr), reinterpret_cast<const uint32_t *>(a->inverse.ptr),
+        reinterpret_cast<const float *>(a->route_weights.ptr), reinterpret_cast<float *>(a->combined_output.ptr),
+        a->tokens, a->width, a->width ? a->compact_output.len / a->width : 0, ctx->status_word);
+    fe2o3_count_launch(1);
+    return fe2o3_cuda_status(cudaGetLastError(), "moe_expert_combine_v1");
+}
