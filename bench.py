@@ -1,0 +1,377 @@
+#!/usr/bin/env python
+"""Benchmark of the fe2o3 example hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+One JSON line on stdout (rank 0).  A "step" is one pass of the workload's hot
+path over one batch of seeded synthetic input.  `value` is timed with CUDA
+events with inputs resident in HBM; `e2e` is the same pass through the public
+host API with pinned host buffers, host<->device copies inside the timed
+region.  Inputs are synthetic (SplitMix64-keyed generators); no dataset is
+involved.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+HEADLINE = "masked_reduce_u32"
+L2_FLUSH_BYTES = 256 << 20
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons through NVML (read-only) in a thread
+    while the timed region runs."""
+
+    REASONS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
+
+    def __init__(self, index):
+        self.index, self.mhz, self.reasons, self.max_mhz = index, [], set(), None
+        self.stop_flag, self.thread, self.nv, self.handle = threading.Event(), None, None, None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        while not self.stop_flag.is_set():
+            try:
+                self.mhz.append(float(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)))
+                bits = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle))
+                for name, bit in self.REASONS.items():
+                    if bits & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.001)
+
+    def start(self):
+        if self.nv and self.thread is None:
+            self.stop_flag.clear()
+            self.thread = threading.Thread(target=self._loop, daemon=True)
+            self.thread.start()
+
+    def stop(self):
+        if self.thread:
+            self.stop_flag.set()
+            self.thread.join(timeout=2)
+            self.thread = None
+
+    def summary(self):
+        return {"sm_mhz": float(np.median(self.mhz)) if self.mhz else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.mhz)}
+
+
+class Harness:
+    def __init__(self, rank, world, local_rank):
+        import torch
+        import fe2o3_b200 as fe
+        self.torch, self.fe = torch, fe
+        self.rank, self.world = rank, world
+        torch.cuda.set_device(local_rank)
+        self.ctx = fe.GpuContext(local_rank)
+        self.stream = self.ctx.default_stream()  # the legacy default stream, shared with torch
+        self.flush_buf = None
+        self.clocks = None  # set for the headline workload: sampled over its timed region
+
+    def barrier(self):
+        if self.world > 1:
+            self.torch.distributed.barrier()
+        self.torch.cuda.synchronize()
+
+    def flush_l2(self):
+        if self.flush_buf is None:
+            self.flush_buf = self.torch.empty(L2_FLUSH_BYTES, dtype=self.torch.uint8, device="cuda")
+        self.flush_buf.zero_()
+
+    def time_steps(self, step, steps, warmup, flush):
+        """Returns per-step device milliseconds (list of `steps`)."""
+        fe = self.fe
+        for _ in range(warmup):
+            if flush:
+                self.flush_l2()
+            step()
+        ev = [(fe.Event(self.ctx), fe.Event(self.ctx)) for _ in range(steps)]
+        self.barrier()
+        if self.clocks:
+            self.clocks.start()
+        for s, e in ev:
+            if flush:
+                self.flush_l2()
+            s.record(self.stream)
+            step()
+            e.record(self.stream)
+        self.barrier()
+        if self.clocks:
+            self.clocks.stop()
+        return [e.elapsed_time_ms_since(s) for s, e in ev]
+
+    def max_over_ranks(self, x):
+        if self.world == 1:
+            return x
+        t = self.torch.tensor([x], dtype=self.torch.float64, device="cuda")
+        self.torch.distributed.all_reduce(t, op=self.torch.distributed.ReduceOp.MAX)
+        return float(t.item())
+
+
+def roofline(bound, achieved, peak, unit, traffic=None, peak_source="measured"):
+    return {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
+            "traffic": traffic, "peak_source": f"of {peak_source}"}
+
+
+# ------------------------------------------------------------------ workloads
+
+def wl_masked_reduce(h, steps, warmup, n=1 << 28, cpu=True):
+    fe = h.fe
+    from fe2o3_b200 import synth
+    ctx, stream = h.ctx, h.stream
+    peaks = measured_peaks()
+    host_v = ctx.pinned(n, np.uint32)
+    host_a = ctx.pinned(n, np.uint32)
+    host_o = ctx.pinned(1, np.uint32)
+    synth.u32_below(1, 1 + h.rank * 16, n, 1 << 16, out=host_v)
+    synth.bernoulli(1, 2 + h.rank * 16, n, 0.75, flag_value=7, packed=False, flags_out=host_a)
+    v = fe.DeviceBuffer.zeroed(stream, n, np.uint32)
+    a = fe.DeviceBuffer.zeroed(stream, n, np.uint32)
+    o = fe.DeviceBuffer.zeroed(stream, 1, np.uint32)
+    v.copy_from_host_async(stream, host_v)
+    a.copy_from_host_async(stream, host_a)
+    stream.synchronize()
+    prep = fe.prepare(ctx, "masked_reduce_u32", values=v, active=a, output=o)
+    l0 = fe.launch_count()
+    ms = h.time_steps(lambda: prep.launch(stream), steps, warmup, flush=False)
+    launches = fe.launch_count() - l0 - warmup
+    o.copy_to_host_async(stream, host_o)
+    stream.synchronize()
+    got = int(host_o[0])
+    step_ms = h.max_over_ranks(float(np.mean(ms)))
+    alg_bytes = n * 8 + 4
+    res = {"ms_per_step": step_ms, "value": h.world * n / (step_ms * 1e-3), "unit": "elements/s",
+           "launches": launches,
+           "roofline": roofline("hbm", alg_bytes / (float(np.mean(ms)) * 1e-3) / 1e9, peaks["hbm_gbs"], "GB/s",
+                                peak_source=peaks["source"]),
+           "workload": {"workload": "masked_reduce_u32", "elements": n, "values": "uniform[0,2^16) seed 1",
+                        "mask": "Bernoulli(0.75) u32 flags {0,7}", "algorithmic_bytes_per_step": alg_bytes,
+                        "l2": "inputs (2 GiB) larger than L2"}}
+
+    # end to end: pinned host -> device, launch, result back to host, every step
+    def e2e_step():
+        v.copy_from_host_async(stream, host_v)
+        a.copy_from_host_async(stream, host_a)
+        prep.launch(stream)
+        o.copy_to_host_async(stream, host_o)
+        stream.synchronize()
+    e2e_steps = max(2, min(steps, 5))
+    e2e_step()
+    h.barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    h.barrier()
+    e2e_s = h.max_over_ranks((time.perf_counter() - t0) / e2e_steps)
+    res["e2e"] = {"value": h.world * n / e2e_s, "unit": "elements/s", "h2d_bytes_per_step": 8 * n,
+                  "d2h_bytes_per_step": 4, "ms_per_step": e2e_s * 1e3}
+    if cpu and h.rank == 0:
+        import oracle
+        oracle.build()
+        best, want = None, None
+        for _ in range(5):
+            t0 = time.perf_counter()
+            want = oracle.masked_sum_u32(host_v, host_a, parallel=True)
+            dt = time.perf_counter() - t0
+            best = dt if best is None else min(best, dt)
+        res["cpu_baseline"] = {"value": n / best, "unit": "elements/s", "cores": os.cpu_count(), "kind": "port",
+                               "sample": f"the full {n}-element workload, best of 5 passes of the OpenMP oracle"}
+        res["parity"] = {"bit_exact": got == want, "gpu": got, "oracle": want}
+        if got != want:
+            raise SystemExit(f"masked_reduce_u32 mismatch: gpu {got} oracle {want}")
+    return res
+
+
+def wl_row_softmax(h, steps, warmup, rows=65536, cols=1024, cpu=True):
+    fe = h.fe
+    from fe2o3_b200 import synth
+    ctx, stream = h.ctx, h.stream
+    peaks = measured_peaks()
+    n = rows * cols
+    host_x = ctx.pinned(n, np.float32)
+    host_y = ctx.pinned(n, np.float32)
+    synth.normal_f32(2, 1, n, 2.0, out=host_x)
+    x = fe.DeviceBuffer.zeroed(stream, n, np.float32)
+    y = fe.DeviceBuffer.zeroed(stream, n, np.float32)
+    x.copy_from_host_async(stream, host_x)
+    stream.synchronize()
+    prep = fe.prepare(ctx, "row_softmax_v1", input=x, output=y, rows=rows, cols=cols)
+    ms = h.time_steps(lambda: prep.launch(stream), steps, warmup, flush=False)
+    step_ms = float(np.mean(ms))
+    alg = n * 8
+    res = {"ms_per_step": step_ms, "value": alg / (step_ms * 1e-3) / 1e9, "unit": "GB/s",
+           "roofline": roofline("hbm", alg / (step_ms * 1e-3) / 1e9, peaks["hbm_gbs"], "GB/s", peak_source=peaks["source"]),
+           "workload": {"workload": "row_softmax_v1", "rows": rows, "cols": cols, "algorithmic_bytes_per_step": alg,
+                        "l2": "input+output (512 MiB) larger than L2"}}
+    y.copy_to_host_async(stream, host_y)
+    stream.synchronize()
+    t0 = time.perf_counter()
+    x.copy_from_host_async(stream, host_x)
+    prep.launch(stream)
+    y.copy_to_host_async(stream, host_y)
+    stream.synchronize()
+    dt = time.perf_counter() - t0
+    res["e2e"] = {"value": alg / dt / 1e9, "unit": "GB/s", "h2d_bytes_per_step": 4 * n, "d2h_bytes_per_step": 4 * n}
+    if cpu:
+        import oracle
+        sample = 4096
+        t0 = time.perf_counter()
+        st, want = oracle.row_softmax(host_x[: sample * cols].reshape(sample, cols))
+        dt = time.perf_counter() - t0
+        got = host_y[: sample * cols].reshape(sample, cols)
+        rel = float((np.abs(got - want) / np.maximum(np.abs(want), 1e-30)).max())
+        res["cpu_baseline"] = {"value": sample * cols * 8 / dt / 1e9, "unit": "GB/s", "cores": os.cpu_count(),
+                               "kind": "port", "sample": f"first {sample} rows"}
+        res["parity"] = {"max_rel": rel, "tolerance": 1e-5, "ok": bool(st == 0 and rel <= 1e-5)}
+    return res
+
+
+def wl_gemm(h, steps, warmup, m=8192, n=8192, k=8192, cpu=True):
+    fe = h.fe
+    from fe2o3_b200 import synth
+    ctx, stream = h.ctx, h.stream
+    peaks = measured_peaks()
+    a_h, b_h = synth.uniform_bf16(0, 1, m * k), synth.uniform_bf16(0, 2, k * n)
+    a, b = fe.DeviceBuffer.from_host(stream, a_h), fe.DeviceBuffer.from_host(stream, b_h)
+    c = fe.DeviceBuffer.zeroed(stream, m * n, np.float32)
+    prep = fe.prepare(ctx, "tiled_gemm_v1", schedule=fe.SCHEDULE_TCGEN05, a=a, b=b, c=c, m=m, n=n, k=k)
+    ms = h.time_steps(lambda: prep.launch(stream), steps, warmup, flush=False)
+    if ctx.take_kernel_status(stream):
+        raise RuntimeError("tensor-core GEMM reported a kernel status word")
+    step_ms = float(np.mean(ms))
+    flops = 2.0 * m * n * k
+    tf = flops / (step_ms * 1e-3) / 1e12
+    res = {"ms_per_step": step_ms, "value": tf, "unit": "TFLOP/s",
+           "roofline": roofline("tensor", tf, peaks["bf16_tflops"], "TFLOP/s", peak_source=peaks["source"]),
+           "workload": {"workload": "tiled_gemm_v1", "m": m, "n": n, "k": k, "dtype": "bf16 in, f32 out",
+                        "algorithmic_flops_per_step": flops, "l2": "A+B (256 MiB) larger than L2"}}
+    if cpu:
+        import oracle
+        rows = 8
+        got = c.to_host_vec(stream)[: rows * n]
+        t0 = time.perf_counter()
+        want = oracle.gemm_bf16_rows(rows, n, k, a_h[: rows * k], b_h)
+        dt = time.perf_counter() - t0
+        err = float(np.abs(got - want).max())
+        res["cpu_baseline"] = {"value": 2.0 * rows * n * k / dt / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count(),
+                               "kind": "port", "sample": f"first {rows} rows of C"}
+        res["parity"] = {"max_abs": err, "tolerance": 1e-3 * float(np.sqrt(k)) / 3, "ok": bool(err <= 1e-3 * np.sqrt(k) / 3)}
+    return res
+
+
+WORKLOADS = {"masked_reduce_u32": wl_masked_reduce, "row_softmax_v1": wl_row_softmax, "tiled_gemm_v1": wl_gemm}
+UNITS = {"masked_reduce_u32": ("masked u32 reduction throughput", "elements/s", "u32")}
+
+
+def run_reference_arm(args):
+    """The reference's CPU implementation of the headline workload (the oracle port:
+    the reference is Rust and cannot be compiled here), all host threads."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import oracle
+    oracle.build()
+    from fe2o3_b200 import synth
+    n = 1 << 28
+    v = synth.u32_below(1, 1, n, 1 << 16)
+    a, _ = synth.bernoulli(1, 2, n, 0.75, flag_value=7, packed=False)
+    for _ in range(args.warmup):
+        oracle.masked_sum_u32(v, a, parallel=True)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        oracle.masked_sum_u32(v, a, parallel=True)
+    dt = (time.perf_counter() - t0) / args.steps
+    val = n / dt
+    print(json.dumps({
+        "impl": "reference", "metric": UNITS[HEADLINE][0], "value": val, "unit": "elements/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "u32", "data": "synthetic",
+        "config": {"workload": "masked_reduce_u32", "elements": n},
+        "cpu_baseline": {"value": val, "unit": "elements/s", "cores": os.cpu_count(), "kind": "port",
+                         "sample": "the full 2^28-element workload per step"},
+        "e2e": {"value": val, "unit": "elements/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default=HEADLINE)
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--no-extra", action="store_true", help="skip the secondary ops in the `ops` object")
+    ap.add_argument("--small", action="store_true", help="reduced sizes (profiler captures)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        return run_reference_arm(args)
+
+    import torch
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    h = Harness(rank, world, local_rank)
+    kw = {}
+    if args.small:
+        kw = {"masked_reduce_u32": {"n": 1 << 26}, "row_softmax_v1": {"rows": 16384},
+              "tiled_gemm_v1": {"m": 2048, "n": 2048, "k": 2048}}.get(args.workload, {})
+    clocks = ClockSampler(local_rank)
+    h.clocks = clocks
+    res = WORKLOADS[args.workload](h, args.steps, args.warmup, **kw)
+    h.clocks = None
+    ops = {}
+    if not args.no_extra and world == 1 and not args.small:
+        for name, fn in WORKLOADS.items():
+            if name == args.workload:
+                continue
+            try:
+                r = fn(h, min(args.steps, 10), args.warmup)
+                ops[name] = {k: r[k] for k in ("value", "unit", "ms_per_step", "roofline", "cpu_baseline", "parity", "e2e")
+                             if k in r}
+            except Exception as e:  # a secondary op must not take the headline down
+                ops[name] = {"error": f"{type(e).__name__}: {e}"}
+    if rank == 0:
+        metric, unit, dtype = UNITS.get(args.workload, (args.workload, res["unit"], "f32"))
+        line = {"metric": metric, "value": res["value"], "unit": res["unit"], "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
+                "config": res["workload"], "roofline": res["roofline"], "e2e": res.get("e2e"),
+                "cpu_baseline": res.get("cpu_baseline"), "gpu_launches": res.get("launches", args.steps),
+                "clocks": clocks.summary(), "parity": res.get("parity"), "ops": ops}
+        print(json.dumps(line))
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
