@@ -215,6 +215,8 @@ int regions_for(uint32_t op, const void *args, Region *r, int32_t *status) {
                 *status = unsupported("tiled_gemm_v1 admits M, N, K multiples of 16 (tails rejected)");
                 return 0;
             }
+            // empty output: no dispatch, operand storage is not inspected (oracle.rs:296-298)
+            if ((uint64_t)a->m * a->n == 0) return 0;
             r[0] = RGN("A", a->a, (uint64_t)a->m * a->k, eb, false);
             r[1] = RGN("B", a->b, (uint64_t)a->k * a->n, eb, false);
             r[2] = RGN("C", a->c, (uint64_t)a->m * a->n, 4, true);
@@ -226,6 +228,7 @@ int regions_for(uint32_t op, const void *args, Region *r, int32_t *status) {
                 *status = unsupported("StrideTooSmall: lda >= k, ldb >= n, ldc >= n required");
                 return 0;
             }
+            if ((uint64_t)a->m * a->n == 0) return 0;
             uint64_t ea, ebx, ec;
             if (!extent(a->m, a->k, a->lda, &ea) || !extent(a->k, a->n, a->ldb, &ebx) ||
                 !extent(a->m, a->n, a->ldc, &ec)) {

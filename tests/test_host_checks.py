@@ -71,6 +71,8 @@ def test_gemm_admission_matches_the_planner():
     # zero-K: A and B are empty, C still has its extent (tests/numerical_contract.rs:31-48)
     fe.check_args("tiled_gemm_general_v1", fe.make_args("tiled_gemm_general_v1", a=(0, 0), b=(0, 0), c=sl(0, 8), m=2,
                                                         n=3, k=0, lda=0, ldb=3, ldc=5))
+    # empty output: nothing is dispatched and operand storage is not inspected (tests/inputs_oracle.rs:253-272)
+    fe.check_args("tiled_gemm_v1", fe.make_args("tiled_gemm_v1", a=sl(0, 1), b=sl(4096, 1), c=(0, 0), m=0, n=16, k=16))
     assert err("scalar_gemm_v1", a=sl(0, 6), b=sl(4096, 6), c=sl(8, 4), m=2, n=2, k=3) == "OutputAliasesInput"
     assert err("scalar_gemm_v1", a=(0, 6), b=sl(4096, 6), c=sl(8192, 4), m=2, n=2, k=3) == "NullAddress"
     assert err("scalar_gemm_v1", a=(BASE + 2, 6), b=sl(4096, 6), c=sl(8192, 4), m=2, n=2, k=3) == "Alignment"
