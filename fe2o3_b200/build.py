@@ -1,6 +1,6 @@
 """Builds libfe2o3_b200.so in-tree with nvcc for sm_100a.
 
-Usage: python -m fe2o3_b200.build [--force] [--verbose]
+Usage: python fe2o3_b200/build.py [--force] [--verbose]
 """
 import os
 import subprocess
