@@ -1,7 +1,7 @@
 """ctypes binding of libfe2o3_b200.so (the C ABI declared in include/fe2o3_b200.h).
 
 There is no CPU fallback: if the shared library is missing, importing this
-module raises.  Build it with `python -m fe2o3_b200.build`.
+module raises.  Build it with `python fe2o3_b200/build.py`.
 """
 import ctypes as C
 import os
@@ -11,7 +11,7 @@ LIB_PATH = os.path.join(_HERE, "libfe2o3_b200.so")
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(
-        f"{LIB_PATH} is missing: the CUDA library must be built (python -m fe2o3_b200.build); "
+        f"{LIB_PATH} is missing: the CUDA library must be built (python fe2o3_b200/build.py); "
         "fe2o3_b200 has no CPU fallback")
 
 lib = C.CDLL(LIB_PATH)
@@ -114,7 +114,7 @@ EXPORTS = [
     "fe2o3_ctx_take_kernel_status", "fe2o3_load_executable", "fe2o3_resolve_kernel", "fe2o3_launch_and_wait",
     "fe2o3_unload_executable", "fe2o3_synth_uniform_f32", "fe2o3_synth_normal_f32", "fe2o3_synth_normal_bf16",
     "fe2o3_synth_uniform_bf16", "fe2o3_synth_u32_below", "fe2o3_synth_bernoulli", "fe2o3_synth_gemm_inputs_v1",
-    "fe2o3_bf16_from_f32", "fe2o3_launch_count",
+    "fe2o3_bf16_from_f32", "fe2o3_launch_count", "fe2o3_masked_reduce_u32_noalloc",
 ] + [f"fe2o3_{op}_check" for op in OPS] + [f"fe2o3_{op}_prepare" for op in OPS]
 
 lib.fe2o3_status_string.restype = C.c_char_p

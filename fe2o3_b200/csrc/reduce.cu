@@ -350,3 +350,83 @@ int32_t launch_scoped_atomic_add(fe2o3_ctx *ctx, cudaStream_t s, const void *arg
     fe2o3_count_launch(1);
     return fe2o3_cuda_status(cudaGetLastError(), "scoped_atomic_add_u32_v1");
 }
+
+// ---- allocation-free entry point ---------------------------------------------------
+// Some hosts must not call the device allocator once they are running: a process
+// whose device memory is already handed out in full to another runtime's pool
+// (cudaMalloc would fail), or a caller inside a section that cannot absorb the
+// device-wide synchronisation an allocation or free may imply.  For them the
+// masked sum is also offered with its scratch (per-block partial sums plus the
+// arrival counter) in a fixed device array that every GPU loading this library
+// carries until the process exits.
+//
+// The array's name in host code is only a host-side stand-in, not a device
+// address, so the address is taken once per device with cudaGetSymbolAddress
+// while that device is current and handed to the kernel as an ordinary pointer.
+#define FE2O3_NOALLOC_MAX_BLOCKS 1024u
+static __device__ __align__(256) uint32_t g_noalloc_scratch[FE2O3_NOALLOC_MAX_BLOCKS + 64];  // 4352 bytes
+
+#include <mutex>
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_noalloc_mutex;
+uint32_t *g_noalloc_ptr[kMaxDevices];
+int g_noalloc_sms[kMaxDevices];
+}  // namespace
+
+extern "C" int32_t fe2o3_masked_reduce_u32_noalloc(const uint32_t *values, const uint32_t *active, uint64_t n,
+                                                   uint32_t *output, void *cuda_stream) {
+    if (!output || (n && (!values || !active))) {
+        fe2o3_set_error("NullAddress: values, active and output must be device pointers");
+        return FE2O3_ERR_NULL_ADDRESS;
+    }
+    if (((reinterpret_cast<uintptr_t>(values) | reinterpret_cast<uintptr_t>(active) | reinterpret_cast<uintptr_t>(output)) & 3u) != 0) {
+        fe2o3_set_error("Alignment: u32 pointers must be 4-byte aligned");
+        return FE2O3_ERR_ALIGNMENT;
+    }
+    if (n > FE2O3_NOALLOC_MAX_ELEMENTS) {
+        fe2o3_set_error("UnsupportedShape: %llu elements exceed the allocation-free limit of %llu; use "
+                        "fe2o3_masked_reduce_u32_prepare for larger inputs",
+                        (unsigned long long)n, (unsigned long long)FE2O3_NOALLOC_MAX_ELEMENTS);
+        return FE2O3_ERR_UNSUPPORTED_SHAPE;
+    }
+    int device = -1;
+    FE2O3_CUDA(cudaGetDevice(&device));
+    if (device < 0 || device >= kMaxDevices) {
+        fe2o3_set_error("device index %d outside the supported range", device);
+        return FE2O3_ERR_INVALID_ARGUMENT;
+    }
+    uint32_t *scratch;
+    int sms;
+    {
+        // One-time set-up per device (the first call on that device does it).
+        std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+        if (!g_noalloc_ptr[device]) {
+            void *p = nullptr;
+            FE2O3_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+            int v = 0;
+            FE2O3_CUDA(cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, device));
+            g_noalloc_sms[device] = v;
+            g_noalloc_ptr[device] = static_cast<uint32_t *>(p);
+        }
+        scratch = g_noalloc_ptr[device];
+        sms = g_noalloc_sms[device];
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+    uint64_t want = (n / 4 + kReduceThreads - 1) / kReduceThreads;
+    uint64_t cap = (uint64_t)sms * 4u;
+    if (cap > FE2O3_NOALLOC_MAX_BLOCKS) cap = FE2O3_NOALLOC_MAX_BLOCKS;
+    if (want < 1) want = 1;
+    const uint32_t grid = (uint32_t)(want < cap ? want : cap);
+    uint32_t *counter = scratch + FE2O3_NOALLOC_MAX_BLOCKS;
+    // The array keeps whatever the previous call left: the arrival counter must start at zero.
+    FE2O3_CUDA(cudaMemsetAsync(counter, 0, sizeof(uint32_t), s));
+    fe2o3_masked_reduce_u32_args a;
+    a.values = fe2o3_slice{reinterpret_cast<uint64_t>(values), n};
+    a.active = fe2o3_slice{reinterpret_cast<uint64_t>(active), n};
+    a.output = fe2o3_slice{reinterpret_cast<uint64_t>(output), 1};
+    masked_reduce_u32_kernel<<<grid, kReduceThreads, 0, s>>>(a, scratch, counter, nullptr);
+    fe2o3_count_launch(1);
+    return fe2o3_cuda_status(cudaGetLastError(), "masked_reduce_u32_noalloc");
+}

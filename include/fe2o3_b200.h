@@ -426,6 +426,32 @@ int32_t fe2o3_synth_gemm_inputs_v1(uint32_t m, uint32_t n, uint32_t k, uint64_t 
 /* crates/fe2o3-device/src/half.rs:182-190 */
 uint16_t fe2o3_bf16_from_f32(float value);
 
+/* ---- allocation-free masked sum ------------------------------------------ */
+/* No counterpart in the reference.  The same masked u32 wrapping sum as
+ * fe2o3_masked_reduce_u32_prepare + launch, for hosts that must not touch the
+ * device allocator while they run: processes whose device memory is already
+ * owned in full by another runtime's pool, or callers in a section that cannot
+ * take the device-wide synchronisation an allocation may imply.  It needs no
+ * fe2o3_ctx and calls no cudaMalloc, cudaFree or allocating library routine:
+ * its scratch (per-block partial sums and an arrival counter) is a fixed
+ * 4352-byte device array that every GPU loading the library holds until the
+ * process exits.
+ *   values, active : device pointers to n u32 each (flag 0 = inactive)
+ *   output         : device pointer to one u32
+ *   cuda_stream    : a cudaStream_t (NULL = default stream); the launch is
+ *                    asynchronous on it, on the calling thread's current device
+ * Limits and rules:
+ *   - n <= FE2O3_NOALLOC_MAX_ELEMENTS, larger inputs are rejected with
+ *     FE2O3_ERR_UNSUPPORTED_SHAPE (use the prepared entry point instead);
+ *   - the first call on each device looks up the scratch array's device address
+ *     (one-time set-up); make that first call before any stream capture begins;
+ *   - all calls on a device share the one scratch array: two calls whose kernels
+ *     can overlap on the GPU (different streams, or different threads) race and
+ *     give wrong sums; issue them on one stream or order them with events. */
+#define FE2O3_NOALLOC_MAX_ELEMENTS (1ull << 31)
+int32_t fe2o3_masked_reduce_u32_noalloc(const uint32_t *values, const uint32_t *active, uint64_t n,
+                                        uint32_t *output, void *cuda_stream);
+
 /* Number of kernels this library has launched in the calling process. */
 uint64_t fe2o3_launch_count(void);
 
