@@ -287,8 +287,159 @@ def wl_gemm(h, steps, warmup, m=8192, n=8192, k=8192, cpu=True):
     return res
 
 
-WORKLOADS = {"masked_reduce_u32": wl_masked_reduce, "row_softmax_v1": wl_row_softmax, "tiled_gemm_v1": wl_gemm}
-UNITS = {"masked_reduce_u32": ("masked u32 reduction throughput", "elements/s", "u32")}
+def wl_attention(h, steps, warmup, batch=4, heads=16, seq=2048, dim=64, cpu=True):
+    fe = h.fe
+    from fe2o3_b200 import synth
+    ctx, stream = h.ctx, h.stream
+    peaks = measured_peaks()
+    n = batch * heads * seq * dim
+    host = [ctx.pinned(n, np.uint16) for _ in range(3)]
+    for i, buf in enumerate(host):
+        synth.normal_bf16(3, 1 + i, n, 1.0, out=buf)
+    host_o = ctx.pinned(n, np.float32)
+    q, k, v = (fe.DeviceBuffer.from_host(stream, b) for b in host)
+    o = fe.DeviceBuffer.zeroed(stream, n, np.float32)
+    scale = 1.0 / float(np.sqrt(dim))
+    prep = fe.prepare(ctx, "flash_attention_v1", q=q, k=k, v=v, output=o, batch=batch, heads=heads, seq=seq, dim=dim,
+                      scale=scale, causal=0, input_dtype=fe.DTYPE_BF16)
+    ms = h.time_steps(lambda: prep.launch(stream), steps, warmup, flush=True)
+    if ctx.take_kernel_status(stream):
+        raise RuntimeError("attention reported a kernel status word")
+    step_ms = float(np.mean(ms))
+    flops = 4.0 * batch * heads * seq * seq * dim
+    tf = flops / (step_ms * 1e-3) / 1e12
+    res = {"ms_per_step": step_ms, "value": tf, "unit": "TFLOP/s",
+           "roofline": roofline("tensor", tf, peaks["bf16_tflops"], "TFLOP/s", peak_source=peaks["source"]),
+           "workload": {"workload": "flash_attention_v1", "batch": batch, "heads": heads, "seq": seq, "dim": dim,
+                        "causal": False, "dtype": "bf16 in, f32 out", "algorithmic_flops_per_step": flops,
+                        "l2": "256 MiB L2 flush between steps"}}
+
+    def e2e_step():
+        for d, s in zip((q, k, v), host):
+            d.copy_from_host_async(stream, s)
+        prep.launch(stream)
+        o.copy_to_host_async(stream, host_o)
+        stream.synchronize()
+    e2e_step()
+    t0 = time.perf_counter()
+    for _ in range(3):
+        e2e_step()
+    dt = (time.perf_counter() - t0) / 3
+    res["e2e"] = {"value": flops / dt / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": 6 * n, "d2h_bytes_per_step": 4 * n}
+    if cpu:
+        import oracle
+        qs = 64  # bounded sample: the first 64 query rows of head (0,0) against all keys
+        S, D = seq, dim
+        f = lambda b: synth.bf16_to_f32(b[: S * D]).reshape(1, 1, S, D)
+        t0 = time.perf_counter()
+        st, want = oracle.flash_attention(f(host[0]), f(host[1]), f(host[2]), scale, False)
+        dt = time.perf_counter() - t0
+        got = host_o[: S * D].reshape(S, D)
+        err = np.abs(got - want[0, 0]) - (2e-3 * np.abs(want).max() + 2e-2 * np.abs(want[0, 0]))
+        res["cpu_baseline"] = {"value": 4.0 * S * S * D / dt / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count(),
+                               "kind": "port", "sample": "head (0,0): 2048 queries x 2048 keys, f64 two-pass oracle"}
+        res["parity"] = {"max_abs": float(np.abs(got - want[0, 0]).max()), "tolerance": "2e-3*max|e| + 2e-2*|e|",
+                         "ok": bool(st == 0 and err.max() <= 0)}
+    return res
+
+
+MOE_SHAPE = dict(tokens=16384, d_model=2048, d_ff=4096, experts=8)
+
+
+def moe_inputs(rank, world, tokens, d_model, d_ff, experts):
+    """This rank's shard of the seeded MoE inputs (x rows and expert weights)."""
+    from fe2o3_b200 import synth
+    t_local, per = tokens // world, experts // world
+    full_x = synth.normal_bf16(4, 1, tokens * d_model, 1.0)
+    x = full_x[rank * t_local * d_model:(rank + 1) * t_local * d_model]
+    wg = synth.normal_bf16(4, 2, d_model * experts, 0.02)
+    # expert e's matrices are streams (4, 100 + e) and (4, 200 + e): shards are independent of `world`
+    w1 = np.concatenate([synth.normal_bf16(4, 100 + e, d_model * d_ff, 0.02) for e in range(rank * per, (rank + 1) * per)])
+    w2 = np.concatenate([synth.normal_bf16(4, 200 + e, d_ff * d_model, 0.02) for e in range(rank * per, (rank + 1) * per)])
+    return x, wg, w1, w2
+
+
+def wl_moe(h, steps, warmup, cpu=True, **shape):
+    fe = h.fe
+    from fe2o3_b200.moe import MoeTop2Layer
+    shape = {**MOE_SHAPE, **shape}
+    T, d, f, E = shape["tokens"], shape["d_model"], shape["d_ff"], shape["experts"]
+    peaks = measured_peaks()
+    layer = MoeTop2Layer(h.ctx, h.stream, T, d, f, E, rank=h.rank, world=h.world)
+    x, wg, w1, w2 = moe_inputs(h.rank, h.world, T, d, f, E)
+    layer.load(x, wg, w1, w2)
+    l0 = fe.launch_count()
+    ms = h.time_steps(layer.forward, steps, warmup, flush=False)
+    launches = (fe.launch_count() - l0) * steps // (steps + warmup)
+    if h.ctx.take_kernel_status(h.stream):
+        raise RuntimeError("MoE reported a kernel status word")
+    step_ms = h.max_over_ranks(float(np.mean(ms)))
+    flops = T * 2 * 4.0 * d * f + 2.0 * T * d * E
+    tf = flops / (step_ms * 1e-3) / 1e12
+    res = {"ms_per_step": step_ms, "value": T / (step_ms * 1e-3), "unit": "tokens/s", "launches": launches,
+           "scaling": "strong",
+           "roofline": roofline("tensor", tf / h.world, peaks["bf16_tflops_sustained"], "TFLOP/s",
+                                peak_source=peaks["source"] + " (sustained, per GPU)"),
+           "workload": {"workload": "moe_top2_v1", **shape, "gate": "softmax(x*Wg), top-2 renormalised",
+                        "ffn": "GELU(erf), bf16 hidden", "parallelism": f"ep{h.world}" if h.world > 1 else "single",
+                        "algorithmic_flops_per_step": flops,
+                        "l2": "weights (256 MiB) + activations larger than L2"}}
+    torch = h.torch
+    t_local = T // h.world
+    host_x = torch.from_numpy(x.view(np.int16).copy()).pin_memory()
+    host_out = torch.empty(t_local * d, dtype=torch.float32).pin_memory()
+
+    def e2e_step():
+        layer.x.view(torch.int16).copy_(host_x, non_blocking=True)
+        out = layer.forward()
+        host_out.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    e2e_step()
+    h.barrier()
+    t0 = time.perf_counter()
+    for _ in range(5):
+        e2e_step()
+    h.barrier()
+    dt = h.max_over_ranks((time.perf_counter() - t0) / 5)
+    res["e2e"] = {"value": T / dt, "unit": "tokens/s", "h2d_bytes_per_step": 2 * t_local * d * h.world,
+                  "d2h_bytes_per_step": 4 * t_local * d * h.world, "ms_per_step": dt * 1e3}
+    if cpu and h.rank == 0:
+        import oracle
+        oracle.build()
+        sample = 64  # tokens of rank 0 checked end to end against the oracle
+        out = host_out.numpy().reshape(t_local, d)[:sample]
+        t0 = time.perf_counter()
+        xs = x[: sample * d]
+        logits = oracle.moe_gate_logits(xs, wg, sample, d, E)
+        _, routing = oracle.moe_top2_route(logits, sample, E, 2 * sample)
+        w = oracle.moe_route_weights(logits, routing["top2_experts"], sample, E)
+        if h.world == 1:
+            w1_all, w2_all = w1, w2
+        else:
+            from fe2o3_b200 import synth
+            w1_all = np.concatenate([synth.normal_bf16(4, 100 + e, d * f, 0.02) for e in range(E)])
+            w2_all = np.concatenate([synth.normal_bf16(4, 200 + e, f * d, 0.02) for e in range(E)])
+        compact = oracle.moe_expert_ffn(xs, w1_all, w2_all, routing["top2_experts"], routing["inverse"], sample, d, f, E)
+        _, want = oracle.moe_combine(compact, routing["inverse"], w, sample, d)
+        dt = time.perf_counter() - t0
+        want = want.reshape(sample, d)
+        top2_gpu = layer.top2.cpu().numpy().view(np.uint32)[: 2 * sample]
+        err = np.abs(out - want) - (2e-3 * np.abs(want).max() + 2e-2 * np.abs(want))
+        res["cpu_baseline"] = {"value": sample / dt, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port",
+                               "sample": f"the first {sample} tokens through gate, routing, FFN and combine"}
+        res["parity"] = {"routing_bit_exact": bool((top2_gpu == routing["top2_experts"]).all()),
+                         "max_abs": float(np.abs(out - want).max()), "tolerance": "2e-3*max|e| + 2e-2*|e|",
+                         "ok": bool(err.max() <= 0 and (top2_gpu == routing["top2_experts"]).all())}
+    return res
+
+
+WORKLOADS = {"masked_reduce_u32": wl_masked_reduce, "row_softmax_v1": wl_row_softmax, "tiled_gemm_v1": wl_gemm,
+             "flash_attention_v1": wl_attention, "moe_top2_v1": wl_moe}
+UNITS = {"masked_reduce_u32": ("masked u32 reduction throughput", "elements/s", "u32"),
+         "moe_top2_v1": ("MoE top-2 layer throughput", "tokens/s", "bf16"),
+         "tiled_gemm_v1": ("tiled GEMM throughput", "TFLOP/s", "bf16"),
+         "flash_attention_v1": ("flash attention throughput", "TFLOP/s", "bf16"),
+         "row_softmax_v1": ("row softmax bandwidth", "GB/s", "f32")}
 
 
 def run_reference_arm(args):
@@ -329,6 +480,7 @@ def main():
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary ops in the `ops` object")
     ap.add_argument("--small", action="store_true", help="reduced sizes (profiler captures)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-oracle leg (profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -343,8 +495,11 @@ def main():
     h = Harness(rank, world, local_rank)
     kw = {}
     if args.small:
-        kw = {"masked_reduce_u32": {"n": 1 << 26}, "row_softmax_v1": {"rows": 16384},
-              "tiled_gemm_v1": {"m": 2048, "n": 2048, "k": 2048}}.get(args.workload, {})
+        kw = {"masked_reduce_u32": {"n": 1 << 26}, "row_softmax_v1": {"rows": 32768},
+              "tiled_gemm_v1": {"m": 4096, "n": 4096, "k": 4096},
+              "moe_top2_v1": {"tokens": 2048}}.get(args.workload, {})
+    if args.no_cpu:
+        kw["cpu"] = False
     clocks = ClockSampler(local_rank)
     h.clocks = clocks
     res = WORKLOADS[args.workload](h, args.steps, args.warmup, **kw)
@@ -364,7 +519,7 @@ def main():
         metric, unit, dtype = UNITS.get(args.workload, (args.workload, res["unit"], "f32"))
         line = {"metric": metric, "value": res["value"], "unit": res["unit"], "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True,
-                "scaling": "weak", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
+                "scaling": res.get("scaling", "weak"), "vs_baseline": None, "dtype": dtype, "data": "synthetic",
                 "config": res["workload"], "roofline": res["roofline"], "e2e": res.get("e2e"),
                 "cpu_baseline": res.get("cpu_baseline"), "gpu_launches": res.get("launches", args.steps),
                 "clocks": clocks.summary(), "parity": res.get("parity"), "ops": ops}

@@ -50,6 +50,9 @@ MoeExpertFfnArgs = _struct("MoeExpertFfnArgs", ["x", "w1", "w2", "permutation", 
                            [("tokens", u32), ("d_model", u32), ("d_ff", u32), ("experts", u32)])
 MoeCombineArgs = _struct("MoeCombineArgs", ["compact_output", "inverse", "route_weights", "combined_output"],
                          [("tokens", u32), ("width", u32)])
+MoeCompactArgs = _struct("MoeCompactArgs", ["x", "permutation", "compact_x"], [("tokens", u32), ("d_model", u32)])
+MoeGroupedFfnArgs = _struct("MoeGroupedFfnArgs", ["compact_x", "w1", "w2", "group_offsets", "hidden", "compact_output"],
+                            [("d_model", u32), ("d_ff", u32), ("groups", u32), ("experts_cycle", u32)])
 MaskedReduceArgs = _struct("MaskedReduceArgs", ["values", "active", "output"])
 MaskedReducePackedArgs = _struct("MaskedReducePackedArgs", ["values", "mask", "output"])
 WaveLdsArgs = _struct("WaveLdsArgs", ["values", "active", "wave_out", "workgroup_out"])
@@ -91,6 +94,8 @@ OPS = {
     "moe_route_weights_v1": (MoeRouteWeightsArgs, 56, False),
     "moe_expert_ffn_v1": (MoeExpertFfnArgs, 144, False),
     "moe_expert_combine_v1": (MoeCombineArgs, 72, False),
+    "moe_compact_v1": (MoeCompactArgs, 56, False),
+    "moe_grouped_ffn_v1": (MoeGroupedFfnArgs, 112, False),
     "masked_reduce_u32": (MaskedReduceArgs, 48, False),
     "masked_reduce_u32_packed": (MaskedReducePackedArgs, 48, False),
     "wave_lds_v1": (WaveLdsArgs, 64, False),

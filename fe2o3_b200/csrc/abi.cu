@@ -75,7 +75,8 @@ struct fe2o3_event {
 enum OpId : uint32_t {
     OP_SCALAR_GEMM, OP_TILED_GEMM, OP_TILED_GEMM_GENERAL, OP_FLASH_ATTENTION, OP_ROW_SOFTMAX, OP_MOE_TOP2,
     OP_MOE_GATE, OP_MOE_ROUTE_WEIGHTS, OP_MOE_EXPERT_FFN, OP_MOE_COMBINE, OP_MASKED_REDUCE, OP_MASKED_REDUCE_PACKED,
-    OP_WAVE_LDS, OP_WAVE64_COLLECTIVES, OP_WAVE64_SEGMENTED, OP_LDS_REDUCE_I32, OP_SCOPED_ATOMIC_ADD, OP_COUNT
+    OP_WAVE_LDS, OP_WAVE64_COLLECTIVES, OP_WAVE64_SEGMENTED, OP_LDS_REDUCE_I32, OP_SCOPED_ATOMIC_ADD,
+    OP_MOE_COMPACT, OP_MOE_GROUPED_FFN, OP_COUNT
 };
 
 struct OpInfo {
@@ -102,6 +103,8 @@ static const OpInfo kOps[OP_COUNT] = {
     {"wave64_collectives_segmented", sizeof(fe2o3_wave64_collectives_segmented_args), launch_wave64_collectives_segmented},
     {"lds_publish_read_reduce_i32_v1", sizeof(fe2o3_lds_publish_read_reduce_i32_v1_args), launch_lds_reduce_i32},
     {"scoped_atomic_add_u32_v1", sizeof(fe2o3_scoped_atomic_add_u32_v1_args), launch_scoped_atomic_add},
+    {"moe_compact_v1", sizeof(fe2o3_moe_compact_v1_args), nullptr},
+    {"moe_grouped_ffn_v1", sizeof(fe2o3_moe_grouped_ffn_v1_args), nullptr},
 };
 
 struct fe2o3_prepared {
@@ -316,6 +319,31 @@ int regions_for(uint32_t op, const void *args, Region *r, int32_t *status) {
             r[7] = RGN("CompactOutput", a->compact_output, rows * a->d_model, 4, true);
             return 8;
         }
+        case OP_MOE_COMPACT: {
+            const fe2o3_moe_compact_v1_args *a = static_cast<const fe2o3_moe_compact_v1_args *>(args);
+            if (a->d_model == 0 || (a->d_model % 8)) { *status = unsupported("d_model must be a positive multiple of 8"); return 0; }
+            r[0] = RGN("X", a->x, (uint64_t)a->tokens * a->d_model, 2, false);
+            r[1] = RGN("Permutation", a->permutation, a->permutation.len, 4, false);
+            r[2] = RGN("CompactX", a->compact_x, a->permutation.len * a->d_model, 2, true);
+            return 3;
+        }
+        case OP_MOE_GROUPED_FFN: {
+            const fe2o3_moe_grouped_ffn_v1_args *a = static_cast<const fe2o3_moe_grouped_ffn_v1_args *>(args);
+            if (a->d_model == 0 || a->d_ff == 0 || (a->d_model % 8) || (a->d_ff % 8) || a->groups < 1 || a->groups > 32 ||
+                a->experts_cycle < 1 || a->experts_cycle > a->groups) {
+                *status = unsupported("d_model, d_ff positive multiples of 8; 1 <= experts_cycle <= groups <= 32");
+                return 0;
+            }
+            if (a->compact_output.len % a->d_model) { *status = unsupported("compact_output is not whole rows"); return 0; }
+            const uint64_t rows = a->compact_output.len / a->d_model;
+            r[0] = RGN("CompactX", a->compact_x, rows * a->d_model, 2, false);
+            r[1] = RGN("W1", a->w1, (uint64_t)a->experts_cycle * a->d_model * a->d_ff, 2, false);
+            r[2] = RGN("W2", a->w2, (uint64_t)a->experts_cycle * a->d_ff * a->d_model, 2, false);
+            r[3] = RGN("GroupOffsets", a->group_offsets, a->groups + 1, 4, false);
+            r[4] = RGN("Hidden", a->hidden, rows * a->d_ff, 2, true);
+            r[5] = RGN("CompactOutput", a->compact_output, rows * a->d_model, 4, true);
+            return 6;
+        }
         case OP_MOE_COMBINE: {
             const fe2o3_moe_expert_combine_v1_args *a = static_cast<const fe2o3_moe_expert_combine_v1_args *>(args);
             if (a->width == 0 || a->compact_output.len % a->width) {
@@ -469,6 +497,16 @@ int32_t launch_prepared(fe2o3_prepared *p, cudaStream_t s) {
             int32_t st = launch_moe_compact(s, a->x.ptr, a->permutation.ptr, a->compact_x.ptr, rows, a->d_model, a->tokens);
             if (st != FE2O3_OK) return st;
             st = gemm_tc_launch(&p->gemm[0], s);
+            if (st != FE2O3_OK) return st;
+            return gemm_tc_launch(&p->gemm[1], s);
+        }
+        case OP_MOE_COMPACT: {
+            const fe2o3_moe_compact_v1_args *a = reinterpret_cast<const fe2o3_moe_compact_v1_args *>(p->kernarg);
+            return launch_moe_compact(s, a->x.ptr, a->permutation.ptr, a->compact_x.ptr, (uint32_t)a->permutation.len,
+                                      a->d_model, a->tokens);
+        }
+        case OP_MOE_GROUPED_FFN: {
+            int32_t st = gemm_tc_launch(&p->gemm[0], s);
             if (st != FE2O3_OK) return st;
             return gemm_tc_launch(&p->gemm[1], s);
         }
@@ -910,6 +948,35 @@ int32_t fe2o3_moe_expert_ffn_v1_prepare(fe2o3_ctx *ctx, const fe2o3_moe_expert_f
     return FE2O3_OK;
 }
 
+int32_t fe2o3_moe_compact_v1_check(const fe2o3_moe_compact_v1_args *args) { return check_op(OP_MOE_COMPACT, args); }
+int32_t fe2o3_moe_grouped_ffn_v1_check(const fe2o3_moe_grouped_ffn_v1_args *args) {
+    return check_op(OP_MOE_GROUPED_FFN, args);
+}
+int32_t fe2o3_moe_compact_v1_prepare(fe2o3_ctx *ctx, const fe2o3_moe_compact_v1_args *a, fe2o3_prepared **out) {
+    int32_t st = prepare_common(ctx, OP_MOE_COMPACT, a, out);
+    if (st != FE2O3_OK) return st;
+    (*out)->geo = fe2o3_geometry{{(uint32_t)a->permutation.len, 1, 1}, {256, 1, 1}, 0, 1};
+    return FE2O3_OK;
+}
+int32_t fe2o3_moe_grouped_ffn_v1_prepare(fe2o3_ctx *ctx, const fe2o3_moe_grouped_ffn_v1_args *a,
+                                         fe2o3_prepared **out) {
+    int32_t st = prepare_common(ctx, OP_MOE_GROUPED_FFN, a, out);
+    if (st != FE2O3_OK) return st;
+    fe2o3_prepared *p = *out;
+    const uint32_t rows = (uint32_t)(a->compact_output.len / a->d_model);
+    const uint32_t *off = reinterpret_cast<const uint32_t *>(a->group_offsets.ptr);
+    st = gemm_tc_plan(ctx, &p->gemm[0], a->compact_x.ptr, a->w1.ptr, a->hidden.ptr, rows, a->d_ff, a->d_model,
+                      a->d_model, a->d_ff, a->d_ff, 1.f, 0.f, 2u, off, a->groups, a->experts_cycle, a->experts_cycle);
+    if (st == FE2O3_OK)
+        st = gemm_tc_plan(ctx, &p->gemm[1], a->hidden.ptr, a->w2.ptr, a->compact_output.ptr, rows, a->d_model, a->d_ff,
+                          a->d_ff, a->d_model, a->d_model, 1.f, 0.f, 0u, off, a->groups, a->experts_cycle,
+                          a->experts_cycle);
+    if (st != FE2O3_OK) return fail_prepare(out, st);
+    gemm_tc_geometry(&p->gemm[0], &p->geo);
+    p->geo.launches = 2;
+    return FE2O3_OK;
+}
+
 // ---- launch ------------------------------------------------------------------------------------
 int32_t fe2o3_prepared_launch(fe2o3_prepared *p, fe2o3_stream *stream) {
     if (!p || !stream) return FE2O3_ERR_INVALID_ARGUMENT;
@@ -992,6 +1059,8 @@ int32_t fe2o3_launch_and_wait(fe2o3_executable *exe, uint32_t kernel_id, const v
         case OP_TILED_GEMM_GENERAL: st = fe2o3_tiled_gemm_general_v1_prepare(exe->ctx, (const fe2o3_tiled_gemm_general_v1_args *)kernarg, FE2O3_GEMM_SCHEDULE_AUTO, &p); break;
         case OP_FLASH_ATTENTION: st = fe2o3_flash_attention_v1_prepare(exe->ctx, (const fe2o3_flash_attention_v1_args *)kernarg, &p); break;
         case OP_MOE_EXPERT_FFN: st = fe2o3_moe_expert_ffn_v1_prepare(exe->ctx, (const fe2o3_moe_expert_ffn_v1_args *)kernarg, &p); break;
+        case OP_MOE_COMPACT: st = fe2o3_moe_compact_v1_prepare(exe->ctx, (const fe2o3_moe_compact_v1_args *)kernarg, &p); break;
+        case OP_MOE_GROUPED_FFN: st = fe2o3_moe_grouped_ffn_v1_prepare(exe->ctx, (const fe2o3_moe_grouped_ffn_v1_args *)kernarg, &p); break;
         default:
             st = prepare_common(exe->ctx, kernel_id, kernarg, &p);
             if (st == FE2O3_OK) st = finish_simple(p);

@@ -157,7 +157,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     for (int j = 0; j < BN / 64; ++j) {
                         if (p.experts)
                             tma_load_3d(sb + j * 8192, &tmB, &full[stage], (int32_t)(t.n0 * BN + j * 64),
-                                        (int32_t)(kb * BK), (int32_t)t.expert);
+                                        (int32_t)(kb * BK), (int32_t)(p.expert_mod ? t.expert % p.expert_mod : t.expert));
                         else
                             tma_load_2d(sb + j * 8192, &tmB, &full[stage], (int32_t)(t.n0 * BN + j * 64),
                                         (int32_t)(kb * BK));
@@ -339,14 +339,14 @@ bool gemm_tc_supported(uint64_t a, uint64_t b, uint32_t lda, uint32_t ldb, uint3
 // bound on rows (the capacity of A and C).
 int32_t gemm_tc_plan(fe2o3_ctx *ctx, GemmTcPlan *plan, uint64_t a, uint64_t b, uint64_t c, uint32_t M, uint32_t N,
                      uint32_t K, uint32_t lda, uint32_t ldb, uint32_t ldc, float alpha, float beta, uint32_t epilogue,
-                     const uint32_t *expert_offsets, uint32_t experts) {
+                     const uint32_t *expert_offsets, uint32_t experts, uint32_t expert_mod, uint32_t b_matrices) {
     plan->bn = (N > 128) ? 256 : 128;
     uint64_t dA[2] = {K, M}, sA[1] = {(uint64_t)lda * 2};
     uint32_t bA[2] = {BK, BM};
     int32_t st = fe2o3_make_tmap_bf16(&plan->tmA, a, 2, dA, sA, bA);
     if (st != FE2O3_OK) return st;
     if (experts) {
-        uint64_t dB[3] = {N, K, experts}, sB[2] = {(uint64_t)ldb * 2, (uint64_t)ldb * 2 * K};
+        uint64_t dB[3] = {N, K, b_matrices ? b_matrices : experts}, sB[2] = {(uint64_t)ldb * 2, (uint64_t)ldb * 2 * K};
         uint32_t bB[3] = {64, BK, 1};
         st = fe2o3_make_tmap_bf16(&plan->tmB, b, 3, dB, sB, bB);
     } else {
@@ -356,7 +356,7 @@ int32_t gemm_tc_plan(fe2o3_ctx *ctx, GemmTcPlan *plan, uint64_t a, uint64_t b, u
     }
     if (st != FE2O3_OK) return st;
     plan->p = GemmParams{reinterpret_cast<void *>(c), M, N, K, ldc, alpha, beta, epilogue, expert_offsets, experts,
-                         ctx->status_word};
+                         expert_mod, ctx->status_word};
     const uint32_t n_tiles = (N + plan->bn - 1) / plan->bn;
     const uint64_t m_tiles = (uint64_t)(M + BM - 1) / BM + experts;  // grouped: each expert may add a ragged tile
     uint64_t tiles = m_tiles * n_tiles;

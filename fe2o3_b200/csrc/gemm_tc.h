@@ -13,7 +13,8 @@ struct GemmParams {
     // grouped mode: rows of A/C are partitioned by expert_offsets[0..experts];
     // B has one [K][N] matrix per expert (third TMA coordinate).
     const uint32_t *expert_offsets;
-    uint32_t experts;        // 0 = plain GEMM
+    uint32_t experts;        // 0 = plain GEMM; otherwise the number of row groups
+    uint32_t expert_mod;     // group g reads B matrix (g % expert_mod); 0 = identity
     uint32_t *status;
 };
 
@@ -30,6 +31,6 @@ int32_t fe2o3_make_tmap_bf16(CUtensorMap *out, uint64_t base, uint32_t rank, con
 bool gemm_tc_supported(uint64_t a, uint64_t b, uint32_t lda, uint32_t ldb, uint32_t K);
 int32_t gemm_tc_plan(fe2o3_ctx *ctx, GemmTcPlan *plan, uint64_t a, uint64_t b, uint64_t c, uint32_t M, uint32_t N,
                      uint32_t K, uint32_t lda, uint32_t ldb, uint32_t ldc, float alpha, float beta, uint32_t epilogue,
-                     const uint32_t *expert_offsets, uint32_t experts);
+                     const uint32_t *expert_offsets, uint32_t experts, uint32_t expert_mod = 0, uint32_t b_matrices = 0);
 int32_t gemm_tc_launch(const GemmTcPlan *plan, cudaStream_t s);
 void gemm_tc_geometry(const GemmTcPlan *plan, fe2o3_geometry *geo);

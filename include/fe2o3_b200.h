@@ -246,6 +246,24 @@ typedef struct fe2o3_moe_expert_ffn_v1_args {
     uint32_t tokens, d_model, d_ff, experts;
 } fe2o3_moe_expert_ffn_v1_args;
 
+/* The two halves of the expert schedule as separate launches, for the
+ * expert-parallel layout where an all-to-all sits between them.
+ * moe_compact_v1: compact_x[slot,:] = x[permutation[slot]/2,:], zero rows for
+ * unused slots (pipeline.rs:181-215); rows = permutation.len.
+ * moe_grouped_ffn_v1: GELU(x*W1)*W2 over `groups` consecutive row segments
+ * given by group_offsets[0..groups]; segment g uses expert (g % experts_cycle)
+ * of w1 [experts_cycle][d_model][d_ff] and w2 [experts_cycle][d_ff][d_model]
+ * (rows that arrive source-rank-major, local-expert-minor). */
+typedef struct fe2o3_moe_compact_v1_args {
+    fe2o3_slice x, permutation, compact_x;
+    uint32_t tokens, d_model;
+} fe2o3_moe_compact_v1_args;
+
+typedef struct fe2o3_moe_grouped_ffn_v1_args {
+    fe2o3_slice compact_x, w1, w2, group_offsets, hidden, compact_output;
+    uint32_t d_model, d_ff, groups, experts_cycle;
+} fe2o3_moe_grouped_ffn_v1_args;
+
 /* examples/moe_expert_v1/src/kernel.rs:104-109
  * moe_expert_combine_f32_t8_k2_o16_v1(compact_output, inverse, route_weights,
  * combined_output) generalised to tokens x width. */
@@ -319,6 +337,8 @@ int32_t fe2o3_moe_gate_v1_check(const fe2o3_moe_gate_v1_args *args);
 int32_t fe2o3_moe_route_weights_v1_check(const fe2o3_moe_route_weights_v1_args *args);
 int32_t fe2o3_moe_expert_ffn_v1_check(const fe2o3_moe_expert_ffn_v1_args *args);
 int32_t fe2o3_moe_expert_combine_v1_check(const fe2o3_moe_expert_combine_v1_args *args);
+int32_t fe2o3_moe_compact_v1_check(const fe2o3_moe_compact_v1_args *args);
+int32_t fe2o3_moe_grouped_ffn_v1_check(const fe2o3_moe_grouped_ffn_v1_args *args);
 int32_t fe2o3_masked_reduce_u32_check(const fe2o3_masked_reduce_u32_args *args);
 int32_t fe2o3_masked_reduce_u32_packed_check(const fe2o3_masked_reduce_u32_packed_args *args);
 int32_t fe2o3_wave_lds_v1_check(const fe2o3_wave_lds_v1_args *args);
@@ -347,6 +367,9 @@ int32_t fe2o3_moe_expert_ffn_v1_prepare(fe2o3_ctx *ctx, const fe2o3_moe_expert_f
                                         fe2o3_prepared **out);
 int32_t fe2o3_moe_expert_combine_v1_prepare(fe2o3_ctx *ctx, const fe2o3_moe_expert_combine_v1_args *args,
                                             fe2o3_prepared **out);
+int32_t fe2o3_moe_compact_v1_prepare(fe2o3_ctx *ctx, const fe2o3_moe_compact_v1_args *args, fe2o3_prepared **out);
+int32_t fe2o3_moe_grouped_ffn_v1_prepare(fe2o3_ctx *ctx, const fe2o3_moe_grouped_ffn_v1_args *args,
+                                         fe2o3_prepared **out);
 int32_t fe2o3_masked_reduce_u32_prepare(fe2o3_ctx *ctx, const fe2o3_masked_reduce_u32_args *args,
                                         fe2o3_prepared **out);
 int32_t fe2o3_masked_reduce_u32_packed_prepare(fe2o3_ctx *ctx, const fe2o3_masked_reduce_u32_packed_args *args,
