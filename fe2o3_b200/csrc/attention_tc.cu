@@ -5,14 +5,18 @@
 // exp(m_old - m_new), running denominator, out = acc / l) applied per block of
 // 128 keys instead of per key, with both contractions on tcgen05:
 //   S = Q * K^T   (A = Q tile, B = K tile, both K-major, accumulator in TMEM)
-//   PV = P * V    (A = P written to shared memory as bf16, B = V tile, MN-major)
+//   O += P * V    (A = P written to shared memory as bf16, B = V tile, MN-major,
+//                  accumulator O stays in TMEM for the whole key loop)
 // One CTA owns one (batch, head) and 256 query rows as two 128-row tiles that
 // share every K/V tile.  Ten warps: 0 = TMA producer, 1 = MMA issuer and TMEM
 // owner, 2-5 = softmax for tile 0, 6-9 = softmax for tile 1.  A softmax thread
-// owns one query row (TMEM lane), so row maxima and sums need no shuffles; the
-// output accumulator lives in registers and each PV block is added with the
-// block's rescale factor.  Scores are scaled inside exp2: p = 2^(s*c - m*c),
-// c = scale * log2(e).  All waits are bounded.
+// owns one query row (one TMEM lane): it reads its 128 scores once into
+// registers and releases S at once, so the next Q*K^T overlaps the exponentials.
+// The exponent offset is a per-row reference maximum that is only moved (and O
+// and l rescaled through TMEM) when the block maximum exceeds it by more than
+// 2^8; the final quotient O / l is independent of the offset, so the result is
+// the same function as the reference recurrence.  Scores are scaled inside
+// exp2: p = 2^(s*c - m*c), c = scale * log2(e).  All waits are bounded.
 #include "common.cuh"
 #include "gemm_tc.h"
 
@@ -27,6 +31,7 @@ constexpr int BKV = 128;         // keys per block
 constexpr int QT = 2;            // query tiles per CTA
 constexpr int KV_STAGES = 2;
 constexpr int kThreads = 32 * (2 + 4 * QT);
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 constexpr uint32_t kTileBytes = 128 * D * 2;     // 16 KiB: a 128 x 64 bf16 tile
 constexpr uint32_t kPBytes = BQ * BKV * 2;       // 32 KiB: P tile as two 64-key sub-tiles
@@ -37,7 +42,7 @@ constexpr uint32_t kOffP = kOffV + KV_STAGES * kTileBytes;
 constexpr uint32_t kOffBar = kOffP + QT * kPBytes;
 constexpr uint32_t kSmemTotal = kOffBar + 512 + 1024;
 
-// TMEM columns: S tile t at t*128 (128 f32 columns), PV tile t at 256 + t*64.
+// TMEM columns: S tile t at t*128 (128 f32 columns), O tile t at 256 + t*64.
 constexpr uint32_t kTmemCols = 512;
 
 struct AttnParams {
@@ -68,9 +73,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     uint64_t *s_full = v_empty + KV_STAGES;        // QT
     uint64_t *s_empty = s_full + QT;
     uint64_t *p_ready = s_empty + QT;
-    uint64_t *pv_full = p_ready + QT;
-    uint64_t *pv_empty = pv_full + QT;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(pv_empty + QT);
+    uint64_t *pv_done = p_ready + QT;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(pv_done + QT);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t q_blocks = (p.seq + QT * BQ - 1) / (QT * BQ);
@@ -92,8 +96,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             mbar_init(&s_full[t], 1);
             mbar_init(&s_empty[t], 4);
             mbar_init(&p_ready[t], 4);
-            mbar_init(&pv_full[t], 1);
-            mbar_init(&pv_empty[t], 4);
+            mbar_init(&pv_done[t], 1);
         }
         mbar_fence_init();
     }
@@ -117,28 +120,28 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             for (int t = 0; t < QT; ++t)
                 tma_load_3d(smem + kOffQ + t * kTileBytes, &tmQ, q_full, 0, (int32_t)(q0 + t * BQ), (int32_t)head);
             uint32_t last_k[KV_STAGES], last_v[KV_STAGES];
-            bool ever[KV_STAGES];
-            for (int i = 0; i < KV_STAGES; ++i) { last_k[i] = last_v[i] = 0; ever[i] = false; }
+            bool k_armed[KV_STAGES], v_armed[KV_STAGES];
+            for (int i = 0; i < KV_STAGES; ++i) { last_k[i] = last_v[i] = 0; k_armed[i] = v_armed[i] = false; }
             uint32_t stage = 0, phase = 0;
             for (uint32_t j = 0; j < nkv && ok; ++j) {
                 if (!mbar_wait(&k_empty[stage], phase ^ 1)) { ok = false; break; }
                 mbar_arrive_expect_tx(&k_full[stage], kTileBytes);
                 tma_load_3d(smem + kOffK + stage * kTileBytes, &tmK, &k_full[stage], 0, (int32_t)(j * BKV), (int32_t)head);
                 last_k[stage] = phase;
-                if (!mbar_wait(&v_empty[stage], phase ^ 1)) { ever[stage] = true; last_v[stage] = 2; ok = false; break; }
+                k_armed[stage] = true;
+                if (!mbar_wait(&v_empty[stage], phase ^ 1)) { ok = false; break; }
                 mbar_arrive_expect_tx(&v_full[stage], kTileBytes);
                 tma_load_3d(smem + kOffV + stage * kTileBytes, &tmV, &v_full[stage], 0, (int32_t)(j * BKV), (int32_t)head);
                 last_v[stage] = phase;
-                ever[stage] = true;
+                v_armed[stage] = true;
                 if (++stage == KV_STAGES) { stage = 0; phase ^= 1; }
             }
             if (!ok) kstatus_set(p.status, FE2O3_KSTATUS_WAIT_EXPIRED);
             // drain this thread's copies before the CTA can exit
             mbar_wait(q_full, 0);
             for (int i = 0; i < KV_STAGES; ++i) {
-                if (!ever[i]) continue;
-                mbar_wait(&k_full[i], last_k[i]);
-                if (last_v[i] != 2) mbar_wait(&v_full[i], last_v[i]);
+                if (k_armed[i]) mbar_wait(&k_full[i], last_k[i]);
+                if (v_armed[i]) mbar_wait(&v_full[i], last_v[i]);
             }
         }
     } else if (warp == 1) {
@@ -154,15 +157,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 if (!mbar_wait(&v_full[vst], vph)) return false;
                 for (int t = 0; t < QT; ++t) {
                     if (!mbar_wait(&p_ready[t], jj & 1)) return false;
-                    if (!mbar_wait(&pv_empty[t], (jj & 1) ^ 1)) return false;
                     tc_fence_after();
 #pragma unroll
                     for (int kk = 0; kk < BKV / 16; ++kk) {
                         const uint64_t adesc = umma_smem_desc(sP + t * kPBytes + (kk / 4) * kTileBytes + (kk % 4) * 32, 16, 1024);
                         const uint64_t bdesc = umma_smem_desc(sV + vst * kTileBytes + kk * 2048, 8192, 1024);
-                        umma_f16(tmem_base + 256 + t * D, adesc, bdesc, idesc_pv, kk != 0);
+                        umma_f16(tmem_base + 256 + t * D, adesc, bdesc, idesc_pv, (jj | (uint32_t)kk) != 0u);
                     }
-                    umma_commit(&pv_full[t]);
+                    umma_commit(&pv_done[t]);
                 }
                 umma_commit(&v_empty[vst]);
                 if (++vst == KV_STAGES) { vst = 0; vph ^= 1; }
@@ -197,121 +199,134 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const uint32_t qrow = q0 + t * BQ + r;      // query index inside the head
         const uint32_t lane_addr = (quad * 32u) << 16;
         const uint32_t tS = tmem_base + t * BKV + lane_addr;
-        const uint32_t tPV = tmem_base + 256 + t * D + lane_addr;
+        const uint32_t tO = tmem_base + 256 + t * D + lane_addr;
         uint8_t *prow = smem + kOffP + t * kPBytes + (r >> 3) * 1024 + (r & 7) * 128;
         const float c = p.scale_log2;
-        float m = -INFINITY, l = 0.0f, alpha_prev = 0.0f;
-        float o[D];
-#pragma unroll
-        for (int i = 0; i < D; ++i) o[i] = 0.0f;
+        float m_ref = -INFINITY;   // exponent offset, in raw score units
+        float l = 0.0f;
         bool ok = true;
-
-        auto consume_pv = [&](uint32_t jj) -> bool {
-            if (!mbar_wait(&pv_full[t], jj & 1)) return false;
-            tc_fence_after();
-#pragma unroll
-            for (int h = 0; h < D / 32; ++h) {
-                uint32_t v[32];
-                tmem_ld_32x32b_x32(tPV + h * 32, v);
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) o[h * 32 + i] = fmaf(o[h * 32 + i], alpha_prev, __uint_as_float(v[i]));
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&pv_empty[t]);
-            return true;
-        };
 
         for (uint32_t j = 0; j < nkv; ++j) {
             if (!mbar_wait(&s_full[t], j & 1)) { ok = false; break; }
             tc_fence_after();
+            // the whole score row into registers, then S is free for the next Q*K^T
+            uint32_t sv[BKV];
+            {
+                uint32_t (&s0)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sv[0]);
+                uint32_t (&s1)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sv[32]);
+                uint32_t (&s2)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sv[64]);
+                uint32_t (&s3)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sv[96]);
+                tmem_ld_32x32b_x32(tS, s0);
+                tmem_ld_32x32b_x32(tS + 32, s1);
+                tmem_ld_32x32b_x32(tS + 64, s2);
+                tmem_ld_32x32b_x32(tS + 96, s3);
+                tmem_ld_wait();
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_empty[t]);
+
             const uint32_t key0 = j * BKV;
             const bool need_mask = (key0 + BKV > p.seq) || (p.causal && key0 + BKV - 1 > q0 + t * BQ);
-            // pass 1: row maximum of the raw scores
-            float rowmax = -INFINITY;
-#pragma unroll 1
-            for (int ch = 0; ch < BKV / 32; ++ch) {
-                uint32_t v[32];
-                tmem_ld_32x32b_x32(tS + ch * 32, v);
-                tmem_ld_wait();
-                if (need_mask) {
+            if (need_mask) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const uint32_t key = key0 + ch * 32 + i;
-                        const bool valid = key < p.seq && (!p.causal || key <= qrow);
-                        rowmax = fmaxf(rowmax, valid ? __uint_as_float(v[i]) : -INFINITY);
-                    }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) rowmax = fmaxf(rowmax, __uint_as_float(v[i]));
+                for (int i = 0; i < BKV; ++i) {
+                    const uint32_t key = key0 + i;
+                    const bool valid = key < p.seq && (!p.causal || key <= qrow);
+                    if (!valid) sv[i] = 0xff800000u;  // -inf
                 }
             }
-            const float m_new = fmaxf(m, rowmax);
-            // a row with no admitted key yet keeps m = -inf; use 0 as the exponent offset then
-            const float m_use = m_new == -INFINITY ? 0.0f : m_new;
-            const float alpha = exp2f((m - m_use) * c);
-            // previous block's PV must be complete before P is overwritten; fold it in now
-            if (j > 0 && !consume_pv(j - 1)) { ok = false; break; }
-            // pass 2: p = 2^(s*c - m*c), row sum, P tile to shared memory (128-byte swizzled rows)
-            const float mc = m_use * c;
-            float rowsum = 0.0f;
-#pragma unroll 1
-            for (int ch = 0; ch < BKV / 32; ++ch) {
-                uint32_t v[32];
-                tmem_ld_32x32b_x32(tS + ch * 32, v);
-                tmem_ld_wait();
-                float pr[32];
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float s = __uint_as_float(v[i]);
-                    if (need_mask) {
-                        const uint32_t key = key0 + ch * 32 + i;
-                        const bool valid = key < p.seq && (!p.causal || key <= qrow);
-                        s = valid ? s : -INFINITY;
+            for (int i = 0; i < BKV; i += 4) {
+                mx0 = fmaxf(mx0, __uint_as_float(sv[i]));
+                mx1 = fmaxf(mx1, __uint_as_float(sv[i + 1]));
+                mx2 = fmaxf(mx2, __uint_as_float(sv[i + 2]));
+                mx3 = fmaxf(mx3, __uint_as_float(sv[i + 3]));
+            }
+            const float rowmax = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+            // move the reference only when the block maximum outgrows it by more than the threshold
+            const bool move = (rowmax - m_ref) * c > kRescaleThreshold;  // true for the first admitted key (m_ref = -inf)
+            // P of the previous block must have been consumed and O must be quiescent
+            if (j > 0) {
+                if (!mbar_wait(&pv_done[t], (j - 1) & 1)) { ok = false; break; }
+                tc_fence_after();
+                if (__any_sync(0xffffffffu, move)) {
+                    const float factor = move ? ex2_approx((m_ref - rowmax) * c) : 1.0f;  // 0 when m_ref = -inf
+#pragma unroll
+                    for (int h = 0; h < D / 32; ++h) {
+                        uint32_t ov[32];
+                        tmem_ld_32x32b_x32(tO + h * 32, ov);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * factor);
+                        tmem_st_32x32b_x32(tO + h * 32, ov);
                     }
-                    pr[i] = exp2f(fmaf(s, c, -mc));
-                    rowsum += pr[i];
+                    tmem_st_wait();
+                    l *= factor;
                 }
-                // 32 keys = four 16-byte chunks; chunk index inside the 64-key sub-tile is XOR-swizzled by row
+            }
+            if (move) m_ref = rowmax;
+            // p = 2^(s*c - m_ref*c); a row with no admitted key so far keeps m_ref = -inf: use offset 0, p = 0
+            const float mc = (m_ref == -INFINITY ? 0.0f : m_ref) * c;
+            float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+#pragma unroll
+            for (int ch = 0; ch < BKV / 32; ++ch) {
                 uint8_t *sub = prow + (ch >> 1) * kTileBytes;
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
+                    float e[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) e[i] = ex2_approx(fmaf(__uint_as_float(sv[ch * 32 + q * 8 + i]), c, -mc));
+                    sum0 += e[0] + e[4];
+                    sum1 += e[1] + e[5];
+                    sum2 += e[2] + e[6];
+                    sum3 += e[3] + e[7];
+                    // 16-byte chunk index inside the 64-key sub-tile is XOR-swizzled by the row
                     const uint32_t chunk = ((ch & 1) * 4 + q) ^ (r & 7);
-                    uint4 w = make_uint4(pack_bf16x2(pr[q * 8 + 0], pr[q * 8 + 1]), pack_bf16x2(pr[q * 8 + 2], pr[q * 8 + 3]),
-                                         pack_bf16x2(pr[q * 8 + 4], pr[q * 8 + 5]), pack_bf16x2(pr[q * 8 + 6], pr[q * 8 + 7]));
-                    *reinterpret_cast<uint4 *>(sub + chunk * 16) = w;
+                    *reinterpret_cast<uint4 *>(sub + chunk * 16) =
+                        make_uint4(pack_bf16x2(e[0], e[1]), pack_bf16x2(e[2], e[3]), pack_bf16x2(e[4], e[5]),
+                                   pack_bf16x2(e[6], e[7]));
                 }
             }
-            l = fmaf(l, alpha, rowsum);
-            m = m_new;
-            alpha_prev = alpha;
-            // S has been read twice: release it; publish P to the async proxy
-            tc_fence_before();
+            l += (sum0 + sum1) + (sum2 + sum3);
+            // publish P (generic-proxy writes) and any O rescale (TMEM stores) to the MMA issuer
             fence_proxy_async_smem();
+            tc_fence_before();
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(&s_empty[t]);
-                mbar_arrive(&p_ready[t]);
-            }
+            if (lane == 0) mbar_arrive(&p_ready[t]);
         }
-        if (ok && nkv > 0 && !consume_pv(nkv - 1)) ok = false;
+        if (ok && nkv > 0 && !mbar_wait(&pv_done[t], (nkv - 1) & 1)) ok = false;
         if (!ok) {
             if (lane == 0) kstatus_set(p.status, FE2O3_KSTATUS_WAIT_EXPIRED);
-        } else if (qrow < p.seq) {
+        } else if (nkv > 0) {
+            tc_fence_after();
             const float inv = 1.0f / l;
             bool finite = isfinite(l) && l > 0.0f;
+            float *dst = p.out + ((uint64_t)head * p.seq + qrow) * D;
+            uint32_t ov[D];
+            {
+                uint32_t (&o0)[32] = *reinterpret_cast<uint32_t (*)[32]>(&ov[0]);
+                uint32_t (&o1)[32] = *reinterpret_cast<uint32_t (*)[32]>(&ov[32]);
+                tmem_ld_32x32b_x32(tO, o0);  // every lane takes part in the collective loads
+                tmem_ld_32x32b_x32(tO + 32, o1);
+                tmem_ld_wait();
+            }
+            float o[D];
 #pragma unroll
             for (int i = 0; i < D; ++i) {
-                o[i] *= inv;
+                o[i] = __uint_as_float(ov[i]) * inv;
                 finite = finite && isfinite(o[i]);
             }
-            if (!finite) {
-                kstatus_set(p.status, FE2O3_KSTATUS_NONFINITE);  // finite-input policy: row left unwritten
-            } else {
-                float4 *dst = reinterpret_cast<float4 *>(p.out + ((uint64_t)head * p.seq + qrow) * D);
+            // finite-input policy: a row with a non-finite result is left unwritten and reported
+            if (qrow < p.seq) {
+                if (!finite) {
+                    kstatus_set(p.status, FE2O3_KSTATUS_NONFINITE);
+                } else {
 #pragma unroll
-                for (int i = 0; i < D / 4; ++i) dst[i] = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+                    for (int i = 0; i < D / 4; ++i)
+                        reinterpret_cast<float4 *>(dst)[i] = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+                }
             }
         }
     }
