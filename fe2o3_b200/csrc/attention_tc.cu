@@ -210,18 +210,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             if (!mbar_wait(&s_full[t], j & 1)) { ok = false; break; }
             tc_fence_after();
             // the whole score row into registers, then S is free for the next Q*K^T
-            uint32_t sv[BKV];
-            {
-                uint32_t (&s0)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sv[0]);
-                uint32_t (&s1)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sv[32]);
-                uint32_t (&s2)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sv[64]);
-                uint32_t (&s3)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sv[96]);
-                tmem_ld_32x32b_x32(tS, s0);
-                tmem_ld_32x32b_x32(tS + 32, s1);
-                tmem_ld_32x32b_x32(tS + 64, s2);
-                tmem_ld_32x32b_x32(tS + 96, s3);
-                tmem_ld_wait();
-            }
+            uint32_t s0[32], s1[32], s2[32], s3[32];
+            tmem_ld_32x32b_x32(tS, s0);
+            tmem_ld_32x32b_x32(tS + 32, s1);
+            tmem_ld_32x32b_x32(tS + 64, s2);
+            tmem_ld_32x32b_x32(tS + 96, s3);
+            tmem_ld_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&s_empty[t]);
@@ -229,20 +223,26 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             const uint32_t key0 = j * BKV;
             const bool need_mask = (key0 + BKV > p.seq) || (p.causal && key0 + BKV - 1 > q0 + t * BQ);
             if (need_mask) {
+                auto mask32 = [&](uint32_t (&s)[32], uint32_t base) {
 #pragma unroll
-                for (int i = 0; i < BKV; ++i) {
-                    const uint32_t key = key0 + i;
-                    const bool valid = key < p.seq && (!p.causal || key <= qrow);
-                    if (!valid) sv[i] = 0xff800000u;  // -inf
-                }
+                    for (int i = 0; i < 32; ++i) {
+                        const uint32_t key = base + i;
+                        const bool valid = key < p.seq && (!p.causal || key <= qrow);
+                        if (!valid) s[i] = 0xff800000u;  // -inf
+                    }
+                };
+                mask32(s0, key0);
+                mask32(s1, key0 + 32);
+                mask32(s2, key0 + 64);
+                mask32(s3, key0 + 96);
             }
             float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-            for (int i = 0; i < BKV; i += 4) {
-                mx0 = fmaxf(mx0, __uint_as_float(sv[i]));
-                mx1 = fmaxf(mx1, __uint_as_float(sv[i + 1]));
-                mx2 = fmaxf(mx2, __uint_as_float(sv[i + 2]));
-                mx3 = fmaxf(mx3, __uint_as_float(sv[i + 3]));
+            for (int i = 0; i < 32; ++i) {
+                mx0 = fmaxf(mx0, __uint_as_float(s0[i]));
+                mx1 = fmaxf(mx1, __uint_as_float(s1[i]));
+                mx2 = fmaxf(mx2, __uint_as_float(s2[i]));
+                mx3 = fmaxf(mx3, __uint_as_float(s3[i]));
             }
             const float rowmax = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
             // move the reference only when the block maximum outgrows it by more than the threshold
@@ -253,14 +253,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 tc_fence_after();
                 if (__any_sync(0xffffffffu, move)) {
                     const float factor = move ? ex2_approx((m_ref - rowmax) * c) : 1.0f;  // 0 when m_ref = -inf
-#pragma unroll
-                    for (int h = 0; h < D / 32; ++h) {
-                        uint32_t ov[32];
-                        tmem_ld_32x32b_x32(tO + h * 32, ov);
+#pragma unroll 1
+                    for (int h = 0; h < D / 8; ++h) {
+                        uint32_t ov[8];
+                        tmem_ld_32x32b_x8(tO + h * 8, ov);
                         tmem_ld_wait();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * factor);
-                        tmem_st_32x32b_x32(tO + h * 32, ov);
+                        for (int i = 0; i < 8; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * factor);
+                        tmem_st_32x32b_x8(tO + h * 8, ov);
                     }
                     tmem_st_wait();
                     l *= factor;
@@ -270,14 +270,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             // p = 2^(s*c - m_ref*c); a row with no admitted key so far keeps m_ref = -inf: use offset 0, p = 0
             const float mc = (m_ref == -INFINITY ? 0.0f : m_ref) * c;
             float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
-#pragma unroll
-            for (int ch = 0; ch < BKV / 32; ++ch) {
+            auto exp32 = [&](const uint32_t (&s)[32], int ch) {
                 uint8_t *sub = prow + (ch >> 1) * kTileBytes;
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     float e[8];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) e[i] = ex2_approx(fmaf(__uint_as_float(sv[ch * 32 + q * 8 + i]), c, -mc));
+                    for (int i = 0; i < 8; ++i) e[i] = ex2_approx(fmaf(__uint_as_float(s[q * 8 + i]), c, -mc));
                     sum0 += e[0] + e[4];
                     sum1 += e[1] + e[5];
                     sum2 += e[2] + e[6];
@@ -288,7 +287,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                         make_uint4(pack_bf16x2(e[0], e[1]), pack_bf16x2(e[2], e[3]), pack_bf16x2(e[4], e[5]),
                                    pack_bf16x2(e[6], e[7]));
                 }
-            }
+            };
+            exp32(s0, 0);
+            exp32(s1, 1);
+            exp32(s2, 2);
+            exp32(s3, 3);
             l += (sum0 + sum1) + (sum2 + sum3);
             // publish P (generic-proxy writes) and any O rescale (TMEM stores) to the MMA issuer
             fence_proxy_async_smem();
