@@ -590,6 +590,14 @@ int32_t fe2o3_ctx_create(int32_t device, fe2o3_ctx **out) {
     ctx->status_word = dev + ctx->reduce_scratch_elems;
     e = cudaMallocHost(&ctx->host_status, 64);
     if (e != cudaSuccess) { cudaFree(dev); delete ctx; return fe2o3_cuda_status(e, "cudaMallocHost"); }
+    e = cudaMalloc(&ctx->route_scratch, FE2O3_ROUTE_SCRATCH_ELEMS * sizeof(uint32_t));
+    if (e != cudaSuccess) {
+        cudaFree(dev);
+        cudaFreeHost(ctx->host_status);
+        delete ctx;
+        return fe2o3_cuda_status(e, "cudaMalloc(routing scratch)");
+    }
+    cudaMemset(ctx->route_scratch, 0, FE2O3_ROUTE_SCRATCH_ELEMS * sizeof(uint32_t));
     *out = ctx;
     return FE2O3_OK;
 }
@@ -600,6 +608,7 @@ int32_t fe2o3_ctx_destroy(fe2o3_ctx *ctx) {
     cudaError_t e = cudaDeviceSynchronize();
     if (e == cudaSuccess) {  // quiescent: safe to free; otherwise leak (completion is ambiguous)
         cudaFree(ctx->reduce_scratch);
+        cudaFree(ctx->route_scratch);
         cudaFreeHost(ctx->host_status);
     }
     delete ctx;

@@ -53,10 +53,11 @@ struct AttnParams {
     uint32_t *status;
 };
 
+// Two probabilities to packed bf16 on the integer pipe (round half up: add half an ulp, keep the
+// upper 16 bits).  The conversion instruction shares the quarter-rate unit with ex2, which is the
+// bottleneck of this kernel; inputs here are finite and non-negative, so no NaN handling is needed.
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
-    uint32_t r;
-    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-    return r;
+    return __byte_perm(__float_as_uint(lo) + 0x8000u, __float_as_uint(hi) + 0x8000u, 0x7632);
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -74,7 +75,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     uint64_t *s_empty = s_full + QT;
     uint64_t *p_ready = s_empty + QT;
     uint64_t *pv_done = p_ready + QT;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(pv_done + QT);
+    uint64_t *stagger = pv_done + QT;              // 1: tile 0 finished its first exponential phase
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(stagger + 1);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t q_blocks = (p.seq + QT * BQ - 1) / (QT * BQ);
@@ -98,6 +100,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             mbar_init(&p_ready[t], 4);
             mbar_init(&pv_done[t], 1);
         }
+        mbar_init(stagger, 4);
         mbar_fence_init();
     }
     if (warp == 1) {
@@ -153,17 +156,22 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                            sP = smem_u32(smem + kOffP);
             bool ok = mbar_wait(q_full, 0);
             uint32_t kst = 0, kph = 0, vst = 0, vph = 0;
+            // Descriptors are built once; inside the loops only the 16-byte-unit start address field moves.
+            const uint64_t dQ = umma_smem_desc(sQ, 16, 1024), dK = umma_smem_desc(sK, 16, 1024),
+                           dV = umma_smem_desc(sV, 8192, 1024), dP = umma_smem_desc(sP, 16, 1024);
             auto issue_pv = [&](uint32_t jj) -> bool {
                 if (!mbar_wait(&v_full[vst], vph)) return false;
+                const uint64_t dVs = dV + ((vst * kTileBytes) >> 4);
                 for (int t = 0; t < QT; ++t) {
                     if (!mbar_wait(&p_ready[t], jj & 1)) return false;
                     tc_fence_after();
+                    const uint64_t dPt = dP + ((t * kPBytes) >> 4);
+                    const uint32_t dst = tmem_base + 256 + t * D;
+                    umma_f16(dst, dPt, dVs, idesc_pv, jj != 0u);
 #pragma unroll
-                    for (int kk = 0; kk < BKV / 16; ++kk) {
-                        const uint64_t adesc = umma_smem_desc(sP + t * kPBytes + (kk / 4) * kTileBytes + (kk % 4) * 32, 16, 1024);
-                        const uint64_t bdesc = umma_smem_desc(sV + vst * kTileBytes + kk * 2048, 8192, 1024);
-                        umma_f16(tmem_base + 256 + t * D, adesc, bdesc, idesc_pv, (jj | (uint32_t)kk) != 0u);
-                    }
+                    for (int kk = 1; kk < BKV / 16; ++kk)
+                        umma_f16(dst, dPt + (((kk / 4) * kTileBytes + (kk % 4) * 32) >> 4), dVs + ((kk * 2048) >> 4),
+                                 idesc_pv, 1u);
                     umma_commit(&pv_done[t]);
                 }
                 umma_commit(&v_empty[vst]);
@@ -175,12 +183,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 for (int t = 0; t < QT && ok; ++t) {
                     if (!mbar_wait(&s_empty[t], (j & 1) ^ 1)) { ok = false; break; }
                     tc_fence_after();
+                    const uint64_t dQt = dQ + ((t * kTileBytes) >> 4), dKs = dK + ((kst * kTileBytes) >> 4);
 #pragma unroll
-                    for (int kk = 0; kk < D / 16; ++kk) {
-                        const uint64_t adesc = umma_smem_desc(sQ + t * kTileBytes + kk * 32, 16, 1024);
-                        const uint64_t bdesc = umma_smem_desc(sK + kst * kTileBytes + kk * 32, 16, 1024);
-                        umma_f16(tmem_base + t * BKV, adesc, bdesc, idesc_qk, kk != 0);
-                    }
+                    for (int kk = 0; kk < D / 16; ++kk)
+                        umma_f16(tmem_base + t * BKV, dQt + ((kk * 32) >> 4), dKs + ((kk * 32) >> 4), idesc_qk, kk != 0);
                     umma_commit(&s_full[t]);
                 }
                 if (!ok) break;
@@ -247,12 +253,44 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             const float rowmax = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
             // move the reference only when the block maximum outgrows it by more than the threshold
             const bool move = (rowmax - m_ref) * c > kRescaleThreshold;  // true for the first admitted key (m_ref = -inf)
+            const float factor = move ? ex2_approx((m_ref - rowmax) * c) : 1.0f;  // 0 when m_ref = -inf
+            if (move) m_ref = rowmax;
+            // p = 2^(s*c - m_ref*c); a row with no admitted key so far keeps m_ref = -inf: use offset 0, p = 0
+            const float mc = (m_ref == -INFINITY ? 0.0f : m_ref) * c;
+            // The two tiles share the exponential unit: tile 1 starts its first exponential phase when
+            // tile 0 has finished its own, so that afterwards one tile's exponentials overlap the other
+            // tile's loads, maxima and stores instead of competing with them.
+            if (j == 0 && t == 1 && !mbar_wait(stagger, 0)) { ok = false; break; }
+            float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+            // exponentials stay in registers as packed bf16 pairs until the P buffer is free
+            auto exp32 = [&](const uint32_t (&s)[32], uint32_t (&pk)[16]) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    float e[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) e[i] = ex2_approx(fmaf(__uint_as_float(s[q * 8 + i]), c, -mc));
+                    sum0 += e[0] + e[4];
+                    sum1 += e[1] + e[5];
+                    sum2 += e[2] + e[6];
+                    sum3 += e[3] + e[7];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) pk[q * 4 + i] = pack_bf16x2(e[2 * i], e[2 * i + 1]);
+                }
+            };
+            uint32_t pk0[16], pk1[16], pk2[16], pk3[16];
+            exp32(s0, pk0);
+            exp32(s1, pk1);
+            exp32(s2, pk2);
+            exp32(s3, pk3);
+            if (j == 0 && t == 0) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(stagger);
+            }
             // P of the previous block must have been consumed and O must be quiescent
             if (j > 0) {
                 if (!mbar_wait(&pv_done[t], (j - 1) & 1)) { ok = false; break; }
                 tc_fence_after();
                 if (__any_sync(0xffffffffu, move)) {
-                    const float factor = move ? ex2_approx((m_ref - rowmax) * c) : 1.0f;  // 0 when m_ref = -inf
 #pragma unroll 1
                     for (int h = 0; h < D / 8; ++h) {
                         uint32_t ov[8];
@@ -263,36 +301,22 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                         tmem_st_32x32b_x8(tO + h * 8, ov);
                     }
                     tmem_st_wait();
-                    l *= factor;
                 }
             }
-            if (move) m_ref = rowmax;
-            // p = 2^(s*c - m_ref*c); a row with no admitted key so far keeps m_ref = -inf: use offset 0, p = 0
-            const float mc = (m_ref == -INFINITY ? 0.0f : m_ref) * c;
-            float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
-            auto exp32 = [&](const uint32_t (&s)[32], int ch) {
+            l = fmaf(l, factor, (sum0 + sum1) + (sum2 + sum3));
+            // 32 keys = four 16-byte chunks; the chunk index inside the 64-key sub-tile is XOR-swizzled by the row
+            auto store32 = [&](const uint32_t (&pk)[16], int ch) {
                 uint8_t *sub = prow + (ch >> 1) * kTileBytes;
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
-                    float e[8];
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) e[i] = ex2_approx(fmaf(__uint_as_float(s[q * 8 + i]), c, -mc));
-                    sum0 += e[0] + e[4];
-                    sum1 += e[1] + e[5];
-                    sum2 += e[2] + e[6];
-                    sum3 += e[3] + e[7];
-                    // 16-byte chunk index inside the 64-key sub-tile is XOR-swizzled by the row
                     const uint32_t chunk = ((ch & 1) * 4 + q) ^ (r & 7);
-                    *reinterpret_cast<uint4 *>(sub + chunk * 16) =
-                        make_uint4(pack_bf16x2(e[0], e[1]), pack_bf16x2(e[2], e[3]), pack_bf16x2(e[4], e[5]),
-                                   pack_bf16x2(e[6], e[7]));
+                    *reinterpret_cast<uint4 *>(sub + chunk * 16) = make_uint4(pk[q * 4], pk[q * 4 + 1], pk[q * 4 + 2], pk[q * 4 + 3]);
                 }
             };
-            exp32(s0, 0);
-            exp32(s1, 1);
-            exp32(s2, 2);
-            exp32(s3, 3);
-            l += (sum0 + sum1) + (sum2 + sum3);
+            store32(pk0, 0);
+            store32(pk1, 1);
+            store32(pk2, 2);
+            store32(pk3, 3);
             // publish P (generic-proxy writes) and any O rescale (TMEM stores) to the MMA issuer
             fence_proxy_async_smem();
             tc_fence_before();

@@ -18,7 +18,12 @@ struct fe2o3_ctx {
     uint32_t *reduce_scratch;  // device: per-block partial sums + arrival counter
     uint32_t reduce_scratch_elems;
     uint32_t *host_status;     // pinned mirror for status read-back
+    uint32_t *route_scratch;   // device: per-block expert counts, per-block flags, arrival counter (MoE routing)
 };
+
+// Routing scratch layout: [FE2O3_ROUTE_MAX_BLOCKS][32] counts, [FE2O3_ROUTE_MAX_BLOCKS] flags, 1 summary, 1 counter.
+#define FE2O3_ROUTE_MAX_BLOCKS 16384u
+#define FE2O3_ROUTE_SCRATCH_ELEMS (FE2O3_ROUTE_MAX_BLOCKS * 33u + 64u)
 
 struct fe2o3_stream {
     fe2o3_ctx *ctx;

@@ -179,6 +179,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             constexpr uint32_t idesc = umma_idesc(1u, BM, BN, 0u, 1u);
             uint32_t stage = 0, phase = 0, it = 0;
             bool ok = true;
+            const uint64_t desc_a0 = umma_smem_desc(smem_u32(smem), 16, 1024);
+            const uint64_t desc_b0 = umma_smem_desc(smem_u32(smem) + L::kABytes, 8192, 1024);
             for (uint32_t id = blockIdx.x; ok; id += gridDim.x, ++it) {
                 TileCoord t = decode_tile(id, p, n_tiles, s_off);
                 if (!t.valid) break;
@@ -189,16 +191,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 for (uint32_t kb = 0; kb < num_kb; ++kb) {
                     if (!mbar_wait(&full[stage], phase)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t sa = smem_u32(smem + stage * L::kStageBytes);
-                    const uint32_t sb = sa + L::kABytes;
+                    // only the 16-byte-unit start address field of the descriptors moves
+                    const uint64_t adesc = desc_a0 + ((stage * L::kStageBytes) >> 4);
+                    const uint64_t bdesc = desc_b0 + ((stage * L::kStageBytes) >> 4);
+                    // A: K-major, advance 16 elements = 32 bytes inside the 128-byte row
+                    // B: MN-major, advance 16 k-rows = 2 KiB; 64-column groups are 8 KiB apart
+                    umma_f16(d_tmem, adesc, bdesc, idesc, kb != 0u);
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k) {
-                        // A: K-major, advance 16 elements = 32 bytes inside the 128-byte row
-                        const uint64_t adesc = umma_smem_desc(sa + k * UMMA_K * 2, 16, 1024);
-                        // B: MN-major, advance 16 k-rows = 2 KiB; 64-column groups are 8 KiB apart
-                        const uint64_t bdesc = umma_smem_desc(sb + k * UMMA_K * 128, 8192, 1024);
-                        umma_f16(d_tmem, adesc, bdesc, idesc, (kb | (uint32_t)k) != 0u);
-                    }
+                    for (int k = 1; k < BK / UMMA_K; ++k)
+                        umma_f16(d_tmem, adesc + ((k * UMMA_K * 2) >> 4), bdesc + ((k * UMMA_K * 128) >> 4), idesc, 1u);
                     umma_commit(&empty[stage]);
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }

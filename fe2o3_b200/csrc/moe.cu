@@ -1,6 +1,8 @@
 // MoE routing-side kernels: gate logits, top-2 selection with stable slot
 // packing, route weights, activation compaction and the weighted combine.
 // The expert FFN itself is the grouped tensor-core GEMM in gemm_tc.cu.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace {
@@ -158,6 +160,245 @@ moe_top2_kernel(fe2o3_moe_top2_v1_args a, uint32_t *status) {
     }
 }
 
+// ---- gate logits, one thread per token ---------------------------------------
+// Same arithmetic as moe_gate_kernel (every output is its own sequential f32
+// chain), arranged for latency: a thread owns one token and keeps E independent
+// accumulators, so E dependent-add chains are in flight per thread instead of
+// one.  64 tokens per block; x is staged k-major in shared memory so that the
+// per-k reads of a warp are conflict-free, Wg rows are broadcast reads.
+constexpr int kGate2Tokens = 64, kGate2KC = 64;
+
+template <int E>
+__global__ void __launch_bounds__(kGate2Tokens)
+moe_gate_token_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict__ wg, float *__restrict__ logits,
+                      uint32_t tokens, uint32_t d_model) {
+    __shared__ float xs[kGate2KC][kGate2Tokens + 1];
+    __shared__ __align__(16) float ws[kGate2KC][E];
+    const uint32_t tid = threadIdx.x;
+    const uint32_t t0 = blockIdx.x * kGate2Tokens;
+    float acc[E];
+#pragma unroll
+    for (int e = 0; e < E; ++e) acc[e] = 0.0f;
+    const bool vec = (d_model % 8u) == 0 && (reinterpret_cast<uint64_t>(x) & 15u) == 0;
+    for (uint32_t k0 = 0; k0 < d_model; k0 += kGate2KC) {
+        const uint32_t kc = min((uint32_t)kGate2KC, d_model - k0);
+        if (vec && kc == kGate2KC) {
+            // 8 lanes cover one token's 64 k values (128 bytes): coalesced 16-byte loads
+#pragma unroll
+            for (int pass = 0; pass < kGate2Tokens / 8; ++pass) {
+                const uint32_t tt = pass * 8 + (tid >> 3), c = tid & 7;
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (t0 + tt < tokens) v = __ldg(reinterpret_cast<const uint4 *>(x + (uint64_t)(t0 + tt) * d_model + k0) + c);
+                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    xs[c * 8 + 2 * i][tt] = __uint_as_float(w[i] << 16);
+                    xs[c * 8 + 2 * i + 1][tt] = __uint_as_float(w[i] & 0xffff0000u);
+                }
+            }
+        } else {
+            for (uint32_t i = tid; i < kGate2Tokens * kGate2KC; i += kGate2Tokens) {
+                const uint32_t tt = i / kGate2KC, kk = i % kGate2KC;
+                xs[kk][tt] = (t0 + tt < tokens && kk < kc) ? bf16_bits_to_f32(x[(uint64_t)(t0 + tt) * d_model + k0 + kk]) : 0.0f;
+            }
+        }
+        for (uint32_t i = tid; i < kc * E; i += kGate2Tokens) (&ws[0][0])[i] = bf16_bits_to_f32(wg[(uint64_t)k0 * E + i]);
+        __syncthreads();
+        for (uint32_t kk = 0; kk < kc; ++kk) {
+            const float xv = xs[kk][tid];
+#pragma unroll
+            for (int e = 0; e < E; ++e) acc[e] = __fadd_rn(acc[e], __fmul_rn(xv, ws[kk][e]));
+        }
+        __syncthreads();
+    }
+    if (t0 + tid < tokens) {
+#pragma unroll
+        for (int e = 0; e < E; ++e) logits[(uint64_t)(t0 + tid) * E + e] = acc[e];
+    }
+}
+
+// ---- top-2 routing over many blocks --------------------------------------------
+// Same result as moe_top2_kernel.  Block b owns tokens [256 b, 256 b + 256).
+// Pass 1 counts, per block and expert, the routes the block requests and checks
+// its logits; the last block to arrive scans the per-block counts over blocks
+// (exclusive, in block order) and publishes requested / admitted / offsets.
+// Pass 2 recomputes the selections, ranks each route inside its block with warp
+// ballots (route order = token order, rank 0 before rank 1) and adds the block's
+// base: a deterministic stable rank without atomics.  Nothing is written when any
+// logit is non-finite.
+constexpr int kRouteBlock = 256;
+
+__device__ __forceinline__ void top2_of_row(const float *row, uint32_t E, uint32_t &best, uint32_t &second, bool &finite) {
+    best = kDrop;
+    second = kDrop;
+    float bs = 0.f, ss = 0.f;
+    finite = true;
+    for (uint32_t e = 0; e < E; ++e) {
+        const float sc = row[e];
+        finite = finite && isfinite(sc);
+        if (best == kDrop || precedes(sc, e, bs, best)) {
+            second = best; ss = bs;
+            best = e; bs = sc;
+        } else if (second == kDrop || precedes(sc, e, ss, second)) {
+            second = e; ss = sc;
+        }
+    }
+}
+
+// Ranks of this thread's two routes among the block's routes to the same experts, and the block's
+// per-expert totals in s_total[E].  All 256 threads must call it.
+__device__ __forceinline__ void block_ranks(uint32_t best, uint32_t second, bool active, uint32_t E, uint32_t (*s_warp)[32],
+                                            uint32_t *s_total, uint32_t &rank_best, uint32_t &rank_second) {
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t lt = (1u << lane) - 1u;
+    uint32_t pa = 0, pb = 0;
+    for (uint32_t e = 0; e < E; ++e) {
+        const uint32_t mb = __ballot_sync(0xffffffffu, active && best == e);
+        const uint32_t ms = __ballot_sync(0xffffffffu, active && second == e);
+        const uint32_t before = __popc(mb & lt) + __popc(ms & lt);
+        if (best == e) pa = before;
+        if (second == e) pb = before;
+        if (lane == 0) s_warp[warp][e] = __popc(mb) + __popc(ms);
+    }
+    __syncthreads();
+    uint32_t base_a = 0, base_b = 0;
+    for (uint32_t w = 0; w < warp; ++w) {
+        if (active) { base_a += s_warp[w][best]; base_b += s_warp[w][second]; }
+    }
+    rank_best = pa + base_a;
+    rank_second = pb + base_b;
+    if (threadIdx.x < E) {
+        uint32_t tot = 0;
+        for (uint32_t w = 0; w < kRouteBlock / 32; ++w) tot += s_warp[w][threadIdx.x];
+        s_total[threadIdx.x] = tot;
+    }
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(kRouteBlock)
+moe_route_count_kernel(fe2o3_moe_top2_v1_args a, uint32_t *scratch, uint32_t *status) {
+    __shared__ uint32_t s_warp[kRouteBlock / 32][32];
+    __shared__ uint32_t s_total[32];
+    __shared__ int s_bad;
+    __shared__ bool s_last;
+    const uint32_t T = a.tokens, E = a.experts;
+    const uint64_t R = 2ull * T;
+    uint32_t *counts = scratch;                                   // [blocks][32]
+    uint32_t *flags = scratch + FE2O3_ROUTE_MAX_BLOCKS * 32u;      // [blocks]
+    uint32_t *summary = flags + FE2O3_ROUTE_MAX_BLOCKS;            // [0] = any non-finite logit
+    uint32_t *counter = summary + 1;
+    if (a.logits.len != (uint64_t)T * E || a.top2_experts.len != R || a.requested_counts.len != E ||
+        a.admitted_counts.len != E || a.expert_offsets.len != E + 1 || a.route_slots.len != R ||
+        a.permutation.len != R || a.inverse.len != R || E < 2 || E > 32) {
+        if (blockIdx.x == 0 && threadIdx.x == 0) {
+            kstatus_set(status, FE2O3_KSTATUS_LENGTH);
+            summary[0] = 2u;
+        }
+        return;
+    }
+    if (threadIdx.x == 0) s_bad = 0;
+    __syncthreads();
+    const uint32_t t = blockIdx.x * kRouteBlock + threadIdx.x;
+    const bool active = t < T;
+    uint32_t best = 0, second = 0;
+    bool finite = true;
+    if (active) top2_of_row(reinterpret_cast<const float *>(a.logits.ptr) + (uint64_t)t * E, E, best, second, finite);
+    if (!finite) atomicExch(&s_bad, 1);
+    uint32_t ra, rb;
+    block_ranks(best, second, active, E, s_warp, s_total, ra, rb);
+    if (threadIdx.x < E) counts[blockIdx.x * 32u + threadIdx.x] = s_total[threadIdx.x];
+    if (threadIdx.x == 0) {
+        flags[blockIdx.x] = (uint32_t)s_bad;
+        __threadfence();
+        s_last = atomicAdd(counter, 1u) == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // last block: exclusive scan of the per-block counts over blocks, one warp per expert
+    uint32_t bad = 0;
+    for (uint32_t b = threadIdx.x; b < gridDim.x; b += kRouteBlock) bad |= __ldcg(flags + b);
+    if (bad) atomicExch(&s_bad, 2);
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (uint32_t e = warp; e < E; e += kRouteBlock / 32) {
+        uint32_t running = 0;
+        for (uint32_t b0 = 0; b0 < gridDim.x; b0 += 32) {
+            const uint32_t b = b0 + lane;
+            const uint32_t v = b < gridDim.x ? __ldcg(counts + b * 32u + e) : 0u;
+            uint32_t inc = v;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const uint32_t n = __shfl_up_sync(0xffffffffu, inc, off);
+                if ((int)lane >= off) inc += n;
+            }
+            if (b < gridDim.x) counts[b * 32u + e] = running + inc - v;
+            running += __shfl_sync(0xffffffffu, inc, 31);
+        }
+        if (lane == 0) s_total[e] = running;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const bool any_bad = s_bad != 0;
+        summary[0] = any_bad ? 1u : 0u;
+        if (any_bad) {
+            kstatus_set(status, FE2O3_KSTATUS_NONFINITE);
+        } else {
+            uint32_t *requested = reinterpret_cast<uint32_t *>(a.requested_counts.ptr);
+            uint32_t *admitted = reinterpret_cast<uint32_t *>(a.admitted_counts.ptr);
+            uint32_t *offsets = reinterpret_cast<uint32_t *>(a.expert_offsets.ptr);
+            uint32_t off = 0;
+            offsets[0] = 0;
+            for (uint32_t e = 0; e < E; ++e) {
+                const uint32_t adm = s_total[e] > a.capacity ? a.capacity : s_total[e];
+                requested[e] = s_total[e];
+                admitted[e] = adm;
+                off += adm;
+                offsets[e + 1] = off;
+            }
+        }
+        *counter = 0u;  // re-arm for the next launch
+    }
+}
+
+__global__ void __launch_bounds__(kRouteBlock)
+moe_route_place_kernel(fe2o3_moe_top2_v1_args a, const uint32_t *scratch) {
+    __shared__ uint32_t s_warp[kRouteBlock / 32][32];
+    __shared__ uint32_t s_total[32];
+    const uint32_t T = a.tokens, E = a.experts, cap = a.capacity;
+    const uint64_t R = 2ull * T;
+    const uint32_t *base = scratch + blockIdx.x * 32u;
+    const uint32_t *summary = scratch + FE2O3_ROUTE_MAX_BLOCKS * 33u;
+    if (__ldcg(summary) != 0u) return;  // failure preserves every output
+    const uint32_t *offsets = reinterpret_cast<const uint32_t *>(a.expert_offsets.ptr);
+    uint32_t *top2 = reinterpret_cast<uint32_t *>(a.top2_experts.ptr);
+    uint32_t *slots = reinterpret_cast<uint32_t *>(a.route_slots.ptr);
+    uint32_t *perm = reinterpret_cast<uint32_t *>(a.permutation.ptr);
+    uint32_t *inverse = reinterpret_cast<uint32_t *>(a.inverse.ptr);
+    const uint32_t t = blockIdx.x * kRouteBlock + threadIdx.x;
+    const bool active = t < T;
+    uint32_t best = 0, second = 0;
+    bool finite = true;
+    if (active) top2_of_row(reinterpret_cast<const float *>(a.logits.ptr) + (uint64_t)t * E, E, best, second, finite);
+    uint32_t ra, rb;
+    block_ranks(best, second, active, E, s_warp, s_total, ra, rb);
+    // unused tail of the permutation
+    const uint64_t accepted = offsets[E];
+    for (uint64_t s = accepted + (uint64_t)blockIdx.x * kRouteBlock + threadIdx.x; s < R; s += (uint64_t)gridDim.x * kRouteBlock)
+        perm[s] = kDrop;
+    if (!active) return;
+    const uint32_t ga = __ldcg(base + best) + ra, gb = __ldcg(base + second) + rb;
+    const uint32_t sa = ga < cap ? offsets[best] + ga : kDrop;
+    const uint32_t sb = gb < cap ? offsets[second] + gb : kDrop;
+    top2[2ull * t] = best;
+    top2[2ull * t + 1] = second;
+    slots[2ull * t] = sa;
+    slots[2ull * t + 1] = sb;
+    inverse[2ull * t] = sa;
+    inverse[2ull * t + 1] = sb;
+    if (sa != kDrop) perm[sa] = 2u * t;
+    if (sb != kDrop) perm[sb] = 2u * t + 1u;
+}
+
 // ---- route weights ------------------------------------------------------------
 // Softmax over the experts renormalised over the two winners equals a softmax
 // over the two winning logits: e1 = exp(l1 - l0) <= 1, w0 = 1/(1+e1) in
@@ -252,6 +493,19 @@ int32_t launch_moe_gate(fe2o3_ctx *, cudaStream_t s, const void *args, fe2o3_geo
     const uint32_t tpb = E >= 256 ? 1 : 256 / E;
     const uint32_t grid = ceil_div_u32(a->tokens, tpb);
     const uint32_t smem = (tpb * (kGateKC + 1) + kGateKC * E) * sizeof(float);
+    const bool per_token = E == 4 || E == 8 || E == 16;
+    if (per_token) {
+        const uint32_t g2 = ceil_div_u32(a->tokens, kGate2Tokens);
+        if (geo) *geo = fe2o3_geometry{{g2, 1, 1}, {kGate2Tokens, 1, 1}, 0, 1};
+        if (plan_only || a->tokens == 0) return FE2O3_OK;
+        const uint16_t *x = reinterpret_cast<const uint16_t *>(a->x.ptr), *wg = reinterpret_cast<const uint16_t *>(a->wg.ptr);
+        float *lg = reinterpret_cast<float *>(a->logits.ptr);
+        if (E == 4) moe_gate_token_kernel<4><<<g2, kGate2Tokens, 0, s>>>(x, wg, lg, a->tokens, a->d_model);
+        else if (E == 8) moe_gate_token_kernel<8><<<g2, kGate2Tokens, 0, s>>>(x, wg, lg, a->tokens, a->d_model);
+        else moe_gate_token_kernel<16><<<g2, kGate2Tokens, 0, s>>>(x, wg, lg, a->tokens, a->d_model);
+        fe2o3_count_launch(1);
+        return fe2o3_cuda_status(cudaGetLastError(), "moe_gate_v1");
+    }
     if (geo) *geo = fe2o3_geometry{{grid, 1, 1}, {E, tpb, 1}, smem, 1};
     if (plan_only || a->tokens == 0) return FE2O3_OK;
     if (smem > 48 * 1024)
@@ -266,6 +520,17 @@ int32_t launch_moe_gate(fe2o3_ctx *, cudaStream_t s, const void *args, fe2o3_geo
 
 int32_t launch_moe_top2(fe2o3_ctx *ctx, cudaStream_t s, const void *args, fe2o3_geometry *geo, bool plan_only) {
     const fe2o3_moe_top2_v1_args *a = static_cast<const fe2o3_moe_top2_v1_args *>(args);
+    const uint32_t blocks = ceil_div_u32(a->tokens ? a->tokens : 1, kRouteBlock);
+    // FE2O3_ROUTE_SINGLE_BLOCK=1 selects the one-block kernel (otherwise used beyond 4M tokens)
+    static const bool force_single = getenv("FE2O3_ROUTE_SINGLE_BLOCK") != nullptr;
+    if (blocks <= FE2O3_ROUTE_MAX_BLOCKS && !force_single) {
+        if (geo) *geo = fe2o3_geometry{{blocks, 1, 1}, {kRouteBlock, 1, 1}, 0, 2};
+        if (plan_only) return FE2O3_OK;
+        moe_route_count_kernel<<<blocks, kRouteBlock, 0, s>>>(*a, ctx->route_scratch, ctx->status_word);
+        moe_route_place_kernel<<<blocks, kRouteBlock, 0, s>>>(*a, ctx->route_scratch);
+        fe2o3_count_launch(2);
+        return fe2o3_cuda_status(cudaGetLastError(), "moe_top2_v1");
+    }
     const uint32_t smem = a->experts * kRouteThreads * sizeof(uint32_t);
     if (geo) *geo = fe2o3_geometry{{1, 1, 1}, {kRouteThreads, 1, 1}, smem, 1};
     if (plan_only) return FE2O3_OK;

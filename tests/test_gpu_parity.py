@@ -387,6 +387,74 @@ def test_moe_routing_reference_vectors_bit_exact(gpu, orc):
         L.unchanged()
 
 
+ROUTE_ARRAYS = ("top2_experts", "requested_counts", "admitted_counts", "expert_offsets", "route_slots", "permutation",
+                "inverse")
+
+
+@pytest.mark.parametrize("T,E,cap", [(1, 2, 1), (255, 4, 100), (256, 8, 512), (257, 8, 40), (5000, 8, 10000),
+                                     (16384, 8, 32768), (3001, 16, 300), (1000, 32, 7), (70000, 8, 20000)])
+def test_moe_routing_many_blocks_bit_exact(gpu, orc, T, E, cap):
+    fe, ctx, stream = gpu
+    from fe2o3_b200 import synth
+    # logits quantised to multiples of 1/4 so that equal scores (the tie-break) are common
+    lg = np.round(synth.normal_f32(4, 50 + E, T * E, 1.5) * 4) / 4
+    L = Guarded(fe, stream, lg.astype(np.float32))
+    sizes = dict(top2_experts=2 * T, requested_counts=E, admitted_counts=E, expert_offsets=E + 1, route_slots=2 * T,
+                 permutation=2 * T, inverse=2 * T)
+    outs = {k: Guarded(fe, stream, np.full(n, 0x12345678, np.uint32)) for k, n in sizes.items()}
+    for _ in range(2):  # the second launch checks that the arrival counter re-arms
+        run(fe, ctx, stream, "moe_top2_v1", logits=L.slice, tokens=T, experts=E, capacity=cap,
+            **{k: g.slice for k, g in outs.items()})
+        st, want = orc.moe_top2_route(lg, T, E, cap, independent=True)
+        assert st == 0
+        got = {k: outs[k].read() for k in ROUTE_ARRAYS}
+        for k in ROUTE_ARRAYS:
+            assert (got[k] == want[k]).all(), k
+        assert orc.moe_validate_routing(lg, T, E, cap, got) == 0
+    L.unchanged()
+
+
+def test_moe_routing_single_block_kernel_in_subprocess():
+    """The one-block routing kernel (used beyond 4M tokens) is selected with an environment switch."""
+    import os
+    import subprocess
+    import sys
+    code = """
+import numpy as np, sys
+sys.path.insert(0, %r)
+import fe2o3_b200 as fe, oracle
+from fe2o3_b200 import synth
+ctx = fe.GpuContext(0); s = ctx.default_stream()
+T, E, cap = 3000, 8, 500
+lg = (np.round(synth.normal_f32(4, 9, T * E, 1.5) * 4) / 4).astype(np.float32)
+L = fe.DeviceBuffer.from_host(s, lg)
+names = dict(top2_experts=2*T, requested_counts=E, admitted_counts=E, expert_offsets=E+1, route_slots=2*T, permutation=2*T, inverse=2*T)
+outs = {k: fe.DeviceBuffer.zeroed(s, n, np.uint32) for k, n in names.items()}
+p = fe.prepare(ctx, "moe_top2_v1", logits=L, tokens=T, experts=E, capacity=cap, **outs)
+assert p.geometry.grid[0] == 1 and p.geometry.workgroup[0] == 1024
+p.launch_and_wait(s)
+st, want = oracle.moe_top2_route(lg, T, E, cap, independent=True)
+for k in names:
+    assert (outs[k].to_host_vec(s) == want[k]).all(), k
+print("ok")
+""" % os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, FE2O3_ROUTE_SINGLE_BLOCK="1")
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "ok" in r.stdout, r.stdout + r.stderr
+
+
+@pytest.mark.parametrize("T,d,E", [(100, 64, 8), (300, 200, 4), (257, 2048, 8), (64, 136, 16), (50, 96, 5), (33, 70, 8)])
+def test_moe_gate_logits_bit_exact(gpu, orc, T, d, E):
+    fe, ctx, stream = gpu
+    from fe2o3_b200 import synth
+    x, wg = synth.normal_bf16(4, 1, T * d, 1.0), synth.normal_bf16(4, 2, d * E, 0.02)
+    X, W = Guarded(fe, stream, x), Guarded(fe, stream, wg)
+    LG = Guarded(fe, stream, np.full(T * E, np.nan, np.float32))
+    run(fe, ctx, stream, "moe_gate_v1", x=X.slice, wg=W.slice, logits=LG.slice, tokens=T, d_model=d, experts=E)
+    assert (bits(LG.read()) == bits(orc.moe_gate_logits(x, wg, T, d, E))).all()
+    X.unchanged(); W.unchanged()
+
+
 def test_moe_routing_failure_preserves_outputs(gpu):
     # examples/moe_top2_v1/tests/oracle.rs:110-141
     fe, ctx, stream = gpu
