@@ -23,7 +23,7 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-HEADLINE = "masked_reduce_u32"
+HEADLINE = "moe_top2_v1"
 L2_FLUSH_BYTES = 256 << 20
 
 
@@ -196,6 +196,7 @@ def wl_masked_reduce(h, steps, warmup, n=1 << 28, cpu=True):
     if cpu and h.rank == 0:
         import oracle
         oracle.build()
+        oracle.set_threads(os.cpu_count())
         best, want = None, None
         for _ in range(5):
             t0 = time.perf_counter()
@@ -242,6 +243,7 @@ def wl_row_softmax(h, steps, warmup, rows=65536, cols=1024, cpu=True):
     res["e2e"] = {"value": alg / dt / 1e9, "unit": "GB/s", "h2d_bytes_per_step": 4 * n, "d2h_bytes_per_step": 4 * n}
     if cpu:
         import oracle
+        oracle.set_threads(os.cpu_count())
         sample = 4096
         t0 = time.perf_counter()
         st, want = oracle.row_softmax(host_x[: sample * cols].reshape(sample, cols))
@@ -275,6 +277,7 @@ def wl_gemm(h, steps, warmup, m=8192, n=8192, k=8192, cpu=True):
                         "algorithmic_flops_per_step": flops, "l2": "A+B (256 MiB) larger than L2"}}
     if cpu:
         import oracle
+        oracle.set_threads(os.cpu_count())
         rows = 8
         got = c.to_host_vec(stream)[: rows * n]
         t0 = time.perf_counter()
@@ -328,6 +331,7 @@ def wl_attention(h, steps, warmup, batch=4, heads=16, seq=2048, dim=64, cpu=True
     res["e2e"] = {"value": flops / dt / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": 6 * n, "d2h_bytes_per_step": 4 * n}
     if cpu:
         import oracle
+        oracle.set_threads(os.cpu_count())
         qs = 64  # bounded sample: the first 64 query rows of head (0,0) against all keys
         S, D = seq, dim
         f = lambda b: synth.bf16_to_f32(b[: S * D]).reshape(1, 1, S, D)
@@ -406,6 +410,7 @@ def wl_moe(h, steps, warmup, cpu=True, **shape):
     if cpu and h.rank == 0:
         import oracle
         oracle.build()
+        oracle.set_threads(os.cpu_count())
         sample = 64  # tokens of rank 0 checked end to end against the oracle
         out = host_out.numpy().reshape(t_local, d)[:sample]
         t0 = time.perf_counter()
@@ -450,25 +455,49 @@ def run_reference_arm(args):
         return
     import oracle
     oracle.build()
+    cores = oracle.set_threads(os.cpu_count())
     from fe2o3_b200 import synth
-    n = 1 << 28
-    v = synth.u32_below(1, 1, n, 1 << 16)
-    a, _ = synth.bernoulli(1, 2, n, 0.75, flag_value=7, packed=False)
-    for _ in range(args.warmup):
-        oracle.masked_sum_u32(v, a, parallel=True)
+    if args.workload == "masked_reduce_u32":
+        n = 1 << 28
+        v = synth.u32_below(1, 1, n, 1 << 16)
+        a, _ = synth.bernoulli(1, 2, n, 0.75, flag_value=7, packed=False)
+        step = lambda: oracle.masked_sum_u32(v, a, parallel=True)
+        units, unit, dtype, scaling = n, "elements/s", "u32", "weak"
+        config = {"workload": "masked_reduce_u32", "elements": n}
+        sample = "the full 2^28-element workload per step"
+    elif args.workload == "moe_top2_v1":
+        T, d, f, E = (MOE_SHAPE[k] for k in ("tokens", "d_model", "d_ff", "experts"))
+        sample_tokens = 128  # bounded sample of the 16384-token batch per step
+        x = synth.normal_bf16(4, 1, T * d, 1.0)[: sample_tokens * d]
+        wg = synth.normal_bf16(4, 2, d * E, 0.02)
+        w1 = np.concatenate([synth.normal_bf16(4, 100 + e, d * f, 0.02) for e in range(E)])
+        w2 = np.concatenate([synth.normal_bf16(4, 200 + e, f * d, 0.02) for e in range(E)])
+
+        def step():
+            logits = oracle.moe_gate_logits(x, wg, sample_tokens, d, E)
+            _, routing = oracle.moe_top2_route(logits, sample_tokens, E, 2 * sample_tokens)
+            w = oracle.moe_route_weights(logits, routing["top2_experts"], sample_tokens, E)
+            compact = oracle.moe_expert_ffn(x, w1, w2, routing["top2_experts"], routing["inverse"], sample_tokens, d, f, E)
+            return oracle.moe_combine(compact, routing["inverse"], w, sample_tokens, d)
+        units, unit, dtype, scaling = sample_tokens, "tokens/s", "bf16", "strong"
+        config = {"workload": "moe_top2_v1", **MOE_SHAPE}
+        sample = f"{sample_tokens} tokens of the batch per step through gate, routing, FFN and combine"
+    else:
+        print(json.dumps({"impl": "reference", "unavailable": f"no CPU reference arm for workload {args.workload}"}))
+        return
+    for _ in range(min(args.warmup, 3)):
+        step()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        oracle.masked_sum_u32(v, a, parallel=True)
+        step()
     dt = (time.perf_counter() - t0) / args.steps
-    val = n / dt
+    val = units / dt
     print(json.dumps({
-        "impl": "reference", "metric": UNITS[HEADLINE][0], "value": val, "unit": "elements/s", "n_gpus": args.gpus,
+        "impl": "reference", "metric": UNITS[args.workload][0], "value": val, "unit": unit, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "u32", "data": "synthetic",
-        "config": {"workload": "masked_reduce_u32", "elements": n},
-        "cpu_baseline": {"value": val, "unit": "elements/s", "cores": os.cpu_count(), "kind": "port",
-                         "sample": "the full 2^28-element workload per step"},
-        "e2e": {"value": val, "unit": "elements/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        "scaling": scaling, "vs_baseline": None, "dtype": dtype, "data": "synthetic", "config": config,
+        "cpu_baseline": {"value": val, "unit": unit, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
 
 
 def main():

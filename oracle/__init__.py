@@ -55,6 +55,11 @@ def _c(a, dt):
 u64, f32c, f64c, i32c = C.c_uint64, C.c_float, C.c_double, C.c_int
 
 
+def set_threads(n):
+    lib().orc_set_threads(C.c_int(int(n)))
+    return int(lib().orc_get_max_threads())
+
+
 def mix64(v):
     return lib().orc_mix64(v & 0xFFFFFFFFFFFFFFFF)
 

@@ -21,6 +21,7 @@
  * reference test that pins them: "parity unpinned" for those extensions.
  */
 #include <math.h>
+#include <omp.h>
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
@@ -812,3 +813,8 @@ int orc_scoped_atomic_add_u32(const uint32_t *values, const uint32_t *eligible, 
     *final_value = (uint32_t)exact;
     return ORC_OK;
 }
+
+/* The launcher of a multi-process job may export OMP_NUM_THREADS=1; the timed
+ * CPU baseline sets its thread count explicitly. */
+void orc_set_threads(int n) { if (n > 0) omp_set_num_threads(n); }
+int orc_get_max_threads(void) { return omp_get_max_threads(); }
