@@ -385,7 +385,7 @@ def wl_moe(h, steps, warmup, cpu=True, **shape):
            "roofline": roofline("tensor", tf / h.world, peaks["bf16_tflops_sustained"], "TFLOP/s",
                                 peak_source=peaks["source"] + " (sustained, per GPU)"),
            "workload": {"workload": "moe_top2_v1", **shape, "gate": "softmax(x*Wg), top-2 renormalised",
-                        "ffn": "GELU(erf), bf16 hidden", "parallelism": f"ep{h.world}" if h.world > 1 else "single",
+                        "ffn": "GELU(erf), bf16 hidden", "parallelism": f"ep{h.world}" if h.world > 1 else "single", "exchange": layer.exchange,
                         "algorithmic_flops_per_step": flops,
                         "l2": "weights (256 MiB) + activations larger than L2"}}
     torch = h.torch
@@ -520,6 +520,7 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # keep stdout for the one JSON line
         torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     h = Harness(rank, world, local_rank)
     kw = {}

@@ -205,6 +205,11 @@ class Prepared:
         check(lib.fe2o3_prepared_kernarg(self._h, buf, C.byref(n)), "kernarg")
         return bytes(buf[: n.value])
 
+    def patch_kernarg(self, offset, data: bytes):
+        """Overwrite scalar bytes of the packed block (e.g. the exchange epoch)."""
+        buf = (C.c_uint8 * len(data)).from_buffer_copy(data)
+        check(lib.fe2o3_prepared_patch_kernarg(self._h, C.c_uint64(offset), buf, C.c_uint64(len(data))), "patch_kernarg")
+
     @property
     def symbol(self):
         return lib.fe2o3_prepared_symbol(self._h).decode()

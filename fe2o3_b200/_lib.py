@@ -53,6 +53,12 @@ MoeCombineArgs = _struct("MoeCombineArgs", ["compact_output", "inverse", "route_
 MoeCompactArgs = _struct("MoeCompactArgs", ["x", "permutation", "compact_x"], [("tokens", u32), ("d_model", u32)])
 MoeGroupedFfnArgs = _struct("MoeGroupedFfnArgs", ["compact_x", "w1", "w2", "group_offsets", "hidden", "compact_output"],
                             [("d_model", u32), ("d_ff", u32), ("groups", u32), ("experts_cycle", u32)])
+MoeEpExchangeArgs = _struct("MoeEpExchangeArgs",
+                            ["x", "top2_experts", "permutation", "inverse", "expert_offsets", "requested_counts",
+                             "route_weights", "group_offsets", "remote_rows", "combined_output", "peer_recv_x",
+                             "peer_ffn_out", "peer_counts", "peer_flags"],
+                            [("tokens", u32), ("d_model", u32), ("experts", u32), ("world", u32), ("rank", u32),
+                             ("epoch", u32), ("max_rows", u32), ("phase", u32)])
 MaskedReduceArgs = _struct("MaskedReduceArgs", ["values", "active", "output"])
 MaskedReducePackedArgs = _struct("MaskedReducePackedArgs", ["values", "mask", "output"])
 WaveLdsArgs = _struct("WaveLdsArgs", ["values", "active", "wave_out", "workgroup_out"])
@@ -96,6 +102,7 @@ OPS = {
     "moe_expert_combine_v1": (MoeCombineArgs, 72, False),
     "moe_compact_v1": (MoeCompactArgs, 56, False),
     "moe_grouped_ffn_v1": (MoeGroupedFfnArgs, 112, False),
+    "moe_ep_exchange_v1": (MoeEpExchangeArgs, 256, False),
     "masked_reduce_u32": (MaskedReduceArgs, 48, False),
     "masked_reduce_u32_packed": (MaskedReducePackedArgs, 48, False),
     "wave_lds_v1": (WaveLdsArgs, 64, False),
@@ -115,7 +122,7 @@ EXPORTS = [
     "fe2o3_pinned_alloc", "fe2o3_pinned_free", "fe2o3_event_create", "fe2o3_event_record", "fe2o3_event_sync",
     "fe2o3_event_query", "fe2o3_event_elapsed_ms", "fe2o3_event_destroy", "fe2o3_peer_access_enable",
     "fe2o3_status_string", "fe2o3_last_error", "fe2o3_prepared_launch", "fe2o3_prepared_launch_and_wait",
-    "fe2o3_prepared_geometry", "fe2o3_prepared_kernarg", "fe2o3_prepared_symbol", "fe2o3_prepared_destroy",
+    "fe2o3_prepared_geometry", "fe2o3_prepared_kernarg", "fe2o3_prepared_patch_kernarg", "fe2o3_prepared_symbol", "fe2o3_prepared_destroy",
     "fe2o3_ctx_take_kernel_status", "fe2o3_load_executable", "fe2o3_resolve_kernel", "fe2o3_launch_and_wait",
     "fe2o3_unload_executable", "fe2o3_synth_uniform_f32", "fe2o3_synth_normal_f32", "fe2o3_synth_normal_bf16",
     "fe2o3_synth_uniform_bf16", "fe2o3_synth_u32_below", "fe2o3_synth_bernoulli", "fe2o3_synth_gemm_inputs_v1",

@@ -28,6 +28,7 @@ int32_t launch_moe_gate(fe2o3_ctx *, cudaStream_t, const void *, fe2o3_geometry 
 int32_t launch_moe_top2(fe2o3_ctx *, cudaStream_t, const void *, fe2o3_geometry *, bool);
 int32_t launch_moe_route_weights(fe2o3_ctx *, cudaStream_t, const void *, fe2o3_geometry *, bool);
 int32_t launch_moe_combine(fe2o3_ctx *, cudaStream_t, const void *, fe2o3_geometry *, bool);
+int32_t launch_moe_ep_exchange(fe2o3_ctx *, cudaStream_t, const void *, fe2o3_geometry *, bool);
 int32_t launch_moe_compact(cudaStream_t, uint64_t x, uint64_t perm, uint64_t compact_x, uint32_t rows,
                            uint32_t d_model, uint32_t tokens);
 int32_t launch_gemm_exact(cudaStream_t, uint32_t dtype, bool epilogue, uint64_t a, uint64_t b, uint64_t c, uint32_t M,
@@ -76,7 +77,7 @@ enum OpId : uint32_t {
     OP_SCALAR_GEMM, OP_TILED_GEMM, OP_TILED_GEMM_GENERAL, OP_FLASH_ATTENTION, OP_ROW_SOFTMAX, OP_MOE_TOP2,
     OP_MOE_GATE, OP_MOE_ROUTE_WEIGHTS, OP_MOE_EXPERT_FFN, OP_MOE_COMBINE, OP_MASKED_REDUCE, OP_MASKED_REDUCE_PACKED,
     OP_WAVE_LDS, OP_WAVE64_COLLECTIVES, OP_WAVE64_SEGMENTED, OP_LDS_REDUCE_I32, OP_SCOPED_ATOMIC_ADD,
-    OP_MOE_COMPACT, OP_MOE_GROUPED_FFN, OP_COUNT
+    OP_MOE_COMPACT, OP_MOE_GROUPED_FFN, OP_MOE_EP_EXCHANGE, OP_COUNT
 };
 
 struct OpInfo {
@@ -105,12 +106,13 @@ static const OpInfo kOps[OP_COUNT] = {
     {"scoped_atomic_add_u32_v1", sizeof(fe2o3_scoped_atomic_add_u32_v1_args), launch_scoped_atomic_add},
     {"moe_compact_v1", sizeof(fe2o3_moe_compact_v1_args), nullptr},
     {"moe_grouped_ffn_v1", sizeof(fe2o3_moe_grouped_ffn_v1_args), nullptr},
+    {"moe_ep_exchange_v1", sizeof(fe2o3_moe_ep_exchange_v1_args), launch_moe_ep_exchange},
 };
 
 struct fe2o3_prepared {
     fe2o3_ctx *ctx;
     uint32_t op;
-    alignas(8) uint8_t kernarg[192];
+    alignas(8) uint8_t kernarg[320];
     uint32_t schedule;   // GEMM: resolved schedule
     GemmTcPlan gemm[2];  // tcgen05 plans (FFN uses both)
     AttnTcPlan *attn;
@@ -135,7 +137,7 @@ struct Region {
 bool mul_overflow(uint64_t a, uint64_t b, uint64_t *r) { return __builtin_mul_overflow(a, b, r); }
 
 int32_t check_regions(const Region *r, int n) {
-    uint64_t lo[16], hi[16];
+    uint64_t lo[20], hi[20];
     for (int i = 0; i < n; ++i) {
         if (r[i].s.len != r[i].expected) {
             fe2o3_set_error("Length{role=%s, expected=%llu, actual=%llu}", r[i].role,
@@ -344,6 +346,31 @@ int regions_for(uint32_t op, const void *args, Region *r, int32_t *status) {
             r[5] = RGN("CompactOutput", a->compact_output, rows * a->d_model, 4, true);
             return 6;
         }
+        case OP_MOE_EP_EXCHANGE: {
+            const fe2o3_moe_ep_exchange_v1_args *a = static_cast<const fe2o3_moe_ep_exchange_v1_args *>(args);
+            if (a->world < 1 || a->world > 32 || a->experts < 2 || a->experts > 32 || a->experts % a->world ||
+                a->d_model == 0 || (a->d_model % 8) || a->rank >= a->world || a->phase > FE2O3_MOE_EP_COMBINE ||
+                a->tokens > 0x7fffffffu) {
+                *status = unsupported("1 <= world <= 32 dividing experts (2..32), d_model a positive multiple of 8, rank < world");
+                return 0;
+            }
+            const uint64_t R = 2ull * a->tokens;
+            r[0] = RGN("X", a->x, (uint64_t)a->tokens * a->d_model, 2, false);
+            r[1] = RGN("Top2Experts", a->top2_experts, R, 4, false);
+            r[2] = RGN("Permutation", a->permutation, R, 4, false);
+            r[3] = RGN("Inverse", a->inverse, R, 4, false);
+            r[4] = RGN("ExpertOffsets", a->expert_offsets, a->experts + 1, 4, false);
+            r[5] = RGN("RequestedCounts", a->requested_counts, a->experts, 4, false);
+            r[6] = RGN("RouteWeights", a->route_weights, R, 4, false);
+            r[7] = RGN("PeerRecvX", a->peer_recv_x, a->world, 8, false);
+            r[8] = RGN("PeerFfnOut", a->peer_ffn_out, a->world, 8, false);
+            r[9] = RGN("PeerCounts", a->peer_counts, a->world, 8, false);
+            r[10] = RGN("PeerFlags", a->peer_flags, a->world, 8, false);
+            r[11] = RGN("GroupOffsets", a->group_offsets, a->experts + 1, 4, true);
+            r[12] = RGN("RemoteRows", a->remote_rows, R, 4, true);
+            r[13] = RGN("CombinedOutput", a->combined_output, (uint64_t)a->tokens * a->d_model, 4, true);
+            return 14;
+        }
         case OP_MOE_COMBINE: {
             const fe2o3_moe_expert_combine_v1_args *a = static_cast<const fe2o3_moe_expert_combine_v1_args *>(args);
             if (a->width == 0 || a->compact_output.len % a->width) {
@@ -417,7 +444,7 @@ int regions_for(uint32_t op, const void *args, Region *r, int32_t *status) {
 
 int32_t check_op(uint32_t op, const void *args) {
     if (!args) { fe2o3_set_error("null argument block"); return FE2O3_ERR_INVALID_ARGUMENT; }
-    Region r[16];
+    Region r[20];
     int32_t st;
     int n = regions_for(op, args, r, &st);
     if (st != FE2O3_OK) return st;
@@ -449,7 +476,7 @@ int32_t prepare_common(fe2o3_ctx *ctx, uint32_t op, const void *args, fe2o3_prep
     *out = nullptr;
     int32_t st = check_op(op, args);
     if (st != FE2O3_OK) return st;
-    Region r[16];
+    Region r[20];
     int n = regions_for(op, args, r, &st);
     st = check_ctx_device(ctx, r, n);
     if (st != FE2O3_OK) return st;
@@ -875,6 +902,7 @@ DEFINE_CHECK(wave64_collectives_v1, OP_WAVE64_COLLECTIVES)
 DEFINE_CHECK(wave64_collectives_segmented, OP_WAVE64_SEGMENTED)
 DEFINE_CHECK(lds_publish_read_reduce_i32_v1, OP_LDS_REDUCE_I32)
 DEFINE_CHECK(scoped_atomic_add_u32_v1, OP_SCOPED_ATOMIC_ADD)
+DEFINE_CHECK(moe_ep_exchange_v1, OP_MOE_EP_EXCHANGE)
 
 // ---- prepare ---------------------------------------------------------------------------------
 #define DEFINE_SIMPLE_PREPARE(name, op)                                                                 \
@@ -895,6 +923,7 @@ DEFINE_SIMPLE_PREPARE(wave64_collectives_v1, OP_WAVE64_COLLECTIVES)
 DEFINE_SIMPLE_PREPARE(wave64_collectives_segmented, OP_WAVE64_SEGMENTED)
 DEFINE_SIMPLE_PREPARE(lds_publish_read_reduce_i32_v1, OP_LDS_REDUCE_I32)
 DEFINE_SIMPLE_PREPARE(scoped_atomic_add_u32_v1, OP_SCOPED_ATOMIC_ADD)
+DEFINE_SIMPLE_PREPARE(moe_ep_exchange_v1, OP_MOE_EP_EXCHANGE)
 
 static int32_t fail_prepare(fe2o3_prepared **out, int32_t st) {
     fe2o3_prepared_destroy(*out);
@@ -1021,6 +1050,17 @@ int32_t fe2o3_prepared_kernarg(const fe2o3_prepared *p, void *out, uint64_t *byt
     const bool ok = *bytes >= n;
     *bytes = n;
     return ok || !out ? FE2O3_OK : FE2O3_ERR_LENGTH;
+}
+int32_t fe2o3_prepared_patch_kernarg(fe2o3_prepared *p, uint64_t offset, const void *data, uint64_t bytes) {
+    if (!p || !data) return FE2O3_ERR_INVALID_ARGUMENT;
+    const uint64_t n = kOps[p->op].kernarg_bytes;
+    if (offset > n || bytes > n - offset) {
+        fe2o3_set_error("InvalidRegion: patch [%llu, +%llu) outside the %llu-byte block", (unsigned long long)offset,
+                        (unsigned long long)bytes, (unsigned long long)n);
+        return FE2O3_ERR_INVALID_REGION;
+    }
+    memcpy(p->kernarg + offset, data, bytes);
+    return FE2O3_OK;
 }
 const char *fe2o3_prepared_symbol(const fe2o3_prepared *p) { return p ? kOps[p->op].symbol : ""; }
 int32_t fe2o3_prepared_destroy(fe2o3_prepared *p) {

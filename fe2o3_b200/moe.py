@@ -39,9 +39,10 @@ def split_plan(counts, rank, world):
 
 
 class MoeTop2Layer:
-    def __init__(self, ctx, stream, tokens, d_model, d_ff, experts, rank=0, world=1, capacity=None):
+    def __init__(self, ctx, stream, tokens, d_model, d_ff, experts, rank=0, world=1, capacity=None, exchange="auto"):
         import torch
         self.torch = torch
+        self.exchange = "none" if world == 1 else exchange
         assert experts % world == 0 and tokens % world == 0
         self.ctx, self.stream = ctx, stream
         self.rank, self.world = rank, world
@@ -66,9 +67,18 @@ class MoeTop2Layer:
         self.max_rows = R * world
         self.compact_x = z(R * d, torch.bfloat16)            # local routes, expert-major
         self.compact_out = z(R * d, torch.float32)           # FFN rows back in local slot order
+        if world > 1 and self.exchange in ("auto", "peer"):
+            try:
+                self._setup_peer_buffers(dev)
+                self.exchange = "peer"
+            except Exception as err:  # symmetric memory unavailable: use the NCCL all-to-all path
+                if self.exchange == "peer":
+                    raise
+                self.exchange, self.exchange_fallback_reason = "nccl", f"{type(err).__name__}: {err}"
         if world > 1:
-            self.recv_x = z(self.max_rows * d, torch.bfloat16)
-            self.ffn_out = z(self.max_rows * d, torch.float32)
+            if self.exchange == "nccl":
+                self.recv_x = z(self.max_rows * d, torch.bfloat16)
+                self.ffn_out = z(self.max_rows * d, torch.float32)
             self.group_offsets = z(E + 1, torch.int32)
             self.counts_all = z(world * E, torch.int32)
             self.host_counts = torch.zeros(world * E, dtype=torch.int32).pin_memory()
@@ -97,7 +107,38 @@ class MoeTop2Layer:
                            experts_cycle=self.per)
         self.k_combine = P("moe_expert_combine_v1", compact_output=self.compact_out, inverse=self.inverse,
                            route_weights=self.weights, combined_output=self.out, tokens=T, width=d)
+        if self.exchange == "peer":
+            from ._lib import MoeEpExchangeArgs
+            self.remote_rows = z(R, torch.int32)
+            self.epoch, self._epoch_offset = 0, MoeEpExchangeArgs.epoch.offset
+            self.k_phase = [P("moe_ep_exchange_v1", x=self.x, top2_experts=self.top2, permutation=self.perm,
+                              inverse=self.inverse, expert_offsets=self.offsets, requested_counts=self.requested,
+                              route_weights=self.weights, group_offsets=self.group_offsets,
+                              remote_rows=self.remote_rows, combined_output=self.out, peer_recv_x=self.peer_recv_x,
+                              peer_ffn_out=self.peer_ffn_out, peer_counts=self.peer_counts,
+                              peer_flags=self.peer_flags, tokens=T, d_model=d, experts=E, world=world, rank=rank,
+                              epoch=0, max_rows=self.max_rows, phase=ph) for ph in range(4)]
         self.launches_per_step = 7 if world == 1 else 8
+
+    def _setup_peer_buffers(self, dev):
+        """Receive buffer, expert-output buffer, counts table and flags in symmetric (peer-mapped) memory."""
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        t = self.torch
+        d, E, W = self.d, self.E, self.world
+        sizes = [self.max_rows * d * 2, self.max_rows * d * 4, W * E * 4, 4096]
+        self._symm, ptrs = [], []
+        for nbytes in sizes:
+            buf = symm_mem.empty(nbytes, dtype=t.uint8, device=dev)
+            hdl = symm_mem.rendezvous(buf, dist.group.WORLD)
+            buf.zero_()
+            self._symm.append((buf, hdl))
+            ptrs.append(t.tensor([int(p) for p in hdl.buffer_ptrs], dtype=t.int64, device=dev))
+        self.peer_recv_x, self.peer_ffn_out, self.peer_counts, self.peer_flags = ptrs
+        self.recv_x = self._symm[0][0].view(t.bfloat16)
+        self.ffn_out = self._symm[1][0].view(t.float32)
+        t.cuda.synchronize()
+        dist.barrier()
 
     # ---- host-side loading -------------------------------------------------------------
     def load(self, x_bits, wg_bits, w1_bits, w2_bits):
@@ -114,9 +155,20 @@ class MoeTop2Layer:
         self.k_weights.launch(s)
         if self.world == 1:
             self.k_ffn.launch(s)
+            self.k_combine.launch(s)
+        elif self.exchange == "peer":
+            self.epoch += 1
+            word = int(self.epoch & 0xFFFFFFFF).to_bytes(4, "little")
+            for k in self.k_phase:
+                k.patch_kernarg(self._epoch_offset, word)
+            self.k_phase[0].launch(s)   # counts exchange + rows to their experts' ranks
+            self.k_phase[1].launch(s)   # wait for every source's rows
+            self.k_ffn.launch(s)
+            self.k_phase[2].launch(s)   # expert outputs ready
+            self.k_phase[3].launch(s)   # pull and combine
         else:
             self._exchange_forward()
-        self.k_combine.launch(s)
+            self.k_combine.launch(s)
         return self.out
 
     def _exchange_forward(self):

@@ -264,6 +264,27 @@ typedef struct fe2o3_moe_grouped_ffn_v1_args {
     uint32_t d_model, d_ff, groups, experts_cycle;
 } fe2o3_moe_grouped_ffn_v1_args;
 
+/* Expert-parallel exchange over peer memory (no counterpart in the reference,
+ * which is single-device).  One rank per GPU; rank r owns tokens/world tokens
+ * and experts [r*experts/world, (r+1)*experts/world).  The peer_* slices are
+ * device arrays of `world` u64 addresses, entry p being rank p's buffer, mapped
+ * into this process: recv_x [max_rows][d_model] bf16, ffn_out
+ * [max_rows][d_model] f32, counts [world][experts] u32, flags [3*world + 1] u32
+ * (zero before the first pass).  `epoch` must increase by one per layer pass on
+ * every rank (see fe2o3_prepared_patch_kernarg).  Phases, in stream order:
+ * DISPATCH (counts exchange + rows to their expert's rank + group_offsets for
+ * fe2o3_moe_grouped_ffn_v1 on recv_x), WAIT_ROWS, the FFN, FFN_DONE, COMBINE
+ * (pull the two expert rows, weighted sum in rank order).  Waits are bounded. */
+#define FE2O3_MOE_EP_DISPATCH 0u
+#define FE2O3_MOE_EP_WAIT_ROWS 1u
+#define FE2O3_MOE_EP_FFN_DONE 2u
+#define FE2O3_MOE_EP_COMBINE 3u
+typedef struct fe2o3_moe_ep_exchange_v1_args {
+    fe2o3_slice x, top2_experts, permutation, inverse, expert_offsets, requested_counts, route_weights,
+        group_offsets, remote_rows, combined_output, peer_recv_x, peer_ffn_out, peer_counts, peer_flags;
+    uint32_t tokens, d_model, experts, world, rank, epoch, max_rows, phase;
+} fe2o3_moe_ep_exchange_v1_args;
+
 /* examples/moe_expert_v1/src/kernel.rs:104-109
  * moe_expert_combine_f32_t8_k2_o16_v1(compact_output, inverse, route_weights,
  * combined_output) generalised to tokens x width. */
@@ -339,6 +360,7 @@ int32_t fe2o3_moe_expert_ffn_v1_check(const fe2o3_moe_expert_ffn_v1_args *args);
 int32_t fe2o3_moe_expert_combine_v1_check(const fe2o3_moe_expert_combine_v1_args *args);
 int32_t fe2o3_moe_compact_v1_check(const fe2o3_moe_compact_v1_args *args);
 int32_t fe2o3_moe_grouped_ffn_v1_check(const fe2o3_moe_grouped_ffn_v1_args *args);
+int32_t fe2o3_moe_ep_exchange_v1_check(const fe2o3_moe_ep_exchange_v1_args *args);
 int32_t fe2o3_masked_reduce_u32_check(const fe2o3_masked_reduce_u32_args *args);
 int32_t fe2o3_masked_reduce_u32_packed_check(const fe2o3_masked_reduce_u32_packed_args *args);
 int32_t fe2o3_wave_lds_v1_check(const fe2o3_wave_lds_v1_args *args);
@@ -369,6 +391,8 @@ int32_t fe2o3_moe_expert_combine_v1_prepare(fe2o3_ctx *ctx, const fe2o3_moe_expe
                                             fe2o3_prepared **out);
 int32_t fe2o3_moe_compact_v1_prepare(fe2o3_ctx *ctx, const fe2o3_moe_compact_v1_args *args, fe2o3_prepared **out);
 int32_t fe2o3_moe_grouped_ffn_v1_prepare(fe2o3_ctx *ctx, const fe2o3_moe_grouped_ffn_v1_args *args,
+                                         fe2o3_prepared **out);
+int32_t fe2o3_moe_ep_exchange_v1_prepare(fe2o3_ctx *ctx, const fe2o3_moe_ep_exchange_v1_args *args,
                                          fe2o3_prepared **out);
 int32_t fe2o3_masked_reduce_u32_prepare(fe2o3_ctx *ctx, const fe2o3_masked_reduce_u32_args *args,
                                         fe2o3_prepared **out);
@@ -409,6 +433,9 @@ int32_t fe2o3_prepared_launch_and_wait(fe2o3_prepared *prepared, fe2o3_stream *s
 int32_t fe2o3_prepared_geometry(const fe2o3_prepared *prepared, fe2o3_geometry *out);
 /* Copies the packed explicit argument block; *bytes in = capacity, out = size. */
 int32_t fe2o3_prepared_kernarg(const fe2o3_prepared *prepared, void *out, uint64_t *bytes);
+/* Overwrites `bytes` bytes of the packed block at `offset`; only the scalar area
+ * after the slices may be patched (e.g. the epoch of fe2o3_moe_ep_exchange_v1). */
+int32_t fe2o3_prepared_patch_kernarg(fe2o3_prepared *prepared, uint64_t offset, const void *data, uint64_t bytes);
 const char *fe2o3_prepared_symbol(const fe2o3_prepared *prepared);
 int32_t fe2o3_prepared_destroy(fe2o3_prepared *prepared);
 

@@ -9,7 +9,7 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 
-def _rank_main(rank, world, port, shape, results):
+def _rank_main(rank, world, port, shape, exchange, results):
     import torch
     import torch.distributed as dist
     os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -23,14 +23,14 @@ def _rank_main(rank, world, port, shape, results):
         from fe2o3_b200.moe import MoeTop2Layer
         T, d, f, E = shape
         ctx = fe.GpuContext(rank)
-        layer = MoeTop2Layer(ctx, ctx.default_stream(), T, d, f, E, rank=rank, world=world)
+        layer = MoeTop2Layer(ctx, ctx.default_stream(), T, d, f, E, rank=rank, world=world, exchange=exchange)
         per, tl = E // world, T // world
         x = synth.normal_bf16(4, 1, T * d, 1.0)[rank * tl * d:(rank + 1) * tl * d]
         wg = synth.normal_bf16(4, 2, d * E, 0.02)
         w1 = np.concatenate([synth.normal_bf16(4, 100 + e, d * f, 0.02) for e in range(rank * per, (rank + 1) * per)])
         w2 = np.concatenate([synth.normal_bf16(4, 200 + e, f * d, 0.02) for e in range(rank * per, (rank + 1) * per)])
         layer.load(x, wg, w1, w2)
-        for _ in range(2):  # two passes: buffers and counters are reusable
+        for _ in range(3):  # several passes: buffers, counters and epoch flags are reusable
             out = layer.forward()
         torch.cuda.synchronize()
         assert ctx.take_kernel_status(ctx.default_stream()) == 0
@@ -39,8 +39,9 @@ def _rank_main(rank, world, port, shape, results):
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("exchange", ["peer", "nccl"])
 @pytest.mark.parametrize("shape", [(512, 256, 512, 8), (1024, 128, 256, 4)])
-def test_expert_parallel_moe_two_gpus(orc, shape):
+def test_expert_parallel_moe_two_gpus(orc, shape, exchange):
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
@@ -51,7 +52,7 @@ def test_expert_parallel_moe_two_gpus(orc, shape):
     port = 29600 + (os.getpid() % 1000)
     with mp.Manager() as m:
         results = m.dict()
-        mp.spawn(_rank_main, args=(world, port, shape, results), nprocs=world, join=True)
+        mp.spawn(_rank_main, args=(world, port, shape, exchange, results), nprocs=world, join=True)
         outs = [results[r] for r in range(world)]
     out = np.concatenate([o[0] for o in outs]).reshape(T, d)
     top2 = np.concatenate([o[1] for o in outs])
