@@ -56,7 +56,7 @@ MoeGroupedFfnArgs = _struct("MoeGroupedFfnArgs", ["compact_x", "w1", "w2", "grou
 MoeEpExchangeArgs = _struct("MoeEpExchangeArgs",
                             ["x", "top2_experts", "permutation", "inverse", "expert_offsets", "requested_counts",
                              "route_weights", "group_offsets", "remote_rows", "combined_output", "peer_recv_x",
-                             "peer_ffn_out", "peer_counts", "peer_flags"],
+                             "peer_ffn_out", "peer_counts", "peer_flags", "epoch_counter"],
                             [("tokens", u32), ("d_model", u32), ("experts", u32), ("world", u32), ("rank", u32),
                              ("epoch", u32), ("max_rows", u32), ("phase", u32)])
 MaskedReduceArgs = _struct("MaskedReduceArgs", ["values", "active", "output"])
@@ -102,7 +102,7 @@ OPS = {
     "moe_expert_combine_v1": (MoeCombineArgs, 72, False),
     "moe_compact_v1": (MoeCompactArgs, 56, False),
     "moe_grouped_ffn_v1": (MoeGroupedFfnArgs, 112, False),
-    "moe_ep_exchange_v1": (MoeEpExchangeArgs, 256, False),
+    "moe_ep_exchange_v1": (MoeEpExchangeArgs, 272, False),
     "masked_reduce_u32": (MaskedReduceArgs, 48, False),
     "masked_reduce_u32_packed": (MaskedReducePackedArgs, 48, False),
     "wave_lds_v1": (WaveLdsArgs, 64, False),

@@ -349,7 +349,7 @@ int regions_for(uint32_t op, const void *args, Region *r, int32_t *status) {
         case OP_MOE_EP_EXCHANGE: {
             const fe2o3_moe_ep_exchange_v1_args *a = static_cast<const fe2o3_moe_ep_exchange_v1_args *>(args);
             if (a->world < 1 || a->world > 32 || a->experts < 2 || a->experts > 32 || a->experts % a->world ||
-                a->d_model == 0 || (a->d_model % 8) || a->rank >= a->world || a->phase > FE2O3_MOE_EP_COMBINE ||
+                a->d_model == 0 || (a->d_model % 8) || a->rank >= a->world || a->phase > FE2O3_MOE_EP_ADVANCE ||
                 a->tokens > 0x7fffffffu) {
                 *status = unsupported("1 <= world <= 32 dividing experts (2..32), d_model a positive multiple of 8, rank < world");
                 return 0;
@@ -369,7 +369,9 @@ int regions_for(uint32_t op, const void *args, Region *r, int32_t *status) {
             r[11] = RGN("GroupOffsets", a->group_offsets, a->experts + 1, 4, true);
             r[12] = RGN("RemoteRows", a->remote_rows, R, 4, true);
             r[13] = RGN("CombinedOutput", a->combined_output, (uint64_t)a->tokens * a->d_model, 4, true);
-            return 14;
+            if (a->epoch_counter.ptr == 0 && a->epoch_counter.len == 0) return 14;
+            r[14] = RGN("EpochCounter", a->epoch_counter, 1, 4, true);
+            return 15;
         }
         case OP_MOE_COMBINE: {
             const fe2o3_moe_expert_combine_v1_args *a = static_cast<const fe2o3_moe_expert_combine_v1_args *>(args);

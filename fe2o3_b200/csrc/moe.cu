@@ -180,34 +180,101 @@ moe_gate_token_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict
 #pragma unroll
     for (int e = 0; e < E; ++e) acc[e] = 0.0f;
     const bool vec = (d_model % 8u) == 0 && (reinterpret_cast<uint64_t>(x) & 15u) == 0;
+    // 8 lanes cover one token's 64 k values (128 bytes): coalesced 16-byte loads, held in registers
+    // one chunk ahead so that the global latency overlaps the arithmetic of the current chunk
+    uint4 pre[kGate2Tokens / 8];
+    auto prefetch = [&](uint32_t k0) {
+#pragma unroll
+        for (int pass = 0; pass < kGate2Tokens / 8; ++pass) {
+            const uint32_t tt = pass * 8 + (tid >> 3), c = tid & 7;
+            pre[pass] = make_uint4(0, 0, 0, 0);
+            if (t0 + tt < tokens) pre[pass] = __ldg(reinterpret_cast<const uint4 *>(x + (uint64_t)(t0 + tt) * d_model + k0) + c);
+        }
+    };
+    // the Wg rows of a full chunk are kGate2KC*E bf16 = kWgVec 16-byte vectors: fetched one chunk ahead too
+    constexpr int kWgVec = kGate2KC * E * 2 / 16, kWgPer = (kWgVec + kGate2Tokens - 1) / kGate2Tokens;
+    const bool wvec = (reinterpret_cast<uint64_t>(wg) & 15u) == 0;
+    uint4 wpre[kWgPer];
+    auto prefetch_w = [&](uint32_t k0) {
+#pragma unroll
+        for (int q = 0; q < kWgPer; ++q) {
+            const uint32_t i = tid + q * kGate2Tokens;
+            wpre[q] = make_uint4(0, 0, 0, 0);
+            if (i < (uint32_t)kWgVec) wpre[q] = __ldg(reinterpret_cast<const uint4 *>(wg + (uint64_t)k0 * E) + i);
+        }
+    };
+    if (vec && d_model >= kGate2KC) prefetch(0);
+    if (wvec && d_model >= kGate2KC) prefetch_w(0);
     for (uint32_t k0 = 0; k0 < d_model; k0 += kGate2KC) {
         const uint32_t kc = min((uint32_t)kGate2KC, d_model - k0);
         if (vec && kc == kGate2KC) {
-            // 8 lanes cover one token's 64 k values (128 bytes): coalesced 16-byte loads
 #pragma unroll
             for (int pass = 0; pass < kGate2Tokens / 8; ++pass) {
                 const uint32_t tt = pass * 8 + (tid >> 3), c = tid & 7;
-                uint4 v = make_uint4(0, 0, 0, 0);
-                if (t0 + tt < tokens) v = __ldg(reinterpret_cast<const uint4 *>(x + (uint64_t)(t0 + tt) * d_model + k0) + c);
-                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+                const uint32_t w[4] = {pre[pass].x, pre[pass].y, pre[pass].z, pre[pass].w};
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     xs[c * 8 + 2 * i][tt] = __uint_as_float(w[i] << 16);
                     xs[c * 8 + 2 * i + 1][tt] = __uint_as_float(w[i] & 0xffff0000u);
                 }
             }
+            if (k0 + 2 * kGate2KC <= d_model) prefetch(k0 + kGate2KC);
         } else {
             for (uint32_t i = tid; i < kGate2Tokens * kGate2KC; i += kGate2Tokens) {
                 const uint32_t tt = i / kGate2KC, kk = i % kGate2KC;
                 xs[kk][tt] = (t0 + tt < tokens && kk < kc) ? bf16_bits_to_f32(x[(uint64_t)(t0 + tt) * d_model + k0 + kk]) : 0.0f;
             }
         }
-        for (uint32_t i = tid; i < kc * E; i += kGate2Tokens) (&ws[0][0])[i] = bf16_bits_to_f32(wg[(uint64_t)k0 * E + i]);
-        __syncthreads();
-        for (uint32_t kk = 0; kk < kc; ++kk) {
-            const float xv = xs[kk][tid];
+        if (wvec && kc == kGate2KC) {
 #pragma unroll
-            for (int e = 0; e < E; ++e) acc[e] = __fadd_rn(acc[e], __fmul_rn(xv, ws[kk][e]));
+            for (int q = 0; q < kWgPer; ++q) {
+                const uint32_t i = tid + q * kGate2Tokens;
+                if (i < (uint32_t)kWgVec) {
+                    const uint32_t w[4] = {wpre[q].x, wpre[q].y, wpre[q].z, wpre[q].w};
+                    float *dst = &ws[0][0] + i * 8;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        dst[2 * j] = __uint_as_float(w[j] << 16);
+                        dst[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+                    }
+                }
+            }
+            if (k0 + 2 * kGate2KC <= d_model) prefetch_w(k0 + kGate2KC);
+        } else {
+            for (uint32_t i = tid; i < kc * E; i += kGate2Tokens) (&ws[0][0])[i] = bf16_bits_to_f32(wg[(uint64_t)k0 * E + i]);
+        }
+        __syncthreads();
+        if (kc == kGate2KC) {
+            // full chunk: eight k steps per iteration with their operands loaded up front, so the E
+            // add chains advance back to back instead of waiting on shared-memory latency
+#pragma unroll 1
+            for (uint32_t kk = 0; kk < kGate2KC; kk += 8) {
+                float xv[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) xv[i] = xs[kk + i][tid];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    float w[E];
+                    if constexpr (E % 4 == 0) {
+#pragma unroll
+                        for (int q = 0; q < E / 4; ++q) {
+                            const float4 v = *reinterpret_cast<const float4 *>(&ws[kk + i][4 * q]);
+                            w[4 * q] = v.x; w[4 * q + 1] = v.y; w[4 * q + 2] = v.z; w[4 * q + 3] = v.w;
+                        }
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < E; ++e) w[e] = ws[kk + i][e];
+                    }
+#pragma unroll
+                    for (int e = 0; e < E; ++e) acc[e] = __fadd_rn(acc[e], __fmul_rn(xv[i], w[e]));
+                }
+            }
+        } else {
+            for (uint32_t kk = 0; kk < kc; ++kk) {
+                const float xv = xs[kk][tid];
+#pragma unroll
+                for (int e = 0; e < E; ++e) acc[e] = __fadd_rn(acc[e], __fmul_rn(xv, ws[kk][e]));
+            }
         }
         __syncthreads();
     }

@@ -55,6 +55,11 @@ __device__ __forceinline__ bool wait_flags(const uint32_t *flags, uint32_t n, ui
     return true;
 }
 
+// the pass number: from the device counter when one is given, else the scalar in the argument block
+__device__ __forceinline__ uint32_t current_epoch(const fe2o3_moe_ep_exchange_v1_args &a) {
+    return a.epoch_counter.len ? __ldcg(reinterpret_cast<const uint32_t *>(a.epoch_counter.ptr)) + 1u : a.epoch;
+}
+
 __global__ void __launch_bounds__(kThreads)
 moe_ep_dispatch_kernel(fe2o3_moe_ep_exchange_v1_args a, uint32_t *status) {
     __shared__ uint32_t s_counts[32 * 32];   // [world][experts], world * experts <= 1024
@@ -63,6 +68,7 @@ moe_ep_dispatch_kernel(fe2o3_moe_ep_exchange_v1_args a, uint32_t *status) {
     __shared__ int s_ok;
     __shared__ bool s_last;
     const uint32_t E = a.experts, W = a.world, me = a.rank, per = E / W;
+    a.epoch = current_epoch(a);
     const uint64_t *peer_counts = reinterpret_cast<const uint64_t *>(a.peer_counts.ptr);
     const uint64_t *peer_flags = reinterpret_cast<const uint64_t *>(a.peer_flags.ptr);
     const uint64_t *peer_recv = reinterpret_cast<const uint64_t *>(a.peer_recv_x.ptr);
@@ -119,20 +125,31 @@ moe_ep_dispatch_kernel(fe2o3_moe_ep_exchange_v1_args a, uint32_t *status) {
     uint32_t *remote_rows = reinterpret_cast<uint32_t *>(a.remote_rows.ptr);
     const uint32_t vec_per_row = a.d_model / 8;
     const uint4 *x = reinterpret_cast<const uint4 *>(a.x.ptr);
-    for (uint32_t slot = blockIdx.x; slot < accepted; slot += gridDim.x) {
+    // one warp per row; a lane keeps up to eight 16-byte loads in flight before the peer stores
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t gwarp = blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5), nwarps = gridDim.x * (kThreads / 32);
+    for (uint32_t slot = gwarp; slot < accepted; slot += nwarps) {
         uint32_t e = 0;
         while (e + 1 < E && slot >= s_off[e + 1]) ++e;
         const uint32_t route = perm[slot];
         const uint32_t dst_rank = e / per;
         const uint32_t dst_row = s_base[e] + (slot - s_off[e]);
         if (route == kDrop || (route >> 1) >= a.tokens || dst_row >= a.max_rows) {
-            if (threadIdx.x == 0) kstatus_set(status, FE2O3_KSTATUS_SLOT_RANGE);
+            if (lane == 0) kstatus_set(status, FE2O3_KSTATUS_SLOT_RANGE);
             continue;
         }
-        if (threadIdx.x == 0) remote_rows[slot] = dst_row;
+        if (lane == 0) remote_rows[slot] = dst_row;
         const uint4 *src = x + (uint64_t)(route >> 1) * vec_per_row;
         uint4 *dst = reinterpret_cast<uint4 *>(peer_recv[dst_rank]) + (uint64_t)dst_row * vec_per_row;
-        for (uint32_t i = threadIdx.x; i < vec_per_row; i += kThreads) dst[i] = __ldg(src + i);
+        for (uint32_t i0 = lane; i0 < vec_per_row; i0 += 32 * 8) {
+            uint4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (i0 + 32 * u < vec_per_row) v[u] = __ldg(src + i0 + 32 * u);
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (i0 + 32 * u < vec_per_row) dst[i0 + 32 * u] = v[u];
+        }
     }
     // all of this rank's rows are written: the last block raises "rows complete" everywhere
     __threadfence_system();
@@ -149,6 +166,11 @@ moe_ep_dispatch_kernel(fe2o3_moe_ep_exchange_v1_args a, uint32_t *status) {
 
 __global__ void moe_ep_flag_kernel(fe2o3_moe_ep_exchange_v1_args a, uint32_t *status) {
     const uint32_t W = a.world, me = a.rank;
+    if (a.phase == FE2O3_MOE_EP_ADVANCE) {
+        if (threadIdx.x == 0 && a.epoch_counter.len) *reinterpret_cast<uint32_t *>(a.epoch_counter.ptr) += 1u;
+        return;
+    }
+    a.epoch = current_epoch(a);
     const uint64_t *peer_flags = reinterpret_cast<const uint64_t *>(a.peer_flags.ptr);
     if (a.phase == FE2O3_MOE_EP_WAIT_ROWS) {
         if (threadIdx.x == 0 && !wait_flags(reinterpret_cast<uint32_t *>(peer_flags[me]) + 1 * W, W, a.epoch))
@@ -164,6 +186,7 @@ __global__ void __launch_bounds__(kThreads)
 moe_ep_combine_kernel(fe2o3_moe_ep_exchange_v1_args a, uint32_t *status) {
     __shared__ int s_ok;
     const uint32_t W = a.world, me = a.rank, per = a.experts / W;
+    a.epoch = current_epoch(a);
     const uint64_t *peer_flags = reinterpret_cast<const uint64_t *>(a.peer_flags.ptr);
     const uint64_t *peer_out = reinterpret_cast<const uint64_t *>(a.peer_ffn_out.ptr);
     const uint32_t t = blockIdx.x;
@@ -196,19 +219,31 @@ moe_ep_combine_kernel(fe2o3_moe_ep_exchange_v1_args a, uint32_t *status) {
     const float4 *p0 = s0 != kDrop ? reinterpret_cast<const float4 *>(peer_out[r0]) + (uint64_t)remote_rows[s0] * nv : nullptr;
     const float4 *p1 = s1 != kDrop ? reinterpret_cast<const float4 *>(peer_out[r1]) + (uint64_t)remote_rows[s1] * nv : nullptr;
     float4 *dst = reinterpret_cast<float4 *>(a.combined_output.ptr) + (uint64_t)t * nv;
-    for (uint32_t i = threadIdx.x; i < nv; i += kThreads) {
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (p0) {
-            const float4 v = p0[i];
-            acc.x = __fadd_rn(acc.x, __fmul_rn(w0, v.x)); acc.y = __fadd_rn(acc.y, __fmul_rn(w0, v.y));
-            acc.z = __fadd_rn(acc.z, __fmul_rn(w0, v.z)); acc.w = __fadd_rn(acc.w, __fmul_rn(w0, v.w));
+    // all of a thread's peer loads are issued before any is used (remote latency is microseconds)
+    constexpr int U = 4;
+    for (uint32_t i0 = threadIdx.x; i0 < nv; i0 += kThreads * U) {
+        float4 v0[U], v1[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint32_t i = i0 + u * kThreads;
+            v0[u] = (p0 && i < nv) ? p0[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            v1[u] = (p1 && i < nv) ? p1[i] : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        if (p1) {
-            const float4 v = p1[i];
-            acc.x = __fadd_rn(acc.x, __fmul_rn(w1, v.x)); acc.y = __fadd_rn(acc.y, __fmul_rn(w1, v.y));
-            acc.z = __fadd_rn(acc.z, __fmul_rn(w1, v.z)); acc.w = __fadd_rn(acc.w, __fmul_rn(w1, v.w));
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint32_t i = i0 + u * kThreads;
+            if (i >= nv) continue;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (p0) {
+                acc.x = __fadd_rn(acc.x, __fmul_rn(w0, v0[u].x)); acc.y = __fadd_rn(acc.y, __fmul_rn(w0, v0[u].y));
+                acc.z = __fadd_rn(acc.z, __fmul_rn(w0, v0[u].z)); acc.w = __fadd_rn(acc.w, __fmul_rn(w0, v0[u].w));
+            }
+            if (p1) {
+                acc.x = __fadd_rn(acc.x, __fmul_rn(w1, v1[u].x)); acc.y = __fadd_rn(acc.y, __fmul_rn(w1, v1[u].y));
+                acc.z = __fadd_rn(acc.z, __fmul_rn(w1, v1[u].z)); acc.w = __fadd_rn(acc.w, __fmul_rn(w1, v1[u].w));
+            }
+            dst[i] = acc;
         }
-        dst[i] = acc;
     }
 }
 
@@ -226,6 +261,7 @@ int32_t launch_moe_ep_exchange(fe2o3_ctx *ctx, cudaStream_t s, const void *args,
         }
         case FE2O3_MOE_EP_WAIT_ROWS:
         case FE2O3_MOE_EP_FFN_DONE:
+        case FE2O3_MOE_EP_ADVANCE:
             if (geo) *geo = fe2o3_geometry{{1, 1, 1}, {32, 1, 1}, 0, 1};
             if (plan_only) return FE2O3_OK;
             moe_ep_flag_kernel<<<1, 32, 0, s>>>(*a, ctx->status_word);

@@ -110,14 +110,15 @@ class MoeTop2Layer:
         if self.exchange == "peer":
             from ._lib import MoeEpExchangeArgs
             self.remote_rows = z(R, torch.int32)
-            self.epoch, self._epoch_offset = 0, MoeEpExchangeArgs.epoch.offset
+            self.epoch_counter = z(1, torch.int32)  # pass number, advanced on the device: passes replay from a graph
             self.k_phase = [P("moe_ep_exchange_v1", x=self.x, top2_experts=self.top2, permutation=self.perm,
                               inverse=self.inverse, expert_offsets=self.offsets, requested_counts=self.requested,
                               route_weights=self.weights, group_offsets=self.group_offsets,
                               remote_rows=self.remote_rows, combined_output=self.out, peer_recv_x=self.peer_recv_x,
                               peer_ffn_out=self.peer_ffn_out, peer_counts=self.peer_counts,
-                              peer_flags=self.peer_flags, tokens=T, d_model=d, experts=E, world=world, rank=rank,
-                              epoch=0, max_rows=self.max_rows, phase=ph) for ph in range(4)]
+                              peer_flags=self.peer_flags, epoch_counter=self.epoch_counter, tokens=T, d_model=d,
+                              experts=E, world=world, rank=rank, epoch=0, max_rows=self.max_rows, phase=ph)
+                            for ph in range(5)]
         self.launches_per_step = 7 if world == 1 else 8
 
     def _setup_peer_buffers(self, dev):
@@ -148,8 +149,9 @@ class MoeTop2Layer:
             dst.view(t.int16).copy_(t.from_numpy(np.ascontiguousarray(src).view(np.int16)))
 
     # ---- one step ------------------------------------------------------------------------
-    def forward(self):
-        s = self.stream
+    def forward(self, stream=None):
+        """Enqueues one layer pass on `stream` (default: the layer's stream) and returns the output tensor."""
+        s = stream or self.stream
         self.k_gate.launch(s)
         self.k_top2.launch(s)
         self.k_weights.launch(s)
@@ -157,18 +159,34 @@ class MoeTop2Layer:
             self.k_ffn.launch(s)
             self.k_combine.launch(s)
         elif self.exchange == "peer":
-            self.epoch += 1
-            word = int(self.epoch & 0xFFFFFFFF).to_bytes(4, "little")
-            for k in self.k_phase:
-                k.patch_kernarg(self._epoch_offset, word)
             self.k_phase[0].launch(s)   # counts exchange + rows to their experts' ranks
             self.k_phase[1].launch(s)   # wait for every source's rows
             self.k_ffn.launch(s)
             self.k_phase[2].launch(s)   # expert outputs ready
             self.k_phase[3].launch(s)   # pull and combine
+            self.k_phase[4].launch(s)   # advance the pass number
         else:
             self._exchange_forward()
             self.k_combine.launch(s)
+        return self.out
+
+    # ---- CUDA graph of one pass ---------------------------------------------------------
+    def capture(self):
+        """Captures one pass into a CUDA graph (every exchange mode except "nccl", whose split sizes
+        need the host).  Call after at least one eager pass.  Returns False when not capturable."""
+        if self.exchange == "nccl":
+            return False
+        t = self.torch
+        self._side = t.cuda.Stream()
+        self._side_stream = self.ctx.wrap_stream(self._side.cuda_stream)
+        self._graph = t.cuda.CUDAGraph()
+        t.cuda.synchronize()
+        with t.cuda.graph(self._graph, stream=self._side):
+            self.forward(self._side_stream)
+        return True
+
+    def replay(self):
+        self._graph.replay()
         return self.out
 
     def _exchange_forward(self):

@@ -270,8 +270,12 @@ typedef struct fe2o3_moe_grouped_ffn_v1_args {
  * device arrays of `world` u64 addresses, entry p being rank p's buffer, mapped
  * into this process: recv_x [max_rows][d_model] bf16, ffn_out
  * [max_rows][d_model] f32, counts [world][experts] u32, flags [3*world + 1] u32
- * (zero before the first pass).  `epoch` must increase by one per layer pass on
- * every rank (see fe2o3_prepared_patch_kernarg).  Phases, in stream order:
+ * (zero before the first pass).  The pass number ("epoch") must increase by one
+ * per layer pass on every rank: either patch `epoch` before each pass
+ * (fe2o3_prepared_patch_kernarg) or give `epoch_counter`, one local u32 that
+ * starts at 0 (the phases then use *epoch_counter + 1 and the ADVANCE phase,
+ * launched last, increments it, which lets a whole pass be replayed from a CUDA
+ * graph).  Phases, in stream order:
  * DISPATCH (counts exchange + rows to their expert's rank + group_offsets for
  * fe2o3_moe_grouped_ffn_v1 on recv_x), WAIT_ROWS, the FFN, FFN_DONE, COMBINE
  * (pull the two expert rows, weighted sum in rank order).  Waits are bounded. */
@@ -279,9 +283,11 @@ typedef struct fe2o3_moe_grouped_ffn_v1_args {
 #define FE2O3_MOE_EP_WAIT_ROWS 1u
 #define FE2O3_MOE_EP_FFN_DONE 2u
 #define FE2O3_MOE_EP_COMBINE 3u
+#define FE2O3_MOE_EP_ADVANCE 4u
 typedef struct fe2o3_moe_ep_exchange_v1_args {
     fe2o3_slice x, top2_experts, permutation, inverse, expert_offsets, requested_counts, route_weights,
-        group_offsets, remote_rows, combined_output, peer_recv_x, peer_ffn_out, peer_counts, peer_flags;
+        group_offsets, remote_rows, combined_output, peer_recv_x, peer_ffn_out, peer_counts, peer_flags,
+        epoch_counter;
     uint32_t tokens, d_model, experts, world, rank, epoch, max_rows, phase;
 } fe2o3_moe_ep_exchange_v1_args;
 
