@@ -160,127 +160,122 @@ moe_top2_kernel(fe2o3_moe_top2_v1_args a, uint32_t *status) {
     }
 }
 
-// ---- gate logits, one thread per token ---------------------------------------
-// Same arithmetic as moe_gate_kernel (every output is its own sequential f32
-// chain), arranged for latency: a thread owns one token and keeps E independent
-// accumulators, so E dependent-add chains are in flight per thread instead of
-// one.  64 tokens per block; x is staged k-major in shared memory so that the
-// per-k reads of a warp are conflict-free, Wg rows are broadcast reads.
-constexpr int kGate2Tokens = 64, kGate2KC = 64;
+// ---- gate logits, staged and prefetched -----------------------------------------
+// Same arithmetic as moe_gate_kernel: every output runs its own sequential f32
+// chain (product, then sum, increasing k).  A warp covers 32 tokens and a group
+// of EPT = 4 experts: lane = token, so the x operand is one conflict-free
+// shared-memory read per k and the four Wg operands one broadcast 16-byte read;
+// four independent add chains per thread hide the add latency.  (One output per
+// thread needs two shared-memory reads per multiply-add and is bound by
+// shared-memory bandwidth; all E outputs per thread leaves one warp per
+// scheduler and is bound by that warp's issue rate.)  Per 64-wide k chunk the x
+// rows and Wg rows are fetched one chunk ahead into registers, so global latency
+// overlaps the arithmetic.
+constexpr int kGate2Tokens = 32, kGate2KC = 64;
 
 template <int E>
-__global__ void __launch_bounds__(kGate2Tokens)
-moe_gate_token_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict__ wg, float *__restrict__ logits,
-                      uint32_t tokens, uint32_t d_model) {
+__global__ void __launch_bounds__(32 * (E / (E >= 4 ? 4 : E)))
+moe_gate_staged_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict__ wg, float *__restrict__ logits,
+                       uint32_t tokens, uint32_t d_model) {
+    constexpr int EPT = E >= 4 ? 4 : E;                     // experts per thread
+    constexpr int kThreads = 32 * (E / EPT);
+    constexpr int kXVec = kGate2Tokens * kGate2KC * 2 / 16; // 256 16-byte vectors of x per chunk
+    constexpr int kXPer = kXVec / kThreads;
+    constexpr int kWVec = kGate2KC * E * 2 / 16;            // 16-byte vectors of Wg per chunk
+    constexpr int kWPer = (kWVec + kThreads - 1) / kThreads;
     __shared__ float xs[kGate2KC][kGate2Tokens + 1];
     __shared__ __align__(16) float ws[kGate2KC][E];
-    const uint32_t tid = threadIdx.x;
+    const uint32_t tid = threadIdx.x, lane = tid & 31, e0 = (tid >> 5) * EPT;
     const uint32_t t0 = blockIdx.x * kGate2Tokens;
-    float acc[E];
+    float acc[EPT];
 #pragma unroll
-    for (int e = 0; e < E; ++e) acc[e] = 0.0f;
-    const bool vec = (d_model % 8u) == 0 && (reinterpret_cast<uint64_t>(x) & 15u) == 0;
-    // 8 lanes cover one token's 64 k values (128 bytes): coalesced 16-byte loads, held in registers
-    // one chunk ahead so that the global latency overlaps the arithmetic of the current chunk
-    uint4 pre[kGate2Tokens / 8];
+    for (int q = 0; q < EPT; ++q) acc[q] = 0.0f;
+    const bool vec = (d_model % 8u) == 0 && ((reinterpret_cast<uint64_t>(x) | reinterpret_cast<uint64_t>(wg)) & 15u) == 0;
+    uint4 xpre[kXPer], wpre[kWPer];
     auto prefetch = [&](uint32_t k0) {
+        // 8 consecutive threads cover one token's 64 k values (128 bytes)
 #pragma unroll
-        for (int pass = 0; pass < kGate2Tokens / 8; ++pass) {
-            const uint32_t tt = pass * 8 + (tid >> 3), c = tid & 7;
-            pre[pass] = make_uint4(0, 0, 0, 0);
-            if (t0 + tt < tokens) pre[pass] = __ldg(reinterpret_cast<const uint4 *>(x + (uint64_t)(t0 + tt) * d_model + k0) + c);
+        for (int q = 0; q < kXPer; ++q) {
+            const uint32_t v = tid + q * kThreads;
+            xpre[q] = make_uint4(0, 0, 0, 0);
+            if (t0 + (v >> 3) < tokens)
+                xpre[q] = __ldg(reinterpret_cast<const uint4 *>(x + (uint64_t)(t0 + (v >> 3)) * d_model + k0) + (v & 7));
         }
-    };
-    // the Wg rows of a full chunk are kGate2KC*E bf16 = kWgVec 16-byte vectors: fetched one chunk ahead too
-    constexpr int kWgVec = kGate2KC * E * 2 / 16, kWgPer = (kWgVec + kGate2Tokens - 1) / kGate2Tokens;
-    const bool wvec = (reinterpret_cast<uint64_t>(wg) & 15u) == 0;
-    uint4 wpre[kWgPer];
-    auto prefetch_w = [&](uint32_t k0) {
 #pragma unroll
-        for (int q = 0; q < kWgPer; ++q) {
-            const uint32_t i = tid + q * kGate2Tokens;
+        for (int q = 0; q < kWPer; ++q) {
+            const uint32_t v = tid + q * kThreads;
             wpre[q] = make_uint4(0, 0, 0, 0);
-            if (i < (uint32_t)kWgVec) wpre[q] = __ldg(reinterpret_cast<const uint4 *>(wg + (uint64_t)k0 * E) + i);
+            if (v < (uint32_t)kWVec) wpre[q] = __ldg(reinterpret_cast<const uint4 *>(wg + (uint64_t)k0 * E) + v);
         }
     };
     if (vec && d_model >= kGate2KC) prefetch(0);
-    if (wvec && d_model >= kGate2KC) prefetch_w(0);
     for (uint32_t k0 = 0; k0 < d_model; k0 += kGate2KC) {
         const uint32_t kc = min((uint32_t)kGate2KC, d_model - k0);
         if (vec && kc == kGate2KC) {
 #pragma unroll
-            for (int pass = 0; pass < kGate2Tokens / 8; ++pass) {
-                const uint32_t tt = pass * 8 + (tid >> 3), c = tid & 7;
-                const uint32_t w[4] = {pre[pass].x, pre[pass].y, pre[pass].z, pre[pass].w};
+            for (int q = 0; q < kXPer; ++q) {
+                const uint32_t v = tid + q * kThreads, tt = v >> 3, c = v & 7;
+                const uint32_t w[4] = {xpre[q].x, xpre[q].y, xpre[q].z, xpre[q].w};
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     xs[c * 8 + 2 * i][tt] = __uint_as_float(w[i] << 16);
                     xs[c * 8 + 2 * i + 1][tt] = __uint_as_float(w[i] & 0xffff0000u);
                 }
             }
-            if (k0 + 2 * kGate2KC <= d_model) prefetch(k0 + kGate2KC);
-        } else {
-            for (uint32_t i = tid; i < kGate2Tokens * kGate2KC; i += kGate2Tokens) {
-                const uint32_t tt = i / kGate2KC, kk = i % kGate2KC;
-                xs[kk][tt] = (t0 + tt < tokens && kk < kc) ? bf16_bits_to_f32(x[(uint64_t)(t0 + tt) * d_model + k0 + kk]) : 0.0f;
-            }
-        }
-        if (wvec && kc == kGate2KC) {
 #pragma unroll
-            for (int q = 0; q < kWgPer; ++q) {
-                const uint32_t i = tid + q * kGate2Tokens;
-                if (i < (uint32_t)kWgVec) {
+            for (int q = 0; q < kWPer; ++q) {
+                const uint32_t v = tid + q * kThreads;
+                if (v < (uint32_t)kWVec) {
                     const uint32_t w[4] = {wpre[q].x, wpre[q].y, wpre[q].z, wpre[q].w};
-                    float *dst = &ws[0][0] + i * 8;
+                    float *dst = &ws[0][0] + v * 8;
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        dst[2 * j] = __uint_as_float(w[j] << 16);
-                        dst[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+                    for (int i = 0; i < 4; ++i) {
+                        dst[2 * i] = __uint_as_float(w[i] << 16);
+                        dst[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
                     }
                 }
             }
-            if (k0 + 2 * kGate2KC <= d_model) prefetch_w(k0 + kGate2KC);
+            if (k0 + 2 * kGate2KC <= d_model) prefetch(k0 + kGate2KC);
         } else {
-            for (uint32_t i = tid; i < kc * E; i += kGate2Tokens) (&ws[0][0])[i] = bf16_bits_to_f32(wg[(uint64_t)k0 * E + i]);
+            for (uint32_t i = tid; i < (uint32_t)kGate2Tokens * kGate2KC; i += kThreads) {
+                const uint32_t tt = i / kGate2KC, kk = i % kGate2KC;
+                xs[kk][tt] = (t0 + tt < tokens && kk < kc) ? bf16_bits_to_f32(x[(uint64_t)(t0 + tt) * d_model + k0 + kk]) : 0.0f;
+            }
+            for (uint32_t i = tid; i < kc * E; i += kThreads) (&ws[0][0])[i] = bf16_bits_to_f32(wg[(uint64_t)k0 * E + i]);
         }
         __syncthreads();
         if (kc == kGate2KC) {
-            // full chunk: eight k steps per iteration with their operands loaded up front, so the E
-            // add chains advance back to back instead of waiting on shared-memory latency
 #pragma unroll 1
             for (uint32_t kk = 0; kk < kGate2KC; kk += 8) {
                 float xv[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) xv[i] = xs[kk + i][tid];
+                for (int i = 0; i < 8; ++i) xv[i] = xs[kk + i][lane];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    float w[E];
-                    if constexpr (E % 4 == 0) {
-#pragma unroll
-                        for (int q = 0; q < E / 4; ++q) {
-                            const float4 v = *reinterpret_cast<const float4 *>(&ws[kk + i][4 * q]);
-                            w[4 * q] = v.x; w[4 * q + 1] = v.y; w[4 * q + 2] = v.z; w[4 * q + 3] = v.w;
-                        }
+                    float w[EPT];
+                    if constexpr (EPT == 4) {
+                        const float4 v = *reinterpret_cast<const float4 *>(&ws[kk + i][e0]);
+                        w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
                     } else {
 #pragma unroll
-                        for (int e = 0; e < E; ++e) w[e] = ws[kk + i][e];
+                        for (int q = 0; q < EPT; ++q) w[q] = ws[kk + i][e0 + q];
                     }
 #pragma unroll
-                    for (int e = 0; e < E; ++e) acc[e] = __fadd_rn(acc[e], __fmul_rn(xv[i], w[e]));
+                    for (int q = 0; q < EPT; ++q) acc[q] = __fadd_rn(acc[q], __fmul_rn(xv[i], w[q]));
                 }
             }
         } else {
             for (uint32_t kk = 0; kk < kc; ++kk) {
-                const float xv = xs[kk][tid];
+                const float xv = xs[kk][lane];
 #pragma unroll
-                for (int e = 0; e < E; ++e) acc[e] = __fadd_rn(acc[e], __fmul_rn(xv, ws[kk][e]));
+                for (int q = 0; q < EPT; ++q) acc[q] = __fadd_rn(acc[q], __fmul_rn(xv, ws[kk][e0 + q]));
             }
         }
         __syncthreads();
     }
-    if (t0 + tid < tokens) {
+    if (t0 + lane < tokens) {
 #pragma unroll
-        for (int e = 0; e < E; ++e) logits[(uint64_t)(t0 + tid) * E + e] = acc[e];
+        for (int q = 0; q < EPT; ++q) logits[(uint64_t)(t0 + lane) * E + e0 + q] = acc[q];
     }
 }
 
@@ -562,14 +557,14 @@ int32_t launch_moe_gate(fe2o3_ctx *, cudaStream_t s, const void *args, fe2o3_geo
     const uint32_t smem = (tpb * (kGateKC + 1) + kGateKC * E) * sizeof(float);
     const bool per_token = E == 4 || E == 8 || E == 16;
     if (per_token) {
-        const uint32_t g2 = ceil_div_u32(a->tokens, kGate2Tokens);
-        if (geo) *geo = fe2o3_geometry{{g2, 1, 1}, {kGate2Tokens, 1, 1}, 0, 1};
+        const uint32_t g2 = ceil_div_u32(a->tokens, kGate2Tokens), thr = 32 * (E / 4);
+        if (geo) *geo = fe2o3_geometry{{g2, 1, 1}, {thr, 1, 1}, 0, 1};
         if (plan_only || a->tokens == 0) return FE2O3_OK;
         const uint16_t *x = reinterpret_cast<const uint16_t *>(a->x.ptr), *wg = reinterpret_cast<const uint16_t *>(a->wg.ptr);
         float *lg = reinterpret_cast<float *>(a->logits.ptr);
-        if (E == 4) moe_gate_token_kernel<4><<<g2, kGate2Tokens, 0, s>>>(x, wg, lg, a->tokens, a->d_model);
-        else if (E == 8) moe_gate_token_kernel<8><<<g2, kGate2Tokens, 0, s>>>(x, wg, lg, a->tokens, a->d_model);
-        else moe_gate_token_kernel<16><<<g2, kGate2Tokens, 0, s>>>(x, wg, lg, a->tokens, a->d_model);
+        if (E == 4) moe_gate_staged_kernel<4><<<g2, thr, 0, s>>>(x, wg, lg, a->tokens, a->d_model);
+        else if (E == 8) moe_gate_staged_kernel<8><<<g2, thr, 0, s>>>(x, wg, lg, a->tokens, a->d_model);
+        else moe_gate_staged_kernel<16><<<g2, thr, 0, s>>>(x, wg, lg, a->tokens, a->d_model);
         fe2o3_count_launch(1);
         return fe2o3_cuda_status(cudaGetLastError(), "moe_gate_v1");
     }
