@@ -5,8 +5,8 @@
 // exp(m_old - m_new), running denominator, out = acc / l) applied per block of
 // 128 keys instead of per key, with both contractions on tcgen05:
 //   S = Q * K^T   (A = Q tile, B = K tile, both K-major, accumulator in TMEM)
-//   O += P * V    (A = P written to shared memory as bf16, B = V tile, MN-major,
-//                  accumulator O stays in TMEM for the whole key loop)
+//   O += P * V    (A = P written as packed bf16 into tensor memory, B = V tile,
+//                  MN-major, accumulator O stays in TMEM for the whole key loop)
 // One CTA owns one (batch, head) and 256 query rows as two 128-row tiles that
 // share every K/V tile.  Ten warps: 0 = TMA producer, 1 = MMA issuer and TMEM
 // owner, 2-5 = softmax for tile 0, 6-9 = softmax for tile 1.  A softmax thread
@@ -29,21 +29,22 @@ constexpr int D = 64;            // head dimension handled by this kernel
 constexpr int BQ = 128;          // query rows per tile
 constexpr int BKV = 128;         // keys per block
 constexpr int QT = 2;            // query tiles per CTA
-constexpr int KV_STAGES = 2;
+constexpr int KV_STAGES = 4;
 constexpr int kThreads = 32 * (2 + 4 * QT);
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 constexpr uint32_t kTileBytes = 128 * D * 2;     // 16 KiB: a 128 x 64 bf16 tile
-constexpr uint32_t kPBytes = BQ * BKV * 2;       // 32 KiB: P tile as two 64-key sub-tiles
 constexpr uint32_t kOffQ = 0;
 constexpr uint32_t kOffK = kOffQ + QT * kTileBytes;
 constexpr uint32_t kOffV = kOffK + KV_STAGES * kTileBytes;
-constexpr uint32_t kOffP = kOffV + KV_STAGES * kTileBytes;
-constexpr uint32_t kOffBar = kOffP + QT * kPBytes;
+constexpr uint32_t kOffBar = kOffV + KV_STAGES * kTileBytes;
 constexpr uint32_t kSmemTotal = kOffBar + 512 + 1024;
 
-// TMEM columns: S tile t at t*128 (128 f32 columns), O tile t at 256 + t*64.
+// TMEM columns: S tile t at t*128 (128 f32 columns), O tile t at 256 + t*64 (64 f32 columns),
+// P tile t at 384 + t*64 (128 bf16 per row = 64 columns).
 constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kColO = 256, kColP = 384;
+constexpr uint32_t kIssuerIdleLimit = 1u << 22;
 
 struct AttnParams {
     float *out;
@@ -152,49 +153,57 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (lane == 0) {
             constexpr uint32_t idesc_qk = umma_idesc(1u, BQ, BKV, 0u, 0u);
             constexpr uint32_t idesc_pv = umma_idesc(1u, BQ, D, 0u, 1u);
-            const uint32_t sQ = smem_u32(smem + kOffQ), sK = smem_u32(smem + kOffK), sV = smem_u32(smem + kOffV),
-                           sP = smem_u32(smem + kOffP);
+            const uint32_t sQ = smem_u32(smem + kOffQ), sK = smem_u32(smem + kOffK), sV = smem_u32(smem + kOffV);
             bool ok = mbar_wait(q_full, 0);
-            uint32_t kst = 0, kph = 0, vst = 0, vph = 0;
             // Descriptors are built once; inside the loops only the 16-byte-unit start address field moves.
             const uint64_t dQ = umma_smem_desc(sQ, 16, 1024), dK = umma_smem_desc(sK, 16, 1024),
-                           dV = umma_smem_desc(sV, 8192, 1024), dP = umma_smem_desc(sP, 16, 1024);
-            auto issue_pv = [&](uint32_t jj) -> bool {
-                if (!mbar_wait(&v_full[vst], vph)) return false;
-                const uint64_t dVs = dV + ((vst * kTileBytes) >> 4);
+                           dV = umma_smem_desc(sV, 8192, 1024);
+            // The issuer polls: whichever of the four next operations (Q*K^T or P*V, tile 0 or 1) has
+            // its operands ready is issued, so one tile never waits behind the other tile's softmax.
+            uint32_t qk_j[QT], pv_j[QT], k_used[KV_STAGES], v_used[KV_STAGES];
+            for (int t = 0; t < QT; ++t) qk_j[t] = pv_j[t] = 0;
+            for (int i = 0; i < KV_STAGES; ++i) k_used[i] = v_used[i] = 0;
+            uint32_t idle = 0;
+            while (ok && (pv_j[0] < nkv || pv_j[QT - 1] < nkv)) {
+                bool progress = false;
+#pragma unroll
                 for (int t = 0; t < QT; ++t) {
-                    if (!mbar_wait(&p_ready[t], jj & 1)) return false;
-                    tc_fence_after();
-                    const uint64_t dPt = dP + ((t * kPBytes) >> 4);
-                    const uint32_t dst = tmem_base + 256 + t * D;
-                    umma_f16(dst, dPt, dVs, idesc_pv, jj != 0u);
+                    uint32_t j = pv_j[t];
+                    if (j < nkv) {
+                        const uint32_t st = j % KV_STAGES, ph = (j / KV_STAGES) & 1;
+                        if (mbar_try_wait(&p_ready[t], j & 1) && mbar_try_wait(&v_full[st], ph)) {
+                            tc_fence_after();
+                            const uint64_t dVs = dV + ((st * kTileBytes) >> 4);
+                            const uint32_t dst = tmem_base + kColO + t * D, src = tmem_base + kColP + t * (BKV / 2);
+                            umma_f16_ts(dst, src, dVs, idesc_pv, j != 0u);
 #pragma unroll
-                    for (int kk = 1; kk < BKV / 16; ++kk)
-                        umma_f16(dst, dPt + (((kk / 4) * kTileBytes + (kk % 4) * 32) >> 4), dVs + ((kk * 2048) >> 4),
-                                 idesc_pv, 1u);
-                    umma_commit(&pv_done[t]);
-                }
-                umma_commit(&v_empty[vst]);
-                if (++vst == KV_STAGES) { vst = 0; vph ^= 1; }
-                return true;
-            };
-            for (uint32_t j = 0; j < nkv && ok; ++j) {
-                if (!mbar_wait(&k_full[kst], kph)) { ok = false; break; }
-                for (int t = 0; t < QT && ok; ++t) {
-                    if (!mbar_wait(&s_empty[t], (j & 1) ^ 1)) { ok = false; break; }
-                    tc_fence_after();
-                    const uint64_t dQt = dQ + ((t * kTileBytes) >> 4), dKs = dK + ((kst * kTileBytes) >> 4);
+                            for (int kk = 1; kk < BKV / 16; ++kk)
+                                umma_f16_ts(dst, src + kk * 8, dVs + ((kk * 2048) >> 4), idesc_pv, 1u);
+                            umma_commit(&pv_done[t]);
+                            if (++v_used[st] == QT) { umma_commit(&v_empty[st]); v_used[st] = 0; }
+                            pv_j[t] = j + 1;
+                            progress = true;
+                        }
+                    }
+                    j = qk_j[t];
+                    if (j < nkv) {
+                        const uint32_t st = j % KV_STAGES, ph = (j / KV_STAGES) & 1;
+                        if (mbar_try_wait(&s_empty[t], (j & 1) ^ 1) && mbar_try_wait(&k_full[st], ph)) {
+                            tc_fence_after();
+                            const uint64_t dQt = dQ + ((t * kTileBytes) >> 4), dKs = dK + ((st * kTileBytes) >> 4);
 #pragma unroll
-                    for (int kk = 0; kk < D / 16; ++kk)
-                        umma_f16(tmem_base + t * BKV, dQt + ((kk * 32) >> 4), dKs + ((kk * 32) >> 4), idesc_qk, kk != 0);
-                    umma_commit(&s_full[t]);
+                            for (int kk = 0; kk < D / 16; ++kk)
+                                umma_f16(tmem_base + t * BKV, dQt + ((kk * 32) >> 4), dKs + ((kk * 32) >> 4), idesc_qk, kk != 0);
+                            umma_commit(&s_full[t]);
+                            if (++k_used[st] == QT) { umma_commit(&k_empty[st]); k_used[st] = 0; }
+                            qk_j[t] = j + 1;
+                            progress = true;
+                        }
+                    }
                 }
-                if (!ok) break;
-                umma_commit(&k_empty[kst]);
-                if (++kst == KV_STAGES) { kst = 0; kph ^= 1; }
-                if (j > 0 && !issue_pv(j - 1)) { ok = false; break; }
+                if (progress) idle = 0;
+                else if (++idle > kIssuerIdleLimit) ok = false;
             }
-            if (ok && nkv > 0 && !issue_pv(nkv - 1)) ok = false;
             if (!ok) kstatus_set(p.status, FE2O3_KSTATUS_WAIT_EXPIRED);
         }
     } else {
@@ -205,8 +214,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const uint32_t qrow = q0 + t * BQ + r;      // query index inside the head
         const uint32_t lane_addr = (quad * 32u) << 16;
         const uint32_t tS = tmem_base + t * BKV + lane_addr;
-        const uint32_t tO = tmem_base + 256 + t * D + lane_addr;
-        uint8_t *prow = smem + kOffP + t * kPBytes + (r >> 3) * 1024 + (r & 7) * 128;
+        const uint32_t tO = tmem_base + kColO + t * D + lane_addr;
+        const uint32_t tP = tmem_base + kColP + t * (BKV / 2) + lane_addr;
         const float c = p.scale_log2;
         float m_ref = -INFINITY;   // exponent offset, in raw score units
         float l = 0.0f;
@@ -304,21 +313,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 }
             }
             l = fmaf(l, factor, (sum0 + sum1) + (sum2 + sum3));
-            // 32 keys = four 16-byte chunks; the chunk index inside the 64-key sub-tile is XOR-swizzled by the row
-            auto store32 = [&](const uint32_t (&pk)[16], int ch) {
-                uint8_t *sub = prow + (ch >> 1) * kTileBytes;
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const uint32_t chunk = ((ch & 1) * 4 + q) ^ (r & 7);
-                    *reinterpret_cast<uint4 *>(sub + chunk * 16) = make_uint4(pk[q * 4], pk[q * 4 + 1], pk[q * 4 + 2], pk[q * 4 + 3]);
-                }
-            };
-            store32(pk0, 0);
-            store32(pk1, 1);
-            store32(pk2, 2);
-            store32(pk3, 3);
-            // publish P (generic-proxy writes) and any O rescale (TMEM stores) to the MMA issuer
-            fence_proxy_async_smem();
+            // P as packed bf16 pairs into tensor memory: 16 columns per 32 keys
+            tmem_st_32x32b_x16(tP, pk0);
+            tmem_st_32x32b_x16(tP + 16, pk1);
+            tmem_st_32x32b_x16(tP + 32, pk2);
+            tmem_st_32x32b_x16(tP + 48, pk3);
+            tmem_st_wait();
+            // publish P and any O rescale (both TMEM stores) to the MMA issuer
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&p_ready[t]);
