@@ -7,16 +7,26 @@
 //   S = Q * K^T   (A = Q tile, B = K tile, both K-major, accumulator in TMEM)
 //   O += P * V    (A = P written as packed bf16 into tensor memory, B = V tile,
 //                  MN-major, accumulator O stays in TMEM for the whole key loop)
-// One CTA owns one (batch, head) and 256 query rows as two 128-row tiles that
-// share every K/V tile.  Ten warps: 0 = TMA producer, 1 = MMA issuer and TMEM
-// owner, 2-5 = softmax for tile 0, 6-9 = softmax for tile 1.  A softmax thread
-// owns one query row (one TMEM lane): it reads its 128 scores once into
-// registers and releases S at once, so the next Q*K^T overlaps the exponentials.
-// The exponent offset is a per-row reference maximum that is only moved (and O
-// and l rescaled through TMEM) when the block maximum exceeds it by more than
-// 2^8; the final quotient O / l is independent of the offset, so the result is
-// the same function as the reference recurrence.  Scores are scaled inside
-// exp2: p = 2^(s*c - m*c), c = scale * log2(e).  All waits are bounded.
+//
+// Work units.  A unit is one (batch, head) and 256 query rows handled as two
+// 128-row tiles that share every K/V tile.  The kernel is persistent: one CTA
+// per SM walks units b, b + grid, b + 2*grid, ... with every mbarrier ring
+// running on across units, so the loads and the first Q*K^T of the next unit
+// overlap the last exponentials and the output of the current one.  When the
+// last round would leave more than half of the SMs idle its units are split
+// into single 128-row tiles, one per CTA.
+//
+// Twelve warps: 0 = TMA producer, 1 and 2 = MMA issuers of tile 0 and tile 1
+// (warp 1 owns the TMEM allocation), 3 idle, 4-7 = softmax for tile 0, 8-11 =
+// softmax for tile 1.  A softmax thread owns one query row (one TMEM lane): it
+// reads its 128 scores once into registers and releases S at once, so the next
+// Q*K^T overlaps the exponentials.  The exponent offset is a per-row reference
+// maximum that is only moved (and O and l rescaled through TMEM) when the block
+// maximum exceeds it by more than 2^8; the final quotient O / l is independent
+// of the offset, so the result is the same function as the reference
+// recurrence.  Scores are scaled inside exp2: p = 2^(s*c - m*c),
+// c = scale * log2(e).  The output leaves through shared memory and bulk tensor
+// stores.  All waits are bounded.
 #include "common.cuh"
 #include "gemm_tc.h"
 
@@ -28,14 +38,19 @@ namespace {
 constexpr int D = 64;            // head dimension handled by this kernel
 constexpr int BQ = 128;          // query rows per tile
 constexpr int BKV = 128;         // keys per block
-constexpr int QT = 2;            // query tiles per CTA
+constexpr int QT = 2;            // query tiles per unit
+constexpr int Q_STAGES = 2;
 constexpr int KV_STAGES = 4;
-constexpr int kThreads = 32 * (2 + 4 * QT);
+constexpr uint32_t kQEmptyParties = QT * (1 + 4);   // per tile: its issuer and its four softmax warps (output staging)
+constexpr int kSoftmaxWarps = 4 * QT;       // one softmax thread per query row
+constexpr int kThreads = 32 * (4 + kSoftmaxWarps);
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
+constexpr float kTruncGain = 1.001953125f;           // 1 + 2^-9: half a bf16 ulp, relative
+constexpr float kTruncBiasLog2 = 0.0028150157f;      // log2(kTruncGain)
 
 constexpr uint32_t kTileBytes = 128 * D * 2;     // 16 KiB: a 128 x 64 bf16 tile
 constexpr uint32_t kOffQ = 0;
-constexpr uint32_t kOffK = kOffQ + QT * kTileBytes;
+constexpr uint32_t kOffK = kOffQ + Q_STAGES * QT * kTileBytes;
 constexpr uint32_t kOffV = kOffK + KV_STAGES * kTileBytes;
 constexpr uint32_t kOffBar = kOffV + KV_STAGES * kTileBytes;
 constexpr uint32_t kSmemTotal = kOffBar + 512 + 1024;
@@ -44,31 +59,51 @@ constexpr uint32_t kSmemTotal = kOffBar + 512 + 1024;
 // P tile t at 384 + t*64 (128 bf16 per row = 64 columns).
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColO = 256, kColP = 384;
-constexpr uint32_t kIssuerIdleLimit = 1u << 22;
 
 struct AttnParams {
     float *out;
     uint32_t bh, seq;
     float scale_log2;   // scale * log2(e)
     uint32_t causal;
+    uint32_t q_blocks;  // 256-row blocks per head
+    uint32_t n_full;    // units of two tiles: indices [0, n_full)
+    uint32_t n_half;    // single-tile units: indices [n_full, n_full + n_half), two per 256-row block
     uint32_t *status;
 };
 
-// Two probabilities to packed bf16 on the integer pipe (round half up: add half an ulp, keep the
-// upper 16 bits).  The conversion instruction shares the quarter-rate unit with ex2, which is the
-// bottleneck of this kernel; inputs here are finite and non-negative, so no NaN handling is needed.
-__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
-    return __byte_perm(__float_as_uint(lo) + 0x8000u, __float_as_uint(hi) + 0x8000u, 0x7632);
+struct Unit {
+    uint32_t head, q0, nt, nkv;
+};
+
+// The i-th unit of this CTA; false when the CTA has no i-th unit.  Every role walks the same sequence.
+__device__ __forceinline__ bool unit_at(const AttnParams &p, uint32_t i, Unit &u) {
+    const uint32_t idx = blockIdx.x + i * gridDim.x;
+    uint32_t block, sub;
+    if (idx < p.n_full) {
+        block = idx; sub = 0; u.nt = QT;
+    } else if (idx - p.n_full < p.n_half) {
+        block = p.n_full + ((idx - p.n_full) >> 1); sub = (idx - p.n_full) & 1; u.nt = 1;
+    } else {
+        return false;
+    }
+    u.head = block / p.q_blocks;
+    uint32_t qb = block % p.q_blocks;
+    if (p.causal) qb = p.q_blocks - 1 - qb;   // the longest key ranges first
+    u.q0 = qb * (QT * BQ) + sub * BQ;
+    const uint32_t kv_limit = p.causal ? min(p.seq, u.q0 + u.nt * BQ) : p.seq;
+    u.nkv = u.q0 < p.seq ? (kv_limit + BKV - 1) / BKV : 0;
+    return true;
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                    const __grid_constant__ CUtensorMap tmV, AttnParams p) {
+                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, AttnParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kOffBar);
-    uint64_t *q_full = bars;                       // 1
-    uint64_t *k_full = q_full + 1;                 // KV_STAGES
+    uint64_t *q_full = bars;                       // Q_STAGES
+    uint64_t *q_empty = q_full + Q_STAGES;
+    uint64_t *k_full = q_empty + Q_STAGES;         // KV_STAGES
     uint64_t *k_empty = k_full + KV_STAGES;
     uint64_t *v_full = k_empty + KV_STAGES;
     uint64_t *v_empty = v_full + KV_STAGES;
@@ -80,20 +115,17 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(stagger + 1);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t q_blocks = (p.seq + QT * BQ - 1) / (QT * BQ);
-    const uint32_t head = blockIdx.x / q_blocks;
-    const uint32_t q0 = (blockIdx.x % q_blocks) * (QT * BQ);
-    // keys this CTA must visit
-    const uint32_t kv_limit = p.causal ? min(p.seq, q0 + QT * BQ) : p.seq;
-    const uint32_t nkv = (kv_limit + BKV - 1) / BKV;
 
     if (threadIdx.x == 0) {
-        mbar_init(q_full, 1);
+        for (int i = 0; i < Q_STAGES; ++i) {
+            mbar_init(&q_full[i], 1);
+            mbar_init(&q_empty[i], kQEmptyParties);
+        }
         for (int i = 0; i < KV_STAGES; ++i) {
             mbar_init(&k_full[i], 1);
-            mbar_init(&k_empty[i], 1);
+            mbar_init(&k_empty[i], QT);
             mbar_init(&v_full[i], 1);
-            mbar_init(&v_empty[i], 1);
+            mbar_init(&v_empty[i], QT);
         }
         for (int t = 0; t < QT; ++t) {
             mbar_init(&s_full[t], 1);
@@ -115,248 +147,328 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
     if (warp == 0) {
         // ---------------------------------------------------------- TMA producer
-        if (lane == 0) {
+        // The whole warp runs the loop converged; one elected lane issues the copies.
+        if (elect_one()) {
             tma_prefetch_desc(&tmQ);
             tma_prefetch_desc(&tmK);
             tma_prefetch_desc(&tmV);
-            bool ok = true;
-            mbar_arrive_expect_tx(q_full, QT * kTileBytes);
-            for (int t = 0; t < QT; ++t)
-                tma_load_3d(smem + kOffQ + t * kTileBytes, &tmQ, q_full, 0, (int32_t)(q0 + t * BQ), (int32_t)head);
-            uint32_t last_k[KV_STAGES], last_v[KV_STAGES];
-            bool k_armed[KV_STAGES], v_armed[KV_STAGES];
-            for (int i = 0; i < KV_STAGES; ++i) { last_k[i] = last_v[i] = 0; k_armed[i] = v_armed[i] = false; }
-            uint32_t stage = 0, phase = 0;
-            for (uint32_t j = 0; j < nkv && ok; ++j) {
-                if (!mbar_wait(&k_empty[stage], phase ^ 1)) { ok = false; break; }
-                mbar_arrive_expect_tx(&k_full[stage], kTileBytes);
-                tma_load_3d(smem + kOffK + stage * kTileBytes, &tmK, &k_full[stage], 0, (int32_t)(j * BKV), (int32_t)head);
-                last_k[stage] = phase;
-                k_armed[stage] = true;
-                if (!mbar_wait(&v_empty[stage], phase ^ 1)) { ok = false; break; }
-                mbar_arrive_expect_tx(&v_full[stage], kTileBytes);
-                tma_load_3d(smem + kOffV + stage * kTileBytes, &tmV, &v_full[stage], 0, (int32_t)(j * BKV), (int32_t)head);
-                last_v[stage] = phase;
-                v_armed[stage] = true;
-                if (++stage == KV_STAGES) { stage = 0; phase ^= 1; }
-            }
-            if (!ok) kstatus_set(p.status, FE2O3_KSTATUS_WAIT_EXPIRED);
-            // drain this thread's copies before the CTA can exit
-            mbar_wait(q_full, 0);
-            for (int i = 0; i < KV_STAGES; ++i) {
-                if (k_armed[i]) mbar_wait(&k_full[i], last_k[i]);
-                if (v_armed[i]) mbar_wait(&v_full[i], last_v[i]);
-            }
+            tma_prefetch_desc(&tmO);
         }
-    } else if (warp == 1) {
-        // ---------------------------------------------------------- MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc_qk = umma_idesc(1u, BQ, BKV, 0u, 0u);
-            constexpr uint32_t idesc_pv = umma_idesc(1u, BQ, D, 0u, 1u);
-            const uint32_t sQ = smem_u32(smem + kOffQ), sK = smem_u32(smem + kOffK), sV = smem_u32(smem + kOffV);
-            bool ok = mbar_wait(q_full, 0);
-            // Descriptors are built once; inside the loops only the 16-byte-unit start address field moves.
-            const uint64_t dQ = umma_smem_desc(sQ, 16, 1024), dK = umma_smem_desc(sK, 16, 1024),
-                           dV = umma_smem_desc(sV, 8192, 1024);
-            // The issuer polls: whichever of the four next operations (Q*K^T or P*V, tile 0 or 1) has
-            // its operands ready is issued, so one tile never waits behind the other tile's softmax.
-            uint32_t qk_j[QT], pv_j[QT], k_used[KV_STAGES], v_used[KV_STAGES];
-            for (int t = 0; t < QT; ++t) qk_j[t] = pv_j[t] = 0;
-            for (int i = 0; i < KV_STAGES; ++i) k_used[i] = v_used[i] = 0;
-            uint32_t idle = 0;
-            while (ok && (pv_j[0] < nkv || pv_j[QT - 1] < nkv)) {
-                bool progress = false;
-#pragma unroll
-                for (int t = 0; t < QT; ++t) {
-                    uint32_t j = pv_j[t];
-                    if (j < nkv) {
-                        const uint32_t st = j % KV_STAGES, ph = (j / KV_STAGES) & 1;
-                        if (mbar_try_wait(&p_ready[t], j & 1) && mbar_try_wait(&v_full[st], ph)) {
-                            tc_fence_after();
-                            const uint64_t dVs = dV + ((st * kTileBytes) >> 4);
-                            const uint32_t dst = tmem_base + kColO + t * D, src = tmem_base + kColP + t * (BKV / 2);
-                            umma_f16_ts(dst, src, dVs, idesc_pv, j != 0u);
-#pragma unroll
-                            for (int kk = 1; kk < BKV / 16; ++kk)
-                                umma_f16_ts(dst, src + kk * 8, dVs + ((kk * 2048) >> 4), idesc_pv, 1u);
-                            umma_commit(&pv_done[t]);
-                            if (++v_used[st] == QT) { umma_commit(&v_empty[st]); v_used[st] = 0; }
-                            pv_j[t] = j + 1;
-                            progress = true;
-                        }
-                    }
-                    j = qk_j[t];
-                    if (j < nkv) {
-                        const uint32_t st = j % KV_STAGES, ph = (j / KV_STAGES) & 1;
-                        if (mbar_try_wait(&s_empty[t], (j & 1) ^ 1) && mbar_try_wait(&k_full[st], ph)) {
-                            tc_fence_after();
-                            const uint64_t dQt = dQ + ((t * kTileBytes) >> 4), dKs = dK + ((st * kTileBytes) >> 4);
-#pragma unroll
-                            for (int kk = 0; kk < D / 16; ++kk)
-                                umma_f16(tmem_base + t * BKV, dQt + ((kk * 32) >> 4), dKs + ((kk * 32) >> 4), idesc_qk, kk != 0);
-                            umma_commit(&s_full[t]);
-                            if (++k_used[st] == QT) { umma_commit(&k_empty[st]); k_used[st] = 0; }
-                            qk_j[t] = j + 1;
-                            progress = true;
-                        }
-                    }
+        __syncwarp();
+        bool ok = true;
+        uint32_t g = 0;          // K/V blocks loaded so far, over all units
+        uint32_t n_units = 0;
+        Unit u;
+        for (uint32_t i = 0; ok && unit_at(p, i, u); ++i) {
+            if (u.nkv == 0) continue;   // every role skips a unit without keys (rows beyond seq)
+            const uint32_t qs = n_units % Q_STAGES, qph = (n_units / Q_STAGES) & 1;
+            ++n_units;
+            if (!mbar_wait(&q_empty[qs], qph ^ 1)) { ok = false; break; }
+            if (elect_one()) {
+                mbar_arrive_expect_tx(&q_full[qs], u.nt * kTileBytes);
+                for (uint32_t t = 0; t < u.nt; ++t)
+                    tma_load_3d(smem + kOffQ + (qs * QT + t) * kTileBytes, &tmQ, &q_full[qs], 0, (int32_t)(u.q0 + t * BQ),
+                                (int32_t)u.head);
+            }
+            __syncwarp();
+            for (uint32_t j = 0; j < u.nkv; ++j, ++g) {
+                const uint32_t st = g % KV_STAGES, ph = (g / KV_STAGES) & 1;
+                if (!mbar_wait(&k_empty[st], ph ^ 1)) { ok = false; break; }
+                if (elect_one()) {
+                    mbar_arrive_expect_tx(&k_full[st], kTileBytes);
+                    tma_load_3d(smem + kOffK + st * kTileBytes, &tmK, &k_full[st], 0, (int32_t)(j * BKV), (int32_t)u.head);
                 }
-                if (progress) idle = 0;
-                else if (++idle > kIssuerIdleLimit) ok = false;
+                __syncwarp();
+                if (!mbar_wait(&v_empty[st], ph ^ 1)) {
+                    ok = false;
+                    mbar_wait(&k_full[st], ph);   // the K copy just issued must land before the CTA exits
+                    break;
+                }
+                if (elect_one()) {
+                    mbar_arrive_expect_tx(&v_full[st], kTileBytes);
+                    tma_load_3d(smem + kOffV + st * kTileBytes, &tmV, &v_full[st], 0, (int32_t)(j * BKV), (int32_t)u.head);
+                }
+                __syncwarp();
             }
-            if (!ok) kstatus_set(p.status, FE2O3_KSTATUS_WAIT_EXPIRED);
         }
+        if (!ok && lane == 0) kstatus_set(p.status, FE2O3_KSTATUS_WAIT_EXPIRED);
+        // drain the copies before the CTA can exit: the newest phase of every ring slot in use
+        for (uint32_t b = 0; b < KV_STAGES && b < g; ++b) {
+            const uint32_t last = g - 1 - b, st = last % KV_STAGES, ph = (last / KV_STAGES) & 1;
+            mbar_wait(&k_full[st], ph);
+            mbar_wait(&v_full[st], ph);
+        }
+        for (uint32_t b = 0; b < Q_STAGES && b < n_units; ++b) {
+            const uint32_t last = n_units - 1 - b;
+            mbar_wait(&q_full[last % Q_STAGES], (last / Q_STAGES) & 1);
+        }
+    } else if (warp == 1 || warp == 2) {
+        // ---------------------------------------------------------- MMA issuers, one warp per query tile
+        // A single thread cannot issue the 24 small MMAs of a step (eight of them only 32 tensor-core
+        // cycles long) fast enough for two tiles, so each tile has its own issuer.  The warp runs
+        // converged and one elected lane issues.  Per tile the order is fixed: Q*K^T of block b+1 (its
+        // S buffer is free as soon as the softmax has read block b), then P*V of block b (ready at the
+        // end of that softmax step); block b+1 may already belong to the next unit.
+        const uint32_t t = warp - 1;
+        constexpr uint32_t idesc_qk = umma_idesc(1u, BQ, BKV, 0u, 0u);
+        constexpr uint32_t idesc_pv = umma_idesc(1u, BQ, D, 0u, 1u);
+        const uint32_t sQ = smem_u32(smem + kOffQ), sK = smem_u32(smem + kOffK), sV = smem_u32(smem + kOffV);
+        // Descriptors are built once; inside the loops only the 16-byte-unit start address field moves.
+        const uint64_t dQ = umma_smem_desc(sQ, 16, 1024), dK = umma_smem_desc(sK, 16, 1024),
+                       dV = umma_smem_desc(sV, 8192, 1024);
+        const uint32_t tS = tmem_base + t * BKV, tO = tmem_base + kColO + t * D, tP = tmem_base + kColP + t * (BKV / 2);
+        bool ok = true;
+        uint32_t g = 0;    // key blocks over all units: ring position of K/V
+        uint32_t gt = 0;   // key blocks this tile has processed: parity of s_* / p_ready / pv_done
+        uint32_t n = 0;    // units with keys seen so far (selects the Q stage)
+        bool pending = false;                       // a P*V whose Q*K^T successor has been issued (or has none)
+        uint32_t pv_st = 0, pv_ph = 0, pv_gt = 0, pv_acc = 0;
+        auto issue_pv = [&]() {
+            if (!mbar_wait(&p_ready[t], pv_gt & 1) || !mbar_wait(&v_full[pv_st], pv_ph)) { ok = false; return; }
+            tc_fence_after();
+            if (elect_one()) {
+                const uint64_t dVs = dV + ((pv_st * kTileBytes) >> 4);
+                umma_f16_ts(tO, tP, dVs, idesc_pv, pv_acc);
+#pragma unroll
+                for (int kk = 1; kk < BKV / 16; ++kk) umma_f16_ts(tO, tP + kk * 8, dVs + ((kk * 2048) >> 4), idesc_pv, 1u);
+                umma_commit(&pv_done[t]);
+                umma_commit(&v_empty[pv_st]);
+            }
+            __syncwarp();
+            pending = false;
+        };
+        Unit u;
+        for (uint32_t i = 0; ok && unit_at(p, i, u); ++i) {
+            if (u.nkv == 0) continue;
+            const uint32_t qs = n % Q_STAGES, qph = (n / Q_STAGES) & 1;
+            ++n;
+            if (t >= u.nt) {
+                // a unit of one tile: this tile only hands its K/V blocks and its Q stage on
+                if (pending) issue_pv();
+                for (uint32_t j = 0; ok && j < u.nkv; ++j, ++g) {
+                    const uint32_t st = g % KV_STAGES, ph = (g / KV_STAGES) & 1;
+                    if (!mbar_wait(&k_full[st], ph)) { ok = false; break; }
+                    if (lane == 0) mbar_arrive(&k_empty[st]);
+                    if (!mbar_wait(&v_full[st], ph)) { ok = false; break; }
+                    if (lane == 0) mbar_arrive(&v_empty[st]);
+                }
+                if (ok && !mbar_wait(&q_full[qs], qph)) ok = false;
+                if (ok && lane == 0) mbar_arrive_n(&q_empty[qs], 1 + 4);   // for the absent tile's issuer and softmax warps
+                continue;
+            }
+            if (!mbar_wait(&q_full[qs], qph)) { ok = false; break; }
+            const uint64_t dQt = dQ + (((qs * QT + t) * kTileBytes) >> 4);
+            for (uint32_t j = 0; ok && j < u.nkv; ++j, ++g, ++gt) {
+                const uint32_t st = g % KV_STAGES, ph = (g / KV_STAGES) & 1;
+                if (!mbar_wait(&s_empty[t], (gt & 1) ^ 1) || !mbar_wait(&k_full[st], ph)) { ok = false; break; }
+                tc_fence_after();
+                if (elect_one()) {
+                    const uint64_t dKs = dK + ((st * kTileBytes) >> 4);
+#pragma unroll
+                    for (int kk = 0; kk < D / 16; ++kk)
+                        umma_f16(tS, dQt + ((kk * 32) >> 4), dKs + ((kk * 32) >> 4), idesc_qk, kk != 0);
+                    umma_commit(&s_full[t]);
+                    umma_commit(&k_empty[st]);
+                    if (j + 1 == u.nkv) umma_commit(&q_empty[qs]);
+                }
+                __syncwarp();
+                if (pending) issue_pv();
+                pv_st = st; pv_ph = ph; pv_gt = gt; pv_acc = j != 0u;
+                pending = true;
+            }
+        }
+        if (ok && pending) issue_pv();
+        if (!ok && lane == 0) kstatus_set(p.status, FE2O3_KSTATUS_WAIT_EXPIRED);
+    } else if (warp == 3) {
+        // idle: keeps the softmax warps at four per scheduler and their TMEM quadrant equal to warp % 4
     } else {
         // ---------------------------------------------------------- softmax warps
-        const uint32_t t = (warp - 2) / 4;          // query tile of this warp
-        const uint32_t quad = warp & 3;             // TMEM lane quadrant
-        const uint32_t r = quad * 32 + lane;        // row inside the tile
-        const uint32_t qrow = q0 + t * BQ + r;      // query index inside the head
+        constexpr int NCH = BKV / 32;                       // 32-column chunks of the score row
+        const uint32_t sw = warp - 4;                       // 0 .. 4*QT-1
+        const uint32_t t = sw / 4;                          // query tile of this warp
+        const uint32_t quad = warp & 3;                     // TMEM lane quadrant this warp may access
+        const uint32_t r = quad * 32 + lane;                // row inside the tile
         const uint32_t lane_addr = (quad * 32u) << 16;
         const uint32_t tS = tmem_base + t * BKV + lane_addr;
         const uint32_t tO = tmem_base + kColO + t * D + lane_addr;
         const uint32_t tP = tmem_base + kColP + t * (BKV / 2) + lane_addr;
         const float c = p.scale_log2;
-        float m_ref = -INFINITY;   // exponent offset, in raw score units
-        float l = 0.0f;
+        auto wait_all = [&](uint64_t *bar, uint32_t parity) { return __all_sync(0xffffffffu, mbar_wait(bar, parity)) != 0; };
         bool ok = true;
+        uint32_t gt = 0;             // key blocks this tile has processed, over all units
+        uint32_t n = 0;              // units with keys seen so far (selects the Q stage)
+        Unit u;
+        for (uint32_t ui = 0; ok && unit_at(p, ui, u); ++ui) {
+            if (u.nkv == 0) continue;
+            const uint32_t qs = n % Q_STAGES;
+            ++n;
+            if (t >= u.nt) continue;
+            const uint32_t qrow = u.q0 + t * BQ + r;   // query index inside the head
+            float m_ref = -INFINITY;   // exponent offset, in raw score units
+            float l = 0.0f;            // running denominator
 
-        for (uint32_t j = 0; j < nkv; ++j) {
-            if (!mbar_wait(&s_full[t], j & 1)) { ok = false; break; }
-            tc_fence_after();
-            // the whole score row into registers, then S is free for the next Q*K^T
-            uint32_t s0[32], s1[32], s2[32], s3[32];
-            tmem_ld_32x32b_x32(tS, s0);
-            tmem_ld_32x32b_x32(tS + 32, s1);
-            tmem_ld_32x32b_x32(tS + 64, s2);
-            tmem_ld_32x32b_x32(tS + 96, s3);
-            tmem_ld_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&s_empty[t]);
-
-            const uint32_t key0 = j * BKV;
-            const bool need_mask = (key0 + BKV > p.seq) || (p.causal && key0 + BKV - 1 > q0 + t * BQ);
-            if (need_mask) {
-                auto mask32 = [&](uint32_t (&s)[32], uint32_t base) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const uint32_t key = base + i;
-                        const bool valid = key < p.seq && (!p.causal || key <= qrow);
-                        if (!valid) s[i] = 0xff800000u;  // -inf
-                    }
-                };
-                mask32(s0, key0);
-                mask32(s1, key0 + 32);
-                mask32(s2, key0 + 64);
-                mask32(s3, key0 + 96);
-            }
-            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                mx0 = fmaxf(mx0, __uint_as_float(s0[i]));
-                mx1 = fmaxf(mx1, __uint_as_float(s1[i]));
-                mx2 = fmaxf(mx2, __uint_as_float(s2[i]));
-                mx3 = fmaxf(mx3, __uint_as_float(s3[i]));
-            }
-            const float rowmax = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-            // move the reference only when the block maximum outgrows it by more than the threshold
-            const bool move = (rowmax - m_ref) * c > kRescaleThreshold;  // true for the first admitted key (m_ref = -inf)
-            const float factor = move ? ex2_approx((m_ref - rowmax) * c) : 1.0f;  // 0 when m_ref = -inf
-            if (move) m_ref = rowmax;
-            // p = 2^(s*c - m_ref*c); a row with no admitted key so far keeps m_ref = -inf: use offset 0, p = 0
-            const float mc = (m_ref == -INFINITY ? 0.0f : m_ref) * c;
-            // The two tiles share the exponential unit: tile 1 starts its first exponential phase when
-            // tile 0 has finished its own, so that afterwards one tile's exponentials overlap the other
-            // tile's loads, maxima and stores instead of competing with them.
-            if (j == 0 && t == 1 && !mbar_wait(stagger, 0)) { ok = false; break; }
-            float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
-            // exponentials stay in registers as packed bf16 pairs until the P buffer is free
-            auto exp32 = [&](const uint32_t (&s)[32], uint32_t (&pk)[16]) {
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    float e[8];
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) e[i] = ex2_approx(fmaf(__uint_as_float(s[q * 8 + i]), c, -mc));
-                    sum0 += e[0] + e[4];
-                    sum1 += e[1] + e[5];
-                    sum2 += e[2] + e[6];
-                    sum3 += e[3] + e[7];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) pk[q * 4 + i] = pack_bf16x2(e[2 * i], e[2 * i + 1]);
-                }
-            };
-            uint32_t pk0[16], pk1[16], pk2[16], pk3[16];
-            exp32(s0, pk0);
-            exp32(s1, pk1);
-            exp32(s2, pk2);
-            exp32(s3, pk3);
-            if (j == 0 && t == 0) {
-                __syncwarp();
-                if (lane == 0) mbar_arrive(stagger);
-            }
-            // P of the previous block must have been consumed and O must be quiescent
-            if (j > 0) {
-                if (!mbar_wait(&pv_done[t], (j - 1) & 1)) { ok = false; break; }
+            for (uint32_t j = 0; j < u.nkv; ++j, ++gt) {
+                if (!wait_all(&s_full[t], gt & 1)) { ok = false; break; }
                 tc_fence_after();
-                if (__any_sync(0xffffffffu, move)) {
-#pragma unroll 1
-                    for (int h = 0; h < D / 8; ++h) {
-                        uint32_t ov[8];
-                        tmem_ld_32x32b_x8(tO + h * 8, ov);
-                        tmem_ld_wait();
+                // the score row into registers, then S is free for the next Q*K^T
+                uint32_t s[NCH][32];
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * factor);
-                        tmem_st_32x32b_x8(tO + h * 8, ov);
+                for (int ch = 0; ch < NCH; ++ch) tmem_ld_32x32b_x32(tS + ch * 32, s[ch]);
+                tmem_ld_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&s_empty[t]);
+
+                const uint32_t key0 = j * BKV;
+                const bool need_mask = (key0 + BKV > p.seq) || (p.causal && key0 + BKV - 1 > u.q0 + t * BQ);
+                if (need_mask) {
+#pragma unroll
+                    for (int ch = 0; ch < NCH; ++ch) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const uint32_t key = key0 + ch * 32 + i;
+                            const bool valid = key < p.seq && (!p.causal || key <= qrow);
+                            if (!valid) s[ch][i] = 0xff800000u;  // -inf
+                        }
                     }
-                    tmem_st_wait();
+                }
+                float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int ch = 0; ch < NCH; ++ch) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q)
+                            mx[q] = max3(mx[q], __uint_as_float(s[ch][i + 2 * q]), __uint_as_float(s[ch][i + 2 * q + 1]));
+                    }
+                }
+                const float rowmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+                // move the reference only when the block maximum outgrows it by more than the threshold
+                const bool move = (rowmax - m_ref) * c > kRescaleThreshold;  // true for the first admitted key (m_ref = -inf)
+                const float factor = move ? ex2_approx((m_ref - rowmax) * c) : 1.0f;  // 0 when m_ref = -inf
+                if (move) m_ref = rowmax;
+                // p = 2^(s*c - m_ref*c); a row with no admitted key so far keeps m_ref = -inf: use offset 0, p = 0
+                const float mc = (m_ref == -INFINITY ? 0.0f : m_ref) * c;
+                // The two tiles share the exponential unit: tile 1 starts its first exponential phase when
+                // tile 0 has finished its own, so that afterwards one tile's exponentials overlap the other
+                // tile's loads, maxima and stores instead of competing with them.
+                if (gt == 0 && t == 1 && u.nt == QT && !wait_all(stagger, 0)) { ok = false; break; }
+                // Exponentials stay in registers as packed bf16 pairs until the P buffer is free.  The scale
+                // and the sums run as packed pairs of f32.  P is cut to bf16 by truncation, which one byte
+                // permute does for two values; the exponent carries a bias of log2(1 + 2^-9) so that the
+                // truncation error is centred on zero like a rounding error, and the bias (also present in
+                // the sums) is divided out with the denominator at the end.
+                const float mcb = mc - kTruncBiasLog2;
+                const uint64_t c2 = pack_f32x2(c, c), nmc2 = pack_f32x2(-mcb, -mcb);
+                uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};   // four pairs of +0.0f
+                uint32_t pk[NCH][16];
+#pragma unroll
+                for (int ch = 0; ch < NCH; ++ch) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        float e[8];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const uint64_t x2 = fma_f32x2(
+                                pack_f32x2(__uint_as_float(s[ch][q * 8 + 2 * i]), __uint_as_float(s[ch][q * 8 + 2 * i + 1])), c2, nmc2);
+                            float x0, x1;
+                            unpack_f32x2(x2, x0, x1);
+                            e[2 * i] = ex2_approx(x0);
+                            e[2 * i + 1] = ex2_approx(x1);
+                        }
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) sum2[i] = add_f32x2(sum2[i], pack_f32x2(e[2 * i], e[2 * i + 1]));
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            pk[ch][q * 4 + i] = __byte_perm(__float_as_uint(e[2 * i]), __float_as_uint(e[2 * i + 1]), 0x7632);
+                    }
+                }
+                float sum[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    float lo, hi;
+                    unpack_f32x2(sum2[i], lo, hi);
+                    sum[i] = lo + hi;
+                }
+                if (gt == 0 && t == 0) {
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(stagger);
+                }
+                // P of the previous block must have been consumed and O must be quiescent
+                if (j > 0) {
+                    if (!wait_all(&pv_done[t], (gt - 1) & 1)) { ok = false; break; }
+                    tc_fence_after();
+                    if (__any_sync(0xffffffffu, move)) {
+#pragma unroll 1
+                        for (int g = 0; g < D / 8; ++g) {
+                            uint32_t ov[8];
+                            tmem_ld_32x32b_x8(tO + g * 8, ov);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * factor);
+                            tmem_st_32x32b_x8(tO + g * 8, ov);
+                        }
+                    }
+                }
+                l = fmaf(l, factor, (sum[0] + sum[1]) + (sum[2] + sum[3]));
+                // P as packed bf16 pairs into tensor memory: 16 columns per 32 keys
+#pragma unroll
+                for (int ch = 0; ch < NCH; ++ch) tmem_st_32x32b_x16(tP + ch * 16, pk[ch]);
+                tmem_st_wait();
+                // publish P and any O rescale (both TMEM stores) to the MMA issuer
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&p_ready[t]);
+            }
+            if (!ok) break;
+            if (!wait_all(&pv_done[t], (gt - 1) & 1)) { ok = false; break; }
+            tc_fence_after();
+            // Output.  The unit's Q tile is dead once its last Q*K^T has completed (the s_full wait above
+            // proved that), so this warp stages its 32 rows, 32 columns at a time, in its 4 KiB slice of
+            // that tile (128-byte swizzle, so the 16-byte writes of a warp spread over all banks) and hands
+            // them to the copy engine: full-line writes that do not hold the warp.  The Q stage is given
+            // back to the producer when the copies have read the slice.
+            const float inv = kTruncGain / l;   // the sums carry the gain of the truncation bias
+            bool finite = isfinite(l) && l > 0.0f;
+            uint8_t *slice = smem + kOffQ + (qs * QT + t) * kTileBytes + quad * 4096;
+            const uint32_t row0 = u.q0 + t * BQ + quad * 32;   // first query row of this warp
+#pragma unroll
+            for (int g = 0; g < D / 32; ++g) {
+                uint32_t ov[32];
+                tmem_ld_32x32b_x32(tO + g * 32, ov);  // every lane takes part in the collective load
+                tmem_ld_wait();
+                float o[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    o[i] = __uint_as_float(ov[i]) * inv;
+                    finite = finite && isfinite(o[i]);
+                }
+                if (g > 0) {
+                    if (lane == 0) tma_store_wait_read();   // the slice is still being read by the previous copy
+                    __syncwarp();
+                }
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                    *reinterpret_cast<float4 *>(slice + lane * 128 + ((k ^ (lane & 7)) * 16)) =
+                        make_float4(o[4 * k], o[4 * k + 1], o[4 * k + 2], o[4 * k + 3]);
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0 && row0 < p.seq) {   // rows beyond seq are clipped by the copy engine
+                    tma_store_3d(&tmO, slice, g * 32, (int32_t)row0, (int32_t)u.head);
+                    tma_store_commit();
                 }
             }
-            l = fmaf(l, factor, (sum0 + sum1) + (sum2 + sum3));
-            // P as packed bf16 pairs into tensor memory: 16 columns per 32 keys
-            tmem_st_32x32b_x16(tP, pk0);
-            tmem_st_32x32b_x16(tP + 16, pk1);
-            tmem_st_32x32b_x16(tP + 32, pk2);
-            tmem_st_32x32b_x16(tP + 48, pk3);
-            tmem_st_wait();
-            // publish P and any O rescale (both TMEM stores) to the MMA issuer
+            // finite-input policy: a non-finite result is reported through the status word
+            if (!finite && qrow < p.seq) kstatus_set(p.status, FE2O3_KSTATUS_NONFINITE);
+            if (lane == 0) {
+                tma_store_wait_read();
+                mbar_arrive(&q_empty[qs]);
+            }
+            // the next unit's first P*V overwrites O: order this thread's reads of O before its p_ready arrival
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&p_ready[t]);
         }
-        if (ok && nkv > 0 && !mbar_wait(&pv_done[t], (nkv - 1) & 1)) ok = false;
-        if (!ok) {
-            if (lane == 0) kstatus_set(p.status, FE2O3_KSTATUS_WAIT_EXPIRED);
-        } else if (nkv > 0) {
-            tc_fence_after();
-            const float inv = 1.0f / l;
-            bool finite = isfinite(l) && l > 0.0f;
-            float *dst = p.out + ((uint64_t)head * p.seq + qrow) * D;
-            uint32_t ov[D];
-            {
-                uint32_t (&o0)[32] = *reinterpret_cast<uint32_t (*)[32]>(&ov[0]);
-                uint32_t (&o1)[32] = *reinterpret_cast<uint32_t (*)[32]>(&ov[32]);
-                tmem_ld_32x32b_x32(tO, o0);  // every lane takes part in the collective loads
-                tmem_ld_32x32b_x32(tO + 32, o1);
-                tmem_ld_wait();
-            }
-            float o[D];
-#pragma unroll
-            for (int i = 0; i < D; ++i) {
-                o[i] = __uint_as_float(ov[i]) * inv;
-                finite = finite && isfinite(o[i]);
-            }
-            // finite-input policy: a row with a non-finite result is left unwritten and reported
-            if (qrow < p.seq) {
-                if (!finite) {
-                    kstatus_set(p.status, FE2O3_KSTATUS_NONFINITE);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < D / 4; ++i)
-                        reinterpret_cast<float4 *>(dst)[i] = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
-                }
-            }
-        }
+        if (!ok && lane == 0) kstatus_set(p.status, FE2O3_KSTATUS_WAIT_EXPIRED);
     }
     tc_fence_before();
     __syncthreads();
@@ -369,7 +481,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 }  // namespace
 
 struct AttnTcPlan {
-    CUtensorMap tmQ, tmK, tmV;
+    CUtensorMap tmQ, tmK, tmV, tmO;
     AttnParams p;
     uint32_t grid;
 };
@@ -389,10 +501,34 @@ int32_t attention_tc_plan(fe2o3_ctx *ctx, const fe2o3_flash_attention_v1_args *a
     int32_t st = fe2o3_make_tmap_bf16(&plan->tmQ, a->q.ptr, 3, dims, strides, box);
     if (st == FE2O3_OK) st = fe2o3_make_tmap_bf16(&plan->tmK, a->k.ptr, 3, dims, strides, box);
     if (st == FE2O3_OK) st = fe2o3_make_tmap_bf16(&plan->tmV, a->v.ptr, 3, dims, strides, box);
+    if (st == FE2O3_OK) {
+        // output: f32 [bh][seq][64], stored in boxes of 32 rows x 32 columns (128 bytes per row)
+        uint64_t ostrides[2] = {D * 4, (uint64_t)a->seq * D * 4};
+        uint32_t obox[3] = {32, 32, 1};
+        st = fe2o3_make_tmap_f32(&plan->tmO, a->output.ptr, 3, dims, ostrides, obox);
+    }
     if (st != FE2O3_OK) { delete plan; return st; }
+    // Schedule: one CTA per SM; full rounds of two-tile units, and a last partial round that is split
+    // into single tiles when that keeps every tile on its own CTA.
+    const uint32_t q_blocks = (a->seq + QT * BQ - 1) / (QT * BQ);
+    const uint32_t units = bh * q_blocks;
+    const uint32_t sms = ctx->sm_count > 0 ? (uint32_t)ctx->sm_count : 1u;
+    uint32_t grid, n_full = units, n_half = 0;
+    if (2 * units <= sms) {
+        grid = 2 * units;
+        n_full = 0;
+        n_half = 2 * units;
+    } else {
+        grid = units < sms ? units : sms;
+        const uint32_t rem = units % grid;
+        if (rem != 0 && 2 * rem <= grid) {
+            n_full = units - rem;
+            n_half = 2 * rem;
+        }
+    }
     plan->p = AttnParams{reinterpret_cast<float *>(a->output.ptr), bh, a->seq, a->scale * 1.4426950408889634f, a->causal,
-                         ctx->status_word};
-    plan->grid = bh * ((a->seq + QT * BQ - 1) / (QT * BQ));
+                         q_blocks, n_full, n_half, ctx->status_word};
+    plan->grid = grid;
     *out = plan;
     return FE2O3_OK;
 }
@@ -403,7 +539,7 @@ int32_t attention_tc_launch(const AttnTcPlan *plan, cudaStream_t s) {
         cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTotal);
     });
     if (plan->grid == 0) return FE2O3_OK;
-    attention_tc_kernel<<<plan->grid, kThreads, kSmemTotal, s>>>(plan->tmQ, plan->tmK, plan->tmV, plan->p);
+    attention_tc_kernel<<<plan->grid, kThreads, kSmemTotal, s>>>(plan->tmQ, plan->tmK, plan->tmV, plan->tmO, plan->p);
     fe2o3_count_launch(1);
     return fe2o3_cuda_status(cudaGetLastError(), "flash_attention_v1(tcgen05)");
 }

@@ -305,10 +305,10 @@ EncodeTiledFn encode_fn() {
 
 }  // namespace
 
-// Encodes a bf16 tensor map with 128-byte swizzle.  dims/strides innermost first;
+// Encodes a tensor map with 128-byte swizzle.  dims/strides innermost first;
 // strides in bytes for dimensions 1..rank-1.
-int32_t fe2o3_make_tmap_bf16(CUtensorMap *out, uint64_t base, uint32_t rank, const uint64_t *dims,
-                             const uint64_t *strides_bytes, const uint32_t *box) {
+static int32_t make_tmap(CUtensorMap *out, CUtensorMapDataType dtype, uint64_t base, uint32_t rank, const uint64_t *dims,
+                         const uint64_t *strides_bytes, const uint32_t *box) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) {
         fe2o3_set_error("cuTensorMapEncodeTiled is not available from the driver");
@@ -319,7 +319,7 @@ int32_t fe2o3_make_tmap_bf16(CUtensorMap *out, uint64_t base, uint32_t rank, con
     cuuint32_t b[5], es[5];
     for (uint32_t i = 0; i < rank; ++i) { d[i] = dims[i]; b[i] = box[i]; es[i] = 1; }
     for (uint32_t i = 0; i + 1 < rank; ++i) st[i] = strides_bytes[i];
-    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, reinterpret_cast<void *>(base), d, st, b, es,
+    CUresult r = fn(out, dtype, rank, reinterpret_cast<void *>(base), d, st, b, es,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
@@ -327,6 +327,15 @@ int32_t fe2o3_make_tmap_bf16(CUtensorMap *out, uint64_t base, uint32_t rank, con
         return FE2O3_ERR_INVALID_ARGUMENT;
     }
     return FE2O3_OK;
+}
+
+int32_t fe2o3_make_tmap_bf16(CUtensorMap *out, uint64_t base, uint32_t rank, const uint64_t *dims,
+                             const uint64_t *strides_bytes, const uint32_t *box) {
+    return make_tmap(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, base, rank, dims, strides_bytes, box);
+}
+int32_t fe2o3_make_tmap_f32(CUtensorMap *out, uint64_t base, uint32_t rank, const uint64_t *dims,
+                            const uint64_t *strides_bytes, const uint32_t *box) {
+    return make_tmap(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, base, rank, dims, strides_bytes, box);
 }
 
 // The tensor-core schedule needs 16-byte aligned bases and leading dimensions

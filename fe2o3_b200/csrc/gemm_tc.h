@@ -28,6 +28,8 @@ struct GemmTcPlan {
 
 int32_t fe2o3_make_tmap_bf16(CUtensorMap *out, uint64_t base, uint32_t rank, const uint64_t *dims,
                              const uint64_t *strides_bytes, const uint32_t *box);
+int32_t fe2o3_make_tmap_f32(CUtensorMap *out, uint64_t base, uint32_t rank, const uint64_t *dims,
+                            const uint64_t *strides_bytes, const uint32_t *box);
 bool gemm_tc_supported(uint64_t a, uint64_t b, uint32_t lda, uint32_t ldb, uint32_t K);
 int32_t gemm_tc_plan(fe2o3_ctx *ctx, GemmTcPlan *plan, uint64_t a, uint64_t b, uint64_t c, uint32_t M, uint32_t N,
                      uint32_t K, uint32_t lda, uint32_t ldb, uint32_t ldc, float alpha, float beta, uint32_t epilogue,
