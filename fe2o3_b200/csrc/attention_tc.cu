@@ -163,7 +163,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             if (u.nkv == 0) continue;   // every role skips a unit without keys (rows beyond seq)
             const uint32_t qs = n_units % Q_STAGES, qph = (n_units / Q_STAGES) & 1;
             ++n_units;
-            if (!mbar_wait(&q_empty[qs], qph ^ 1)) { ok = false; break; }
+            if (!mbar_wait_warp(&q_empty[qs], qph ^ 1)) { ok = false; break; }
             if (elect_one()) {
                 mbar_arrive_expect_tx(&q_full[qs], u.nt * kTileBytes);
                 for (uint32_t t = 0; t < u.nt; ++t)
@@ -173,15 +173,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             __syncwarp();
             for (uint32_t j = 0; j < u.nkv; ++j, ++g) {
                 const uint32_t st = g % KV_STAGES, ph = (g / KV_STAGES) & 1;
-                if (!mbar_wait(&k_empty[st], ph ^ 1)) { ok = false; break; }
+                if (!mbar_wait_warp(&k_empty[st], ph ^ 1)) { ok = false; break; }
                 if (elect_one()) {
                     mbar_arrive_expect_tx(&k_full[st], kTileBytes);
                     tma_load_3d(smem + kOffK + st * kTileBytes, &tmK, &k_full[st], 0, (int32_t)(j * BKV), (int32_t)u.head);
                 }
                 __syncwarp();
-                if (!mbar_wait(&v_empty[st], ph ^ 1)) {
+                if (!mbar_wait_warp(&v_empty[st], ph ^ 1)) {
                     ok = false;
-                    mbar_wait(&k_full[st], ph);   // the K copy just issued must land before the CTA exits
+                    mbar_wait_warp(&k_full[st], ph);   // the K copy just issued must land before the CTA exits
                     break;
                 }
                 if (elect_one()) {
@@ -195,12 +195,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         // drain the copies before the CTA can exit: the newest phase of every ring slot in use
         for (uint32_t b = 0; b < KV_STAGES && b < g; ++b) {
             const uint32_t last = g - 1 - b, st = last % KV_STAGES, ph = (last / KV_STAGES) & 1;
-            mbar_wait(&k_full[st], ph);
-            mbar_wait(&v_full[st], ph);
+            mbar_wait_warp(&k_full[st], ph);
+            mbar_wait_warp(&v_full[st], ph);
         }
         for (uint32_t b = 0; b < Q_STAGES && b < n_units; ++b) {
             const uint32_t last = n_units - 1 - b;
-            mbar_wait(&q_full[last % Q_STAGES], (last / Q_STAGES) & 1);
+            mbar_wait_warp(&q_full[last % Q_STAGES], (last / Q_STAGES) & 1);
         }
     } else if (warp == 1 || warp == 2) {
         // ---------------------------------------------------------- MMA issuers, one warp per query tile
@@ -224,7 +224,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         bool pending = false;                       // a P*V whose Q*K^T successor has been issued (or has none)
         uint32_t pv_st = 0, pv_ph = 0, pv_gt = 0, pv_acc = 0;
         auto issue_pv = [&]() {
-            if (!mbar_wait(&p_ready[t], pv_gt & 1) || !mbar_wait(&v_full[pv_st], pv_ph)) { ok = false; return; }
+            if (!mbar_wait_warp(&p_ready[t], pv_gt & 1) || !mbar_wait_warp(&v_full[pv_st], pv_ph)) { ok = false; return; }
             tc_fence_after();
             if (elect_one()) {
                 const uint64_t dVs = dV + ((pv_st * kTileBytes) >> 4);
@@ -247,20 +247,20 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 if (pending) issue_pv();
                 for (uint32_t j = 0; ok && j < u.nkv; ++j, ++g) {
                     const uint32_t st = g % KV_STAGES, ph = (g / KV_STAGES) & 1;
-                    if (!mbar_wait(&k_full[st], ph)) { ok = false; break; }
+                    if (!mbar_wait_warp(&k_full[st], ph)) { ok = false; break; }
                     if (lane == 0) mbar_arrive(&k_empty[st]);
-                    if (!mbar_wait(&v_full[st], ph)) { ok = false; break; }
+                    if (!mbar_wait_warp(&v_full[st], ph)) { ok = false; break; }
                     if (lane == 0) mbar_arrive(&v_empty[st]);
                 }
-                if (ok && !mbar_wait(&q_full[qs], qph)) ok = false;
+                if (ok && !mbar_wait_warp(&q_full[qs], qph)) ok = false;
                 if (ok && lane == 0) mbar_arrive_n(&q_empty[qs], 1 + 4);   // for the absent tile's issuer and softmax warps
                 continue;
             }
-            if (!mbar_wait(&q_full[qs], qph)) { ok = false; break; }
+            if (!mbar_wait_warp(&q_full[qs], qph)) { ok = false; break; }
             const uint64_t dQt = dQ + (((qs * QT + t) * kTileBytes) >> 4);
             for (uint32_t j = 0; ok && j < u.nkv; ++j, ++g, ++gt) {
                 const uint32_t st = g % KV_STAGES, ph = (g / KV_STAGES) & 1;
-                if (!mbar_wait(&s_empty[t], (gt & 1) ^ 1) || !mbar_wait(&k_full[st], ph)) { ok = false; break; }
+                if (!mbar_wait_warp(&s_empty[t], (gt & 1) ^ 1) || !mbar_wait_warp(&k_full[st], ph)) { ok = false; break; }
                 tc_fence_after();
                 if (elect_one()) {
                     const uint64_t dKs = dK + ((st * kTileBytes) >> 4);
@@ -293,7 +293,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const uint32_t tO = tmem_base + kColO + t * D + lane_addr;
         const uint32_t tP = tmem_base + kColP + t * (BKV / 2) + lane_addr;
         const float c = p.scale_log2;
-        auto wait_all = [&](uint64_t *bar, uint32_t parity) { return __all_sync(0xffffffffu, mbar_wait(bar, parity)) != 0; };
         bool ok = true;
         uint32_t gt = 0;             // key blocks this tile has processed, over all units
         uint32_t n = 0;              // units with keys seen so far (selects the Q stage)
@@ -308,7 +307,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             float l = 0.0f;            // running denominator
 
             for (uint32_t j = 0; j < u.nkv; ++j, ++gt) {
-                if (!wait_all(&s_full[t], gt & 1)) { ok = false; break; }
+                if (!mbar_wait_warp(&s_full[t], gt & 1)) { ok = false; break; }
                 tc_fence_after();
                 // the score row into registers, then S is free for the next Q*K^T
                 uint32_t s[NCH][32];
@@ -352,7 +351,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 // The two tiles share the exponential unit: tile 1 starts its first exponential phase when
                 // tile 0 has finished its own, so that afterwards one tile's exponentials overlap the other
                 // tile's loads, maxima and stores instead of competing with them.
-                if (gt == 0 && t == 1 && u.nt == QT && !wait_all(stagger, 0)) { ok = false; break; }
+                if (gt == 0 && t == 1 && u.nt == QT && !mbar_wait_warp(stagger, 0)) { ok = false; break; }
                 // Exponentials stay in registers as packed bf16 pairs until the P buffer is free.  The scale
                 // and the sums run as packed pairs of f32.  P is cut to bf16 by truncation, which one byte
                 // permute does for two values; the exponent carries a bias of log2(1 + 2^-9) so that the
@@ -396,7 +395,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 }
                 // P of the previous block must have been consumed and O must be quiescent
                 if (j > 0) {
-                    if (!wait_all(&pv_done[t], (gt - 1) & 1)) { ok = false; break; }
+                    if (!mbar_wait_warp(&pv_done[t], (gt - 1) & 1)) { ok = false; break; }
                     tc_fence_after();
                     if (__any_sync(0xffffffffu, move)) {
 #pragma unroll 1
@@ -421,7 +420,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 if (lane == 0) mbar_arrive(&p_ready[t]);
             }
             if (!ok) break;
-            if (!wait_all(&pv_done[t], (gt - 1) & 1)) { ok = false; break; }
+            if (!mbar_wait_warp(&pv_done[t], (gt - 1) & 1)) { ok = false; break; }
             tc_fence_after();
             // Output.  The unit's Q tile is dead once its last Q*K^T has completed (the s_full wait above
             // proved that), so this warp stages its 32 rows, 32 columns at a time, in its 4 KiB slice of

@@ -130,6 +130,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
     }
     return false;
 }
+// The same wait for a role that keeps its whole warp converged: every lane polls and the verdict is
+// made warp-uniform, so no lane can leave the role's loop while the others go on to a warp-wide
+// instruction (elect, __syncwarp, a collective TMEM load).
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t *bar, uint32_t parity) {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity)) != 0;
+}
 // Arrival with a count: stands in for `n` parties at once.
 __device__ __forceinline__ void mbar_arrive_n(uint64_t *bar, uint32_t n) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(n) : "memory");
@@ -147,6 +153,12 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap *m, const void *s
     asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
                      reinterpret_cast<uint64_t>(m)),
                  "r"(smem_u32(src)), "r"(x), "r"(y), "r"(z)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *m, const void *src, int32_t x, int32_t y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                     reinterpret_cast<uint64_t>(m)),
+                 "r"(smem_u32(src)), "r"(x), "r"(y)
                  : "memory");
 }
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }

@@ -13,9 +13,10 @@
 // A CTA owns a 128 x BN output tile; one K block is 64 bf16 = 128 bytes.
 //   A stage: one TMA box {64 k, 128 rows}  -> 128 rows x 128 B, 8-row groups 1 KiB apart
 //   B stage: BN/64 TMA boxes {64 n, 64 k}   -> per box 64 k-rows x 128 B (8 KiB)
-// Persistent CTAs (one per SM) walk a static tile list; six warps:
+// Persistent CTAs (one per SM) walk a static tile list; ten warps:
 //   warp 0  TMA producer (one lane)        warp 1  MMA issuer (one lane) + TMEM owner
-//   warps 2-5  epilogue: TMEM -> registers -> global, one TMEM lane quadrant each
+//   warps 2-9  epilogue: TMEM -> registers -> shared memory -> bulk tensor store,
+//              two warps per TMEM lane quadrant, half of the tile's columns each
 // Two accumulator buffers in TMEM let the epilogue of tile i overlap the main
 // loop of tile i+1.  Every wait is bounded: on expiry the kernel records
 // FE2O3_KSTATUS_WAIT_EXPIRED, drains its own copies and returns.
@@ -29,7 +30,8 @@ constexpr int BM = 128;
 constexpr int BK = 64;          // bf16 elements per K block (128 bytes)
 constexpr int UMMA_K = 16;
 constexpr int kStages = 4;
-constexpr int kThreads = 192;
+constexpr int kEpilogueWarps = 8;
+constexpr int kThreads = 32 * (2 + kEpilogueWarps);
 constexpr int kGroupM = 16;     // m-tiles per rasterisation band (keeps a wave's A and B panels in L2)
 
 template <int BN>
@@ -37,7 +39,8 @@ struct SmemLayout {
     static constexpr uint32_t kABytes = BM * BK * 2;
     static constexpr uint32_t kBBytes = BN * BK * 2;
     static constexpr uint32_t kStageBytes = kABytes + kBBytes;
-    static constexpr uint32_t kBarOffset = kStages * kStageBytes;
+    static constexpr uint32_t kStagingOffset = kStages * kStageBytes;          // 4 KiB output slice per epilogue warp
+    static constexpr uint32_t kBarOffset = kStagingOffset + kEpilogueWarps * 4096;
     static constexpr uint32_t kTotal = kBarOffset + 256 + 1024;  // barriers + alignment slack
 };
 
@@ -53,6 +56,7 @@ __device__ __forceinline__ TileCoord decode_tile(uint32_t id, const GemmParams &
     TileCoord t;
     t.valid = false;
     t.expert = 0;
+    t.m0 = t.n0 = t.m_end = 0;
     if (p.experts == 0) {
         const uint32_t m_tiles = (p.M + BM - 1) / BM;
         if (id >= m_tiles * n_tiles) return t;
@@ -76,22 +80,51 @@ __device__ __forceinline__ TileCoord decode_tile(uint32_t id, const GemmParams &
             t.m0 = s_off[e] + (local % mt) * BM;
             t.n0 = local / mt;
             t.m_end = s_off[e + 1];
-            t.expert = e;
+            t.expert = p.expert_mod ? e % p.expert_mod : e;   // index of the B matrix
             t.valid = true;
-            return t;
+            break;
         }
         base += cnt;
     }
+    // The offsets come from shared memory, which the compiler must treat as lane-varying.  Every lane
+    // of the (converged) calling warp holds the same values; taking them from lane 0 lets the TMA
+    // coordinates live in uniform registers instead of being made uniform instruction by instruction
+    // (that made the producer, not the tensor pipe, set the pace of the grouped GEMMs).
+    t.m0 = __shfl_sync(0xffffffffu, t.m0, 0);
+    t.n0 = __shfl_sync(0xffffffffu, t.n0, 0);
+    t.m_end = __shfl_sync(0xffffffffu, t.m_end, 0);
+    t.expert = __shfl_sync(0xffffffffu, t.expert, 0);
+    t.valid = __shfl_sync(0xffffffffu, (uint32_t)t.valid, 0) != 0;
     return t;
 }
 
+// erf by Abramowitz & Stegun 7.1.26 (absolute error below 1.5e-7, far under the bf16 step of the
+// hidden activations this feeds): one reciprocal, one exp2 and a degree-5 polynomial, no branches.
 __device__ __forceinline__ float gelu_erf(float x) {
-    return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));
+    const float z = fabsf(x) * 0.70710678118654752440f;
+    float t;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fmaf(0.3275911f, z, 1.0f)));
+    float poly = fmaf(t, 1.061405429f, -1.453152027f);
+    poly = fmaf(poly, t, 1.421413741f);
+    poly = fmaf(poly, t, -0.284496736f);
+    poly = fmaf(poly, t, 0.254829592f);
+    poly *= t;
+    const float erf_abs = fmaf(-poly, ex2_approx(-1.4426950408889634f * z * z), 1.0f);
+    const float half_x = 0.5f * x;
+    return fmaf(half_x, copysignf(erf_abs, x), half_x);
+}
+
+// Two f32 to packed bf16, round to nearest even (hardware conversion; lo in the lower half).
+__device__ __forceinline__ uint32_t cvt_bf16x2(float lo, float hi) {
+    uint32_t d;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    return d;
 }
 
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ CUtensorMap tmC, GemmParams p) {
     using L = SmemLayout<BN>;
     extern __shared__ uint8_t smem_raw[];
     // 128-byte swizzle atoms are 1 KiB: align the tile region.
@@ -116,7 +149,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&tmem_full[i], 1);
-            mbar_init(&tmem_empty[i], 4);
+            mbar_init(&tmem_empty[i], kEpilogueWarps);
         }
         mbar_fence_init();
     }
@@ -133,64 +166,64 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        // ------------------------------------------------ TMA producer
-        if (lane == 0) {
+        // ------------------------------------------------ TMA producer (warp converged, one elected lane issues)
+        if (elect_one()) {
             tma_prefetch_desc(&tmA);
             tma_prefetch_desc(&tmB);
-            uint32_t stage = 0, phase = 0;
-            uint32_t armed[kStages];
-            bool ever[kStages];
-            for (int i = 0; i < kStages; ++i) { armed[i] = 0; ever[i] = false; }
-            bool ok = true;
-            for (uint32_t id = blockIdx.x; ok; id += gridDim.x) {
-                TileCoord t = decode_tile(id, p, n_tiles, s_off);
-                if (!t.valid) break;
-                for (uint32_t kb = 0; kb < num_kb; ++kb) {
-                    if (!mbar_wait(&empty[stage], phase ^ 1)) { ok = false; break; }
+        }
+        __syncwarp();
+        uint32_t stage = 0, phase = 0, loaded = 0;
+        bool ok = true;
+        for (uint32_t id = blockIdx.x; ok; id += gridDim.x) {
+            TileCoord t = decode_tile(id, p, n_tiles, s_off);
+            if (!t.valid) break;
+            for (uint32_t kb = 0; kb < num_kb; ++kb, ++loaded) {
+                if (!mbar_wait_warp(&empty[stage], phase ^ 1)) { ok = false; break; }
+                if (elect_one()) {
                     uint8_t *sa = smem + stage * L::kStageBytes;
                     uint8_t *sb = sa + L::kABytes;
                     mbar_arrive_expect_tx(&full[stage], L::kStageBytes);
-                    armed[stage] = phase;
-                    ever[stage] = true;
                     tma_load_2d(sa, &tmA, &full[stage], (int32_t)(kb * BK), (int32_t)t.m0);
 #pragma unroll
                     for (int j = 0; j < BN / 64; ++j) {
                         if (p.experts)
-                            tma_load_3d(sb + j * 8192, &tmB, &full[stage], (int32_t)(t.n0 * BN + j * 64),
-                                        (int32_t)(kb * BK), (int32_t)(p.expert_mod ? t.expert % p.expert_mod : t.expert));
+                            tma_load_3d(sb + j * 8192, &tmB, &full[stage], (int32_t)(t.n0 * BN + j * 64), (int32_t)(kb * BK),
+                                        (int32_t)t.expert);
                         else
-                            tma_load_2d(sb + j * 8192, &tmB, &full[stage], (int32_t)(t.n0 * BN + j * 64),
-                                        (int32_t)(kb * BK));
+                            tma_load_2d(sb + j * 8192, &tmB, &full[stage], (int32_t)(t.n0 * BN + j * 64), (int32_t)(kb * BK));
                     }
-                    if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
+                __syncwarp();
+                if (++stage == kStages) { stage = 0; phase ^= 1; }
             }
-            if (!ok) {
-                kstatus_set(p.status, FE2O3_KSTATUS_WAIT_EXPIRED);
-                atomicExch(&s_abort, 1);
-            }
-            // Drain: every copy this thread issued must have landed before the CTA exits.
-            for (int i = 0; i < kStages; ++i)
-                if (ever[i]) mbar_wait(&full[i], armed[i]);
+        }
+        if (!ok && lane == 0) {
+            kstatus_set(p.status, FE2O3_KSTATUS_WAIT_EXPIRED);
+            atomicExch(&s_abort, 1);
+        }
+        // Drain: every copy issued must have landed before the CTA exits (the newest phase of each ring slot).
+        for (uint32_t b = 0; b < kStages && b < loaded; ++b) {
+            const uint32_t last = loaded - 1 - b;
+            mbar_wait_warp(&full[last % kStages], (last / kStages) & 1);
         }
     } else if (warp == 1) {
-        // ------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc(1u, BM, BN, 0u, 1u);
-            uint32_t stage = 0, phase = 0, it = 0;
-            bool ok = true;
-            const uint64_t desc_a0 = umma_smem_desc(smem_u32(smem), 16, 1024);
-            const uint64_t desc_b0 = umma_smem_desc(smem_u32(smem) + L::kABytes, 8192, 1024);
-            for (uint32_t id = blockIdx.x; ok; id += gridDim.x, ++it) {
-                TileCoord t = decode_tile(id, p, n_tiles, s_off);
-                if (!t.valid) break;
-                const uint32_t buf = it & 1, acc_phase = (it >> 1) & 1;
-                if (!mbar_wait(&tmem_empty[buf], acc_phase ^ 1)) { ok = false; break; }
+        // ------------------------------------------------ MMA issuer (warp converged, one elected lane issues)
+        constexpr uint32_t idesc = umma_idesc(1u, BM, BN, 0u, 1u);
+        uint32_t stage = 0, phase = 0, it = 0;
+        bool ok = true;
+        const uint64_t desc_a0 = umma_smem_desc(smem_u32(smem), 16, 1024);
+        const uint64_t desc_b0 = umma_smem_desc(smem_u32(smem) + L::kABytes, 8192, 1024);
+        for (uint32_t id = blockIdx.x; ok; id += gridDim.x, ++it) {
+            TileCoord t = decode_tile(id, p, n_tiles, s_off);
+            if (!t.valid) break;
+            const uint32_t buf = it & 1, acc_phase = (it >> 1) & 1;
+            if (!mbar_wait_warp(&tmem_empty[buf], acc_phase ^ 1)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + buf * BN;
+            for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                if (!mbar_wait_warp(&full[stage], phase)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + buf * BN;
-                for (uint32_t kb = 0; kb < num_kb; ++kb) {
-                    if (!mbar_wait(&full[stage], phase)) { ok = false; break; }
-                    tc_fence_after();
+                if (elect_one()) {
                     // only the 16-byte-unit start address field of the descriptors moves
                     const uint64_t adesc = desc_a0 + ((stage * L::kStageBytes) >> 4);
                     const uint64_t bdesc = desc_b0 + ((stage * L::kStageBytes) >> 4);
@@ -201,76 +234,147 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     for (int k = 1; k < BK / UMMA_K; ++k)
                         umma_f16(d_tmem, adesc + ((k * UMMA_K * 2) >> 4), bdesc + ((k * UMMA_K * 128) >> 4), idesc, 1u);
                     umma_commit(&empty[stage]);
-                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                    if (kb + 1 == num_kb) umma_commit(&tmem_full[buf]);
                 }
-                if (!ok) break;
-                umma_commit(&tmem_full[buf]);
+                __syncwarp();
+                if (++stage == kStages) { stage = 0; phase ^= 1; }
             }
-            if (!ok) {
-                kstatus_set(p.status, FE2O3_KSTATUS_WAIT_EXPIRED);
-                atomicExch(&s_abort, 1);
-            }
+        }
+        if (!ok && lane == 0) {
+            kstatus_set(p.status, FE2O3_KSTATUS_WAIT_EXPIRED);
+            atomicExch(&s_abort, 1);
         }
     } else {
         // ------------------------------------------------ epilogue warps
+        // Eight warps: two per TMEM lane quadrant, each taking half of the tile's columns.  A warp
+        // turns 128 bytes of each of its 32 rows at a time (32 f32 or 64 bf16 columns) into a
+        // 128-byte-swizzled 4 KiB slice of shared memory and hands it to the copy engine, so the
+        // global writes are full lines and do not hold the warp; ragged rows, the alpha/beta form and
+        // outputs the copy engine cannot address are written by the threads directly.
+        const uint32_t ew = warp - 2;
         const uint32_t quad = warp & 3;  // TMEM lane quadrant this warp may read
+        const uint32_t col_half = ew >> 2;
+        constexpr int kChunks = BN / 32 / 2;   // 32-column chunks per warp
+        uint8_t *slice = smem + L::kStagingOffset + ew * 4096;
+        const bool out_bf16 = p.epilogue == EPI_GELU_BF16;
         uint32_t it = 0;
         bool ok = true;
+        bool store_pending = false;
         for (uint32_t id = blockIdx.x; ok; id += gridDim.x, ++it) {
             TileCoord t = decode_tile(id, p, n_tiles, s_off);
             if (!t.valid) break;
             const uint32_t buf = it & 1, acc_phase = (it >> 1) & 1;
-            if (!mbar_wait(&tmem_full[buf], acc_phase)) { ok = false; break; }
+            if (!mbar_wait_warp(&tmem_full[buf], acc_phase)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t row = t.m0 + quad * 32 + lane;
+            const uint32_t row0 = t.m0 + quad * 32;
+            const uint32_t row = row0 + lane;
             const bool row_ok = row < t.m_end;
-            const uint32_t col_base = t.n0 * BN;
+            const bool bulk = p.bulk_store && row0 + 32 <= t.m_end;   // warp-uniform
+            const uint32_t col_base = t.n0 * BN + col_half * (BN / 2);
+            const uint32_t taddr = tmem_base + buf * BN + col_half * (BN / 2) + ((quad * 32u) << 16);
+            if (out_bf16) {
+                // ---- GELU, bf16 output: two chunks (64 columns) per 128-byte group
 #pragma unroll 1
-            for (int chunk = 0; chunk < BN / 32; ++chunk) {
-                uint32_t r[32];
-                tmem_ld_32x32b_x32(tmem_base + buf * BN + chunk * 32 + ((quad * 32u) << 16), r);
-                tmem_ld_wait();
-                const uint32_t col = col_base + chunk * 32;
-                if (!row_ok || col >= p.N) continue;
-                if (p.epilogue == EPI_GELU_BF16) {
-                    uint16_t *dst = reinterpret_cast<uint16_t *>(p.c) + (uint64_t)row * p.ldc + col;
-                    if (col + 32 <= p.N && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
+                for (int g = 0; g < kChunks / 2; ++g) {
+                    uint32_t w[32];
 #pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            uint32_t w[4];
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                const uint32_t lo = f32_to_bf16_bits(gelu_erf(__uint_as_float(r[q * 8 + 2 * j])));
-                                const uint32_t hi = f32_to_bf16_bits(gelu_erf(__uint_as_float(r[q * 8 + 2 * j + 1])));
-                                w[j] = lo | (hi << 16);
-                            }
-                            reinterpret_cast<uint4 *>(dst)[q] = make_uint4(w[0], w[1], w[2], w[3]);
+                    for (int c2 = 0; c2 < 2; ++c2) {
+                        uint32_t r[32];
+                        tmem_ld_32x32b_x32(taddr + (g * 2 + c2) * 32, r);
+                        tmem_ld_wait();
+                        if (g == kChunks / 2 - 1 && c2 == 1) {   // the accumulator has been read completely
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(&tmem_empty[buf]);
                         }
-                    } else {
-                        for (int j = 0; j < 32 && col + j < p.N; ++j)
-                            dst[j] = f32_to_bf16_bits(gelu_erf(__uint_as_float(r[j])));
-                    }
-                } else {
-                    float *dst = reinterpret_cast<float *>(p.c) + (uint64_t)row * p.ldc + col;
-                    const bool vec = col + 32 <= p.N && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0);
-                    if (p.epilogue == EPI_ALPHA_BETA) {
-                        for (int j = 0; j < 32 && col + j < p.N; ++j)
-                            dst[j] = __fadd_rn(__fmul_rn(p.alpha, __uint_as_float(r[j])), __fmul_rn(p.beta, dst[j]));
-                    } else if (vec) {
 #pragma unroll
-                        for (int q = 0; q < 8; ++q)
-                            reinterpret_cast<float4 *>(dst)[q] =
-                                make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
-                                            __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
-                    } else {
-                        for (int j = 0; j < 32 && col + j < p.N; ++j) dst[j] = __uint_as_float(r[j]);
+                        for (int j = 0; j < 16; ++j)
+                            w[c2 * 16 + j] = cvt_bf16x2(gelu_erf(__uint_as_float(r[2 * j])), gelu_erf(__uint_as_float(r[2 * j + 1])));
+                    }
+                    const uint32_t col = col_base + g * 64;
+                    if (col >= p.N) continue;
+                    if (bulk) {
+                        if (store_pending) {
+                            if (lane == 0) tma_store_wait_read();
+                            __syncwarp();
+                        }
+#pragma unroll
+                        for (int k = 0; k < 8; ++k)
+                            *reinterpret_cast<uint4 *>(slice + lane * 128 + ((k ^ (lane & 7)) * 16)) =
+                                make_uint4(w[4 * k], w[4 * k + 1], w[4 * k + 2], w[4 * k + 3]);
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            tma_store_2d(&tmC, slice, (int32_t)col, (int32_t)row0);
+                            tma_store_commit();
+                        }
+                        store_pending = true;
+                    } else if (row_ok) {
+                        uint16_t *dst = reinterpret_cast<uint16_t *>(p.c) + (uint64_t)row * p.ldc + col;
+                        if (col + 64 <= p.N && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
+#pragma unroll
+                            for (int k = 0; k < 8; ++k)
+                                reinterpret_cast<uint4 *>(dst)[k] = make_uint4(w[4 * k], w[4 * k + 1], w[4 * k + 2], w[4 * k + 3]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 64; ++j)
+                                if (col + j < p.N) dst[j] = (uint16_t)(w[j >> 1] >> ((j & 1) * 16));
+                        }
+                    }
+                }
+            } else {
+                // ---- f32 output: one chunk (32 columns) per 128-byte group
+#pragma unroll 1
+                for (int g = 0; g < kChunks; ++g) {
+                    uint32_t r[32];
+                    tmem_ld_32x32b_x32(taddr + g * 32, r);
+                    tmem_ld_wait();
+                    if (g == kChunks - 1) {   // the accumulator has been read completely
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+                    }
+                    const uint32_t col = col_base + g * 32;
+                    if (col >= p.N) continue;
+                    if (bulk && p.epilogue == EPI_STORE) {
+                        if (store_pending) {
+                            if (lane == 0) tma_store_wait_read();
+                            __syncwarp();
+                        }
+#pragma unroll
+                        for (int k = 0; k < 8; ++k)
+                            *reinterpret_cast<uint4 *>(slice + lane * 128 + ((k ^ (lane & 7)) * 16)) =
+                                make_uint4(r[4 * k], r[4 * k + 1], r[4 * k + 2], r[4 * k + 3]);
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            tma_store_2d(&tmC, slice, (int32_t)col, (int32_t)row0);
+                            tma_store_commit();
+                        }
+                        store_pending = true;
+                    } else if (row_ok) {
+                        float *dst = reinterpret_cast<float *>(p.c) + (uint64_t)row * p.ldc + col;
+                        const bool vec = col + 32 <= p.N && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0);
+                        if (p.epilogue == EPI_ALPHA_BETA) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (col + j < p.N)
+                                    dst[j] = __fadd_rn(__fmul_rn(p.alpha, __uint_as_float(r[j])), __fmul_rn(p.beta, dst[j]));
+                        } else if (vec) {
+#pragma unroll
+                            for (int q = 0; q < 8; ++q)
+                                reinterpret_cast<uint4 *>(dst)[q] = make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (col + j < p.N) dst[j] = __uint_as_float(r[j]);
+                        }
                     }
                 }
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&tmem_empty[buf]);
         }
+        // the staging slice must stay intact until the last copy has read it
+        if (store_pending && lane == 0) tma_store_wait_read();
         if (!ok && lane == 0) {
             kstatus_set(p.status, FE2O3_KSTATUS_WAIT_EXPIRED);
             atomicExch(&s_abort, 1);
@@ -365,8 +469,19 @@ int32_t gemm_tc_plan(fe2o3_ctx *ctx, GemmTcPlan *plan, uint64_t a, uint64_t b, u
         st = fe2o3_make_tmap_bf16(&plan->tmB, b, 2, dB, sB, bB);
     }
     if (st != FE2O3_OK) return st;
+    // Output through the copy engine when it can address C: 16-byte aligned base and row pitch.
+    const uint32_t esize = epilogue == EPI_GELU_BF16 ? 2u : 4u;
+    uint32_t bulk = 0;
+    plan->tmC = plan->tmA;   // a valid map when the bulk path is off (never used then)
+    if (epilogue != EPI_ALPHA_BETA && (c & 15u) == 0 && ((uint64_t)ldc * esize) % 16u == 0 && M > 0 && N > 0) {
+        uint64_t dC[2] = {N, M}, sC[1] = {(uint64_t)ldc * esize};
+        uint32_t bC[2] = {128u / esize, 32};
+        st = esize == 2 ? fe2o3_make_tmap_bf16(&plan->tmC, c, 2, dC, sC, bC) : fe2o3_make_tmap_f32(&plan->tmC, c, 2, dC, sC, bC);
+        if (st != FE2O3_OK) return st;
+        bulk = 1;
+    }
     plan->p = GemmParams{reinterpret_cast<void *>(c), M, N, K, ldc, alpha, beta, epilogue, expert_offsets, experts,
-                         expert_mod, ctx->status_word};
+                         expert_mod, bulk, ctx->status_word};
     const uint32_t n_tiles = (N + plan->bn - 1) / plan->bn;
     const uint64_t m_tiles = (uint64_t)(M + BM - 1) / BM + experts;  // grouped: each expert may add a ragged tile
     uint64_t tiles = m_tiles * n_tiles;
@@ -385,9 +500,9 @@ int32_t gemm_tc_launch(const GemmTcPlan *plan, cudaStream_t s) {
     });
     if (plan->p.M == 0 || plan->p.N == 0) return FE2O3_OK;
     if (plan->bn == 256)
-        gemm_tc_kernel<256><<<plan->grid, kThreads, plan->smem, s>>>(plan->tmA, plan->tmB, plan->p);
+        gemm_tc_kernel<256><<<plan->grid, kThreads, plan->smem, s>>>(plan->tmA, plan->tmB, plan->tmC, plan->p);
     else
-        gemm_tc_kernel<128><<<plan->grid, kThreads, plan->smem, s>>>(plan->tmA, plan->tmB, plan->p);
+        gemm_tc_kernel<128><<<plan->grid, kThreads, plan->smem, s>>>(plan->tmA, plan->tmB, plan->tmC, plan->p);
     fe2o3_count_launch(1);
     return fe2o3_cuda_status(cudaGetLastError(), "gemm_tc");
 }

@@ -15,11 +15,12 @@ struct GemmParams {
     const uint32_t *expert_offsets;
     uint32_t experts;        // 0 = plain GEMM; otherwise the number of row groups
     uint32_t expert_mod;     // group g reads B matrix (g % expert_mod); 0 = identity
+    uint32_t bulk_store;     // C is addressable by the copy engine (tensor map tmC is valid)
     uint32_t *status;
 };
 
 struct GemmTcPlan {
-    CUtensorMap tmA, tmB;
+    CUtensorMap tmA, tmB, tmC;
     GemmParams p;
     uint32_t bn;
     uint32_t grid;
