@@ -443,7 +443,9 @@ print("ok")
     assert r.returncode == 0 and "ok" in r.stdout, r.stdout + r.stderr
 
 
-@pytest.mark.parametrize("T,d,E", [(100, 64, 8), (300, 200, 4), (257, 2048, 8), (64, 136, 16), (50, 96, 5), (33, 70, 8)])
+# up to 4096 tokens with d_model % 64 == 0 take the warp-per-eight-tokens kernel, more tokens the 32-token block kernel
+@pytest.mark.parametrize("T,d,E", [(100, 64, 8), (300, 200, 4), (257, 2048, 8), (64, 136, 16), (50, 96, 5), (33, 70, 8),
+                                   (4500, 128, 8), (4200, 192, 16), (1000, 256, 4)])
 def test_moe_gate_logits_bit_exact(gpu, orc, T, d, E):
     fe, ctx, stream = gpu
     from fe2o3_b200 import synth
