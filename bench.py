@@ -136,6 +136,19 @@ class Harness:
         return float(t.item())
 
 
+# DRAM bytes (read + write) of one launch of each workload's dominant kernel at the default full size,
+# from one-pass ncu captures (dram__bytes_read.sum + dram__bytes_write.sum; summary under profiles/).
+# Reported only when the workload runs at exactly that size.
+NCU_TRAFFIC = {
+    ("masked_reduce_u32", 1 << 28): 2147519744 + 3300352,
+    ("row_softmax_v1", 65536 * 1024): 268459008 + 216675072,
+    ("tiled_gemm_v1", (8192, 8192, 8192)): 1046762752 + 250886400,
+    ("flash_attention_v1", (4, 16, 2048, 64)): 50588160 + 2605312,
+    # grouped FFN GEMMs of one pass, average of the two launches (GEMM-1 501 MB, GEMM-2 880 MB)
+    ("moe_top2_v1", (16384, 2048, 4096, 8)): (268686848 + 232546560 + 642772480 + 236861952) // 2,
+}
+
+
 def roofline(bound, achieved, peak, unit, traffic=None, peak_source="measured"):
     return {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
             "traffic": traffic, "peak_source": f"of {peak_source}"}
@@ -171,7 +184,7 @@ def wl_masked_reduce(h, steps, warmup, n=1 << 28, cpu=True):
     res = {"ms_per_step": step_ms, "value": h.world * n / (step_ms * 1e-3), "unit": "elements/s",
            "launches": launches,
            "roofline": roofline("hbm", alg_bytes / (float(np.mean(ms)) * 1e-3) / 1e9, peaks["hbm_gbs"], "GB/s",
-                                peak_source=peaks["source"]),
+                                traffic=NCU_TRAFFIC.get(("masked_reduce_u32", n)), peak_source=peaks["source"]),
            "workload": {"workload": "masked_reduce_u32", "elements": n, "values": "uniform[0,2^16) seed 1",
                         "mask": "Bernoulli(0.75) u32 flags {0,7}", "algorithmic_bytes_per_step": alg_bytes,
                         "l2": "inputs (2 GiB) larger than L2"}}
@@ -229,7 +242,8 @@ def wl_row_softmax(h, steps, warmup, rows=65536, cols=1024, cpu=True):
     step_ms = float(np.mean(ms))
     alg = n * 8
     res = {"ms_per_step": step_ms, "value": alg / (step_ms * 1e-3) / 1e9, "unit": "GB/s",
-           "roofline": roofline("hbm", alg / (step_ms * 1e-3) / 1e9, peaks["hbm_gbs"], "GB/s", peak_source=peaks["source"]),
+           "roofline": roofline("hbm", alg / (step_ms * 1e-3) / 1e9, peaks["hbm_gbs"], "GB/s",
+                                traffic=NCU_TRAFFIC.get(("row_softmax_v1", n)), peak_source=peaks["source"]),
            "workload": {"workload": "row_softmax_v1", "rows": rows, "cols": cols, "algorithmic_bytes_per_step": alg,
                         "l2": "input+output (512 MiB) larger than L2"}}
     y.copy_to_host_async(stream, host_y)
@@ -272,7 +286,8 @@ def wl_gemm(h, steps, warmup, m=8192, n=8192, k=8192, cpu=True):
     flops = 2.0 * m * n * k
     tf = flops / (step_ms * 1e-3) / 1e12
     res = {"ms_per_step": step_ms, "value": tf, "unit": "TFLOP/s",
-           "roofline": roofline("tensor", tf, peaks["bf16_tflops"], "TFLOP/s", peak_source=peaks["source"]),
+           "roofline": roofline("tensor", tf, peaks["bf16_tflops"], "TFLOP/s",
+                                traffic=NCU_TRAFFIC.get(("tiled_gemm_v1", (m, n, k))), peak_source=peaks["source"]),
            "workload": {"workload": "tiled_gemm_v1", "m": m, "n": n, "k": k, "dtype": "bf16 in, f32 out",
                         "algorithmic_flops_per_step": flops, "l2": "A+B (256 MiB) larger than L2"}}
     if cpu:
@@ -312,7 +327,9 @@ def wl_attention(h, steps, warmup, batch=4, heads=16, seq=2048, dim=64, cpu=True
     flops = 4.0 * batch * heads * seq * seq * dim
     tf = flops / (step_ms * 1e-3) / 1e12
     res = {"ms_per_step": step_ms, "value": tf, "unit": "TFLOP/s",
-           "roofline": roofline("tensor", tf, peaks["bf16_tflops"], "TFLOP/s", peak_source=peaks["source"]),
+           "roofline": roofline("tensor", tf, peaks["bf16_tflops"], "TFLOP/s",
+                                traffic=NCU_TRAFFIC.get(("flash_attention_v1", (batch, heads, seq, dim))),
+                                peak_source=peaks["source"]),
            "workload": {"workload": "flash_attention_v1", "batch": batch, "heads": heads, "seq": seq, "dim": dim,
                         "causal": False, "dtype": "bf16 in, f32 out", "algorithmic_flops_per_step": flops,
                         "l2": "256 MiB L2 flush between steps"}}
@@ -385,11 +402,25 @@ def wl_moe(h, steps, warmup, cpu=True, **shape):
         raise RuntimeError("MoE reported a kernel status word")
     step_ms = h.max_over_ranks(float(np.mean(ms)))
     flops = T * 2 * 4.0 * d * f + 2.0 * T * d * E
-    tf = flops / (step_ms * 1e-3) / 1e12
+    # roofline of the dominant kernel: the two grouped FFN GEMMs of this rank, launched alone on the
+    # rows the pass just routed (CUDA events around each pair), against the burst peak
+    ffn = layer.k_ffn if h.world > 1 else fe.prepare(
+        h.ctx, "moe_grouped_ffn_v1", compact_x=layer.compact_x, w1=layer.w1, w2=layer.w2, group_offsets=layer.offsets,
+        hidden=layer.hidden, compact_output=layer.compact_out, d_model=d, d_ff=f, groups=E, experts_cycle=E)
+    ffn_ms = float(np.mean(h.time_steps(lambda: ffn.launch(h.stream), max(3, min(steps, 10)), 3, flush=False)))
+    ffn_rows = int(layer.ffn_rows())
+    ffn_tf = ffn_rows * 4.0 * d * f / (ffn_ms * 1e-3) / 1e12
     res = {"ms_per_step": step_ms, "value": T / (step_ms * 1e-3), "unit": "tokens/s", "launches": launches,
            "scaling": "strong",
-           "roofline": roofline("tensor", tf / h.world, peaks["bf16_tflops_sustained"], "TFLOP/s",
-                                peak_source=peaks["source"] + " (sustained, per GPU)"),
+           "roofline": {**roofline("tensor", ffn_tf, peaks["bf16_tflops"], "TFLOP/s",
+                                   traffic=NCU_TRAFFIC.get(("moe_top2_v1", (T, d, f, E))) if h.world == 1 else None,
+                                   peak_source=peaks["source"]),
+                        "kernel": "gemm_tc_kernel<256>, the two grouped FFN GEMMs (two launches, timed alone)",
+                        "rows": ffn_rows, "ms_per_pair": ffn_ms,
+                        "whole_pass": {"achieved": flops / (step_ms * 1e-3) / 1e12 / h.world,
+                                       "peak": peaks["bf16_tflops_sustained"],
+                                       "frac": flops / (step_ms * 1e-3) / 1e12 / h.world / peaks["bf16_tflops_sustained"],
+                                       "unit": "TFLOP/s", "peak_source": "of " + peaks["source"] + " (sustained, per GPU)"}},
            "workload": {"workload": "moe_top2_v1", **shape, "gate": "softmax(x*Wg), top-2 renormalised",
                         "ffn": "GELU(erf), bf16 hidden", "parallelism": f"ep{h.world}" if h.world > 1 else "single", "exchange": layer.exchange,
                         "cuda_graph": bool(graphed), "kernels_per_pass": per_pass,

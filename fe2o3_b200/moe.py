@@ -149,6 +149,11 @@ class MoeTop2Layer:
             dst.view(t.int16).copy_(t.from_numpy(np.ascontiguousarray(src).view(np.int16)))
 
     # ---- one step ------------------------------------------------------------------------
+    def ffn_rows(self):
+        """Rows the expert FFN of this rank processed in the last pass (device read; synchronises)."""
+        off = self.group_offsets if self.world > 1 else self.offsets
+        return int(off[-1].item())
+
     def forward(self, stream=None):
         """Enqueues one layer pass on `stream` (default: the layer's stream) and returns the output tensor."""
         s = stream or self.stream
