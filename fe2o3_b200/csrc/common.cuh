@@ -124,6 +124,7 @@ __device__ __forceinline__ bool mbar_test(uint64_t *bar, uint32_t parity) {
 // the device; the caller records FE2O3_KSTATUS_WAIT_EXPIRED and unwinds.
 #define FE2O3_SPIN_LIMIT (1u << 22)
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+    if (mbar_test(bar, parity)) return true;   // the common case in a running pipeline: already complete
     for (uint32_t i = 0; i < FE2O3_SPIN_LIMIT; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if (i > 64) __nanosleep(32);
