@@ -200,8 +200,8 @@ class Prepared:
 
     @property
     def kernarg(self):
-        n = C.c_uint64(256)
-        buf = (C.c_uint8 * 256)()
+        n = C.c_uint64(320)
+        buf = (C.c_uint8 * 320)()
         check(lib.fe2o3_prepared_kernarg(self._h, buf, C.byref(n)), "kernarg")
         return bytes(buf[: n.value])
 

@@ -563,3 +563,33 @@ def test_runtime_adapter_resolves_reference_symbols(gpu, orc):
     ev0.record(stream); ev1.record(stream); ev1.synchronize()
     assert ev1.query() and ev1.elapsed_time_ms_since(ev0) >= 0
     assert fe.launch_count() > 0
+
+
+def test_one_shot_lifecycle_over_the_cuda_adapter(gpu, orc):
+    # join -> load -> dispatch_and_wait -> unload (crates/fe2o3-host/src/flash_attention_v1_lifecycle.rs:227-487)
+    fe, ctx, stream = gpu
+    from fe2o3_b200 import lifecycle as lc, _lib
+    x = np.linspace(-4, 4, 4 * 256, dtype=np.float32)
+    i, o = Guarded(fe, stream, x), Guarded(fe, stream, np.zeros(4 * 256, np.float32))
+    prep = fe.prepare(ctx, "row_softmax_v1", input=i.slice, output=o.slice, rows=4, cols=256)
+    receipt = lc.ArtifactReceipt.for_library(_lib.LIB_PATH, prep.symbol)
+    adapter = lc.CudaRuntimeAdapter(ctx, stream)
+    loaded = lc.join(receipt, lc.bind_prepared(ctx, prep, leases=[i, o])).load(adapter)
+    assert loaded.resolution_observation.symbol == "row_softmax_v1"
+    done = loaded.dispatch_and_wait().unload()
+    assert np.abs(o.read() - orc.row_softmax(x.reshape(4, 256))[1].reshape(-1)).max() < 1e-7
+    assert done.receipt_identity == receipt.identity and len(done.unload_identity) == 32
+    # a receipt of other bytes is refused by the adapter before anything is loaded
+    forged = lc.ArtifactReceipt(receipt.identity, receipt.artifact_identity, lc.ContentIdentity.calculate(b"x" * 64),
+                                lc.TARGET, prep.symbol, b"x" * 64)
+    with pytest.raises(lc.LoadError) as err:
+        lc.join(forged, lc.bind_prepared(ctx, prep)).load(lc.CudaRuntimeAdapter(ctx, stream))
+    assert err.value.kind == "LoadAdapter"
+    # a kernel that reports a status word fails the dispatch, and the lifecycle still unloads
+    bad = x.copy()
+    bad[5] = np.nan
+    ib = Guarded(fe, stream, bad)
+    prep2 = fe.prepare(ctx, "row_softmax_v1", input=ib.slice, output=o.slice, rows=4, cols=256)
+    loaded2 = lc.join(lc.ArtifactReceipt.for_library(_lib.LIB_PATH, prep2.symbol), lc.bind_prepared(ctx, prep2)).load(adapter)
+    with pytest.raises(lc.DispatchError):
+        loaded2.dispatch_and_wait()
