@@ -271,26 +271,53 @@ def wl_row_softmax(h, steps, warmup, rows=65536, cols=1024, cpu=True):
 
 
 def wl_gemm(h, steps, warmup, m=8192, n=8192, k=8192, cpu=True):
+    """C = A*B.  On N GPUs the global A has N*m rows: rank g owns the row block [g*m, (g+1)*m) of A and C
+    (its own stream of the generator), B is replicated before timing, and there is no collective in the
+    timed region (weak scaling: m rows per GPU)."""
     fe = h.fe
     from fe2o3_b200 import synth
     ctx, stream = h.ctx, h.stream
     peaks = measured_peaks()
-    a_h, b_h = synth.uniform_bf16(0, 1, m * k), synth.uniform_bf16(0, 2, k * n)
+    # row block g of A is stream (seed 0, domain 1 + 16 g): every rank's block is a pure function of its index
+    a_h, b_h = synth.uniform_bf16(0, 1 + 16 * h.rank, m * k), synth.uniform_bf16(0, 2, k * n)
     a, b = fe.DeviceBuffer.from_host(stream, a_h), fe.DeviceBuffer.from_host(stream, b_h)
     c = fe.DeviceBuffer.zeroed(stream, m * n, np.float32)
     prep = fe.prepare(ctx, "tiled_gemm_v1", schedule=fe.SCHEDULE_TCGEN05, a=a, b=b, c=c, m=m, n=n, k=k)
+    h.barrier()
     ms = h.time_steps(lambda: prep.launch(stream), steps, warmup, flush=False)
     if ctx.take_kernel_status(stream):
         raise RuntimeError("tensor-core GEMM reported a kernel status word")
-    step_ms = float(np.mean(ms))
+    local_ms = float(np.mean(ms))
+    step_ms = h.max_over_ranks(local_ms)
     flops = 2.0 * m * n * k
-    tf = flops / (step_ms * 1e-3) / 1e12
-    res = {"ms_per_step": step_ms, "value": tf, "unit": "TFLOP/s",
+    tf = flops / (local_ms * 1e-3) / 1e12
+    res = {"ms_per_step": step_ms, "value": h.world * flops / (step_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+           "scaling": "weak", "launches": steps,
            "roofline": roofline("tensor", tf, peaks["bf16_tflops"], "TFLOP/s",
                                 traffic=NCU_TRAFFIC.get(("tiled_gemm_v1", (m, n, k))), peak_source=peaks["source"]),
-           "workload": {"workload": "tiled_gemm_v1", "m": m, "n": n, "k": k, "dtype": "bf16 in, f32 out",
-                        "algorithmic_flops_per_step": flops, "l2": "A+B (256 MiB) larger than L2"}}
-    if cpu:
+           "workload": {"workload": "tiled_gemm_v1", "m": m * h.world, "n": n, "k": k, "dtype": "bf16 in, f32 out",
+                        "sharding": f"row blocks of A and C, {m} rows per GPU, B replicated, no collective",
+                        "algorithmic_flops_per_step": flops * h.world, "l2": "A+B (256 MiB) larger than L2"}}
+    # end to end through the C ABI with host buffers: pinned H2D of A and B, the kernel, D2H of C
+    host_a, host_b, host_c = ctx.pinned(m * k, np.uint16), ctx.pinned(k * n, np.uint16), ctx.pinned(m * n, np.float32)
+    host_a[:], host_b[:] = a_h, b_h
+
+    def e2e_step():
+        a.copy_from_host_async(stream, host_a)
+        b.copy_from_host_async(stream, host_b)
+        prep.launch(stream)
+        c.copy_to_host_async(stream, host_c)
+        stream.synchronize()
+    e2e_step()
+    h.barrier()
+    t0 = time.perf_counter()
+    for _ in range(3):
+        e2e_step()
+    h.barrier()
+    dt = h.max_over_ranks((time.perf_counter() - t0) / 3)
+    res["e2e"] = {"value": h.world * flops / dt / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": 2 * (m * k + k * n) * h.world,
+                  "d2h_bytes_per_step": 4 * m * n * h.world, "ms_per_step": dt * 1e3}
+    if cpu and h.rank == 0:
         import oracle
         oracle.set_threads(os.cpu_count())
         rows = 8
