@@ -224,6 +224,50 @@ def wl_masked_reduce(h, steps, warmup, n=1 << 28, cpu=True):
     return res
 
 
+def wl_scan(h, steps, warmup, n=1 << 28, cpu=True):
+    """Device-wide inclusive u32 prefix sum: 4 bytes in and 4 bytes out per element."""
+    fe = h.fe
+    from fe2o3_b200 import synth
+    ctx, stream = h.ctx, h.stream
+    peaks = measured_peaks()
+    host_v = ctx.pinned(n, np.uint32)
+    synth.u32_below(1, 3, n, 1 << 16, out=host_v)
+    host_o = ctx.pinned(n, np.uint32)
+    v = fe.DeviceBuffer.from_host(stream, host_v)
+    o = fe.DeviceBuffer.zeroed(stream, n, np.uint32)
+    prep = fe.prepare(ctx, "device_scan_u32", values=v, output=o, exclusive=0)
+    ms = h.time_steps(lambda: prep.launch(stream), steps, warmup, flush=False)
+    if ctx.take_kernel_status(stream):
+        raise RuntimeError("scan reported a kernel status word")
+    step_ms = h.max_over_ranks(float(np.mean(ms)))
+    alg = n * 8
+    res = {"ms_per_step": step_ms, "value": h.world * n / (step_ms * 1e-3), "unit": "elements/s", "launches": steps,
+           "roofline": roofline("hbm", alg / (float(np.mean(ms)) * 1e-3) / 1e9, peaks["hbm_gbs"], "GB/s",
+                                peak_source=peaks["source"]),
+           "workload": {"workload": "device_scan_u32", "elements": n, "values": "uniform[0,2^16) seed 1 domain 3",
+                        "algorithmic_bytes_per_step": alg, "l2": "input+output (2 GiB) larger than L2"}}
+
+    def e2e_step():
+        v.copy_from_host_async(stream, host_v)
+        prep.launch(stream)
+        o.copy_to_host_async(stream, host_o)
+        stream.synchronize()
+    e2e_step()
+    t0 = time.perf_counter()
+    e2e_step()
+    dt = time.perf_counter() - t0
+    res["e2e"] = {"value": n / dt, "unit": "elements/s", "h2d_bytes_per_step": 4 * n, "d2h_bytes_per_step": 4 * n}
+    if cpu and h.rank == 0:
+        import oracle
+        t0 = time.perf_counter()
+        want = oracle.scan_sum_u32(host_v)
+        dt = time.perf_counter() - t0
+        res["cpu_baseline"] = {"value": n / dt, "unit": "elements/s", "cores": 1, "kind": "port",
+                               "sample": f"the full {n}-element workload, sequential oracle"}
+        res["parity"] = {"bit_exact": bool((host_o == want).all())}
+    return res
+
+
 def wl_row_softmax(h, steps, warmup, rows=65536, cols=1024, cpu=True):
     fe = h.fe
     from fe2o3_b200 import synth
@@ -504,12 +548,13 @@ def wl_moe(h, steps, warmup, cpu=True, **shape):
 
 
 WORKLOADS = {"masked_reduce_u32": wl_masked_reduce, "row_softmax_v1": wl_row_softmax, "tiled_gemm_v1": wl_gemm,
-             "flash_attention_v1": wl_attention, "moe_top2_v1": wl_moe}
+             "flash_attention_v1": wl_attention, "moe_top2_v1": wl_moe, "device_scan_u32": wl_scan}
 UNITS = {"masked_reduce_u32": ("masked u32 reduction throughput", "elements/s", "u32"),
          "moe_top2_v1": ("MoE top-2 layer throughput", "tokens/s", "bf16"),
          "tiled_gemm_v1": ("tiled GEMM throughput", "TFLOP/s", "bf16"),
          "flash_attention_v1": ("flash attention throughput", "TFLOP/s", "bf16"),
-         "row_softmax_v1": ("row softmax bandwidth", "GB/s", "f32")}
+         "row_softmax_v1": ("row softmax bandwidth", "GB/s", "f32"),
+         "device_scan_u32": ("device-wide u32 prefix sum throughput", "elements/s", "u32")}
 
 
 def run_reference_arm(args):
@@ -590,7 +635,7 @@ def main():
     h = Harness(rank, world, local_rank)
     kw = {}
     if args.small:
-        kw = {"masked_reduce_u32": {"n": 1 << 26}, "row_softmax_v1": {"rows": 32768},
+        kw = {"masked_reduce_u32": {"n": 1 << 26}, "device_scan_u32": {"n": 1 << 26}, "row_softmax_v1": {"rows": 32768},
               "tiled_gemm_v1": {"m": 4096, "n": 4096, "k": 4096},
               "moe_top2_v1": {"tokens": 2048}}.get(args.workload, {})
     if args.no_cpu:

@@ -61,6 +61,7 @@ MoeEpExchangeArgs = _struct("MoeEpExchangeArgs",
                              ("epoch", u32), ("max_rows", u32), ("phase", u32)])
 MaskedReduceArgs = _struct("MaskedReduceArgs", ["values", "active", "output"])
 MaskedReducePackedArgs = _struct("MaskedReducePackedArgs", ["values", "mask", "output"])
+DeviceScanArgs = _struct("DeviceScanArgs", ["values", "output"], [("exclusive", u32), ("reserved", u32)])
 WaveLdsArgs = _struct("WaveLdsArgs", ["values", "active", "wave_out", "workgroup_out"])
 
 
@@ -105,6 +106,7 @@ OPS = {
     "moe_ep_exchange_v1": (MoeEpExchangeArgs, 272, False),
     "masked_reduce_u32": (MaskedReduceArgs, 48, False),
     "masked_reduce_u32_packed": (MaskedReducePackedArgs, 48, False),
+    "device_scan_u32": (DeviceScanArgs, 40, False),
     "wave_lds_v1": (WaveLdsArgs, 64, False),
     "wave64_collectives_v1": (Wave64CollectivesArgs, 72, False),
     "wave64_collectives_segmented": (Wave64SegmentedArgs, 80, False),

@@ -313,6 +313,19 @@ typedef struct fe2o3_masked_reduce_u32_packed_args {
     fe2o3_slice values, mask, output;
 } fe2o3_masked_reduce_u32_packed_args;
 
+/* Device-wide prefix sum of u32 values with wrapping addition: the wave64 and
+ * workgroup inclusive_scan_sum / exclusive_scan_sum of
+ * crates/fe2o3-device/src/collective.rs:413-460 and :503-571 extended to a whole
+ * array (output[i] = values[0] + ... + values[i]; the exclusive form is shifted
+ * by one and starts at zero).  values.len == output.len <= 2^31; the output
+ * may not overlap the input; one scan at a time per context. */
+#define FE2O3_SCAN_MAX_ELEMENTS (1ull << 31)
+typedef struct fe2o3_device_scan_u32_args {
+    fe2o3_slice values, output;
+    uint32_t exclusive; /* 0 inclusive, 1 exclusive */
+    uint32_t reserved;
+} fe2o3_device_scan_u32_args;
+
 /* crates/rustc-codegen-fe2o3/tests/fixtures/memory-v1-compiler/src/bin/gfx942_wave_lds_v1.rs:7-15
  * with the runner's (ptr,len)x4 arguments
  * (crates/dialect-amdgcn/tests/fixtures/gfx942_wave_lds_v1_runner.cpp:62-68):
@@ -369,6 +382,7 @@ int32_t fe2o3_moe_grouped_ffn_v1_check(const fe2o3_moe_grouped_ffn_v1_args *args
 int32_t fe2o3_moe_ep_exchange_v1_check(const fe2o3_moe_ep_exchange_v1_args *args);
 int32_t fe2o3_masked_reduce_u32_check(const fe2o3_masked_reduce_u32_args *args);
 int32_t fe2o3_masked_reduce_u32_packed_check(const fe2o3_masked_reduce_u32_packed_args *args);
+int32_t fe2o3_device_scan_u32_check(const fe2o3_device_scan_u32_args *args);
 int32_t fe2o3_wave_lds_v1_check(const fe2o3_wave_lds_v1_args *args);
 int32_t fe2o3_wave64_collectives_v1_check(const fe2o3_wave64_collectives_v1_args *args);
 int32_t fe2o3_wave64_collectives_segmented_check(const fe2o3_wave64_collectives_segmented_args *args);
@@ -404,6 +418,8 @@ int32_t fe2o3_masked_reduce_u32_prepare(fe2o3_ctx *ctx, const fe2o3_masked_reduc
                                         fe2o3_prepared **out);
 int32_t fe2o3_masked_reduce_u32_packed_prepare(fe2o3_ctx *ctx, const fe2o3_masked_reduce_u32_packed_args *args,
                                                fe2o3_prepared **out);
+int32_t fe2o3_device_scan_u32_prepare(fe2o3_ctx *ctx, const fe2o3_device_scan_u32_args *args,
+                                      fe2o3_prepared **out);
 int32_t fe2o3_wave_lds_v1_prepare(fe2o3_ctx *ctx, const fe2o3_wave_lds_v1_args *args, fe2o3_prepared **out);
 int32_t fe2o3_wave64_collectives_v1_prepare(fe2o3_ctx *ctx, const fe2o3_wave64_collectives_v1_args *args,
                                             fe2o3_prepared **out);

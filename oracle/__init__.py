@@ -231,6 +231,13 @@ def masked_sum_u32(values, active, parallel=True):
     return int(fn(_p(v), _p(a), u64(v.size)))
 
 
+def scan_sum_u32(values, exclusive=False):
+    v = _c(values, np.uint32)
+    out = np.empty_like(v)
+    lib().orc_scan_sum_u32(_p(v), u64(v.size), C.c_uint32(1 if exclusive else 0), _p(out))
+    return out
+
+
 def masked_sum_u32_packed(values, mask):
     v = _c(values, np.uint32)
     m = _c(mask, np.uint64)

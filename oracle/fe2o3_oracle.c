@@ -709,6 +709,20 @@ uint32_t orc_masked_sum_u32(const uint32_t *values, const uint32_t *active, uint
     return total;
 }
 
+/* Prefix sum of u32 values with wrapping addition over a whole array: element i
+ * of the inclusive form is values[0] + ... + values[i]; the exclusive form is
+ * shifted by one and starts at zero.  The meaning of inclusive_scan_sum /
+ * exclusive_scan_sum in crates/fe2o3-device/src/collective.rs:413-460 (lane 0 of
+ * the exclusive form receives T::ZERO, :444-446) at array scope. */
+void orc_scan_sum_u32(const uint32_t *values, uint64_t n, uint32_t exclusive, uint32_t *out) {
+    uint32_t run = 0;
+    for (uint64_t i = 0; i < n; ++i) {
+        const uint32_t v = values[i];
+        if (exclusive) { out[i] = run; run += v; }
+        else { run += v; out[i] = run; }
+    }
+}
+
 /* Same sum with OpenMP partial sums; wrapping addition is associative and
  * commutative so the result is bit-identical. */
 uint32_t orc_masked_sum_u32_parallel(const uint32_t *values, const uint32_t *active, uint64_t n) {

@@ -593,3 +593,38 @@ def test_one_shot_lifecycle_over_the_cuda_adapter(gpu, orc):
     loaded2 = lc.join(lc.ArtifactReceipt.for_library(_lib.LIB_PATH, prep2.symbol), lc.bind_prepared(ctx, prep2)).load(adapter)
     with pytest.raises(lc.DispatchError):
         loaded2.dispatch_and_wait()
+
+
+@pytest.mark.parametrize("n", [1, 5, 63, 64, 4095, 4096, 4097, 12289, 100003, (1 << 22) + 3])
+@pytest.mark.parametrize("exclusive", [0, 1])
+def test_device_scan_sum_u32_bit_exact(gpu, orc, n, exclusive):
+    # crates/fe2o3-device/src/collective.rs:413-460 at array scope
+    fe, ctx, stream = gpu
+    rng = np.random.default_rng(n * 2 + exclusive)
+    v = rng.integers(0, 2**32, n, dtype=np.uint64).astype(np.uint32)      # sums wrap many times
+    V, O = Guarded(fe, stream, v), Guarded(fe, stream, np.full(n, 0xdeadbeef, np.uint32))
+    run(fe, ctx, stream, "device_scan_u32", values=V.slice, output=O.slice, exclusive=exclusive)
+    assert (O.read() == orc.scan_sum_u32(v, bool(exclusive))).all()
+    V.unchanged()
+
+
+def test_device_scan_sum_u32_unaligned_repeated_and_rejections(gpu, orc):
+    fe, ctx, stream = gpu
+    v = (np.arange(1, 20001, dtype=np.uint64) * 2654435761 % (2**32)).astype(np.uint32)
+    buf = fe.DeviceBuffer.from_host(stream, v)
+    res = fe.DeviceBuffer.zeroed(stream, v.size, np.uint32)
+    # slices that start one element in: 4-byte aligned only, so the scalar path runs
+    src, dst = buf.view(1, v.size - 1), res.view(1, v.size - 1)
+    p = fe.prepare(ctx, "device_scan_u32", values=src, output=dst, exclusive=0)
+    p.launch_and_wait(stream)
+    got = res.to_host_vec(stream)
+    assert got[0] == 0 and (got[1:] == orc.scan_sum_u32(v[1:])).all()
+    # the same prepared launch again gives the same answer (scratch is cleared by every launch)
+    p.launch_and_wait(stream)
+    assert (res.to_host_vec(stream)[1:] == orc.scan_sum_u32(v[1:])).all()
+    # empty input: accepted, nothing launched
+    fe.prepare(ctx, "device_scan_u32", values=buf.view(0, 0), output=res.view(0, 0), exclusive=1).launch_and_wait(stream)
+    # output overlapping the input, and a short output, are refused by the host check
+    for bad in (dict(values=src, output=src), dict(values=buf.view(0, 8), output=res.view(0, 7))):
+        with pytest.raises(fe.Fe2o3Error):
+            fe.check_args("device_scan_u32", fe.make_args("device_scan_u32", exclusive=0, **bad))

@@ -382,3 +382,23 @@ def test_workgroup_sync_vectors(orc):
     for initial, elig, want in [(17, np.zeros(64), 17), (0, np.ones(64), 2016), (11, lane % 2 == 0, 1003),
                                 (1000, lane % 13 == 0, 1130)]:
         assert orc.scoped_atomic_add_u32(lane, elig.astype(np.uint32), initial) == (0, want)
+
+
+def test_scan_sum_u32_matches_the_reference_wave_and_workgroup_definitions(orc):
+    # crates/fe2o3-device/src/collective.rs:413-460: inclusive prefix in increasing lane order; the exclusive
+    # form gives lane 0 zero and lane r the inclusive value of lane r - 1; addition wraps
+    rng = np.random.default_rng(7)
+    v = rng.integers(0, 2**32, 64, dtype=np.uint64).astype(np.uint32)
+    inc, exc = orc.scan_sum_u32(v), orc.scan_sum_u32(v, exclusive=True)
+    hs = v.copy()                      # the reference's Hillis-Steele wave scan, step by step
+    off = 1
+    while off < 64:
+        prev = hs.copy()
+        hs[off:] = prev[off:] + prev[:-off]
+        off <<= 1
+    assert (inc == hs).all()
+    assert exc[0] == 0 and (exc[1:] == inc[:-1]).all()
+    assert (inc == np.cumsum(v.astype(np.uint64)).astype(np.uint32)).all()      # wrapping
+    big = rng.integers(0, 2**32, 100003, dtype=np.uint64).astype(np.uint32)
+    assert (orc.scan_sum_u32(big) == np.cumsum(big.astype(np.uint64)).astype(np.uint32)).all()
+    assert orc.scan_sum_u32(np.zeros(0, np.uint32)).size == 0
