@@ -593,7 +593,7 @@ def run_reference_arm(args):
         config = {"workload": "moe_top2_v1", **MOE_SHAPE}
         sample = f"{sample_tokens} tokens of the batch per step through gate, routing, FFN and combine"
     else:
-        print(json.dumps({"impl": "reference", "unavailable": f"no CPU reference arm for workload {args.workload}"}))
+        emit({"impl": "reference", "unavailable": f"no CPU reference arm for workload {args.workload}"})
         return
     for _ in range(min(args.warmup, 3)):
         step()
@@ -602,12 +602,15 @@ def run_reference_arm(args):
         step()
     dt = (time.perf_counter() - t0) / args.steps
     val = units / dt
-    print(json.dumps({
+    emit({
         "impl": "reference", "metric": UNITS[args.workload][0], "value": val, "unit": unit, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": scaling, "vs_baseline": None, "dtype": dtype, "data": "synthetic", "config": config,
         "cpu_baseline": {"value": val, "unit": unit, "cores": cores, "kind": "port", "sample": sample},
-        "e2e": {"value": val, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        "e2e": {"value": val, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
+
+
+emit = None   # set by main(): writes the one JSON line to the process's real stdout
 
 
 def main():
@@ -622,6 +625,16 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-oracle leg (profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    # stdout carries exactly one line, the JSON result: anything a library prints to file descriptor 1
+    # while the bench runs (banners, warnings) goes to stderr instead
+    sys.stdout.flush()
+    result_fd = os.dup(1)
+    os.dup2(2, 1)
+    global emit
+
+    def emit(obj):  # noqa: F811
+        sys.stdout.flush()
+        os.write(result_fd, (json.dumps(obj) + "\n").encode())
     if args.impl == "reference":
         return run_reference_arm(args)
 
@@ -663,7 +676,7 @@ def main():
                 "config": res["workload"], "roofline": res["roofline"], "e2e": res.get("e2e"),
                 "cpu_baseline": res.get("cpu_baseline"), "gpu_launches": res.get("launches", args.steps),
                 "clocks": clocks.summary(), "parity": res.get("parity"), "ops": ops}
-        print(json.dumps(line))
+        emit(line)
     if world > 1:
         torch.distributed.destroy_process_group()
 
