@@ -19,13 +19,14 @@ struct fe2o3_ctx {
     uint32_t reduce_scratch_elems;
     uint32_t *host_status;     // pinned mirror for status read-back
     uint32_t *route_scratch;   // device: per-block expert counts, per-block flags, arrival counter (MoE routing)
-    uint32_t *scan_scratch;    // device: ticket + one 64-bit descriptor per 8192-element tile (device-wide scan)
+    uint32_t *scan_scratch;    // device: ticket + one 64-bit descriptor per tile (device-wide scan)
 };
 
 // Routing scratch layout: [FE2O3_ROUTE_MAX_BLOCKS][32] counts, [FE2O3_ROUTE_MAX_BLOCKS] flags, 1 summary, 1 counter.
 #define FE2O3_ROUTE_MAX_BLOCKS 16384u
 #define FE2O3_ROUTE_SCRATCH_ELEMS (FE2O3_ROUTE_MAX_BLOCKS * 33u + 64u)
-// Scan scratch: 64 bytes (ticket) + 8 bytes per tile of 8192 elements at the largest admitted length.
+// Scan scratch: 64 bytes (ticket) + 8 bytes per tile at the largest admitted length (sized for 8192-element tiles;
+// the kernel's tiles are at least that large).
 #define FE2O3_SCAN_SCRATCH_BYTES (64u + (uint32_t)(FE2O3_SCAN_MAX_ELEMENTS / 8192u) * 8u)
 
 struct fe2o3_stream {

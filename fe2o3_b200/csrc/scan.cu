@@ -8,8 +8,8 @@
 // shifts by one and starts at zero, addition wraps) and extends the scope to a
 // whole array in one pass over HBM: 4 bytes read and 4 bytes written per element.
 //
-// Single pass with decoupled look-back.  A tile is 8192 elements: each of the eight
-// warps owns 1024 consecutive elements and walks them in eight coalesced passes of
+// Single pass with decoupled look-back.  A tile is 16384 elements: each of the eight
+// warps owns 2048 consecutive elements and walks them in sixteen coalesced passes of
 // 32 lanes x 16 bytes, carrying its running total from pass to pass in registers,
 // so the block synchronises only once per tile (to combine the warp totals).  Tiles
 // are handed out by an atomic ticket, so a tile only ever waits for tiles that
@@ -17,7 +17,8 @@
 // its predecessors' descriptors, 128 at a time (four per lane, the four loads in
 // flight together), up to the nearest one whose inclusive prefix is known, and
 // publishes the tile's own inclusive prefix.  Measured at 2^28 elements on B200:
-// 32-wide steps over 4096-element tiles 2.3 TB/s, this form 3.4 TB/s; without the
+// 32-wide steps over 4096-element tiles 2.3 TB/s, this form 3.4 TB/s (8192- and
+// 16384-element tiles alike); without the
 // look-back the same loads and stores run at 6.6 TB/s, so what is left is the wait
 // for the predecessors.  Two variants were slower and are not kept: a block-wide
 // 1024-descriptor step (more polling traffic on the descriptor lines) and
@@ -34,9 +35,9 @@
 namespace {
 
 constexpr int kScanThreads = 256;
-constexpr int kPasses = 8;                                          // 16-byte vectors per thread
-constexpr uint32_t kWarpElems = kPasses * 32 * 4;                   // 1024 consecutive elements per warp
-constexpr uint32_t kTileElems = (kScanThreads / 32) * kWarpElems;   // 8192
+constexpr int kPasses = 16;                                         // 16-byte vectors per thread
+constexpr uint32_t kWarpElems = kPasses * 32 * 4;                   // 2048 consecutive elements per warp
+constexpr uint32_t kTileElems = (kScanThreads / 32) * kWarpElems;   // 16384
 constexpr int kWindow = 4;                                          // descriptors per lane and look-back step
 constexpr uint32_t kStateAggregate = 1, kStateInclusive = 2;
 constexpr uint32_t kLookbackSpin = 1u << 22;
@@ -64,7 +65,7 @@ device_scan_u32_kernel(const uint32_t *in, uint32_t *out, uint64_t n, uint32_t e
     if (base >= n) return;
     const bool vec = base + kTileElems <= n && ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0;
 
-    // pass j of this warp is elements [1024 warp + 128 j, +128) of the tile; this lane owns elements 4 lane .. 4 lane + 3 of it
+    // pass j of this warp is elements [2048 warp + 128 j, +128) of the tile; this lane owns elements 4 lane .. 4 lane + 3 of it
     const uint64_t wbase = base + (uint64_t)warp * kWarpElems + lane * 4;
     uint32_t incl[kPasses][4];
 #pragma unroll
@@ -78,7 +79,7 @@ device_scan_u32_kernel(const uint32_t *in, uint32_t *out, uint64_t n, uint32_t e
             for (int c = 0; c < 4; ++c) incl[j][c] = e + c < n ? in[e + c] : 0u;
         }
     }
-    // inclusive scan inside the warp's 1024 elements, in place: thread-local, across the lanes, carried over the passes
+    // inclusive scan inside the warp's 2048 elements, in place: thread-local, across the lanes, carried over the passes
     uint32_t before[kPasses];   // sum of everything in the warp's part before this lane's four elements of pass j
     uint32_t carry = 0;         // sum of this warp's passes before the current one
 #pragma unroll
