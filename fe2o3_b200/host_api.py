@@ -1,0 +1,365 @@
+"""Runtime-neutral dispatch records with the reference's canonical identity preimages.
+
+The dispatch flow of crates/fe2o3-host-api: operation context, resource bindings,
+completion dependencies, the dispatch request and its result, with the same structural
+validation and the same bytes in `encode_identity_preimage()` (magic "F2HOSTP1",
+little-endian, domain-separated; crates/fe2o3-host-api/src/canonical.rs:7-65,
+src/dispatch.rs:234-268 and :350-368, src/common.rs:331-341, :495-500, :580-586), so a run
+log written by a host that launches through this library hashes to the identities a
+reference-side reader computes.  Records are inert descriptions: they own no runtime
+handle and nothing here talks to a device.
+
+Only the dispatch flow is mirrored; the compile, admit, load and wait flows of the crate
+use the same encoder and identity types and are not built.
+"""
+import hashlib
+from dataclasses import dataclass, field
+from typing import Optional, Tuple
+
+PREIMAGE_MAGIC_V1 = b"F2HOSTP1"
+HOST_API_SCHEMA_VERSION_V1 = 1                     # src/lib.rs:48
+IDENTITY_BYTES_V1 = 32                             # src/identity.rs:4
+MAX_DIAGNOSTICS_V1 = 64                            # src/common.rs:18-26
+MAX_DIAGNOSTIC_MESSAGE_BYTES_V1 = 1024
+MAX_CAUSAL_EVENTS_V1 = 64
+MAX_IDENTITY_PREIMAGE_BYTES_V1 = 128 * 1024
+MAX_DISPATCH_BINDINGS_V1 = 128                     # src/dispatch.rs:19-22
+MAX_DISPATCH_DEPENDENCIES_V1 = 128
+
+# identity domains used by the dispatch flow (src/identity.rs:55-272)
+DOMAINS = {
+    "FlowScopeId": b"fe2o3.host.scope.v1",
+    "OperationId": b"fe2o3.host.operation.v1",
+    "LoadedObjectId": b"fe2o3.host.loaded-object.v1",
+    "EntryPointId": b"fe2o3.host.entry-point.v1",
+    "ArgumentSetId": b"fe2o3.host.argument-set.v1",
+    "DispatchContractId": b"fe2o3.host.dispatch-contract.v1",
+    "ServiceInstanceId": b"fe2o3.host.service-instance.v1",
+    "TaskSchemaId": b"fe2o3.host.task-schema.v1",
+    "ResourceId": b"fe2o3.host.resource.v1",
+    "DispatchSubmissionId": b"fe2o3.host.dispatch-submission.v1",
+    "CompletionSignalId": b"fe2o3.host.completion-signal.v1",
+    "LoadResultId": b"fe2o3.host.load.result.v1",
+    "DispatchRequestId": b"fe2o3.host.dispatch.request.v1",
+    "DispatchResultId": b"fe2o3.host.dispatch.result.v1",
+    "CompileEventId": b"fe2o3.host.compile.event.v1",
+    "AdmitEventId": b"fe2o3.host.admit.event.v1",
+    "LoadEventId": b"fe2o3.host.load.event.v1",
+    "DispatchEventId": b"fe2o3.host.dispatch.event.v1",
+    "WaitEventId": b"fe2o3.host.wait.event.v1",
+}
+
+FLOW_COMPILE, FLOW_ADMIT, FLOW_LOAD, FLOW_DISPATCH, FLOW_WAIT = 1, 2, 3, 4, 5          # src/common.rs:165-176
+ACCESS_READ, ACCESS_WRITE, ACCESS_READ_WRITE, ACCESS_ATOMIC = 1, 2, 3, 4               # src/common.rs:506-515
+SEVERITY_NOTE, SEVERITY_WARNING, SEVERITY_ERROR = 1, 2, 3                              # src/common.rs:405-412
+
+
+class HostContractError(ValueError):
+    """kind: the reference's HostContractErrorV1 variant; field: its ContractFieldV1."""
+
+    def __init__(self, kind, field=None):
+        self.kind, self.field = kind, field
+        super().__init__(f"{kind}({field})" if field else kind)
+
+
+def digest(value):
+    """A 32-byte commitment (HostDigestV1: width is checked, nothing is hashed or authenticated)."""
+    b = bytes(value)
+    if len(b) != IDENTITY_BYTES_V1:
+        raise ValueError("a host digest is 32 bytes")
+    return b
+
+
+class Encoder:
+    """canonical.rs:9-65: magic, u16 domain length, domain, u16 schema version, then fields little-endian."""
+
+    def __init__(self, domain):
+        self.bytes = bytearray(PREIMAGE_MAGIC_V1)
+        self.u16(len(domain))
+        self.bytes += domain
+        self.u16(HOST_API_SCHEMA_VERSION_V1)
+
+    def u8(self, v):
+        self.bytes += int(v).to_bytes(1, "little")
+
+    def u16(self, v):
+        self.bytes += (int(v) & 0xffff).to_bytes(2, "little")
+
+    def u32(self, v):
+        self.bytes += int(v).to_bytes(4, "little")
+
+    def u64(self, v):
+        self.bytes += int(v).to_bytes(8, "little")
+
+    def digest(self, d):
+        self.bytes += digest(d)
+
+    def optional_digest(self, d):
+        if d is None:
+            self.u8(0)
+        else:
+            self.u8(1)
+            self.digest(d)
+
+    def text(self, s):
+        raw = s.encode("utf-8")
+        self.u16(len(raw))
+        self.bytes += raw
+
+    def finish(self):
+        assert len(self.bytes) <= MAX_IDENTITY_PREIMAGE_BYTES_V1
+        return bytes(self.bytes)
+
+
+def _strictly_ordered(values, maximum, fld):
+    """common.rs:666-687."""
+    if len(values) > maximum:
+        raise HostContractError("TooManyItems", fld)
+    for a, b in zip(values, values[1:]):
+        if a == b:
+            raise HostContractError("Duplicate", fld)
+        if a > b:
+            raise HostContractError("NonCanonicalOrder", fld)
+
+
+@dataclass(frozen=True)
+class OperationContext:
+    """common.rs:265-342.  causal_events: (flow, 32-byte event identity), strictly increasing."""
+    scope_id: bytes
+    operation_id: bytes
+    attempt: int
+    parent_operation_id: Optional[bytes] = None
+    causal_events: Tuple[Tuple[int, bytes], ...] = ()
+
+    def __post_init__(self):
+        digest(self.scope_id), digest(self.operation_id)
+        if self.attempt == 0:
+            raise HostContractError("Empty", "OperationAttempt")
+        if not 0 < self.attempt < 1 << 16:
+            raise ValueError("attempt is a u16")
+        if self.parent_operation_id is not None and digest(self.parent_operation_id) == self.operation_id:
+            raise HostContractError("Mismatch", "ParentOperation")
+        events = [(int(f), digest(d)) for f, d in self.causal_events]
+        _strictly_ordered(events, MAX_CAUSAL_EVENTS_V1, "CausalEvents")
+
+    def encode(self, e):
+        e.digest(self.scope_id)
+        e.digest(self.operation_id)
+        e.u16(self.attempt)
+        e.optional_digest(self.parent_operation_id)
+        e.u16(len(self.causal_events))
+        for flow, ident in self.causal_events:
+            e.u8(flow)
+            e.digest(ident)
+
+
+@dataclass(frozen=True)
+class ResourceBinding:
+    """common.rs:517-587: one resource range bound to an argument ordinal."""
+    ordinal: int
+    resource_identity: bytes
+    access: int
+    byte_offset: int
+    byte_len: int
+
+    def __post_init__(self):
+        digest(self.resource_identity)
+        if self.access not in (ACCESS_READ, ACCESS_WRITE, ACCESS_READ_WRITE, ACCESS_ATOMIC):
+            raise ValueError("unknown access mode")
+        if self.byte_len == 0:
+            raise HostContractError("Empty", "ResourceRange")
+        if self.byte_offset + self.byte_len >= 1 << 64:
+            raise HostContractError("ArithmeticOverflow", "ResourceRange")
+
+    def encode(self, e):
+        e.u16(self.ordinal)
+        e.digest(self.resource_identity)
+        e.u8(self.access)
+        e.u64(self.byte_offset)
+        e.u64(self.byte_len)
+
+
+@dataclass(frozen=True, order=True)
+class DispatchDependency:
+    """dispatch.rs:24-57: a predecessor completion this dispatch waits for."""
+    completion_signal_identity: bytes
+    producer_submission_identity: bytes
+
+    def encode(self, e):
+        e.digest(self.completion_signal_identity)
+        e.digest(self.producer_submission_identity)
+
+
+@dataclass(frozen=True)
+class PersistentTask:
+    """dispatch.rs:64-75."""
+    service_instance_identity: bytes
+    task_schema_identity: bytes
+    task_tag: int
+    service_epoch: int
+
+
+@dataclass(frozen=True)
+class LoadedResult:
+    """What a dispatch request copies from a successful load result (load.rs LoadOutcomeV1::Loaded)."""
+    identity: bytes
+    loaded_object_identity: bytes
+    load_generation: int
+
+
+@dataclass(frozen=True)
+class Diagnostic:
+    """common.rs:446-500."""
+    code: int
+    severity: int
+    message: str
+    subject: Optional[bytes] = None
+
+    def __post_init__(self):
+        if self.code == 0:
+            raise HostContractError("Empty", "DiagnosticCode")
+        raw = self.message.encode("utf-8")
+        if not raw:
+            raise HostContractError("Empty", "DiagnosticMessage")
+        if len(raw) > MAX_DIAGNOSTIC_MESSAGE_BYTES_V1:
+            raise HostContractError("LimitExceeded", "DiagnosticMessage")
+        if b"\0" in raw:
+            raise HostContractError("DiagnosticContainsNul")
+
+    def encode(self, e):
+        e.u32(self.code)
+        e.u8(self.severity)
+        e.optional_digest(self.subject)
+        e.text(self.message)
+
+
+@dataclass(frozen=True)
+class DispatchRequest:
+    """dispatch.rs:96-268.  `identity` is the caller's commitment and is not part of the preimage."""
+    identity: bytes
+    context: OperationContext
+    load_result: LoadedResult
+    entry_point_identity: bytes
+    dispatch_contract_identity: bytes
+    argument_set_identity: bytes
+    bindings: Tuple[ResourceBinding, ...] = ()
+    dependencies: Tuple[DispatchDependency, ...] = ()
+    kind: Optional[PersistentTask] = None          # None = one finite kernel dispatch
+
+    def __post_init__(self):
+        if len(self.bindings) > MAX_DISPATCH_BINDINGS_V1:
+            raise HostContractError("TooManyItems", "DispatchBindings")
+        for expected, b in enumerate(self.bindings):
+            if b.ordinal != expected:
+                raise HostContractError("NonCanonicalOrder", "DispatchBindings")
+        deps = list(self.dependencies)
+        _strictly_ordered(deps, MAX_DISPATCH_DEPENDENCIES_V1, "DispatchDependencies")
+        if any(a.completion_signal_identity == b.completion_signal_identity for a, b in zip(deps, deps[1:])):
+            raise HostContractError("Duplicate", "DispatchDependencies")
+        if self.kind is not None and self.kind.service_epoch == 0:
+            raise HostContractError("Empty", "ServiceEpoch")
+        if self.load_result.load_generation == 0:
+            raise HostContractError("InvalidOutcome")
+
+    def encode_identity_preimage(self):
+        e = Encoder(DOMAINS["DispatchRequestId"])
+        self.context.encode(e)
+        e.digest(self.load_result.identity)
+        e.digest(self.load_result.loaded_object_identity)
+        e.u64(self.load_result.load_generation)
+        e.digest(self.entry_point_identity)
+        e.digest(self.dispatch_contract_identity)
+        e.digest(self.argument_set_identity)
+        if self.kind is None:
+            e.u8(1)
+        else:
+            e.u8(2)
+            e.digest(self.kind.service_instance_identity)
+            e.digest(self.kind.task_schema_identity)
+            e.u32(self.kind.task_tag)
+            e.u64(self.kind.service_epoch)
+        e.u16(len(self.bindings))
+        for b in self.bindings:
+            b.encode(e)
+        e.u16(len(self.dependencies))
+        for d in self.dependencies:
+            d.encode(e)
+        return e.finish()
+
+
+OUTCOME_SUBMITTED, OUTCOME_REJECTED, OUTCOME_FAILED = 1, 2, 3
+
+
+@dataclass(frozen=True)
+class DispatchResult:
+    """dispatch.rs:270-368: the result of one dispatch request, bound to that request."""
+    identity: bytes
+    request: DispatchRequest
+    outcome: int
+    submission_identity: Optional[bytes] = None
+    completion_signal_identity: Optional[bytes] = None
+    diagnostics: Tuple[Diagnostic, ...] = field(default_factory=tuple)
+
+    def __post_init__(self):
+        if len(self.diagnostics) > MAX_DIAGNOSTICS_V1:
+            raise HostContractError("TooManyItems", "Diagnostics")
+        has_error = any(d.severity == SEVERITY_ERROR for d in self.diagnostics)
+        if self.outcome in (OUTCOME_REJECTED, OUTCOME_FAILED) and not has_error:
+            raise HostContractError("MissingFailureDiagnostic")
+        if self.outcome == OUTCOME_SUBMITTED:
+            if has_error or self.submission_identity is None or self.completion_signal_identity is None:
+                raise HostContractError("InvalidOutcome")
+        elif self.outcome not in (OUTCOME_REJECTED, OUTCOME_FAILED):
+            raise HostContractError("InvalidOutcome")
+
+    def encode_identity_preimage(self):
+        e = Encoder(DOMAINS["DispatchResultId"])
+        e.digest(self.request.identity)
+        e.digest(self.request.load_result.loaded_object_identity)
+        e.u8(self.outcome)
+        if self.outcome == OUTCOME_SUBMITTED:
+            e.digest(self.submission_identity)
+            e.digest(self.completion_signal_identity)
+        e.u16(len(self.diagnostics))
+        for d in self.diagnostics:
+            d.encode(e)
+        return e.finish()
+
+
+# ------------------------------------------------------------------ this library's launches
+def commit(domain_name, *parts):
+    """A commitment an integration may choose: SHA-256 over the identity's domain and the given parts.
+    The reference leaves the digest operation to the integration (identity.rs:6-9)."""
+    h = hashlib.sha256(DOMAINS[domain_name])
+    for p in parts:
+        h.update(len(p).to_bytes(8, "little"))
+        h.update(p)
+    return h.digest()
+
+
+def dispatch_request_for(prepared, op_args, context, load_result, written=(), element_bytes=None):
+    """The dispatch request that describes one prepared launch of this library: entry point = the kernel
+    symbol, argument set = the packed argument bytes, one binding per non-empty slice argument in
+    declaration order.  `written` names the slices the kernel writes; `element_bytes` maps a slice name to
+    its element size (slice lengths are in elements; default 4 bytes)."""
+    from ._lib import Slice
+    bindings, ordinal = [], 0
+    for name, ty in type(op_args)._fields_:
+        if ty is not Slice:
+            continue
+        s = getattr(op_args, name)
+        if s.len == 0:
+            continue
+        resource = commit("ResourceId", name.encode(), int(s.ptr).to_bytes(8, "little"))
+        size = (element_bytes or {}).get(name, 4)
+        bindings.append(ResourceBinding(ordinal, resource, ACCESS_WRITE if name in written else ACCESS_READ, 0, int(s.len) * size))
+        ordinal += 1
+    kernarg = prepared.kernarg
+    req = DispatchRequest(
+        identity=bytes(32), context=context, load_result=load_result,
+        entry_point_identity=commit("EntryPointId", prepared.symbol.encode()),
+        dispatch_contract_identity=commit("DispatchContractId", prepared.symbol.encode(), len(kernarg).to_bytes(8, "little")),
+        argument_set_identity=commit("ArgumentSetId", kernarg), bindings=tuple(bindings))
+    ident = hashlib.sha256(req.encode_identity_preimage()).digest()
+    return DispatchRequest(ident, req.context, req.load_result, req.entry_point_identity, req.dispatch_contract_identity,
+                           req.argument_set_identity, req.bindings, req.dependencies, req.kind)

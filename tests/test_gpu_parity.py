@@ -628,3 +628,21 @@ def test_device_scan_sum_u32_unaligned_repeated_and_rejections(gpu, orc):
     for bad in (dict(values=src, output=src), dict(values=buf.view(0, 8), output=res.view(0, 7))):
         with pytest.raises(fe.Fe2o3Error):
             fe.check_args("device_scan_u32", fe.make_args("device_scan_u32", exclusive=0, **bad))
+
+
+def test_dispatch_record_of_a_prepared_launch(gpu):
+    # crates/fe2o3-host-api/src/dispatch.rs:96-268: the record that describes one launch of this library
+    import hashlib
+    fe, ctx, stream = gpu
+    from fe2o3_b200 import host_api as ha
+    x = np.zeros(4 * 256, np.float32)
+    i, o = Guarded(fe, stream, x), Guarded(fe, stream, x)
+    args = fe.make_args("row_softmax_v1", input=i.slice, output=o.slice, rows=4, cols=256)
+    prep = fe.prepare(ctx, "row_softmax_v1", input=i.slice, output=o.slice, rows=4, cols=256)
+    context = ha.OperationContext(ha.commit("FlowScopeId", b"test"), ha.commit("OperationId", b"softmax"), 1)
+    loaded = ha.LoadedResult(ha.commit("LoadResultId", b"lib"), ha.commit("LoadedObjectId", b"lib"), 1)
+    req = ha.dispatch_request_for(prep, args, context, loaded, written=("output",))
+    assert [b.ordinal for b in req.bindings] == [0, 1] and [b.access for b in req.bindings] == [ha.ACCESS_READ, ha.ACCESS_WRITE]
+    assert all(b.byte_len == 4 * 256 * 4 for b in req.bindings)
+    assert req.identity == hashlib.sha256(req.encode_identity_preimage()).digest()
+    assert req.entry_point_identity == ha.commit("EntryPointId", b"row_softmax_v1")

@@ -1,0 +1,142 @@
+"""Dispatch records of the host API: canonical preimages and structural rejections.
+
+The properties checked are those of crates/fe2o3-host-api/tests/hostile_invariants.rs
+(:159-228 identity domains and preimages, :887-941 preimage bounds) plus byte-level layouts
+written out from crates/fe2o3-host-api/src/canonical.rs:13-21 and src/dispatch.rs:234-268.
+"""
+import struct
+
+import pytest
+
+from fe2o3_b200 import host_api as ha
+
+
+def d(byte):
+    return bytes([byte]) * 32
+
+
+def context(**kw):
+    return ha.OperationContext(d(1), d(2), kw.pop("attempt", 1), kw.pop("parent", None), kw.pop("events", ()))
+
+
+LOADED = ha.LoadedResult(d(3), d(4), 7)
+
+
+def request(**kw):
+    return ha.DispatchRequest(kw.pop("identity", d(9)), kw.pop("context", context()), kw.pop("load", LOADED), d(5), d(6), d(7),
+                              kw.pop("bindings", ()), kw.pop("dependencies", ()), kw.pop("kind", None))
+
+
+def test_identity_domains_are_unique_and_preimages_start_with_magic_and_domain():
+    assert len(set(ha.DOMAINS.values())) == len(ha.DOMAINS)
+    assert all(v.startswith(b"fe2o3.host.") and v.endswith(b".v1") for v in ha.DOMAINS.values())
+    pre = request().encode_identity_preimage()
+    dom = ha.DOMAINS["DispatchRequestId"]
+    assert pre.startswith(b"F2HOSTP1" + struct.pack("<H", len(dom)) + dom + struct.pack("<H", 1))
+
+
+def test_finite_dispatch_request_preimage_layout_byte_for_byte():
+    b0 = ha.ResourceBinding(0, d(0x10), ha.ACCESS_READ, 16, 4096)
+    b1 = ha.ResourceBinding(1, d(0x11), ha.ACCESS_WRITE, 0, 64)
+    dep = ha.DispatchDependency(d(0x20), d(0x21))
+    ctx = context(attempt=3, parent=d(8), events=((ha.FLOW_LOAD, d(0x30)), (ha.FLOW_DISPATCH, d(0x2f))))
+    pre = request(context=ctx, bindings=(b0, b1), dependencies=(dep,)).encode_identity_preimage()
+    dom = ha.DOMAINS["DispatchRequestId"]
+    want = (b"F2HOSTP1" + struct.pack("<H", len(dom)) + dom + struct.pack("<H", 1)
+            + d(1) + d(2) + struct.pack("<H", 3) + b"\x01" + d(8)                       # context
+            + struct.pack("<H", 2) + b"\x03" + d(0x30) + b"\x04" + d(0x2f)                 # causal events
+            + d(3) + d(4) + struct.pack("<Q", 7) + d(5) + d(6) + d(7) + b"\x01"          # load result, ids, finite
+            + struct.pack("<H", 2)
+            + struct.pack("<H", 0) + d(0x10) + b"\x01" + struct.pack("<QQ", 16, 4096)
+            + struct.pack("<H", 1) + d(0x11) + b"\x02" + struct.pack("<QQ", 0, 64)
+            + struct.pack("<H", 1) + d(0x20) + d(0x21))
+    assert pre == want
+
+
+def test_preimage_excludes_the_declared_identity_and_covers_every_field():
+    first = request()
+    assert first.encode_identity_preimage() == request(identity=d(0x77)).encode_identity_preimage()
+    variants = [request(context=context(attempt=2)), request(load=ha.LoadedResult(d(3), d(4), 8)),
+                request(bindings=(ha.ResourceBinding(0, d(1), ha.ACCESS_ATOMIC, 0, 1),)),
+                request(dependencies=(ha.DispatchDependency(d(1), d(2)),)),
+                request(kind=ha.PersistentTask(d(1), d(2), 5, 1))]
+    pres = {v.encode_identity_preimage() for v in variants} | {first.encode_identity_preimage()}
+    assert len(pres) == len(variants) + 1
+
+
+def test_persistent_task_kind_is_encoded_after_tag_two():
+    pre = request(kind=ha.PersistentTask(d(0x41), d(0x42), 0xdeadbeef, 9)).encode_identity_preimage()
+    assert b"\x02" + d(0x41) + d(0x42) + struct.pack("<IQ", 0xdeadbeef, 9) + struct.pack("<HH", 0, 0) == pre[-(1 + 64 + 12 + 4):]
+
+
+def test_structural_rejections():
+    with pytest.raises(ha.HostContractError) as e:
+        context(attempt=0)
+    assert (e.value.kind, e.value.field) == ("Empty", "OperationAttempt")
+    with pytest.raises(ha.HostContractError) as e:
+        context(parent=d(2))
+    assert (e.value.kind, e.value.field) == ("Mismatch", "ParentOperation")
+    with pytest.raises(ha.HostContractError) as e:
+        context(events=((ha.FLOW_WAIT, d(1)), (ha.FLOW_LOAD, d(1))))
+    assert e.value.kind == "NonCanonicalOrder"
+    with pytest.raises(ha.HostContractError) as e:
+        context(events=((ha.FLOW_LOAD, d(1)), (ha.FLOW_LOAD, d(1))))
+    assert e.value.kind == "Duplicate"
+    with pytest.raises(ha.HostContractError) as e:
+        ha.ResourceBinding(0, d(1), ha.ACCESS_READ, 0, 0)
+    assert (e.value.kind, e.value.field) == ("Empty", "ResourceRange")
+    with pytest.raises(ha.HostContractError) as e:
+        ha.ResourceBinding(0, d(1), ha.ACCESS_READ, (1 << 64) - 8, 8)
+    assert e.value.kind == "ArithmeticOverflow"
+    with pytest.raises(ha.HostContractError) as e:      # ordinals must be 0, 1, 2, ...
+        request(bindings=(ha.ResourceBinding(1, d(1), ha.ACCESS_READ, 0, 1),))
+    assert (e.value.kind, e.value.field) == ("NonCanonicalOrder", "DispatchBindings")
+    with pytest.raises(ha.HostContractError) as e:
+        request(bindings=tuple(ha.ResourceBinding(i, d(1), ha.ACCESS_READ, 0, 1) for i in range(129)))
+    assert e.value.kind == "TooManyItems"
+    with pytest.raises(ha.HostContractError) as e:      # two dependencies on one completion signal
+        request(dependencies=(ha.DispatchDependency(d(1), d(2)), ha.DispatchDependency(d(1), d(3))))
+    assert (e.value.kind, e.value.field) == ("Duplicate", "DispatchDependencies")
+    with pytest.raises(ha.HostContractError) as e:
+        request(dependencies=(ha.DispatchDependency(d(2), d(2)), ha.DispatchDependency(d(1), d(3))))
+    assert e.value.kind == "NonCanonicalOrder"
+    with pytest.raises(ha.HostContractError) as e:
+        request(kind=ha.PersistentTask(d(1), d(2), 1, 0))
+    assert (e.value.kind, e.value.field) == ("Empty", "ServiceEpoch")
+
+
+def test_dispatch_result_outcomes_and_diagnostics():
+    req = request()
+    ok = ha.DispatchResult(d(0x50), req, ha.OUTCOME_SUBMITTED, d(0x51), d(0x52),
+                           (ha.Diagnostic(7, ha.SEVERITY_NOTE, "queued", subject=d(0x53)),))
+    dom = ha.DOMAINS["DispatchResultId"]
+    want = (b"F2HOSTP1" + struct.pack("<H", len(dom)) + dom + struct.pack("<H", 1) + d(9) + d(4) + b"\x01" + d(0x51) + d(0x52)
+            + struct.pack("<H", 1) + struct.pack("<I", 7) + b"\x01" + b"\x01" + d(0x53) + struct.pack("<H", 6) + b"queued")
+    assert ok.encode_identity_preimage() == want
+    failed = ha.DispatchResult(d(0x50), req, ha.OUTCOME_FAILED, diagnostics=(ha.Diagnostic(1, ha.SEVERITY_ERROR, "no device"),))
+    assert failed.encode_identity_preimage().endswith(b"\x03" + struct.pack("<H", 1) + struct.pack("<I", 1) + b"\x03\x00"
+                                                      + struct.pack("<H", 9) + b"no device")
+    with pytest.raises(ha.HostContractError) as e:      # a failure needs an error diagnostic
+        ha.DispatchResult(d(0x50), req, ha.OUTCOME_REJECTED)
+    assert e.value.kind == "MissingFailureDiagnostic"
+    with pytest.raises(ha.HostContractError) as e:      # a submission may not carry an error diagnostic
+        ha.DispatchResult(d(0x50), req, ha.OUTCOME_SUBMITTED, d(1), d(2), (ha.Diagnostic(1, ha.SEVERITY_ERROR, "x"),))
+    assert e.value.kind == "InvalidOutcome"
+    for bad, kind in (("", "Empty"), ("a\0b", "DiagnosticContainsNul"), ("x" * 1025, "LimitExceeded")):
+        with pytest.raises(ha.HostContractError) as e:
+            ha.Diagnostic(1, ha.SEVERITY_NOTE, bad)
+        assert e.value.kind == kind
+    with pytest.raises(ha.HostContractError):
+        ha.Diagnostic(0, ha.SEVERITY_NOTE, "zero code")
+
+
+def test_maximum_valid_records_have_bounded_identity_preimages():
+    events = tuple((ha.FLOW_DISPATCH, bytes([i]) * 32) for i in range(64))
+    bindings = tuple(ha.ResourceBinding(i, d(1), ha.ACCESS_READ_WRITE, 0, 1) for i in range(128))
+    deps = tuple(ha.DispatchDependency(bytes([i]) * 32, d(0)) for i in range(128))
+    req = request(context=context(events=events), bindings=bindings, dependencies=deps,
+                  kind=ha.PersistentTask(d(1), d(2), 3, 4))
+    assert len(req.encode_identity_preimage()) <= ha.MAX_IDENTITY_PREIMAGE_BYTES_V1
+    diags = tuple(ha.Diagnostic(1 + i, ha.SEVERITY_ERROR, "m" * 1024, subject=d(1)) for i in range(64))
+    res = ha.DispatchResult(d(1), req, ha.OUTCOME_FAILED, diagnostics=diags)
+    assert len(res.encode_identity_preimage()) <= ha.MAX_IDENTITY_PREIMAGE_BYTES_V1
