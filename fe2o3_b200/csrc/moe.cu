@@ -190,6 +190,7 @@ moe_gate_staged_kernel(const uint16_t *__restrict__ x, const uint16_t *__restric
     float acc[EPT];
 #pragma unroll
     for (int q = 0; q < EPT; ++q) acc[q] = 0.0f;
+    uint64_t acc2[2] = {0ull, 0ull};   // the four accumulators as two packed pairs (EPT == 4)
     const bool vec = (d_model % 8u) == 0 && ((reinterpret_cast<uint64_t>(x) | reinterpret_cast<uint64_t>(wg)) & 15u) == 0;
     uint4 xpre[kXPer], wpre[kWPer];
     auto prefetch = [&](uint32_t k0) {
@@ -252,26 +253,42 @@ moe_gate_staged_kernel(const uint16_t *__restrict__ x, const uint16_t *__restric
                 for (int i = 0; i < 8; ++i) xv[i] = xs[kk + i][lane];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    float w[EPT];
                     if constexpr (EPT == 4) {
+                        // two experts per instruction: the packed forms round each half exactly as the
+                        // scalar multiply and add do, so the logits keep their bits
                         const float4 v = *reinterpret_cast<const float4 *>(&ws[kk + i][e0]);
-                        w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+                        const uint64_t xx = pack_f32x2(xv[i], xv[i]);
+                        acc2[0] = add_f32x2(acc2[0], mul_f32x2(xx, pack_f32x2(v.x, v.y)));
+                        acc2[1] = add_f32x2(acc2[1], mul_f32x2(xx, pack_f32x2(v.z, v.w)));
                     } else {
+                        float w[EPT];
 #pragma unroll
                         for (int q = 0; q < EPT; ++q) w[q] = ws[kk + i][e0 + q];
-                    }
 #pragma unroll
-                    for (int q = 0; q < EPT; ++q) acc[q] = __fadd_rn(acc[q], __fmul_rn(xv[i], w[q]));
+                        for (int q = 0; q < EPT; ++q) acc[q] = __fadd_rn(acc[q], __fmul_rn(xv[i], w[q]));
+                    }
                 }
             }
         } else {
+            if constexpr (EPT == 4) {   // leave the packed accumulators for the ragged chunk
+                unpack_f32x2(acc2[0], acc[0], acc[1]);
+                unpack_f32x2(acc2[1], acc[2], acc[3]);
+            }
             for (uint32_t kk = 0; kk < kc; ++kk) {
                 const float xv = xs[kk][lane];
 #pragma unroll
                 for (int q = 0; q < EPT; ++q) acc[q] = __fadd_rn(acc[q], __fmul_rn(xv, ws[kk][e0 + q]));
             }
+            if constexpr (EPT == 4) {
+                acc2[0] = pack_f32x2(acc[0], acc[1]);
+                acc2[1] = pack_f32x2(acc[2], acc[3]);
+            }
         }
         __syncthreads();
+    }
+    if constexpr (EPT == 4) {
+        unpack_f32x2(acc2[0], acc[0], acc[1]);
+        unpack_f32x2(acc2[1], acc[2], acc[3]);
     }
     if (t0 + lane < tokens) {
 #pragma unroll
