@@ -142,6 +142,7 @@ class Harness:
 NCU_TRAFFIC = {
     ("masked_reduce_u32", 1 << 28): 2147519744 + 3300352,
     ("row_softmax_v1", 65536 * 1024): 268459008 + 216675072,
+    ("device_scan_u32", 1 << 28): 1074373120 + 1021001728,
     ("tiled_gemm_v1", (8192, 8192, 8192)): 1046762752 + 250886400,
     ("flash_attention_v1", (4, 16, 2048, 64)): 50588160 + 2605312,
     # grouped FFN GEMMs of one pass, average of the two launches (GEMM-1 501 MB, GEMM-2 880 MB)
@@ -243,7 +244,7 @@ def wl_scan(h, steps, warmup, n=1 << 28, cpu=True):
     alg = n * 8
     res = {"ms_per_step": step_ms, "value": h.world * n / (step_ms * 1e-3), "unit": "elements/s", "launches": steps,
            "roofline": roofline("hbm", alg / (float(np.mean(ms)) * 1e-3) / 1e9, peaks["hbm_gbs"], "GB/s",
-                                peak_source=peaks["source"]),
+                                traffic=NCU_TRAFFIC.get(("device_scan_u32", n)), peak_source=peaks["source"]),
            "workload": {"workload": "device_scan_u32", "elements": n, "values": "uniform[0,2^16) seed 1 domain 3",
                         "algorithmic_bytes_per_step": alg, "l2": "input+output (2 GiB) larger than L2"}}
 
