@@ -8,39 +8,61 @@
 // shifts by one and starts at zero, addition wraps) and extends the scope to a
 // whole array in one pass over HBM: 4 bytes read and 4 bytes written per element.
 //
-// Single pass with decoupled look-back.  A tile is 16384 elements: each of the eight
-// warps owns 2048 consecutive elements and walks them in sixteen coalesced passes of
-// 32 lanes x 16 bytes, carrying its running total from pass to pass in registers,
-// so the block synchronises only once per tile (to combine the warp totals).  Tiles
-// are handed out by an atomic ticket, so a tile only ever waits for tiles that
-// started before it.  Each tile publishes its aggregate, then warp 0 walks back over
-// its predecessors' descriptors, 128 at a time (four per lane, the four loads in
-// flight together), up to the nearest one whose inclusive prefix is known, and
-// publishes the tile's own inclusive prefix.  Measured at 2^28 elements on B200:
-// 32-wide steps over 4096-element tiles 2.3 TB/s, this form 3.4 TB/s (8192- and
-// 16384-element tiles alike); without the
-// look-back the same loads and stores run at 6.6 TB/s, so what is left is the wait
-// for the predecessors.  Two variants were slower and are not kept: a block-wide
-// 1024-descriptor step (more polling traffic on the descriptor lines) and
-// persistent blocks that prefetch their next tile (a prefetched tile cannot publish
-// its aggregate until its block has finished the tile before it, which lengthens
-// every successor's wait).
+// Single pass, staged through shared memory, with the carries between tiles taken
+// from published tile sums.  One persistent block per SM; tiles of 8192 elements are
+// handed out by an atomic ticket, so a tile only ever waits for tiles that started
+// before it.  Four roles:
+//   warp 0      producer: takes tickets and fills a six-stage ring of 32 KiB tiles
+//               with bulk copies (an mbarrier per stage counts the bytes)
+//   warps 1-4   aggregate: as soon as a tile has landed they sum it and publish its
+//               aggregate, so the aggregates of all tiles in flight appear at the
+//               speed of the memory system, whatever the rest of the block waits for
+//   warp 5      prefix: keeps the sum of everything up to the block's previous tile and
+//               adds the aggregates of the tiles between that one and the next (about
+//               one per SM, fetched in one round trip).  No block waits for another
+//               block's prefix, only for aggregates, so there is no chain across blocks
+//   warps 6-13  finish: scan the tile from shared memory with that prefix and store it
+//               with 16-byte writes; the warp scans of a tile run in lockstep
+// The ring keeps 192 KiB per SM in flight, three times what a register-resident tile
+// per thread allows.  Two earlier forms were measured and replaced: one pass over
+// registers with a decoupled look-back in the same warps (0.53 of the HBM copy rate,
+// bound by the wait for the predecessor's prefix), and this staging with a look-back
+// warp that walked back to the nearest published inclusive prefix (0.68-0.76: with
+// every tile of a wave in flight at once the nearest such prefix is a wave or more
+// behind, and the walk became a serial chain of L2 round trips per SM).
 // A descriptor is one 64-bit word {state, value}; it carries everything its reader
-// needs, so relaxed device-scope accesses are enough (acquire loads would also
-// serialise the four loads of a step: each would have to complete before the
-// next could issue).  The launch clears the ticket and the descriptors first.
-// Waits are bounded and record FE2O3_KSTATUS_WAIT_EXPIRED.
+// needs, so relaxed device-scope accesses are enough.  The launch clears the ticket
+// and the descriptors first.  Every wait is bounded and records
+// FE2O3_KSTATUS_WAIT_EXPIRED.
 #include "common.cuh"
+
+#include <mutex>
 
 namespace {
 
-constexpr int kScanThreads = 256;
-constexpr int kPasses = 16;                                         // 16-byte vectors per thread
-constexpr uint32_t kWarpElems = kPasses * 32 * 4;                   // 2048 consecutive elements per warp
-constexpr uint32_t kTileElems = (kScanThreads / 32) * kWarpElems;   // 16384
-constexpr int kWindow = 4;                                          // descriptors per lane and look-back step
-constexpr uint32_t kStateAggregate = 1, kStateInclusive = 2;
-constexpr uint32_t kLookbackSpin = 1u << 22;
+constexpr int kStages = 6;
+constexpr uint32_t kTileElems = 8192;
+constexpr uint32_t kTileBytes = kTileElems * 4;
+constexpr int kAggWarps = 4;                                        // aggregate warps: 2048 consecutive elements each
+constexpr int kFinishWarps = 8;                                     // scan-and-store warps: 1024 consecutive elements each
+constexpr uint32_t kPart = kTileElems / kFinishWarps;               // 1024
+constexpr int kPartVecs = kPart / 128;                              // a part is 8 rows of 32 lanes x 16 bytes
+constexpr int kLaneVecs = 2;                                        // consecutive 16-byte groups a finish lane owns per pass
+constexpr int kPasses = kPartVecs / kLaneVecs;                      // warp scans per finish warp and tile
+constexpr int kScanThreads = 32 * (1 + kAggWarps + 1 + kFinishWarps);   // 480
+constexpr int kWindow = 6;                                          // descriptors per lane and step of the prefix warp: 192, a little over one tile per SM
+constexpr uint32_t kStateAggregate = 1;   // state 0: not yet published (the launch clears the descriptors)
+constexpr uint32_t kDescSpin = 1u << 22;
+constexpr uint32_t kNoTile = 0xffffffffu;
+
+struct __align__(16) ScanShared {
+    uint64_t full[kStages], empty[kStages], agg_ready[kStages], prefix_ready[kStages];
+    uint32_t tile[kStages];                // ticket of the tile in each stage (kNoTile: the array is exhausted)
+    uint32_t part[kStages][kFinishWarps];  // sums of the eight parts of the tile
+    uint32_t prefix[kStages];              // exclusive prefix of the tile (sum of everything before it)
+    uint32_t arrivals[kStages];            // aggregate warps done with the stage
+};
+constexpr uint32_t kSmemBytes = kStages * kTileBytes + sizeof(ScanShared) + 1024;
 
 __device__ __forceinline__ void desc_store(uint64_t *p, uint32_t state, uint32_t value) {
     const uint64_t v = ((uint64_t)state << 32) | value;
@@ -52,132 +74,225 @@ __device__ __forceinline__ uint64_t desc_load(const uint64_t *p) {
     return v;
 }
 
-__global__ void __launch_bounds__(kScanThreads)
-device_scan_u32_kernel(const uint32_t *in, uint32_t *out, uint64_t n, uint32_t exclusive,
-                       uint32_t *ticket, uint64_t *desc, uint32_t *status) {
-    __shared__ uint32_t s_tile, s_warp[kScanThreads / 32], s_prefix;
-    __shared__ int s_ok;
+__global__ void __launch_bounds__(kScanThreads, 1)
+device_scan_u32_kernel(const uint32_t *in, uint32_t *out, uint64_t n, uint32_t exclusive, uint32_t *ticket,
+                       uint64_t *desc, uint32_t *status) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint32_t *ring = reinterpret_cast<uint32_t *>(smem);
+    ScanShared &sh = *reinterpret_cast<ScanShared *>(smem + kStages * kTileBytes);
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    if (tid == 0) s_tile = atomicAdd(ticket, 1u);
-    __syncthreads();
-    const uint32_t tile = s_tile;
-    const uint64_t base = (uint64_t)tile * kTileElems;
-    if (base >= n) return;
-    const bool vec = base + kTileElems <= n && ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0;
 
-    // pass j of this warp is elements [2048 warp + 128 j, +128) of the tile; this lane owns elements 4 lane .. 4 lane + 3 of it
-    const uint64_t wbase = base + (uint64_t)warp * kWarpElems + lane * 4;
-    uint32_t incl[kPasses][4];
-#pragma unroll
-    for (int j = 0; j < kPasses; ++j) {
-        const uint64_t e = wbase + (uint64_t)j * 128;
-        if (vec) {
-            const uint4 x = __ldcs(reinterpret_cast<const uint4 *>(in + e));
-            incl[j][0] = x.x; incl[j][1] = x.y; incl[j][2] = x.z; incl[j][3] = x.w;
-        } else {
-#pragma unroll
-            for (int c = 0; c < 4; ++c) incl[j][c] = e + c < n ? in[e + c] : 0u;
+    if (tid == 0) {
+        for (int i = 0; i < kStages; ++i) {
+            mbar_init(&sh.full[i], 1);
+            mbar_init(&sh.empty[i], kFinishWarps);
+            mbar_init(&sh.agg_ready[i], 1);
+            mbar_init(&sh.prefix_ready[i], 1);
+            sh.arrivals[i] = 0;
         }
+        mbar_fence_init();
     }
-    // inclusive scan inside the warp's 2048 elements, in place: thread-local, across the lanes, carried over the passes
-    uint32_t before[kPasses];   // sum of everything in the warp's part before this lane's four elements of pass j
-    uint32_t carry = 0;         // sum of this warp's passes before the current one
-#pragma unroll
-    for (int j = 0; j < kPasses; ++j) {
-#pragma unroll
-        for (int c = 1; c < 4; ++c) incl[j][c] += incl[j][c - 1];
-        const uint32_t own = incl[j][3];
-        uint32_t t = own;   // this lane's total, scanned over the warp
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const uint32_t up = __shfl_up_sync(0xffffffffu, t, o);
-            if (lane >= (uint32_t)o) t += up;
-        }
-        before[j] = carry + t - own;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) incl[j][c] += before[j];
-        carry += __shfl_sync(0xffffffffu, t, 31);
-    }
-    if (lane == 0) s_warp[warp] = carry;
     __syncthreads();
-    uint32_t warp_before = 0, aggregate = 0;
-#pragma unroll
-    for (int w = 0; w < kScanThreads / 32; ++w) {
-        const uint32_t wt = s_warp[w];
-        if ((uint32_t)w < warp) warp_before += wt;
-        aggregate += wt;
-    }
 
-    // decoupled look-back by warp 0, 128 predecessors per step (four descriptors per lane, loads in flight together)
     if (warp == 0) {
-        uint32_t prefix = 0;
+        // ------------------------------------------------------------ producer
         bool ok = true;
-        if (tile == 0) {
-            if (lane == 0) desc_store(desc, kStateInclusive, aggregate);
-        } else {
-            if (lane == 0) desc_store(desc + tile, kStateAggregate, aggregate);
-            int64_t idx = (int64_t)tile - 1;   // nearest predecessor not yet accounted for
-            bool done = false;
-            while (ok && !done) {
-                // descriptor q of this lane is predecessor idx - (32 q + lane): q = 0 holds the nearest 32
+        for (uint32_t k = 0; ok; ++k) {
+            const uint32_t st = k % kStages, ph = (k / kStages) & 1;
+            if (!mbar_wait_warp(&sh.empty[st], ph ^ 1)) { ok = false; break; }
+            uint32_t t = 0;
+            if (lane == 0) t = atomicAdd(ticket, 1u);
+            t = __shfl_sync(0xffffffffu, t, 0);
+            const uint64_t base = (uint64_t)t * kTileElems;
+            if (base >= n) {
+                // the array is exhausted: tell the consumers and stop
+                if (lane == 0) {
+                    sh.tile[st] = kNoTile;
+                    mbar_arrive(&sh.full[st]);
+                }
+                __syncwarp();
+                break;
+            }
+            uint32_t *dst = ring + st * kTileElems;
+            if (aligned && base + kTileElems <= n) {
+                if (lane == 0) {
+                    sh.tile[st] = t;
+                    mbar_arrive_expect_tx(&sh.full[st], kTileBytes);
+                    bulk_load_1d(dst, in + base, kTileBytes, &sh.full[st]);
+                }
+            } else {   // the last tile, or input the copy engine cannot address: plain loads, zero beyond the end
+                for (uint32_t i = lane; i < kTileElems; i += 32) dst[i] = base + i < n ? in[base + i] : 0u;
+                __syncwarp();
+                if (lane == 0) {
+                    sh.tile[st] = t;
+                    mbar_arrive(&sh.full[st]);
+                }
+            }
+            __syncwarp();
+        }
+        if (!ok && lane == 0) kstatus_set(status, FE2O3_KSTATUS_WAIT_EXPIRED);
+    } else if (warp <= kAggWarps) {
+        // ------------------------------------------------------------ aggregate warps
+        const uint32_t w = warp - 1;
+        for (uint32_t k = 0;; ++k) {
+            const uint32_t st = k % kStages, ph = (k / kStages) & 1;
+            if (!mbar_wait_warp(&sh.full[st], ph)) {
+                if (lane == 0) kstatus_set(status, FE2O3_KSTATUS_WAIT_EXPIRED);
+                break;
+            }
+            const uint32_t tile = sh.tile[st];
+            if (tile == kNoTile) break;
+            // this warp sums parts 2w and 2w + 1 of the tile
+            const uint4 *src = reinterpret_cast<const uint4 *>(ring + st * kTileElems + w * 2 * kPart) + lane;
+            uint32_t sum0 = 0, sum1 = 0;
+#pragma unroll
+            for (int j = 0; j < kPartVecs; ++j) {
+                const uint4 x = src[j * 32], y = src[(kPartVecs + j) * 32];
+                sum0 += (x.x + x.y) + (x.z + x.w);
+                sum1 += (y.x + y.y) + (y.z + y.w);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                sum0 += __shfl_xor_sync(0xffffffffu, sum0, o);
+                sum1 += __shfl_xor_sync(0xffffffffu, sum1, o);
+            }
+            // the last of the four warps to finish publishes the tile's aggregate
+            uint32_t last = 0;
+            if (lane == 0) {
+                sh.part[st][2 * w] = sum0;
+                sh.part[st][2 * w + 1] = sum1;
+                __threadfence_block();
+                last = atomicAdd(&sh.arrivals[st], 1u) == kAggWarps - 1 ? 1u : 0u;
+            }
+            last = __shfl_sync(0xffffffffu, last, 0);
+            if (last && lane == 0) {
+                __threadfence_block();
+                uint32_t aggregate = 0;
+                for (int q = 0; q < kFinishWarps; ++q) aggregate += sh.part[st][q];
+                sh.arrivals[st] = 0;
+                desc_store(desc + tile, kStateAggregate, aggregate);
+                mbar_arrive(&sh.agg_ready[st]);
+            }
+        }
+    } else if (warp == kAggWarps + 1) {
+        // ------------------------------------------------------------ prefix warp: runs ahead of the finish warps
+        // The block's tiles arrive in ticket order.  The warp keeps the sum of everything up to and
+        // including the block's previous tile, so the prefix of the next one only needs the aggregates
+        // of the tiles in between (about one per SM), which other blocks publish as their data lands.
+        bool ok = true;
+        uint32_t covered = 0;   // tiles [0, covered) are summed in `running`
+        uint32_t running = 0;
+        for (uint32_t k = 0; ok; ++k) {
+            const uint32_t st = k % kStages, ph = (k / kStages) & 1;
+            if (!mbar_wait_warp(&sh.full[st], ph)) { ok = false; break; }
+            const uint32_t tile = sh.tile[st];
+            if (tile == kNoTile) break;
+            uint32_t between = 0;
+            for (uint32_t b = covered; ok && b < tile; b += 32 * kWindow) {
                 uint64_t d[kWindow];
 #pragma unroll
-                for (int q = 0; q < kWindow; ++q) {
-                    const int64_t mine = idx - (32 * q + (int64_t)lane);
-                    d[q] = mine >= 0 ? desc_load(desc + mine) : ((uint64_t)kStateInclusive << 32);   // before the array: 0, final
+                for (int q = 0; q < kWindow; ++q) {   // all loads of the step in flight together
+                    const uint32_t mine = b + 32 * q + lane;
+                    d[q] = mine < tile ? desc_load(desc + mine) : ((uint64_t)kStateAggregate << 32);
                 }
 #pragma unroll
                 for (int q = 0; q < kWindow; ++q) {
-                    if (done || !ok) continue;
-                    const int64_t mine = idx - (32 * q + (int64_t)lane);
+                    const uint32_t mine = b + 32 * q + lane;
                     uint32_t spins = 0;
                     while ((d[q] >> 32) == 0) {
-                        if (++spins > kLookbackSpin) { ok = false; break; }
-                        __nanosleep(100);   // few reloads: pollers and writers share the descriptor lines in L2
+                        if (++spins > kDescSpin) { ok = false; break; }
+                        __nanosleep(100);
                         d[q] = desc_load(desc + mine);
                     }
-                    ok = __all_sync(0xffffffffu, ok);
-                    if (!ok) continue;
-                    // lanes 0 .. first lane holding an inclusive prefix contribute; the walk ends there
-                    const uint32_t final_mask = __ballot_sync(0xffffffffu, (uint32_t)(d[q] >> 32) == kStateInclusive);
-                    const uint32_t last = final_mask ? (uint32_t)__ffs(final_mask) - 1 : 31u;
-                    uint32_t contrib = lane <= last ? (uint32_t)d[q] : 0u;
-#pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) contrib += __shfl_xor_sync(0xffffffffu, contrib, o);
-                    prefix += contrib;
-                    done = final_mask != 0;
+                    between += (uint32_t)d[q];
                 }
-                idx -= 32 * kWindow;
+                ok = __all_sync(0xffffffffu, ok);
             }
-            if (ok && lane == 0) desc_store(desc + tile, kStateInclusive, prefix + aggregate);
+            if (!ok) break;
+            between = __reduce_add_sync(0xffffffffu, between);
+            if (!mbar_wait_warp(&sh.agg_ready[st], ph)) { ok = false; break; }
+            uint32_t aggregate = 0;
+            for (int q = 0; q < kFinishWarps; ++q) aggregate += sh.part[st][q];
+            const uint32_t prefix = running + between;
+            if (lane == 0) {
+                sh.prefix[st] = prefix;
+                mbar_arrive(&sh.prefix_ready[st]);
+            }
+            running = prefix + aggregate;
+            covered = tile + 1;
         }
-        if (lane == 0) {
-            s_prefix = prefix;
-            s_ok = ok ? 1 : 0;
-            if (!ok) kstatus_set(status, FE2O3_KSTATUS_WAIT_EXPIRED);
-        }
-    }
-    __syncthreads();
-    if (!s_ok) return;
-    const uint32_t prefix = s_prefix + warp_before;
+        if (!ok && lane == 0) kstatus_set(status, FE2O3_KSTATUS_WAIT_EXPIRED);   // the finish warps' waits expire in turn
+    } else {
+        // ------------------------------------------------------------ finish warps
+        const uint32_t w = warp - 2 - kAggWarps;
+        for (uint32_t k = 0;; ++k) {
+            const uint32_t st = k % kStages, ph = (k / kStages) & 1;
+            const bool ok = mbar_wait_warp(&sh.full[st], ph);
+            const uint32_t tile = ok ? sh.tile[st] : kNoTile;
+            if (!ok && lane == 0) kstatus_set(status, FE2O3_KSTATUS_WAIT_EXPIRED);
+            if (tile == kNoTile) break;
+            if (!mbar_wait_warp(&sh.prefix_ready[st], ph)) {
+                if (lane == 0) kstatus_set(status, FE2O3_KSTATUS_WAIT_EXPIRED);
+                break;
+            }
+            uint32_t carry = sh.prefix[st];   // everything before this warp's first element
+            for (uint32_t q = 0; q < w; ++q) carry += sh.part[st][q];
+            const uint64_t base = (uint64_t)tile * kTileElems + (uint64_t)w * kPart + lane * (4 * kLaneVecs);
+            const bool vec = aligned && (uint64_t)tile * kTileElems + kTileElems <= n;
+            const uint4 *src = reinterpret_cast<const uint4 *>(ring + st * kTileElems + w * kPart) + lane * kLaneVecs;
+            // Each lane owns kLaneVecs consecutive 16-byte groups per pass, so one warp scan covers
+            // 32 * 4 * kLaneVecs elements.  The passes' warp scans are independent and run in
+            // lockstep: each shuffle step issues one shuffle per pass back to back, and the latency
+            // of a chain is paid once per tile, not once per pass.
+            uint4 x[kPasses][kLaneVecs];
+            uint32_t own[kPasses], t[kPasses];   // each lane's total per pass; the same scanned over the warp
 #pragma unroll
-    for (int j = 0; j < kPasses; ++j) {
-        const uint64_t e = wbase + (uint64_t)j * 128;
-        uint32_t r[4];
-        if (exclusive) {   // element i of the exclusive form is the inclusive value of element i - 1
-            r[0] = before[j] + prefix;
+            for (int j = 0; j < kPasses; ++j) {
+                own[j] = 0;
 #pragma unroll
-            for (int c = 1; c < 4; ++c) r[c] = incl[j][c - 1] + prefix;
-        } else {
+                for (int c = 0; c < kLaneVecs; ++c) {
+                    x[j][c] = src[j * 32 * kLaneVecs + c];
+                    own[j] += (x[j][c].x + x[j][c].y) + (x[j][c].z + x[j][c].w);
+                }
+                t[j] = own[j];
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh.empty[st]);   // the part is in registers: the stage may be refilled
 #pragma unroll
-            for (int c = 0; c < 4; ++c) r[c] = incl[j][c] + prefix;
-        }
-        if (vec) {
-            __stcs(reinterpret_cast<uint4 *>(out + e), make_uint4(r[0], r[1], r[2], r[3]));
-        } else {
+            for (int o = 1; o < 32; o <<= 1) {
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
-                if (e + c < n) out[e + c] = r[c];
+                for (int j = 0; j < kPasses; ++j) {
+                    const uint32_t up = __shfl_up_sync(0xffffffffu, t[j], o);
+                    if (lane >= (uint32_t)o) t[j] += up;
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < kPasses; ++j) {
+                uint32_t run = carry + t[j] - own[j];   // everything before this lane's first element of the pass
+                carry += __shfl_sync(0xffffffffu, t[j], 31);
+#pragma unroll
+                for (int c = 0; c < kLaneVecs; ++c) {
+                    const uint32_t v[4] = {x[j][c].x, x[j][c].x + x[j][c].y, x[j][c].x + x[j][c].y + x[j][c].z,
+                                           x[j][c].x + x[j][c].y + x[j][c].z + x[j][c].w};
+                    uint32_t r[4];
+                    if (exclusive) {   // element i of the exclusive form is the inclusive value of element i - 1
+                        r[0] = run; r[1] = run + v[0]; r[2] = run + v[1]; r[3] = run + v[2];
+                    } else {
+                        r[0] = run + v[0]; r[1] = run + v[1]; r[2] = run + v[2]; r[3] = run + v[3];
+                    }
+                    run += v[3];
+                    const uint64_t e = base + (uint64_t)j * (128 * kLaneVecs) + c * 4;
+                    if (vec) {
+                        __stcs(reinterpret_cast<uint4 *>(out + e), make_uint4(r[0], r[1], r[2], r[3]));
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            if (e + i < n) out[e + i] = r[i];
+                    }
+                }
+            }
         }
     }
 }
@@ -188,15 +303,21 @@ int32_t launch_device_scan_u32(fe2o3_ctx *ctx, cudaStream_t s, const void *args,
     const fe2o3_device_scan_u32_args *a = static_cast<const fe2o3_device_scan_u32_args *>(args);
     const uint64_t n = a->values.len;
     const uint32_t tiles = (uint32_t)((n + kTileElems - 1) / kTileElems);
-    if (geo) *geo = fe2o3_geometry{{tiles ? tiles : 1, 1, 1}, {kScanThreads, 1, 1}, 0, 1};
+    const uint32_t sms = ctx->sm_count > 0 ? (uint32_t)ctx->sm_count : 1u;
+    const uint32_t grid = tiles < sms ? (tiles ? tiles : 1u) : sms;
+    if (geo) *geo = fe2o3_geometry{{grid, 1, 1}, {kScanThreads, 1, 1}, kSmemBytes, 1};
     if (plan_only || n == 0) return FE2O3_OK;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        cudaFuncSetAttribute(device_scan_u32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+    });
     // ticket at word 0, descriptors from byte 64
     uint32_t *ticket = ctx->scan_scratch;
     uint64_t *desc = reinterpret_cast<uint64_t *>(ctx->scan_scratch + 16);
     FE2O3_CUDA(cudaMemsetAsync(ctx->scan_scratch, 0, 64 + (size_t)tiles * 8, s));
-    device_scan_u32_kernel<<<tiles, kScanThreads, 0, s>>>(reinterpret_cast<const uint32_t *>(a->values.ptr),
-                                                           reinterpret_cast<uint32_t *>(a->output.ptr), n, a->exclusive,
-                                                           ticket, desc, ctx->status_word);
+    device_scan_u32_kernel<<<grid, kScanThreads, kSmemBytes, s>>>(reinterpret_cast<const uint32_t *>(a->values.ptr),
+                                                                  reinterpret_cast<uint32_t *>(a->output.ptr), n,
+                                                                  a->exclusive, ticket, desc, ctx->status_word);
     fe2o3_count_launch(1);
     return fe2o3_cuda_status(cudaGetLastError(), "device_scan_sum_u32");
 }
