@@ -49,7 +49,7 @@ constexpr uint32_t kPart = kTileElems / kFinishWarps;               // 1024
 constexpr int kPartVecs = kPart / 128;                              // a part is 8 rows of 32 lanes x 16 bytes
 constexpr int kLaneVecs = 2;                                        // consecutive 16-byte groups a finish lane owns per pass
 constexpr int kPasses = kPartVecs / kLaneVecs;                      // warp scans per finish warp and tile
-constexpr int kScanThreads = 32 * (1 + kAggWarps + 1 + kFinishWarps);   // 480
+constexpr int kScanThreads = 32 * (1 + kAggWarps + 1 + kFinishWarps);   // 448
 constexpr int kWindow = 6;                                          // descriptors per lane and step of the prefix warp: 192, a little over one tile per SM
 constexpr uint32_t kStateAggregate = 1;   // state 0: not yet published (the launch clears the descriptors)
 constexpr uint32_t kDescSpin = 1u << 22;
