@@ -1,7 +1,8 @@
-"""Runtime-neutral dispatch records with the reference's canonical identity preimages.
+"""Runtime-neutral dispatch and wait records with the reference's canonical identity preimages.
 
-The dispatch flow of crates/fe2o3-host-api: operation context, resource bindings,
-completion dependencies, the dispatch request and its result, with the same structural
+The dispatch and wait flows of crates/fe2o3-host-api: operation context, resource bindings,
+completion dependencies, the dispatch request and its result, the bounded wait request over
+completion signals and its result (src/wait.rs:17-359), with the same structural
 validation and the same bytes in `encode_identity_preimage()` (magic "F2HOSTP1",
 little-endian, domain-separated; crates/fe2o3-host-api/src/canonical.rs:7-65,
 src/dispatch.rs:234-268 and :350-368, src/common.rs:331-341, :495-500, :580-586), so a run
@@ -9,8 +10,9 @@ log written by a host that launches through this library hashes to the identitie
 reference-side reader computes.  Records are inert descriptions: they own no runtime
 handle and nothing here talks to a device.
 
-Only the dispatch flow is mirrored; the compile, admit, load and wait flows of the crate
-use the same encoder and identity types and are not built.
+The dispatch and wait flows are mirrored (the two a host that launches a prepared kernel and
+waits for it goes through); the compile, admit and load flows of the crate use the same
+encoder and identity types and are not built.
 """
 import hashlib
 from dataclasses import dataclass, field
@@ -25,6 +27,7 @@ MAX_CAUSAL_EVENTS_V1 = 64
 MAX_IDENTITY_PREIMAGE_BYTES_V1 = 128 * 1024
 MAX_DISPATCH_BINDINGS_V1 = 128                     # src/dispatch.rs:19-22
 MAX_DISPATCH_DEPENDENCIES_V1 = 128
+MAX_WAIT_TARGETS_V1 = 256                          # src/wait.rs:17
 
 # identity domains used by the dispatch flow (src/identity.rs:55-272)
 DOMAINS = {
@@ -42,6 +45,10 @@ DOMAINS = {
     "LoadResultId": b"fe2o3.host.load.result.v1",
     "DispatchRequestId": b"fe2o3.host.dispatch.request.v1",
     "DispatchResultId": b"fe2o3.host.dispatch.result.v1",
+    "CompletionRecordId": b"fe2o3.host.completion-record.v1",
+    "DeadlineId": b"fe2o3.host.deadline.v1",
+    "WaitRequestId": b"fe2o3.host.wait.request.v1",
+    "WaitResultId": b"fe2o3.host.wait.result.v1",
     "CompileEventId": b"fe2o3.host.compile.event.v1",
     "AdmitEventId": b"fe2o3.host.admit.event.v1",
     "LoadEventId": b"fe2o3.host.load.event.v1",
@@ -326,6 +333,120 @@ class DispatchResult:
         return e.finish()
 
 
+# ------------------------------------------------------------------ wait flow (src/wait.rs)
+WAIT_ANY, WAIT_ALL = 1, 2                                                              # wait.rs:20-27
+COMPLETION_SUCCEEDED, COMPLETION_CANCELLED, COMPLETION_FAILED = 1, 2, 3                # wait.rs:30-39
+WAIT_SATISFIED, WAIT_PENDING, WAIT_REJECTED, WAIT_FAILED = 1, 2, 3, 4                  # tags of wait.rs:309-320
+
+
+@dataclass(frozen=True)
+class CompletionObservation:
+    """wait.rs:42-83: one terminal observation of a completion signal."""
+    signal_identity: bytes
+    record_identity: bytes
+    status: int
+
+    def __post_init__(self):
+        if self.status not in (COMPLETION_SUCCEEDED, COMPLETION_CANCELLED, COMPLETION_FAILED):
+            raise HostContractError("InvalidOutcome")
+
+    def encode(self, e):
+        e.digest(self.signal_identity)
+        e.digest(self.record_identity)
+        e.u8(self.status)
+
+
+@dataclass(frozen=True)
+class WaitRequest:
+    """wait.rs:107-207: a wait over a non-empty, strictly ordered set of completion signals."""
+    identity: bytes
+    context: OperationContext
+    mode: int
+    targets: Tuple[bytes, ...]
+    deadline_identity: Optional[bytes] = None
+
+    def __post_init__(self):
+        if self.mode not in (WAIT_ANY, WAIT_ALL):
+            raise HostContractError("InvalidOutcome")
+        if not self.targets:
+            raise HostContractError("Empty", "WaitTargets")
+        _strictly_ordered([digest(t) for t in self.targets], MAX_WAIT_TARGETS_V1, "WaitTargets")
+
+    def validate_dispatch_results(self, dispatch_results):
+        """wait.rs:170-194: exactly one submitted dispatch result per target, and nothing else."""
+        if len(dispatch_results) != len(self.targets):
+            raise HostContractError("MissingDispatchResult")
+        for target in self.targets:
+            matching = sum(1 for r in dispatch_results
+                           if r.outcome == OUTCOME_SUBMITTED and r.completion_signal_identity == target)
+            if matching != 1:
+                raise HostContractError("MissingDispatchResult")
+
+    def encode_identity_preimage(self):
+        e = Encoder(DOMAINS["WaitRequestId"])
+        self.context.encode(e)
+        e.u8(self.mode)
+        e.u16(len(self.targets))
+        for t in self.targets:
+            e.digest(t)
+        e.optional_digest(self.deadline_identity)
+        return e.finish()
+
+
+@dataclass(frozen=True)
+class WaitResult:
+    """wait.rs:209-325: the result of one wait request; target membership and the truth of the
+    Any / All predicate are checked against the request."""
+    identity: bytes
+    request: WaitRequest
+    outcome: int
+    observations: Tuple[CompletionObservation, ...] = ()
+    diagnostics: Tuple[Diagnostic, ...] = field(default_factory=tuple)
+
+    def __post_init__(self):
+        if self.outcome not in (WAIT_SATISFIED, WAIT_PENDING, WAIT_REJECTED, WAIT_FAILED):
+            raise HostContractError("InvalidOutcome")
+        if len(self.diagnostics) > MAX_DIAGNOSTICS_V1:
+            raise HostContractError("TooManyItems", "Diagnostics")
+        has_error = any(d.severity == SEVERITY_ERROR for d in self.diagnostics)
+        if self.outcome in (WAIT_REJECTED, WAIT_FAILED):
+            if not has_error:
+                raise HostContractError("MissingFailureDiagnostic")
+            if self.observations:
+                raise HostContractError("InvalidOutcome")   # the reference's Rejected / Failed carry none
+            return
+        obs = self.observations
+        if len(obs) > MAX_WAIT_TARGETS_V1:
+            raise HostContractError("TooManyItems", "WaitObservations")
+        for a, b in zip(obs, obs[1:]):
+            if a.signal_identity == b.signal_identity:
+                raise HostContractError("Duplicate", "WaitObservations")
+            if a.signal_identity > b.signal_identity:
+                raise HostContractError("NonCanonicalOrder", "WaitObservations")
+        targets = set(self.request.targets)
+        if any(o.signal_identity not in targets for o in obs):
+            raise HostContractError("UnknownWaitTarget")
+        satisfied = len(obs) > 0 if self.request.mode == WAIT_ANY else len(obs) == len(self.request.targets)
+        if satisfied != (self.outcome == WAIT_SATISFIED):
+            raise HostContractError("InvalidWaitDisposition")
+        if has_error:
+            raise HostContractError("InvalidOutcome")
+
+    def encode_identity_preimage(self):
+        e = Encoder(DOMAINS["WaitResultId"])
+        e.digest(self.request.identity)
+        e.u8(self.request.mode)
+        e.u8(self.outcome)
+        if self.outcome in (WAIT_SATISFIED, WAIT_PENDING):
+            e.u16(len(self.observations))
+            for o in self.observations:
+                o.encode(e)
+        e.u16(len(self.diagnostics))
+        for d in self.diagnostics:
+            d.encode(e)
+        return e.finish()
+
+
 # ------------------------------------------------------------------ this library's launches
 def commit(domain_name, *parts):
     """A commitment an integration may choose: SHA-256 over the identity's domain and the given parts.
@@ -363,3 +484,13 @@ def dispatch_request_for(prepared, op_args, context, load_result, written=(), el
     ident = hashlib.sha256(req.encode_identity_preimage()).digest()
     return DispatchRequest(ident, req.context, req.load_result, req.entry_point_identity, req.dispatch_contract_identity,
                            req.argument_set_identity, req.bindings, req.dependencies, req.kind)
+
+
+def wait_request_for(dispatch_results, context, mode=WAIT_ALL, deadline_identity=None):
+    """The wait request over the completion signals of the given submitted dispatch results (targets in
+    canonical order), checked against those results; its identity is the SHA-256 of its preimage."""
+    targets = tuple(sorted(r.completion_signal_identity for r in dispatch_results if r.outcome == OUTCOME_SUBMITTED))
+    req = WaitRequest(bytes(32), context, mode, targets, deadline_identity)
+    req.validate_dispatch_results(list(dispatch_results))
+    ident = hashlib.sha256(req.encode_identity_preimage()).digest()
+    return WaitRequest(ident, context, mode, targets, deadline_identity)

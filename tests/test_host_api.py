@@ -1,7 +1,7 @@
-"""Dispatch records of the host API: canonical preimages and structural rejections.
+"""Dispatch and wait records of the host API: canonical preimages and structural rejections.
 
 The properties checked are those of crates/fe2o3-host-api/tests/hostile_invariants.rs
-(:159-228 identity domains and preimages, :887-941 preimage bounds) plus byte-level layouts
+(:159-228 identity domains and preimages, :771-884 wait predicates, :887-941 preimage bounds) plus byte-level layouts
 written out from crates/fe2o3-host-api/src/canonical.rs:13-21 and src/dispatch.rs:234-268.
 """
 import struct
@@ -140,3 +140,97 @@ def test_maximum_valid_records_have_bounded_identity_preimages():
     diags = tuple(ha.Diagnostic(1 + i, ha.SEVERITY_ERROR, "m" * 1024, subject=d(1)) for i in range(64))
     res = ha.DispatchResult(d(1), req, ha.OUTCOME_FAILED, diagnostics=diags)
     assert len(res.encode_identity_preimage()) <= ha.MAX_IDENTITY_PREIMAGE_BYTES_V1
+
+
+# ---------------------------------------------------------------------------- wait flow
+def wait_request(mode=None, targets=(d(0x40), d(0x41)), **kw):
+    return ha.WaitRequest(kw.pop("identity", d(0x50)), kw.pop("context", context()),
+                          ha.WAIT_ALL if mode is None else mode, tuple(targets), kw.pop("deadline", None))
+
+
+def observed(sig, status=None):
+    return ha.CompletionObservation(sig, d(0x60), ha.COMPLETION_SUCCEEDED if status is None else status)
+
+
+def rejected(kind, field=None):
+    return pytest.raises(ha.HostContractError, match=kind if field is None else f"{kind}\\({field}\\)")
+
+
+def test_wait_request_rejects_empty_duplicate_unordered_and_oversized_target_sets():
+    with rejected("Empty", "WaitTargets"):
+        wait_request(ha.WAIT_ANY, targets=())
+    with rejected("Duplicate", "WaitTargets"):
+        wait_request(targets=(d(0x40), d(0x40)))
+    with rejected("NonCanonicalOrder", "WaitTargets"):
+        wait_request(targets=(d(0x41), d(0x40)))
+    many = tuple((20_000 + i).to_bytes(32, "big") for i in range(ha.MAX_WAIT_TARGETS_V1 + 1))
+    with rejected("TooManyItems", "WaitTargets"):
+        wait_request(targets=many)
+    assert len(wait_request(targets=many[:-1]).targets) == ha.MAX_WAIT_TARGETS_V1
+
+
+def test_wait_result_checks_membership_order_and_the_predicate():
+    a, b = d(0x40), d(0x41)
+    any_req, all_req = wait_request(ha.WAIT_ANY), wait_request(ha.WAIT_ALL)
+    with rejected("InvalidWaitDisposition"):      # Any is not satisfied by nothing
+        ha.WaitResult(d(0x70), any_req, ha.WAIT_SATISFIED, ())
+    with rejected("InvalidWaitDisposition"):      # Any with one observation is not pending
+        ha.WaitResult(d(0x70), any_req, ha.WAIT_PENDING, (observed(a),))
+    with rejected("UnknownWaitTarget"):
+        ha.WaitResult(d(0x70), any_req, ha.WAIT_SATISFIED, (observed(d(0x99)),))
+    with rejected("Duplicate", "WaitObservations"):
+        ha.WaitResult(d(0x70), any_req, ha.WAIT_SATISFIED, (observed(a), observed(a)))
+    with rejected("NonCanonicalOrder", "WaitObservations"):
+        ha.WaitResult(d(0x70), all_req, ha.WAIT_SATISFIED, (observed(b), observed(a)))
+    with rejected("InvalidWaitDisposition"):      # All needs every target
+        ha.WaitResult(d(0x70), all_req, ha.WAIT_SATISFIED, (observed(a),))
+    assert ha.WaitResult(d(0x70), all_req, ha.WAIT_PENDING, (observed(a),)).outcome == ha.WAIT_PENDING
+    assert ha.WaitResult(d(0x70), any_req, ha.WAIT_PENDING, ()).observations == ()
+    done = ha.WaitResult(d(0x70), all_req, ha.WAIT_SATISFIED, (observed(a), observed(b, ha.COMPLETION_FAILED)))
+    assert len(done.observations) == 2
+    err = ha.Diagnostic(7, ha.SEVERITY_ERROR, "device lost")
+    with rejected("InvalidOutcome"):              # a successful wait carries no error diagnostic
+        ha.WaitResult(d(0x70), any_req, ha.WAIT_SATISFIED, (observed(a),), (err,))
+    with rejected("MissingFailureDiagnostic"):
+        ha.WaitResult(d(0x70), any_req, ha.WAIT_FAILED)
+    with rejected("MissingFailureDiagnostic"):
+        ha.WaitResult(d(0x70), any_req, ha.WAIT_REJECTED, (), (ha.Diagnostic(7, ha.SEVERITY_WARNING, "slow"),))
+    assert ha.WaitResult(d(0x70), any_req, ha.WAIT_FAILED, (), (err,)).diagnostics == (err,)
+
+
+def test_wait_preimage_layouts_byte_for_byte():
+    req = wait_request(ha.WAIT_ANY, context=context(attempt=2), deadline=d(0x55))
+    dom = ha.DOMAINS["WaitRequestId"]
+    head = b"F2HOSTP1" + struct.pack("<H", len(dom)) + dom + struct.pack("<H", 1)
+    want = (head + d(1) + d(2) + struct.pack("<H", 2) + b"\x00" + struct.pack("<H", 0)    # context, no parent, no events
+            + b"\x01" + struct.pack("<H", 2) + d(0x40) + d(0x41) + b"\x01" + d(0x55))
+    assert req.encode_identity_preimage() == want
+    assert wait_request(ha.WAIT_ANY, context=context(attempt=2)).encode_identity_preimage() == want[:-33] + b"\x00"
+    assert req.encode_identity_preimage() == wait_request(ha.WAIT_ANY, context=context(attempt=2), deadline=d(0x55),
+                                                          identity=d(0x51)).encode_identity_preimage()
+    warn = ha.Diagnostic(3, ha.SEVERITY_NOTE, "ok", d(0x66))
+    res = ha.WaitResult(d(0x70), req, ha.WAIT_SATISFIED, (observed(d(0x41), ha.COMPLETION_CANCELLED),), (warn,))
+    dom = ha.DOMAINS["WaitResultId"]
+    head = b"F2HOSTP1" + struct.pack("<H", len(dom)) + dom + struct.pack("<H", 1)
+    want = (head + d(0x50) + b"\x01" + b"\x01" + struct.pack("<H", 1) + d(0x41) + d(0x60) + b"\x02"
+            + struct.pack("<H", 1) + struct.pack("<I", 3) + b"\x01" + b"\x01" + d(0x66) + struct.pack("<H", 2) + b"ok")
+    assert res.encode_identity_preimage() == want
+    err = ha.Diagnostic(9, ha.SEVERITY_ERROR, "no")
+    failed = ha.WaitResult(d(0x70), req, ha.WAIT_FAILED, (), (err,)).encode_identity_preimage()
+    assert failed == (head + d(0x50) + b"\x01" + b"\x04" + struct.pack("<H", 1) + struct.pack("<I", 9) + b"\x03" + b"\x00"
+                      + struct.pack("<H", 2) + b"no")
+
+
+def test_wait_request_must_be_backed_by_exactly_its_submitted_dispatch_results():
+    r1 = ha.DispatchResult(d(0x80), request(identity=d(0x0a)), ha.OUTCOME_SUBMITTED, d(0x81), d(0x41))
+    r2 = ha.DispatchResult(d(0x82), request(identity=d(0x0b)), ha.OUTCOME_SUBMITTED, d(0x83), d(0x40))
+    failed = ha.DispatchResult(d(0x84), request(identity=d(0x0c)), ha.OUTCOME_FAILED,
+                               diagnostics=(ha.Diagnostic(1, ha.SEVERITY_ERROR, "launch failed"),))
+    req = ha.wait_request_for([r1, r2], context())
+    assert req.targets == (d(0x40), d(0x41)) and req.mode == ha.WAIT_ALL
+    import hashlib
+    assert req.identity == hashlib.sha256(req.encode_identity_preimage()).digest()
+    req.validate_dispatch_results([r2, r1])
+    for bad in ([r1], [r1, r1], [r1, failed], [r1, r2, failed]):
+        with rejected("MissingDispatchResult"):
+            req.validate_dispatch_results(bad)
