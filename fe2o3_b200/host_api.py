@@ -10,9 +10,9 @@ log written by a host that launches through this library hashes to the identitie
 reference-side reader computes.  Records are inert descriptions: they own no runtime
 handle and nothing here talks to a device.
 
-The dispatch and wait flows are mirrored (the two a host that launches a prepared kernel and
-waits for it goes through); the compile, admit and load flows of the crate use the same
-encoder and identity types and are not built.
+All five flows of the crate are mirrored as records: compile (src/compile.rs), admit
+(src/admit.rs), load (src/load.rs), dispatch and wait.  The per-flow state machines and
+event logs (src/state.rs, src/event.rs) are not built.
 """
 import hashlib
 from dataclasses import dataclass, field
@@ -28,6 +28,8 @@ MAX_IDENTITY_PREIMAGE_BYTES_V1 = 128 * 1024
 MAX_DISPATCH_BINDINGS_V1 = 128                     # src/dispatch.rs:19-22
 MAX_DISPATCH_DEPENDENCIES_V1 = 128
 MAX_WAIT_TARGETS_V1 = 256                          # src/wait.rs:17
+MAX_PAYLOAD_BYTES_V1 = 256 * 1024 * 1024           # src/common.rs:17
+MAX_ADMISSION_CLAIMS_V1 = 128                      # src/admit.rs:17
 
 # identity domains used by the dispatch flow (src/identity.rs:55-272)
 DOMAINS = {
@@ -45,6 +47,21 @@ DOMAINS = {
     "LoadResultId": b"fe2o3.host.load.result.v1",
     "DispatchRequestId": b"fe2o3.host.dispatch.request.v1",
     "DispatchResultId": b"fe2o3.host.dispatch.result.v1",
+    "PayloadId": b"fe2o3.host.payload.v1",
+    "PayloadFormatId": b"fe2o3.host.payload-format.v1",
+    "CompilerProfileId": b"fe2o3.host.compiler-profile.v1",
+    "TargetProfileId": b"fe2o3.host.target-profile.v1",
+    "CompileConfigurationId": b"fe2o3.host.compile-configuration.v1",
+    "AdmissionPolicyId": b"fe2o3.host.admission-policy.v1",
+    "ClaimId": b"fe2o3.host.claim.v1",
+    "AdmissionAssessmentId": b"fe2o3.host.admission-assessment.v1",
+    "LoaderProfileId": b"fe2o3.host.loader-profile.v1",
+    "RuntimeContextId": b"fe2o3.host.runtime-context.v1",
+    "CompileRequestId": b"fe2o3.host.compile.request.v1",
+    "CompileResultId": b"fe2o3.host.compile.result.v1",
+    "AdmitRequestId": b"fe2o3.host.admit.request.v1",
+    "AdmitResultId": b"fe2o3.host.admit.result.v1",
+    "LoadRequestId": b"fe2o3.host.load.request.v1",
     "CompletionRecordId": b"fe2o3.host.completion-record.v1",
     "DeadlineId": b"fe2o3.host.deadline.v1",
     "WaitRequestId": b"fe2o3.host.wait.request.v1",
@@ -330,6 +347,234 @@ class DispatchResult:
         e.u16(len(self.diagnostics))
         for d in self.diagnostics:
             d.encode(e)
+        return e.finish()
+
+
+# ------------------------------------------------------------------ compile, admit and load flows
+RESULT_SUCCEEDED, RESULT_REJECTED, RESULT_FAILED = 1, 2, 3   # outcome tags shared by the three flows
+
+
+def _check_result_diagnostics(outcome, diagnostics):
+    """common.rs:638-657 plus the rule each result repeats: a success carries no error diagnostic."""
+    if outcome not in (RESULT_SUCCEEDED, RESULT_REJECTED, RESULT_FAILED):
+        raise HostContractError("InvalidOutcome")
+    if len(diagnostics) > MAX_DIAGNOSTICS_V1:
+        raise HostContractError("TooManyItems", "Diagnostics")
+    has_error = any(d.severity == SEVERITY_ERROR for d in diagnostics)
+    if outcome != RESULT_SUCCEEDED and not has_error:
+        raise HostContractError("MissingFailureDiagnostic")
+    return has_error
+
+
+def _encode_diagnostics(e, diagnostics):
+    e.u16(len(diagnostics))
+    for d in diagnostics:
+        d.encode(e)
+
+
+@dataclass(frozen=True)
+class PayloadDescriptor:
+    """common.rs:347-400: identity, format and byte length of an opaque payload."""
+    identity: bytes
+    format_identity: bytes
+    byte_len: int
+
+    def __post_init__(self):
+        if self.byte_len == 0:
+            raise HostContractError("Empty", "PayloadBytes")
+        if self.byte_len > MAX_PAYLOAD_BYTES_V1:
+            raise HostContractError("LimitExceeded", "PayloadBytes")
+
+    def encode(self, e):
+        e.digest(self.identity)
+        e.digest(self.format_identity)
+        e.u64(self.byte_len)
+
+
+@dataclass(frozen=True)
+class CompileRequest:
+    """compile.rs:22-131."""
+    identity: bytes
+    context: OperationContext
+    input: PayloadDescriptor
+    compiler_profile_identity: bytes
+    target_profile_identity: bytes
+    configuration_identity: bytes
+    maximum_output_bytes: int
+
+    def __post_init__(self):
+        if self.maximum_output_bytes == 0:
+            raise HostContractError("Empty", "CompileOutputBytes")
+        if self.maximum_output_bytes > MAX_PAYLOAD_BYTES_V1:
+            raise HostContractError("LimitExceeded", "CompileOutputBytes")
+
+    def encode_identity_preimage(self):
+        e = Encoder(DOMAINS["CompileRequestId"])
+        self.context.encode(e)
+        self.input.encode(e)
+        e.digest(self.compiler_profile_identity)
+        e.digest(self.target_profile_identity)
+        e.digest(self.configuration_identity)
+        e.u64(self.maximum_output_bytes)
+        return e.finish()
+
+
+@dataclass(frozen=True)
+class CompileResult:
+    """compile.rs:133-219: `candidate` is the compiled payload of a successful compile."""
+    identity: bytes
+    request: CompileRequest
+    outcome: int
+    candidate: Optional[PayloadDescriptor] = None
+    diagnostics: Tuple[Diagnostic, ...] = field(default_factory=tuple)
+
+    def __post_init__(self):
+        has_error = _check_result_diagnostics(self.outcome, self.diagnostics)
+        if self.outcome == RESULT_SUCCEEDED:
+            if self.candidate is None:
+                raise HostContractError("InvalidOutcome")
+            if self.candidate.byte_len > self.request.maximum_output_bytes:
+                raise HostContractError("LimitExceeded", "CompileOutputBytes")
+            if has_error:
+                raise HostContractError("InvalidOutcome")
+        elif self.candidate is not None:
+            raise HostContractError("InvalidOutcome")
+
+    def encode_identity_preimage(self):
+        e = Encoder(DOMAINS["CompileResultId"])
+        e.digest(self.request.identity)
+        e.u8(self.outcome)
+        if self.outcome == RESULT_SUCCEEDED:
+            self.candidate.encode(e)
+        _encode_diagnostics(e, self.diagnostics)
+        return e.finish()
+
+
+@dataclass(frozen=True)
+class AdmitRequest:
+    """admit.rs:29-117: admission of exactly the candidate a successful compile produced."""
+    identity: bytes
+    context: OperationContext
+    compile_result: CompileResult
+    candidate: PayloadDescriptor
+    policy_identity: bytes
+    required_claims: Tuple[bytes, ...] = ()
+
+    def __post_init__(self):
+        _strictly_ordered([digest(c) for c in self.required_claims], MAX_ADMISSION_CLAIMS_V1, "AdmissionClaims")
+        if self.compile_result.outcome != RESULT_SUCCEEDED:
+            raise HostContractError("InvalidOutcome")
+        if self.compile_result.candidate != self.candidate:
+            raise HostContractError("Mismatch", "UpstreamObject")
+
+    def encode_identity_preimage(self):
+        e = Encoder(DOMAINS["AdmitRequestId"])
+        self.context.encode(e)
+        e.digest(self.compile_result.identity)
+        self.candidate.encode(e)
+        e.digest(self.policy_identity)
+        e.u16(len(self.required_claims))
+        for c in self.required_claims:
+            e.digest(c)
+        return e.finish()
+
+
+@dataclass(frozen=True)
+class AdmitResult:
+    """admit.rs:119-219: `assessment_identity` is set exactly when the candidate was accepted."""
+    identity: bytes
+    request: AdmitRequest
+    outcome: int
+    assessment_identity: Optional[bytes] = None
+    diagnostics: Tuple[Diagnostic, ...] = field(default_factory=tuple)
+
+    def __post_init__(self):
+        has_error = _check_result_diagnostics(self.outcome, self.diagnostics)
+        if self.outcome == RESULT_SUCCEEDED and (has_error or self.assessment_identity is None):
+            raise HostContractError("InvalidOutcome")
+        if self.outcome != RESULT_SUCCEEDED and self.assessment_identity is not None:
+            raise HostContractError("InvalidOutcome")
+
+    @property
+    def candidate_identity(self):
+        return self.request.candidate.identity
+
+    def encode_identity_preimage(self):
+        e = Encoder(DOMAINS["AdmitResultId"])
+        e.digest(self.request.identity)
+        e.digest(self.candidate_identity)
+        e.u8(self.outcome)
+        if self.outcome == RESULT_SUCCEEDED:
+            e.digest(self.assessment_identity)
+        _encode_diagnostics(e, self.diagnostics)
+        return e.finish()
+
+
+@dataclass(frozen=True)
+class LoadRequest:
+    """load.rs:31-117: a load of the artifact an accepted admission names."""
+    identity: bytes
+    context: OperationContext
+    admit_result: AdmitResult
+    artifact_identity: bytes
+    loader_profile_identity: bytes
+    runtime_context_identity: bytes
+
+    def __post_init__(self):
+        if self.admit_result.candidate_identity != self.artifact_identity:
+            raise HostContractError("Mismatch", "UpstreamObject")
+        if self.admit_result.outcome != RESULT_SUCCEEDED:
+            raise HostContractError("InvalidOutcome")
+
+    def encode_identity_preimage(self):
+        e = Encoder(DOMAINS["LoadRequestId"])
+        self.context.encode(e)
+        e.digest(self.admit_result.identity)
+        e.digest(self.admit_result.assessment_identity)
+        e.digest(self.artifact_identity)
+        e.digest(self.loader_profile_identity)
+        e.digest(self.runtime_context_identity)
+        return e.finish()
+
+
+@dataclass(frozen=True)
+class LoadResult:
+    """load.rs:119-239: a successful load names the loaded object and a non-zero generation."""
+    identity: bytes
+    request: LoadRequest
+    outcome: int
+    loaded_object_identity: Optional[bytes] = None
+    load_generation: int = 0
+    diagnostics: Tuple[Diagnostic, ...] = field(default_factory=tuple)
+
+    def __post_init__(self):
+        has_error = _check_result_diagnostics(self.outcome, self.diagnostics)
+        if self.outcome == RESULT_SUCCEEDED:
+            if self.loaded_object_identity is None:
+                raise HostContractError("InvalidOutcome")
+            if self.load_generation == 0:
+                raise HostContractError("Empty", "LoadGeneration")
+            if has_error:
+                raise HostContractError("InvalidOutcome")
+        elif self.loaded_object_identity is not None:
+            raise HostContractError("InvalidOutcome")
+
+    def loaded(self):
+        """What a dispatch request binds to (dispatch.rs:113-131 accepts only a successful load)."""
+        if self.outcome != RESULT_SUCCEEDED:
+            raise HostContractError("InvalidOutcome")
+        return LoadedResult(self.identity, self.loaded_object_identity, self.load_generation)
+
+    def encode_identity_preimage(self):
+        e = Encoder(DOMAINS["LoadResultId"])
+        e.digest(self.request.identity)
+        e.digest(self.request.artifact_identity)
+        e.digest(self.request.runtime_context_identity)
+        e.u8(self.outcome)
+        if self.outcome == RESULT_SUCCEEDED:
+            e.digest(self.loaded_object_identity)
+            e.u64(self.load_generation)
+        _encode_diagnostics(e, self.diagnostics)
         return e.finish()
 
 

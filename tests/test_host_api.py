@@ -1,7 +1,8 @@
 """Dispatch and wait records of the host API: canonical preimages and structural rejections.
 
 The properties checked are those of crates/fe2o3-host-api/tests/hostile_invariants.rs
-(:159-228 identity domains and preimages, :771-884 wait predicates, :887-941 preimage bounds) plus byte-level layouts
+(:159-228 identity domains and preimages, :236-317 scalar bounds, :319-368 upstream substitution,
+:771-884 wait predicates, :887-941 preimage bounds) plus byte-level layouts
 written out from crates/fe2o3-host-api/src/canonical.rs:13-21 and src/dispatch.rs:234-268.
 """
 import struct
@@ -234,3 +235,101 @@ def test_wait_request_must_be_backed_by_exactly_its_submitted_dispatch_results()
     for bad in ([r1], [r1, r1], [r1, failed], [r1, r2, failed]):
         with rejected("MissingDispatchResult"):
             req.validate_dispatch_results(bad)
+
+
+# ---------------------------------------------------------------------------- compile -> admit -> load
+def payload(byte, n):
+    return ha.PayloadDescriptor(d(byte), d(byte + 1), n)
+
+
+def compile_success(max_out=8192):
+    creq = ha.CompileRequest(d(0xa0), context(), payload(0xa1, 2048), d(0xa3), d(0xa4), d(0xa5), max_out)
+    cand = payload(0xa7, 4096)
+    return creq, ha.CompileResult(d(0xa6), creq, ha.RESULT_SUCCEEDED, cand), cand
+
+
+def accepted_load(generation=7):
+    _, cres, cand = compile_success()
+    areq = ha.AdmitRequest(d(0xb0), context(), cres, cand, d(0xb1), (d(0xb2),))
+    ares = ha.AdmitResult(d(0xb3), areq, ha.RESULT_SUCCEEDED, d(0xb4))
+    lreq = ha.LoadRequest(d(0xb5), context(), ares, cand.identity, d(0xb6), d(0xb7))
+    return ha.LoadResult(d(0xb8), lreq, ha.RESULT_SUCCEEDED, d(0xb9), generation)
+
+
+ERR = ha.Diagnostic(1, ha.SEVERITY_ERROR, "error")
+
+
+def test_scalar_bounds_fail_closed():
+    with rejected("Empty", "PayloadBytes"):
+        payload(1, 0)
+    with rejected("LimitExceeded", "PayloadBytes"):
+        payload(1, ha.MAX_PAYLOAD_BYTES_V1 + 1)
+    with rejected("Empty", "CompileOutputBytes"):
+        compile_success(0)
+    with rejected("LimitExceeded", "CompileOutputBytes"):
+        compile_success(ha.MAX_PAYLOAD_BYTES_V1 + 1)
+    with rejected("LimitExceeded", "CompileOutputBytes"):      # the candidate is larger than the request allows
+        compile_success(4095)
+    creq, _, _ = compile_success()
+    with rejected("MissingFailureDiagnostic"):
+        ha.CompileResult(d(0xc0), creq, ha.RESULT_FAILED)
+    with rejected("InvalidOutcome"):                             # a candidate with an error diagnostic
+        ha.CompileResult(d(0xc1), creq, ha.RESULT_SUCCEEDED, payload(0xc2, 32), (ERR,))
+    assert ha.CompileResult(d(0xc3), creq, ha.RESULT_REJECTED, None, (ERR,)).candidate is None
+
+
+def test_upstream_substitution_and_noncanonical_claims_are_rejected():
+    creq, cres, cand = compile_success()
+    with rejected("Mismatch", "UpstreamObject"):                 # another payload of the same size
+        ha.AdmitRequest(d(0xb0), context(), cres, payload(0x99, cand.byte_len), d(0xb1))
+    failed_compile = ha.CompileResult(d(0xc3), creq, ha.RESULT_FAILED, None, (ERR,))
+    with rejected("InvalidOutcome"):
+        ha.AdmitRequest(d(0xb0), context(), failed_compile, cand, d(0xb1))
+    with rejected("NonCanonicalOrder", "AdmissionClaims"):
+        ha.AdmitRequest(d(0xb0), context(), cres, cand, d(0xb1), (d(2), d(1)))
+    with rejected("Duplicate", "AdmissionClaims"):
+        ha.AdmitRequest(d(0xb0), context(), cres, cand, d(0xb1), (d(1), d(1)))
+    areq = ha.AdmitRequest(d(0xb0), context(), cres, cand, d(0xb1))
+    with rejected("InvalidOutcome"):                             # accepted without an assessment
+        ha.AdmitResult(d(0xb3), areq, ha.RESULT_SUCCEEDED)
+    rejected_admit = ha.AdmitResult(d(0xb3), areq, ha.RESULT_REJECTED, None, (ERR,))
+    with rejected("InvalidOutcome"):                             # a load needs an accepted admission
+        ha.LoadRequest(d(0xb5), context(), rejected_admit, cand.identity, d(0xb6), d(0xb7))
+    accepted = ha.AdmitResult(d(0xb3), areq, ha.RESULT_SUCCEEDED, d(0xb4))
+    with rejected("Mismatch", "UpstreamObject"):                 # a load of some other artifact
+        ha.LoadRequest(d(0xb5), context(), accepted, d(0x98), d(0xb6), d(0xb7))
+    lreq = ha.LoadRequest(d(0xb5), context(), accepted, cand.identity, d(0xb6), d(0xb7))
+    with rejected("Empty", "LoadGeneration"):
+        ha.LoadResult(d(0xb8), lreq, ha.RESULT_SUCCEEDED, d(0xb9), 0)
+    failed_load = ha.LoadResult(d(0xb8), lreq, ha.RESULT_FAILED, None, 0, (ERR,))
+    with rejected("InvalidOutcome"):                             # a dispatch cannot bind to a failed load
+        failed_load.loaded()
+
+
+def test_flow_chain_feeds_a_dispatch_and_preimages_follow_the_reference_layouts():
+    load = accepted_load()
+    req = request(load=load.loaded())
+    assert req.load_result == ha.LoadedResult(d(0xb8), d(0xb9), 7)
+    ctx = d(1) + d(2) + struct.pack("<H", 1) + b"\x00" + struct.pack("<H", 0)
+
+    def head(name):
+        dom = ha.DOMAINS[name]
+        return b"F2HOSTP1" + struct.pack("<H", len(dom)) + dom + struct.pack("<H", 1)
+
+    creq, cres, cand = compile_success()
+    assert creq.encode_identity_preimage() == (head("CompileRequestId") + ctx + d(0xa1) + d(0xa2) + struct.pack("<Q", 2048)
+                                               + d(0xa3) + d(0xa4) + d(0xa5) + struct.pack("<Q", 8192))
+    assert cres.encode_identity_preimage() == (head("CompileResultId") + d(0xa0) + b"\x01" + d(0xa7) + d(0xa8)
+                                               + struct.pack("<Q", 4096) + struct.pack("<H", 0))
+    lreq = load.request
+    areq = lreq.admit_result.request
+    assert areq.encode_identity_preimage() == (head("AdmitRequestId") + ctx + d(0xa6) + d(0xa7) + d(0xa8) + struct.pack("<Q", 4096)
+                                               + d(0xb1) + struct.pack("<H", 1) + d(0xb2))
+    assert lreq.admit_result.encode_identity_preimage() == (head("AdmitResultId") + d(0xb0) + d(0xa7) + b"\x01" + d(0xb4)
+                                                            + struct.pack("<H", 0))
+    assert lreq.encode_identity_preimage() == head("LoadRequestId") + ctx + d(0xb3) + d(0xb4) + d(0xa7) + d(0xb6) + d(0xb7)
+    assert load.encode_identity_preimage() == (head("LoadResultId") + d(0xb5) + d(0xa7) + d(0xb7) + b"\x01" + d(0xb9)
+                                               + struct.pack("<Q", 7) + struct.pack("<H", 0))
+    failed = ha.LoadResult(d(0xb8), lreq, ha.RESULT_REJECTED, None, 0, (ERR,))
+    assert failed.encode_identity_preimage() == (head("LoadResultId") + d(0xb5) + d(0xa7) + d(0xb7) + b"\x02" + struct.pack("<H", 1)
+                                                 + struct.pack("<I", 1) + b"\x03" + b"\x00" + struct.pack("<H", 5) + b"error")
