@@ -11,8 +11,8 @@ reference-side reader computes.  Records are inert descriptions: they own no run
 handle and nothing here talks to a device.
 
 All five flows of the crate are mirrored as records: compile (src/compile.rs), admit
-(src/admit.rs), load (src/load.rs), dispatch and wait.  The per-flow state machines and
-event logs (src/state.rs, src/event.rs) are not built.
+(src/admit.rs), load (src/load.rs), dispatch and wait, together with the per-operation state chain (src/state.rs) and the
+state-transition events and event batches (src/event.rs).
 """
 import hashlib
 from dataclasses import dataclass, field
@@ -30,6 +30,7 @@ MAX_DISPATCH_DEPENDENCIES_V1 = 128
 MAX_WAIT_TARGETS_V1 = 256                          # src/wait.rs:17
 MAX_PAYLOAD_BYTES_V1 = 256 * 1024 * 1024           # src/common.rs:17
 MAX_ADMISSION_CLAIMS_V1 = 128                      # src/admit.rs:17
+MAX_EVENT_BATCH_V1 = 512                           # src/event.rs:17
 
 # identity domains used by the dispatch flow (src/identity.rs:55-272)
 DOMAINS = {
@@ -690,6 +691,169 @@ class WaitResult:
         for d in self.diagnostics:
             d.encode(e)
         return e.finish()
+
+
+# ------------------------------------------------------------------ operation states and events
+PHASE_REQUESTED, PHASE_PENDING, PHASE_ACTIVE = 1, 2, 3                                 # tags of state.rs:245-262
+PHASE_SUCCEEDED, PHASE_REJECTED, PHASE_FAILED, PHASE_CANCELLED = 4, 5, 6, 7
+_TERMINAL = (PHASE_SUCCEEDED, PHASE_REJECTED, PHASE_FAILED, PHASE_CANCELLED)
+_WITH_RESULT = (PHASE_SUCCEEDED, PHASE_REJECTED, PHASE_FAILED)
+_FLOW_NAMES = {FLOW_COMPILE: "compile", FLOW_ADMIT: "admit", FLOW_LOAD: "load", FLOW_DISPATCH: "dispatch", FLOW_WAIT: "wait"}
+
+
+def _flow_domain(flow, kind):
+    return b"fe2o3.host." + _FLOW_NAMES[flow].encode() + b"." + kind + b".v1"
+
+
+def can_transition(current, nxt):
+    """state.rs:213-243: phases only move forward, and nothing follows a terminal phase."""
+    if current == PHASE_REQUESTED:
+        return nxt in (PHASE_PENDING, PHASE_ACTIVE) + _TERMINAL
+    if current == PHASE_PENDING:
+        return nxt in (PHASE_ACTIVE,) + _TERMINAL
+    if current == PHASE_ACTIVE:
+        return nxt in _TERMINAL
+    return False
+
+
+@dataclass(frozen=True)
+class Phase:
+    """state.rs:14-53: `result` = (flow, result identity) for the three phases that carry one."""
+    tag: int
+    result: Optional[Tuple[int, bytes]] = None
+
+    def __post_init__(self):
+        if self.tag not in range(1, 8) or (self.tag in _WITH_RESULT) != (self.result is not None):
+            raise HostContractError("InvalidOutcome")
+
+    @property
+    def is_terminal(self):
+        return self.tag in _TERMINAL
+
+    def encode(self, e):
+        e.u8(self.tag)
+        if self.result is not None:
+            e.digest(self.result[1])
+
+
+REQUESTED = Phase(PHASE_REQUESTED)
+
+
+@dataclass(frozen=True)
+class OperationState:
+    """state.rs:55-211: one link of an operation's state chain.  Build with `initial` and `transition`;
+    every identity is a (flow, digest) pair, as the reference's flow-tagged identity enums are."""
+    identity: Tuple[int, bytes]
+    scope_id: bytes
+    operation_id: bytes
+    request_identity: Tuple[int, bytes]
+    revision: int
+    predecessor_identity: Optional[Tuple[int, bytes]]
+    phase: Phase
+
+    @classmethod
+    def initial(cls, identity, context, request_identity):
+        if identity[0] != request_identity[0]:
+            raise HostContractError("Mismatch", "Flow")
+        return cls(identity, context.scope_id, context.operation_id, request_identity, 0, None, REQUESTED)
+
+    def transition(self, identity, phase):
+        if self.phase.is_terminal:
+            raise HostContractError("TerminalStateTransition")
+        if identity[0] != self.identity[0]:
+            raise HostContractError("Mismatch", "Flow")
+        if identity == self.identity:
+            raise HostContractError("Duplicate", "StateIdentity")
+        if phase.result is not None and phase.result[0] != self.request_identity[0]:
+            raise HostContractError("Mismatch", "TerminalResult")
+        if not can_transition(self.phase.tag, phase.tag):
+            raise HostContractError("InvalidStateTransition")
+        if self.revision + 1 >= 1 << 32:
+            raise HostContractError("ArithmeticOverflow", "StateRevision")
+        return OperationState(identity, self.scope_id, self.operation_id, self.request_identity, self.revision + 1,
+                              self.identity, phase)
+
+    def validate_terminal_result(self, result_identity, request_identity, result_class):
+        """state.rs:160-177: the terminal phase names exactly this result (identity and class) of this request.
+        result_class: RESULT_SUCCEEDED / RESULT_REJECTED / RESULT_FAILED."""
+        if request_identity != self.request_identity:
+            raise HostContractError("Mismatch", "RequestIdentity")
+        klass = {PHASE_SUCCEEDED: RESULT_SUCCEEDED, PHASE_REJECTED: RESULT_REJECTED, PHASE_FAILED: RESULT_FAILED}.get(self.phase.tag)
+        if self.phase.result != result_identity or klass != result_class:
+            raise HostContractError("Mismatch", "TerminalResult")
+
+    def _encode_body(self, e):
+        e.digest(self.scope_id)
+        e.digest(self.operation_id)
+        e.u8(self.request_identity[0])
+        e.digest(self.request_identity[1])
+        e.u32(self.revision)
+        e.optional_digest(None if self.predecessor_identity is None else self.predecessor_identity[1])
+
+    def encode_identity_preimage(self):
+        e = Encoder(_flow_domain(self.identity[0], b"state"))
+        self._encode_body(e)
+        self.phase.encode(e)
+        return e.finish()
+
+
+@dataclass(frozen=True)
+class Event:
+    """event.rs:19-95: the event that announces one state of the chain."""
+    identity: Tuple[int, bytes]
+    state: OperationState
+
+    def __post_init__(self):
+        if self.identity[0] != self.state.identity[0]:
+            raise HostContractError("Mismatch", "Flow")
+
+    def validate_state(self, state):
+        if state != self.state:
+            raise HostContractError("Mismatch", "StatePredecessor")
+
+    def encode_identity_preimage(self):
+        e = Encoder(_flow_domain(self.identity[0], b"event"))
+        self.state._encode_body(e)
+        e.digest(self.state.identity[1])
+        self.state.phase.encode(e)
+        return e.finish()
+
+
+@dataclass(frozen=True)
+class EventBatch:
+    """event.rs:97-205: events of one scope in producer order; the events of each operation form an unbroken
+    chain from its Requested state, while different operations may interleave freely."""
+    scope_id: bytes
+    events: Tuple[Event, ...]
+
+    def __post_init__(self):
+        if not self.events:
+            raise HostContractError("Empty", "EventBatch")
+        if len(self.events) > MAX_EVENT_BATCH_V1:
+            raise HostContractError("TooManyItems", "EventBatch")
+        for index, event in enumerate(self.events):
+            cur, earlier = event.state, self.events[:index]
+            if cur.scope_id != self.scope_id:
+                raise HostContractError("Mismatch", "Scope")
+            if any(x.identity == event.identity for x in earlier):
+                raise HostContractError("Duplicate", "EventBatch")
+            if any(x.state.identity == cur.identity for x in earlier):
+                raise HostContractError("Duplicate", "StateIdentity")
+            previous = next((x.state for x in reversed(earlier) if x.state.operation_id == cur.operation_id), None)
+            if previous is None:
+                if cur.revision != 0 or cur.predecessor_identity is not None or cur.phase != REQUESTED:
+                    raise HostContractError("InvalidInitialState")
+                continue
+            if previous.request_identity != cur.request_identity:
+                raise HostContractError("Mismatch", "RequestIdentity")
+            if cur.revision != previous.revision + 1:
+                raise HostContractError("Mismatch", "StateRevision")
+            if cur.predecessor_identity != previous.identity:
+                raise HostContractError("Mismatch", "StatePredecessor")
+            if previous.phase.is_terminal:
+                raise HostContractError("TerminalStateTransition")
+            if not can_transition(previous.phase.tag, cur.phase.tag):
+                raise HostContractError("InvalidStateTransition")
 
 
 # ------------------------------------------------------------------ this library's launches

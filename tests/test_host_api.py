@@ -2,7 +2,7 @@
 
 The properties checked are those of crates/fe2o3-host-api/tests/hostile_invariants.rs
 (:159-228 identity domains and preimages, :236-317 scalar bounds, :319-368 upstream substitution,
-:771-884 wait predicates, :887-941 preimage bounds) plus byte-level layouts
+:539-668 interleaved state chains, :670-768 stale / skipped / terminal states, :771-884 wait predicates, :887-941 preimage bounds) plus byte-level layouts
 written out from crates/fe2o3-host-api/src/canonical.rs:13-21 and src/dispatch.rs:234-268.
 """
 import struct
@@ -333,3 +333,98 @@ def test_flow_chain_feeds_a_dispatch_and_preimages_follow_the_reference_layouts(
     failed = ha.LoadResult(d(0xb8), lreq, ha.RESULT_REJECTED, None, 0, (ERR,))
     assert failed.encode_identity_preimage() == (head("LoadResultId") + d(0xb5) + d(0xa7) + d(0xb7) + b"\x02" + struct.pack("<H", 1)
                                                  + struct.pack("<I", 1) + b"\x03" + b"\x00" + struct.pack("<H", 5) + b"error")
+
+
+# ---------------------------------------------------------------------------- state chains and events
+D = ha.FLOW_DISPATCH
+
+
+def dispatch_pair(op_byte, ident_byte):
+    ctx = ha.OperationContext(d(1), d(op_byte), 1)
+    req = request(identity=d(ident_byte), context=ctx)
+    return req, ha.DispatchResult(d(ident_byte + 1), req, ha.OUTCOME_SUBMITTED, d(ident_byte + 2), d(ident_byte + 3))
+
+
+def test_parallel_dispatches_have_independent_interleavable_state_chains():
+    req_a, res_a = dispatch_pair(0x0a, 0x10)
+    req_b, res_b = dispatch_pair(0x0b, 0x20)
+    a0 = ha.OperationState.initial((D, d(0x30)), req_a.context, (D, req_a.identity))
+    a1 = a0.transition((D, d(0x31)), ha.Phase(ha.PHASE_PENDING))
+    a2 = a1.transition((D, d(0x32)), ha.Phase(ha.PHASE_SUCCEEDED, (D, res_a.identity)))
+    a2.validate_terminal_result((D, res_a.identity), (D, req_a.identity), ha.RESULT_SUCCEEDED)
+    b0 = ha.OperationState.initial((D, d(0x40)), req_b.context, (D, req_b.identity))
+    b1 = b0.transition((D, d(0x41)), ha.Phase(ha.PHASE_ACTIVE))
+    b2 = b1.transition((D, d(0x42)), ha.Phase(ha.PHASE_SUCCEEDED, (D, res_b.identity)))
+    b2.validate_terminal_result((D, res_b.identity), (D, req_b.identity), ha.RESULT_SUCCEEDED)
+    assert (a2.revision, a2.predecessor_identity, b2.revision) == (2, a1.identity, 2)
+    with rejected("Mismatch", "RequestIdentity"):
+        a2.validate_terminal_result((D, res_b.identity), (D, req_b.identity), ha.RESULT_SUCCEEDED)
+    with rejected("Mismatch", "TerminalResult"):      # the right request, another operation's result
+        a2.validate_terminal_result((D, res_b.identity), (D, req_a.identity), ha.RESULT_SUCCEEDED)
+    with rejected("Mismatch", "TerminalResult"):      # the right result under the wrong class
+        a2.validate_terminal_result((D, res_a.identity), (D, req_a.identity), ha.RESULT_FAILED)
+    ev = [ha.Event((D, st.identity[1]), st) for st in (a0, b0, b1, a1, b2, a2)]   # interleaved in producer order
+    assert len(ha.EventBatch(d(1), tuple(ev)).events) == 6
+    with rejected("Mismatch", "StateRevision"):       # b's chain with a link left out
+        ha.EventBatch(d(1), (ev[0], ev[1], ev[4]))
+    fork = a0.transition((D, d(0x33)), ha.Phase(ha.PHASE_ACTIVE))   # another successor of a0: a2 does not follow it
+    with rejected("Mismatch", "StatePredecessor"):
+        ha.EventBatch(d(1), (ev[0], ha.Event((D, d(0x33)), fork), ev[5]))
+    with rejected("Mismatch", "Scope"):
+        ha.EventBatch(d(2), tuple(ev))
+
+
+def test_state_and_event_chains_reject_cross_flow_stale_skipped_and_terminal_use():
+    req, res = dispatch_pair(0x0a, 0x10)
+    with rejected("Mismatch", "Flow"):
+        ha.OperationState.initial((ha.FLOW_LOAD, d(0x30)), req.context, (D, req.identity))
+    s0 = ha.OperationState.initial((D, d(0x31)), req.context, (D, req.identity))
+    with rejected("Mismatch", "TerminalResult"):      # a load result cannot end a dispatch
+        s0.transition((D, d(0x32)), ha.Phase(ha.PHASE_SUCCEEDED, (ha.FLOW_LOAD, d(0x33))))
+    with rejected("Mismatch", "Flow"):
+        s0.transition((ha.FLOW_WAIT, d(0x32)), ha.Phase(ha.PHASE_PENDING))
+    s1 = s0.transition((D, d(0x34)), ha.Phase(ha.PHASE_PENDING))
+    with rejected("Duplicate", "StateIdentity"):
+        s1.transition(s1.identity, ha.Phase(ha.PHASE_ACTIVE))
+    with rejected("InvalidStateTransition"):          # phases do not move backwards
+        s1.transition((D, d(0x35)), ha.REQUESTED)
+    s2 = s1.transition((D, d(0x35)), ha.Phase(ha.PHASE_SUCCEEDED, (D, res.identity)))
+    with rejected("TerminalStateTransition"):
+        s2.transition((D, d(0x36)), ha.Phase(ha.PHASE_CANCELLED))
+    with rejected("InvalidOutcome"):                  # a terminal result phase needs its result, the others take none
+        ha.Phase(ha.PHASE_FAILED)
+    e0, e1, e2 = (ha.Event((D, st.identity[1]), st) for st in (s0, s1, s2))
+    with rejected("Mismatch", "Flow"):
+        ha.Event((ha.FLOW_WAIT, d(0x31)), s0)
+    with rejected("Mismatch", "StatePredecessor"):
+        e0.validate_state(s1)
+    e0.validate_state(s0)
+    with rejected("Mismatch", "StateRevision"):       # a skipped link
+        ha.EventBatch(d(1), (e0, e2))
+    with rejected("Duplicate", "EventBatch"):
+        ha.EventBatch(d(1), (e0, e0))
+    with rejected("Duplicate", "StateIdentity"):
+        ha.EventBatch(d(1), (e0, ha.Event((D, d(0x37)), s0)))
+    with rejected("InvalidInitialState"):             # a chain that does not start at Requested
+        ha.EventBatch(d(1), (e1, e2))
+    with rejected("Empty", "EventBatch"):
+        ha.EventBatch(d(1), ())
+    assert len(ha.EventBatch(d(1), (e0, e1, e2)).events) == 3
+
+
+def test_state_and_event_preimage_layouts():
+    req, res = dispatch_pair(0x0a, 0x10)
+    s0 = ha.OperationState.initial((D, d(0x31)), req.context, (D, req.identity))
+    s1 = s0.transition((D, d(0x34)), ha.Phase(ha.PHASE_FAILED, (D, res.identity)))
+
+    def head(dom):
+        return b"F2HOSTP1" + struct.pack("<H", len(dom)) + dom + struct.pack("<H", 1)
+
+    body0 = d(1) + d(0x0a) + b"\x04" + d(0x10) + struct.pack("<I", 0) + b"\x00"
+    body1 = d(1) + d(0x0a) + b"\x04" + d(0x10) + struct.pack("<I", 1) + b"\x01" + d(0x31)
+    assert s0.encode_identity_preimage() == head(b"fe2o3.host.dispatch.state.v1") + body0 + b"\x01"
+    assert s1.encode_identity_preimage() == head(b"fe2o3.host.dispatch.state.v1") + body1 + b"\x06" + d(0x11)
+    assert ha.Event((D, d(0x50)), s1).encode_identity_preimage() == (head(ha.DOMAINS["DispatchEventId"]) + body1 + d(0x34)
+                                                                     + b"\x06" + d(0x11))
+    w = ha.OperationState.initial((ha.FLOW_WAIT, d(0x60)), req.context, (ha.FLOW_WAIT, d(0x61)))
+    assert w.encode_identity_preimage().startswith(head(b"fe2o3.host.wait.state.v1") + d(1) + d(0x0a) + b"\x05" + d(0x61))
