@@ -107,6 +107,7 @@ OPS = {
     "masked_reduce_u32": (MaskedReduceArgs, 48, False),
     "masked_reduce_u32_packed": (MaskedReducePackedArgs, 48, False),
     "device_scan_u32": (DeviceScanArgs, 40, False),
+    "device_scan_f32": (DeviceScanArgs, 40, False),
     "wave_lds_v1": (WaveLdsArgs, 64, False),
     "wave64_collectives_v1": (Wave64CollectivesArgs, 72, False),
     "wave64_collectives_segmented": (Wave64SegmentedArgs, 80, False),

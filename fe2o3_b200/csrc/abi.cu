@@ -19,6 +19,7 @@ typedef int32_t (*LaunchFn)(fe2o3_ctx *, cudaStream_t, const void *, fe2o3_geome
 int32_t launch_masked_reduce_u32(fe2o3_ctx *, cudaStream_t, const void *, fe2o3_geometry *, bool);
 int32_t launch_masked_reduce_u32_packed(fe2o3_ctx *, cudaStream_t, const void *, fe2o3_geometry *, bool);
 int32_t launch_device_scan_u32(fe2o3_ctx *, cudaStream_t, const void *, fe2o3_geometry *, bool);
+int32_t launch_device_scan_f32(fe2o3_ctx *, cudaStream_t, const void *, fe2o3_geometry *, bool);
 int32_t launch_wave_lds_v1(fe2o3_ctx *, cudaStream_t, const void *, fe2o3_geometry *, bool);
 int32_t launch_wave64_collectives_v1(fe2o3_ctx *, cudaStream_t, const void *, fe2o3_geometry *, bool);
 int32_t launch_wave64_collectives_segmented(fe2o3_ctx *, cudaStream_t, const void *, fe2o3_geometry *, bool);
@@ -78,7 +79,7 @@ enum OpId : uint32_t {
     OP_SCALAR_GEMM, OP_TILED_GEMM, OP_TILED_GEMM_GENERAL, OP_FLASH_ATTENTION, OP_ROW_SOFTMAX, OP_MOE_TOP2,
     OP_MOE_GATE, OP_MOE_ROUTE_WEIGHTS, OP_MOE_EXPERT_FFN, OP_MOE_COMBINE, OP_MASKED_REDUCE, OP_MASKED_REDUCE_PACKED,
     OP_WAVE_LDS, OP_WAVE64_COLLECTIVES, OP_WAVE64_SEGMENTED, OP_LDS_REDUCE_I32, OP_SCOPED_ATOMIC_ADD,
-    OP_MOE_COMPACT, OP_MOE_GROUPED_FFN, OP_MOE_EP_EXCHANGE, OP_DEVICE_SCAN_U32, OP_COUNT
+    OP_MOE_COMPACT, OP_MOE_GROUPED_FFN, OP_MOE_EP_EXCHANGE, OP_DEVICE_SCAN_U32, OP_DEVICE_SCAN_F32, OP_COUNT
 };
 
 struct OpInfo {
@@ -109,6 +110,7 @@ static const OpInfo kOps[OP_COUNT] = {
     {"moe_grouped_ffn_v1", sizeof(fe2o3_moe_grouped_ffn_v1_args), nullptr},
     {"moe_ep_exchange_v1", sizeof(fe2o3_moe_ep_exchange_v1_args), launch_moe_ep_exchange},
     {"device_scan_sum_u32", sizeof(fe2o3_device_scan_u32_args), launch_device_scan_u32},
+    {"device_scan_sum_f32", sizeof(fe2o3_device_scan_f32_args), launch_device_scan_f32},
 };
 
 struct fe2o3_prepared {
@@ -401,7 +403,8 @@ int regions_for(uint32_t op, const void *args, Region *r, int32_t *status) {
             r[2] = RGN("Output", a->output, 1, 4, true);
             return 3;
         }
-        case OP_DEVICE_SCAN_U32: {
+        case OP_DEVICE_SCAN_U32:
+        case OP_DEVICE_SCAN_F32: {   // same block; elements are 4 bytes in both
             const fe2o3_device_scan_u32_args *a = static_cast<const fe2o3_device_scan_u32_args *>(args);
             if (a->values.len > FE2O3_SCAN_MAX_ELEMENTS || a->exclusive > 1u) {
                 *status = unsupported("at most 2^31 elements; exclusive is 0 or 1");
@@ -921,6 +924,7 @@ DEFINE_CHECK(moe_expert_combine_v1, OP_MOE_COMBINE)
 DEFINE_CHECK(masked_reduce_u32, OP_MASKED_REDUCE)
 DEFINE_CHECK(masked_reduce_u32_packed, OP_MASKED_REDUCE_PACKED)
 DEFINE_CHECK(device_scan_u32, OP_DEVICE_SCAN_U32)
+DEFINE_CHECK(device_scan_f32, OP_DEVICE_SCAN_F32)
 DEFINE_CHECK(wave_lds_v1, OP_WAVE_LDS)
 DEFINE_CHECK(wave64_collectives_v1, OP_WAVE64_COLLECTIVES)
 DEFINE_CHECK(wave64_collectives_segmented, OP_WAVE64_SEGMENTED)
@@ -943,6 +947,7 @@ DEFINE_SIMPLE_PREPARE(moe_expert_combine_v1, OP_MOE_COMBINE)
 DEFINE_SIMPLE_PREPARE(masked_reduce_u32, OP_MASKED_REDUCE)
 DEFINE_SIMPLE_PREPARE(masked_reduce_u32_packed, OP_MASKED_REDUCE_PACKED)
 DEFINE_SIMPLE_PREPARE(device_scan_u32, OP_DEVICE_SCAN_U32)
+DEFINE_SIMPLE_PREPARE(device_scan_f32, OP_DEVICE_SCAN_F32)
 DEFINE_SIMPLE_PREPARE(wave_lds_v1, OP_WAVE_LDS)
 DEFINE_SIMPLE_PREPARE(wave64_collectives_v1, OP_WAVE64_COLLECTIVES)
 DEFINE_SIMPLE_PREPARE(wave64_collectives_segmented, OP_WAVE64_SEGMENTED)

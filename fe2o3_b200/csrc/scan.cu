@@ -1,4 +1,5 @@
-// Device-wide inclusive / exclusive prefix sum of u32 values (wrapping addition).
+// Device-wide inclusive / exclusive prefix sum of u32 values (wrapping addition) and of f32 values
+// (each addition rounded to nearest; one kernel template, values carried as 32-bit patterns).
 //
 // The reference defines prefix sums at two scopes: a 64-lane wave
 // (crates/fe2o3-device/src/collective.rs:413-460, Hillis-Steele over lane
@@ -30,6 +31,11 @@
 // warp that walked back to the nearest published inclusive prefix (0.68-0.76: with
 // every tile of a wave in flight at once the nearest such prefix is a wave or more
 // behind, and the walk became a serial chain of L2 round trips per SM).
+// In the f32 form the order of additions must not depend on scheduling, so the prefix warp only
+// ever accumulates whole chunks of 192 tiles from tile 0 and adds the part of the current chunk
+// separately: whichever block computes a tile's prefix performs the same chain of additions, and
+// repeated runs give identical bits.  The lane prefix inside a warp scan comes from a shuffle
+// instead of a subtraction.
 // A descriptor is one 64-bit word {state, value}; it carries everything its reader
 // needs, so relaxed device-scope accesses are enough.  The launch clears the ticket
 // and the descriptors first.  Every wait is bounded and records
@@ -74,9 +80,33 @@ __device__ __forceinline__ uint64_t desc_load(const uint64_t *p) {
     return v;
 }
 
+// Values travel as 32-bit patterns; kFloat selects IEEE binary32 addition (round to nearest) instead of
+// wrapping integer addition.  Zero is the all-zero pattern in both.
+template <bool kFloat>
+__device__ __forceinline__ uint32_t add(uint32_t a, uint32_t b) {
+    if constexpr (kFloat) return __float_as_uint(__fadd_rn(__uint_as_float(a), __uint_as_float(b)));
+    else return a + b;
+}
+template <bool kFloat>
+__device__ __forceinline__ uint32_t sum4(const uint4 &x) {
+    return add<kFloat>(add<kFloat>(x.x, x.y), add<kFloat>(x.z, x.w));
+}
+// sum over the warp in a fixed order (every lane receives it)
+template <bool kFloat>
+__device__ __forceinline__ uint32_t warp_sum(uint32_t v) {
+    if constexpr (kFloat) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v = add<true>(v, __shfl_xor_sync(0xffffffffu, v, o));
+        return v;
+    } else {
+        return __reduce_add_sync(0xffffffffu, v);
+    }
+}
+
+template <bool kFloat>
 __global__ void __launch_bounds__(kScanThreads, 1)
-device_scan_u32_kernel(const uint32_t *in, uint32_t *out, uint64_t n, uint32_t exclusive, uint32_t *ticket,
-                       uint64_t *desc, uint32_t *status) {
+device_scan_kernel(const uint32_t *in, uint32_t *out, uint64_t n, uint32_t exclusive, uint32_t *ticket,
+                   uint64_t *desc, uint32_t *status) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint32_t *ring = reinterpret_cast<uint32_t *>(smem);
@@ -150,14 +180,11 @@ device_scan_u32_kernel(const uint32_t *in, uint32_t *out, uint64_t n, uint32_t e
 #pragma unroll
             for (int j = 0; j < kPartVecs; ++j) {
                 const uint4 x = src[j * 32], y = src[(kPartVecs + j) * 32];
-                sum0 += (x.x + x.y) + (x.z + x.w);
-                sum1 += (y.x + y.y) + (y.z + y.w);
+                sum0 = add<kFloat>(sum0, sum4<kFloat>(x));
+                sum1 = add<kFloat>(sum1, sum4<kFloat>(y));
             }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                sum0 += __shfl_xor_sync(0xffffffffu, sum0, o);
-                sum1 += __shfl_xor_sync(0xffffffffu, sum1, o);
-            }
+            sum0 = warp_sum<kFloat>(sum0);
+            sum1 = warp_sum<kFloat>(sum1);
             // the last of the four warps to finish publishes the tile's aggregate
             uint32_t last = 0;
             if (lane == 0) {
@@ -170,7 +197,7 @@ device_scan_u32_kernel(const uint32_t *in, uint32_t *out, uint64_t n, uint32_t e
             if (last && lane == 0) {
                 __threadfence_block();
                 uint32_t aggregate = 0;
-                for (int q = 0; q < kFinishWarps; ++q) aggregate += sh.part[st][q];
+                for (int q = 0; q < kFinishWarps; ++q) aggregate = add<kFloat>(aggregate, sh.part[st][q]);
                 sh.arrivals[st] = 0;
                 desc_store(desc + tile, kStateAggregate, aggregate);
                 mbar_arrive(&sh.agg_ready[st]);
@@ -189,39 +216,89 @@ device_scan_u32_kernel(const uint32_t *in, uint32_t *out, uint64_t n, uint32_t e
             if (!mbar_wait_warp(&sh.full[st], ph)) { ok = false; break; }
             const uint32_t tile = sh.tile[st];
             if (tile == kNoTile) break;
-            uint32_t between = 0;
-            for (uint32_t b = covered; ok && b < tile; b += 32 * kWindow) {
-                uint64_t d[kWindow];
+            // sum of the published aggregates of tiles [lo, hi): lanes take them 32 apart, then a warp sum
+            auto range_sum = [&](uint32_t lo, uint32_t hi) -> uint32_t {
+                uint32_t acc = 0;
+                for (uint32_t b = lo; ok && b < hi; b += 32 * kWindow) {
+                    uint64_t d[kWindow];
 #pragma unroll
-                for (int q = 0; q < kWindow; ++q) {   // all loads of the step in flight together
-                    const uint32_t mine = b + 32 * q + lane;
-                    d[q] = mine < tile ? desc_load(desc + mine) : ((uint64_t)kStateAggregate << 32);
-                }
-#pragma unroll
-                for (int q = 0; q < kWindow; ++q) {
-                    const uint32_t mine = b + 32 * q + lane;
-                    uint32_t spins = 0;
-                    while ((d[q] >> 32) == 0) {
-                        if (++spins > kDescSpin) { ok = false; break; }
-                        __nanosleep(100);
-                        d[q] = desc_load(desc + mine);
+                    for (int q = 0; q < kWindow; ++q) {   // all loads of the step in flight together
+                        const uint32_t mine = b + 32 * q + lane;
+                        d[q] = mine < hi ? desc_load(desc + mine) : ((uint64_t)kStateAggregate << 32);
                     }
-                    between += (uint32_t)d[q];
+#pragma unroll
+                    for (int q = 0; q < kWindow; ++q) {
+                        const uint32_t mine = b + 32 * q + lane;
+                        uint32_t spins = 0;
+                        while ((d[q] >> 32) == 0) {
+                            if (++spins > kDescSpin) { ok = false; break; }
+                            __nanosleep(100);
+                            d[q] = desc_load(desc + mine);
+                        }
+                        acc = add<kFloat>(acc, (uint32_t)d[q]);
+                    }
+                    ok = __all_sync(0xffffffffu, ok);
                 }
-                ok = __all_sync(0xffffffffu, ok);
+                return warp_sum<kFloat>(acc);
+            };
+            uint32_t prefix;
+            if constexpr (kFloat) {
+                // Rounding makes the order matter.  `running` only ever stops at multiples of kChunk tiles and
+                // advances by whole chunks, so the prefix of a tile is the same chain of additions whichever
+                // block computes it: results do not depend on how the tickets fell.
+                constexpr uint32_t kChunk = 32 * kWindow;
+                while (ok && covered + 2 * kChunk <= tile) {
+                    running = add<true>(running, range_sum(covered, covered + kChunk));
+                    covered += kChunk;
+                }
+                if (covered + kChunk <= tile) {
+                    // the usual case, one whole chunk and a part of the next: both windows' loads go out
+                    // together, so the step costs one round trip; the additions are the same as above
+                    const uint32_t mid = covered + kChunk;
+                    uint64_t d[2][kWindow];
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+#pragma unroll
+                        for (int q = 0; q < kWindow; ++q) {
+                            const uint32_t mine = (h ? mid : covered) + 32 * q + lane;
+                            d[h][q] = mine < (h ? tile : mid) ? desc_load(desc + mine) : ((uint64_t)kStateAggregate << 32);
+                        }
+                    uint32_t acc[2] = {0, 0};
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+#pragma unroll
+                        for (int q = 0; q < kWindow; ++q) {
+                            const uint32_t mine = (h ? mid : covered) + 32 * q + lane;
+                            uint32_t spins = 0;
+                            while ((d[h][q] >> 32) == 0) {
+                                if (++spins > kDescSpin) { ok = false; break; }
+                                __nanosleep(100);
+                                d[h][q] = desc_load(desc + mine);
+                            }
+                            acc[h] = add<true>(acc[h], (uint32_t)d[h][q]);
+                        }
+                    ok = __all_sync(0xffffffffu, ok);
+                    running = add<true>(running, warp_sum<true>(acc[0]));
+                    covered = mid;
+                    prefix = add<true>(running, warp_sum<true>(acc[1]));
+                } else {
+                    prefix = add<true>(running, range_sum(covered, tile));
+                }
+            } else {
+                prefix = running + range_sum(covered, tile);
             }
             if (!ok) break;
-            between = __reduce_add_sync(0xffffffffu, between);
             if (!mbar_wait_warp(&sh.agg_ready[st], ph)) { ok = false; break; }
-            uint32_t aggregate = 0;
-            for (int q = 0; q < kFinishWarps; ++q) aggregate += sh.part[st][q];
-            const uint32_t prefix = running + between;
             if (lane == 0) {
                 sh.prefix[st] = prefix;
                 mbar_arrive(&sh.prefix_ready[st]);
             }
-            running = prefix + aggregate;
-            covered = tile + 1;
+            if constexpr (!kFloat) {
+                uint32_t aggregate = 0;
+                for (int q = 0; q < kFinishWarps; ++q) aggregate += sh.part[st][q];
+                running = prefix + aggregate;
+                covered = tile + 1;
+            }
         }
         if (!ok && lane == 0) kstatus_set(status, FE2O3_KSTATUS_WAIT_EXPIRED);   // the finish warps' waits expire in turn
     } else {
@@ -238,7 +315,7 @@ device_scan_u32_kernel(const uint32_t *in, uint32_t *out, uint64_t n, uint32_t e
                 break;
             }
             uint32_t carry = sh.prefix[st];   // everything before this warp's first element
-            for (uint32_t q = 0; q < w; ++q) carry += sh.part[st][q];
+            for (uint32_t q = 0; q < w; ++q) carry = add<kFloat>(carry, sh.part[st][q]);
             const uint64_t base = (uint64_t)tile * kTileElems + (uint64_t)w * kPart + lane * (4 * kLaneVecs);
             const bool vec = aligned && (uint64_t)tile * kTileElems + kTileElems <= n;
             const uint4 *src = reinterpret_cast<const uint4 *>(ring + st * kTileElems + w * kPart) + lane * kLaneVecs;
@@ -254,7 +331,7 @@ device_scan_u32_kernel(const uint32_t *in, uint32_t *out, uint64_t n, uint32_t e
 #pragma unroll
                 for (int c = 0; c < kLaneVecs; ++c) {
                     x[j][c] = src[j * 32 * kLaneVecs + c];
-                    own[j] += (x[j][c].x + x[j][c].y) + (x[j][c].z + x[j][c].w);
+                    own[j] = add<kFloat>(own[j], sum4<kFloat>(x[j][c]));
                 }
                 t[j] = own[j];
             }
@@ -265,24 +342,35 @@ device_scan_u32_kernel(const uint32_t *in, uint32_t *out, uint64_t n, uint32_t e
 #pragma unroll
                 for (int j = 0; j < kPasses; ++j) {
                     const uint32_t up = __shfl_up_sync(0xffffffffu, t[j], o);
-                    if (lane >= (uint32_t)o) t[j] += up;
+                    if (lane >= (uint32_t)o) t[j] = add<kFloat>(up, t[j]);
                 }
             }
 #pragma unroll
             for (int j = 0; j < kPasses; ++j) {
-                uint32_t run = carry + t[j] - own[j];   // everything before this lane's first element of the pass
-                carry += __shfl_sync(0xffffffffu, t[j], 31);
+                // everything before this lane's first element of the pass
+                uint32_t run;
+                if constexpr (kFloat) {   // no subtraction in floating point: take the lower lane's inclusive total
+                    const uint32_t below = __shfl_up_sync(0xffffffffu, t[j], 1);
+                    run = lane == 0 ? carry : add<true>(carry, below);
+                } else {
+                    run = carry + t[j] - own[j];
+                }
+                carry = add<kFloat>(carry, __shfl_sync(0xffffffffu, t[j], 31));
 #pragma unroll
                 for (int c = 0; c < kLaneVecs; ++c) {
-                    const uint32_t v[4] = {x[j][c].x, x[j][c].x + x[j][c].y, x[j][c].x + x[j][c].y + x[j][c].z,
-                                           x[j][c].x + x[j][c].y + x[j][c].z + x[j][c].w};
+                    // inclusive values of the four elements, each the previous one plus the element
+                    uint32_t inc[4];
+                    inc[0] = add<kFloat>(run, x[j][c].x);
+                    inc[1] = add<kFloat>(inc[0], x[j][c].y);
+                    inc[2] = add<kFloat>(inc[1], x[j][c].z);
+                    inc[3] = add<kFloat>(inc[2], x[j][c].w);
                     uint32_t r[4];
                     if (exclusive) {   // element i of the exclusive form is the inclusive value of element i - 1
-                        r[0] = run; r[1] = run + v[0]; r[2] = run + v[1]; r[3] = run + v[2];
+                        r[0] = run; r[1] = inc[0]; r[2] = inc[1]; r[3] = inc[2];
                     } else {
-                        r[0] = run + v[0]; r[1] = run + v[1]; r[2] = run + v[2]; r[3] = run + v[3];
+                        r[0] = inc[0]; r[1] = inc[1]; r[2] = inc[2]; r[3] = inc[3];
                     }
-                    run += v[3];
+                    run = inc[3];
                     const uint64_t e = base + (uint64_t)j * (128 * kLaneVecs) + c * 4;
                     if (vec) {
                         __stcs(reinterpret_cast<uint4 *>(out + e), make_uint4(r[0], r[1], r[2], r[3]));
@@ -299,7 +387,8 @@ device_scan_u32_kernel(const uint32_t *in, uint32_t *out, uint64_t n, uint32_t e
 
 }  // namespace
 
-int32_t launch_device_scan_u32(fe2o3_ctx *ctx, cudaStream_t s, const void *args, fe2o3_geometry *geo, bool plan_only) {
+template <bool kFloat>
+int32_t launch_device_scan(fe2o3_ctx *ctx, cudaStream_t s, const void *args, fe2o3_geometry *geo, bool plan_only) {
     const fe2o3_device_scan_u32_args *a = static_cast<const fe2o3_device_scan_u32_args *>(args);
     const uint64_t n = a->values.len;
     const uint32_t tiles = (uint32_t)((n + kTileElems - 1) / kTileElems);
@@ -309,15 +398,22 @@ int32_t launch_device_scan_u32(fe2o3_ctx *ctx, cudaStream_t s, const void *args,
     if (plan_only || n == 0) return FE2O3_OK;
     static std::once_flag once;
     std::call_once(once, [] {
-        cudaFuncSetAttribute(device_scan_u32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+        cudaFuncSetAttribute(device_scan_kernel<kFloat>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
     });
     // ticket at word 0, descriptors from byte 64
     uint32_t *ticket = ctx->scan_scratch;
     uint64_t *desc = reinterpret_cast<uint64_t *>(ctx->scan_scratch + 16);
     FE2O3_CUDA(cudaMemsetAsync(ctx->scan_scratch, 0, 64 + (size_t)tiles * 8, s));
-    device_scan_u32_kernel<<<grid, kScanThreads, kSmemBytes, s>>>(reinterpret_cast<const uint32_t *>(a->values.ptr),
-                                                                  reinterpret_cast<uint32_t *>(a->output.ptr), n,
-                                                                  a->exclusive, ticket, desc, ctx->status_word);
+    device_scan_kernel<kFloat><<<grid, kScanThreads, kSmemBytes, s>>>(reinterpret_cast<const uint32_t *>(a->values.ptr),
+                                                                      reinterpret_cast<uint32_t *>(a->output.ptr), n,
+                                                                      a->exclusive, ticket, desc, ctx->status_word);
     fe2o3_count_launch(1);
-    return fe2o3_cuda_status(cudaGetLastError(), "device_scan_sum_u32");
+    return fe2o3_cuda_status(cudaGetLastError(), kFloat ? "device_scan_sum_f32" : "device_scan_sum_u32");
+}
+
+int32_t launch_device_scan_u32(fe2o3_ctx *ctx, cudaStream_t s, const void *args, fe2o3_geometry *geo, bool plan_only) {
+    return launch_device_scan<false>(ctx, s, args, geo, plan_only);
+}
+int32_t launch_device_scan_f32(fe2o3_ctx *ctx, cudaStream_t s, const void *args, fe2o3_geometry *geo, bool plan_only) {
+    return launch_device_scan<true>(ctx, s, args, geo, plan_only);
 }

@@ -326,6 +326,15 @@ typedef struct fe2o3_device_scan_u32_args {
     uint32_t reserved;
 } fe2o3_device_scan_u32_args;
 
+/* The same scan over IEEE binary32 values, each addition rounded to nearest.  No
+ * reference order exists at array scope (the reference defines f32 scans inside one
+ * wave only), so the result is specified by tolerance: output[i] is within
+ * (128 + len / 8192 / 192) * 2^-24 * (|values[0]| + ... + |values[i]|) of the exact
+ * prefix (the bracket bounds the roundings on any path).  The order of additions
+ * depends only on element positions, not on scheduling: repeated runs give identical
+ * bits. */
+typedef fe2o3_device_scan_u32_args fe2o3_device_scan_f32_args;
+
 /* crates/rustc-codegen-fe2o3/tests/fixtures/memory-v1-compiler/src/bin/gfx942_wave_lds_v1.rs:7-15
  * with the runner's (ptr,len)x4 arguments
  * (crates/dialect-amdgcn/tests/fixtures/gfx942_wave_lds_v1_runner.cpp:62-68):
@@ -383,6 +392,7 @@ int32_t fe2o3_moe_ep_exchange_v1_check(const fe2o3_moe_ep_exchange_v1_args *args
 int32_t fe2o3_masked_reduce_u32_check(const fe2o3_masked_reduce_u32_args *args);
 int32_t fe2o3_masked_reduce_u32_packed_check(const fe2o3_masked_reduce_u32_packed_args *args);
 int32_t fe2o3_device_scan_u32_check(const fe2o3_device_scan_u32_args *args);
+int32_t fe2o3_device_scan_f32_check(const fe2o3_device_scan_f32_args *args);
 int32_t fe2o3_wave_lds_v1_check(const fe2o3_wave_lds_v1_args *args);
 int32_t fe2o3_wave64_collectives_v1_check(const fe2o3_wave64_collectives_v1_args *args);
 int32_t fe2o3_wave64_collectives_segmented_check(const fe2o3_wave64_collectives_segmented_args *args);
@@ -419,6 +429,8 @@ int32_t fe2o3_masked_reduce_u32_prepare(fe2o3_ctx *ctx, const fe2o3_masked_reduc
 int32_t fe2o3_masked_reduce_u32_packed_prepare(fe2o3_ctx *ctx, const fe2o3_masked_reduce_u32_packed_args *args,
                                                fe2o3_prepared **out);
 int32_t fe2o3_device_scan_u32_prepare(fe2o3_ctx *ctx, const fe2o3_device_scan_u32_args *args,
+                                      fe2o3_prepared **out);
+int32_t fe2o3_device_scan_f32_prepare(fe2o3_ctx *ctx, const fe2o3_device_scan_f32_args *args,
                                       fe2o3_prepared **out);
 int32_t fe2o3_wave_lds_v1_prepare(fe2o3_ctx *ctx, const fe2o3_wave_lds_v1_args *args, fe2o3_prepared **out);
 int32_t fe2o3_wave64_collectives_v1_prepare(fe2o3_ctx *ctx, const fe2o3_wave64_collectives_v1_args *args,

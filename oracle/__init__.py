@@ -238,6 +238,19 @@ def scan_sum_u32(values, exclusive=False):
     return out
 
 
+def scan_sum_f32(values, exclusive=False):
+    """Prefix sums of binary32 values accumulated in binary64 (the exact sum to about 2^-53 per step), and the
+    prefix sums of their magnitudes, which scale the tolerance of a binary32 scan.  The wave-scope definition it
+    extends is crates/fe2o3-device/src/collective.rs:413-460; at array scope the reference fixes no order, so
+    parity is by tolerance against this."""
+    v = _c(values, np.float32).astype(np.float64)
+    inc, mag = np.cumsum(v), np.cumsum(np.abs(v))
+    if exclusive:
+        inc = np.concatenate(([0.0], inc[:-1])) if v.size else inc
+        mag = np.concatenate(([0.0], mag[:-1])) if v.size else mag
+    return inc, mag
+
+
 def masked_sum_u32_packed(values, mask):
     v = _c(values, np.uint32)
     m = _c(mask, np.uint64)

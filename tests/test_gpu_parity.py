@@ -630,6 +630,46 @@ def test_device_scan_sum_u32_unaligned_repeated_and_rejections(gpu, orc):
             fe.check_args("device_scan_u32", fe.make_args("device_scan_u32", exclusive=0, **bad))
 
 
+def scan_f32_tolerance(n, magnitudes):
+    # the bound the header states: (128 + tiles / 192) roundings of 2^-24 each, scaled by the prefix of |values|
+    return (128 + n / 8192 / 192) * 2.0 ** -24 * magnitudes + 1e-30
+
+
+@pytest.mark.parametrize("n", [1, 63, 4097, 100003, (1 << 22) + 3, 1 << 24])
+@pytest.mark.parametrize("exclusive", [0, 1])
+def test_device_scan_sum_f32_within_stated_tolerance_and_reproducible(gpu, orc, n, exclusive):
+    fe, ctx, stream = gpu
+    rng = np.random.default_rng(n * 2 + exclusive)
+    v = rng.standard_normal(n).astype(np.float32)             # mixed signs: the prefix keeps cancelling
+    V, O = Guarded(fe, stream, v), Guarded(fe, stream, np.full(n, np.nan, np.float32))
+    p = fe.prepare(ctx, "device_scan_f32", values=V.slice, output=O.slice, exclusive=exclusive)
+    p.launch_and_wait(stream)
+    first = O.read().copy()
+    want, mag = orc.scan_sum_f32(v, bool(exclusive))
+    err = np.abs(first.astype(np.float64) - want)
+    assert (err <= scan_f32_tolerance(n, mag)).all(), float((err / scan_f32_tolerance(n, mag)).max())
+    if exclusive:
+        assert first[0] == 0.0
+    # the order of additions is fixed by position: a second run gives the same bits
+    p.launch_and_wait(stream)
+    assert (O.read().view(np.uint32) == first.view(np.uint32)).all()
+    V.unchanged()
+
+
+def test_device_scan_sum_f32_exact_on_small_integers_and_propagates_specials(gpu, orc):
+    fe, ctx, stream = gpu
+    n = 300001
+    v = (np.arange(n) % 7).astype(np.float32)                 # every partial sum is an integer below 2^24: exact
+    V, O = Guarded(fe, stream, v), Guarded(fe, stream, np.zeros(n, np.float32))
+    run(fe, ctx, stream, "device_scan_f32", values=V.slice, output=O.slice, exclusive=0)
+    assert (O.read() == np.cumsum(v.astype(np.float64)).astype(np.float32)).all()
+    v[200000] = np.inf                                        # an infinity reaches everything after it, nothing before
+    V2 = Guarded(fe, stream, v)
+    run(fe, ctx, stream, "device_scan_f32", values=V2.slice, output=O.slice, exclusive=0)
+    got = O.read()
+    assert np.isfinite(got[:200000]).all() and np.isposinf(got[200000:]).all()
+
+
 def test_dispatch_record_of_a_prepared_launch(gpu):
     # crates/fe2o3-host-api/src/dispatch.rs:96-268: the record that describes one launch of this library
     import hashlib

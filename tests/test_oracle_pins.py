@@ -402,3 +402,13 @@ def test_scan_sum_u32_matches_the_reference_wave_and_workgroup_definitions(orc):
     big = rng.integers(0, 2**32, 100003, dtype=np.uint64).astype(np.uint32)
     assert (orc.scan_sum_u32(big) == np.cumsum(big.astype(np.uint64)).astype(np.uint32)).all()
     assert orc.scan_sum_u32(np.zeros(0, np.uint32)).size == 0
+
+
+def test_scan_sum_f32_reference_is_the_exact_prefix_and_magnitude(orc):
+    v = np.array([1.5, -2.25, 1e-3, 4.0], np.float32)
+    inc, mag = orc.scan_sum_f32(v)
+    assert inc.tolist() == [1.5, -0.75, -0.75 + float(np.float32(1e-3)), 3.25 + float(np.float32(1e-3))]
+    assert mag.tolist() == [1.5, 3.75, 3.75 + float(np.float32(1e-3)), 7.75 + float(np.float32(1e-3))]
+    exc, emag = orc.scan_sum_f32(v, exclusive=True)
+    assert exc.tolist() == [0.0] + inc[:-1].tolist() and emag.tolist() == [0.0] + mag[:-1].tolist()
+    assert orc.scan_sum_f32(np.zeros(0, np.float32))[0].size == 0
