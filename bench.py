@@ -142,7 +142,7 @@ class Harness:
 NCU_TRAFFIC = {
     ("masked_reduce_u32", 1 << 28): 2147519744 + 3300352,
     ("row_softmax_v1", 65536 * 1024): 268459008 + 216675072,
-    ("device_scan_u32", 1 << 28): 1074100736 + 1014816768,
+    ("device_scan_u32", 1 << 28): 1074060800 + 1014678784,
     ("tiled_gemm_v1", (8192, 8192, 8192)): 1046762752 + 250886400,
     ("flash_attention_v1", (4, 16, 2048, 64)): 50588160 + 2605312,
     # grouped FFN GEMMs of one pass, average of the two launches (GEMM-1 501 MB, GEMM-2 880 MB)
