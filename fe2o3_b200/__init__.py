@@ -162,6 +162,47 @@ class Event:
         return ms.value
 
 
+class PeerRegion:
+    """Device memory that the other processes of the node can map
+    (crates/fe2o3-core/src/peer_access.rs:24-60 across processes)."""
+
+    HANDLE_BYTES = 64
+
+    def __init__(self, ctx, handle):
+        self.ctx, self._h = ctx, handle
+
+    @classmethod
+    def create(cls, ctx, nbytes):
+        h = C.c_void_p()
+        check(lib.fe2o3_peer_region_create(ctx._h, C.c_uint64(nbytes), C.byref(h)), "PeerRegion::create")
+        return cls(ctx, h)
+
+    @classmethod
+    def open(cls, ctx, handle_bytes):
+        h = C.c_void_p()
+        buf = (C.c_uint8 * cls.HANDLE_BYTES).from_buffer_copy(bytes(handle_bytes))
+        check(lib.fe2o3_peer_region_import(ctx._h, buf, C.byref(h)), "PeerRegion::open")
+        return cls(ctx, h)
+
+    def export(self):
+        buf = (C.c_uint8 * self.HANDLE_BYTES)()
+        check(lib.fe2o3_peer_region_export(self._h, buf), "PeerRegion::export")
+        return bytes(buf)
+
+    @property
+    def ptr(self):
+        return int(lib.fe2o3_peer_region_ptr(self._h))
+
+    @property
+    def nbytes(self):
+        return int(lib.fe2o3_peer_region_bytes(self._h))
+
+    def close(self):
+        if self._h:
+            check(lib.fe2o3_peer_region_destroy(self._h), "PeerRegion::close")
+            self._h = None
+
+
 def as_slice(x):
     """DeviceBuffer, Slice, torch tensor, (ptr, len) tuple or None -> Slice."""
     if x is None:

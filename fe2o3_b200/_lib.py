@@ -54,11 +54,16 @@ MoeCompactArgs = _struct("MoeCompactArgs", ["x", "permutation", "compact_x"], [(
 MoeGroupedFfnArgs = _struct("MoeGroupedFfnArgs", ["compact_x", "w1", "w2", "group_offsets", "hidden", "compact_output"],
                             [("d_model", u32), ("d_ff", u32), ("groups", u32), ("experts_cycle", u32)])
 MoeEpExchangeArgs = _struct("MoeEpExchangeArgs",
-                            ["x", "top2_experts", "permutation", "inverse", "expert_offsets", "requested_counts",
-                             "route_weights", "group_offsets", "remote_rows", "combined_output", "peer_recv_x",
-                             "peer_ffn_out", "peer_counts", "peer_flags", "epoch_counter"],
+                            ["x", "top2_experts", "permutation", "inverse", "expert_offsets", "admitted_counts",
+                             "route_weights", "pair_offsets", "combined_output", "peer_recv_x", "peer_recv_meta",
+                             "peer_ret", "peer_counts", "peer_flags", "epoch_counter"],
                             [("tokens", u32), ("d_model", u32), ("experts", u32), ("world", u32), ("rank", u32),
-                             ("epoch", u32), ("max_rows", u32), ("phase", u32)])
+                             ("epoch", u32), ("max_rows", u32), ("phase", u32), ("spin_limit", u32), ("reserved", u32)])
+MoeEpFfnArgs = _struct("MoeEpFfnArgs",
+                       ["recv_x", "w1", "w2", "pair_offsets", "hidden", "recv_meta", "flags", "peer_ret", "peer_flags",
+                        "epoch_counter"],
+                       [("tokens", u32), ("d_model", u32), ("d_ff", u32), ("experts", u32), ("world", u32), ("rank", u32),
+                        ("epoch", u32), ("max_rows", u32), ("spin_limit", u32), ("reserved", u32)])
 MaskedReduceArgs = _struct("MaskedReduceArgs", ["values", "active", "output"])
 MaskedReducePackedArgs = _struct("MaskedReducePackedArgs", ["values", "mask", "output"])
 DeviceScanArgs = _struct("DeviceScanArgs", ["values", "output"], [("exclusive", u32), ("reserved", u32)])
@@ -103,7 +108,8 @@ OPS = {
     "moe_expert_combine_v1": (MoeCombineArgs, 72, False),
     "moe_compact_v1": (MoeCompactArgs, 56, False),
     "moe_grouped_ffn_v1": (MoeGroupedFfnArgs, 112, False),
-    "moe_ep_exchange_v1": (MoeEpExchangeArgs, 272, False),
+    "moe_ep_exchange_v1": (MoeEpExchangeArgs, 280, False),
+    "moe_ep_ffn_v1": (MoeEpFfnArgs, 200, False),
     "masked_reduce_u32": (MaskedReduceArgs, 48, False),
     "masked_reduce_u32_packed": (MaskedReducePackedArgs, 48, False),
     "device_scan_u32": (DeviceScanArgs, 40, False),
@@ -130,6 +136,8 @@ EXPORTS = [
     "fe2o3_unload_executable", "fe2o3_synth_uniform_f32", "fe2o3_synth_normal_f32", "fe2o3_synth_normal_bf16",
     "fe2o3_synth_uniform_bf16", "fe2o3_synth_u32_below", "fe2o3_synth_bernoulli", "fe2o3_synth_gemm_inputs_v1",
     "fe2o3_bf16_from_f32", "fe2o3_launch_count", "fe2o3_masked_reduce_u32_noalloc",
+    "fe2o3_peer_region_create", "fe2o3_peer_region_export", "fe2o3_peer_region_import", "fe2o3_peer_region_ptr",
+    "fe2o3_peer_region_bytes", "fe2o3_peer_region_destroy",
 ] + [f"fe2o3_{op}_check" for op in OPS] + [f"fe2o3_{op}_prepare" for op in OPS]
 
 lib.fe2o3_status_string.restype = C.c_char_p
@@ -142,6 +150,10 @@ lib.fe2o3_buf_ptr.argtypes = [vp]
 lib.fe2o3_buf_len.restype = u64
 lib.fe2o3_buf_len.argtypes = [vp]
 lib.fe2o3_launch_count.restype = u64
+lib.fe2o3_peer_region_ptr.restype = u64
+lib.fe2o3_peer_region_ptr.argtypes = [vp]
+lib.fe2o3_peer_region_bytes.restype = u64
+lib.fe2o3_peer_region_bytes.argtypes = [vp]
 lib.fe2o3_bf16_from_f32.restype = C.c_uint16
 lib.fe2o3_bf16_from_f32.argtypes = [f32]
 for _n in EXPORTS:

@@ -12,9 +12,8 @@ CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libfe2o3_b200.so")
 OBJ = os.path.join(HERE, "build")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--use_fast_math=false",
+FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC,-fopenmp,-fno-fast-math", "-Xptxas", "-v"]
-FLAGS = [f for f in FLAGS if f != "--use_fast_math=false"]
 
 
 def sources():

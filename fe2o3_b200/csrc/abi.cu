@@ -44,6 +44,8 @@ int32_t attention_tc_plan(fe2o3_ctx *, const fe2o3_flash_attention_v1_args *, At
 int32_t attention_tc_launch(const AttnTcPlan *, cudaStream_t);
 void attention_tc_geometry(const AttnTcPlan *, fe2o3_geometry *);
 void attention_tc_free(AttnTcPlan *);
+int32_t attention_tc_init_device();
+int32_t device_scan_init_device();
 
 // ---- error bookkeeping ---------------------------------------------------------
 static thread_local char g_error[512] = "";
@@ -79,7 +81,8 @@ enum OpId : uint32_t {
     OP_SCALAR_GEMM, OP_TILED_GEMM, OP_TILED_GEMM_GENERAL, OP_FLASH_ATTENTION, OP_ROW_SOFTMAX, OP_MOE_TOP2,
     OP_MOE_GATE, OP_MOE_ROUTE_WEIGHTS, OP_MOE_EXPERT_FFN, OP_MOE_COMBINE, OP_MASKED_REDUCE, OP_MASKED_REDUCE_PACKED,
     OP_WAVE_LDS, OP_WAVE64_COLLECTIVES, OP_WAVE64_SEGMENTED, OP_LDS_REDUCE_I32, OP_SCOPED_ATOMIC_ADD,
-    OP_MOE_COMPACT, OP_MOE_GROUPED_FFN, OP_MOE_EP_EXCHANGE, OP_DEVICE_SCAN_U32, OP_DEVICE_SCAN_F32, OP_COUNT
+    OP_MOE_COMPACT, OP_MOE_GROUPED_FFN, OP_MOE_EP_EXCHANGE, OP_DEVICE_SCAN_U32, OP_DEVICE_SCAN_F32, OP_MOE_EP_FFN,
+    OP_COUNT
 };
 
 struct OpInfo {
@@ -111,6 +114,7 @@ static const OpInfo kOps[OP_COUNT] = {
     {"moe_ep_exchange_v1", sizeof(fe2o3_moe_ep_exchange_v1_args), launch_moe_ep_exchange},
     {"device_scan_sum_u32", sizeof(fe2o3_device_scan_u32_args), launch_device_scan_u32},
     {"device_scan_sum_f32", sizeof(fe2o3_device_scan_f32_args), launch_device_scan_f32},
+    {"moe_ep_ffn_v1", sizeof(fe2o3_moe_ep_ffn_v1_args), nullptr},
 };
 
 struct fe2o3_prepared {
@@ -353,8 +357,8 @@ int regions_for(uint32_t op, const void *args, Region *r, int32_t *status) {
         case OP_MOE_EP_EXCHANGE: {
             const fe2o3_moe_ep_exchange_v1_args *a = static_cast<const fe2o3_moe_ep_exchange_v1_args *>(args);
             if (a->world < 1 || a->world > 32 || a->experts < 2 || a->experts > 32 || a->experts % a->world ||
-                a->d_model == 0 || (a->d_model % 8) || a->rank >= a->world || a->phase > FE2O3_MOE_EP_ADVANCE ||
-                a->tokens > 0x7fffffffu) {
+                a->d_model == 0 || (a->d_model % 8) || a->rank >= a->world || a->phase > FE2O3_MOE_EP_COMBINE ||
+                a->tokens > 0x3fffffffu) {
                 *status = unsupported("1 <= world <= 32 dividing experts (2..32), d_model a positive multiple of 8, rank < world");
                 return 0;
             }
@@ -364,18 +368,40 @@ int regions_for(uint32_t op, const void *args, Region *r, int32_t *status) {
             r[2] = RGN("Permutation", a->permutation, R, 4, false);
             r[3] = RGN("Inverse", a->inverse, R, 4, false);
             r[4] = RGN("ExpertOffsets", a->expert_offsets, a->experts + 1, 4, false);
-            r[5] = RGN("RequestedCounts", a->requested_counts, a->experts, 4, false);
+            r[5] = RGN("AdmittedCounts", a->admitted_counts, a->experts, 4, false);
             r[6] = RGN("RouteWeights", a->route_weights, R, 4, false);
             r[7] = RGN("PeerRecvX", a->peer_recv_x, a->world, 8, false);
-            r[8] = RGN("PeerFfnOut", a->peer_ffn_out, a->world, 8, false);
-            r[9] = RGN("PeerCounts", a->peer_counts, a->world, 8, false);
-            r[10] = RGN("PeerFlags", a->peer_flags, a->world, 8, false);
-            r[11] = RGN("GroupOffsets", a->group_offsets, a->experts + 1, 4, true);
-            r[12] = RGN("RemoteRows", a->remote_rows, R, 4, true);
+            r[8] = RGN("PeerRecvMeta", a->peer_recv_meta, a->world, 8, false);
+            r[9] = RGN("PeerRet", a->peer_ret, a->world, 8, false);
+            r[10] = RGN("PeerCounts", a->peer_counts, a->world, 8, false);
+            r[11] = RGN("PeerFlags", a->peer_flags, a->world, 8, false);
+            r[12] = RGN("PairOffsets", a->pair_offsets, a->experts + 1, 4, true);
             r[13] = RGN("CombinedOutput", a->combined_output, (uint64_t)a->tokens * a->d_model, 4, true);
             if (a->epoch_counter.ptr == 0 && a->epoch_counter.len == 0) return 14;
             r[14] = RGN("EpochCounter", a->epoch_counter, 1, 4, true);
             return 15;
+        }
+        case OP_MOE_EP_FFN: {
+            const fe2o3_moe_ep_ffn_v1_args *a = static_cast<const fe2o3_moe_ep_ffn_v1_args *>(args);
+            if (a->world < 1 || a->world > 32 || a->experts < 2 || a->experts > 32 || a->experts % a->world ||
+                a->d_model == 0 || (a->d_model % 8) || a->d_ff == 0 || (a->d_ff % 8) || a->rank >= a->world ||
+                a->max_rows == 0 || a->tokens > 0x3fffffffu) {
+                *status = unsupported("1 <= world <= 32 dividing experts (2..32), d_model and d_ff positive multiples of 8, rank < world, max_rows > 0");
+                return 0;
+            }
+            const uint64_t per = a->experts / a->world;
+            r[0] = RGN("RecvX", a->recv_x, (uint64_t)a->max_rows * a->d_model, 2, false);
+            r[1] = RGN("W1", a->w1, per * a->d_model * a->d_ff, 2, false);
+            r[2] = RGN("W2", a->w2, per * a->d_ff * a->d_model, 2, false);
+            r[3] = RGN("PairOffsets", a->pair_offsets, a->experts + 1, 4, false);
+            r[4] = RGN("RecvMeta", a->recv_meta, 2ull * a->max_rows, 4, false);
+            r[5] = RGN("PeerRet", a->peer_ret, a->world, 8, false);
+            r[6] = RGN("PeerFlags", a->peer_flags, a->world, 8, false);
+            r[7] = RGN("Hidden", a->hidden, (uint64_t)a->max_rows * a->d_ff, 2, true);
+            r[8] = RGN("Flags", a->flags, 3ull * a->world + 3, 4, true);
+            if (a->epoch_counter.ptr == 0 && a->epoch_counter.len == 0) return 9;
+            r[9] = RGN("EpochCounter", a->epoch_counter, 1, 4, false);
+            return 10;
         }
         case OP_MOE_COMBINE: {
             const fe2o3_moe_expert_combine_v1_args *a = static_cast<const fe2o3_moe_expert_combine_v1_args *>(args);
@@ -549,6 +575,17 @@ int32_t launch_prepared(fe2o3_prepared *p, cudaStream_t s) {
             return launch_moe_compact(s, a->x.ptr, a->permutation.ptr, a->compact_x.ptr, (uint32_t)a->permutation.len,
                                       a->d_model, a->tokens);
         }
+        case OP_MOE_EP_FFN: {
+            // the scalars a caller may patch between passes are taken from the packed block at launch
+            const fe2o3_moe_ep_ffn_v1_args *a = reinterpret_cast<const fe2o3_moe_ep_ffn_v1_args *>(p->kernarg);
+            for (int g = 0; g < 2; ++g) {
+                p->gemm[g].p.ep.epoch = a->epoch;
+                p->gemm[g].p.ep.spin_limit = a->spin_limit ? a->spin_limit : FE2O3_EP_DEFAULT_SPIN;
+            }
+            int32_t st = gemm_tc_launch(&p->gemm[0], s);
+            if (st != FE2O3_OK) return st;
+            return gemm_tc_launch(&p->gemm[1], s);
+        }
         case OP_MOE_GROUPED_FFN: {
             int32_t st = gemm_tc_launch(&p->gemm[0], s);
             if (st != FE2O3_OK) return st;
@@ -618,6 +655,11 @@ int32_t fe2o3_ctx_create(int32_t device, fe2o3_ctx **out) {
                         prop.minor);
         return FE2O3_ERR_NOT_SM100;
     }
+    // opt-in shared memory sizes are a per-device function attribute: set them for this device
+    int32_t init = gemm_tc_init_device();
+    if (init == FE2O3_OK) init = attention_tc_init_device();
+    if (init == FE2O3_OK) init = device_scan_init_device();
+    if (init != FE2O3_OK) return init;
     fe2o3_ctx *ctx = new (std::nothrow) fe2o3_ctx();
     if (!ctx) return FE2O3_ERR_SIZE_OVERFLOW;
     ctx->device = device;
@@ -662,6 +704,7 @@ int32_t fe2o3_ctx_destroy(fe2o3_ctx *ctx) {
     if (e == cudaSuccess) {  // quiescent: safe to free; otherwise leak (completion is ambiguous)
         cudaFree(ctx->reduce_scratch);
         cudaFree(ctx->route_scratch);
+        cudaFree(ctx->scan_scratch);
         cudaFreeHost(ctx->host_status);
     }
     delete ctx;
@@ -883,6 +926,57 @@ int32_t fe2o3_peer_access_enable(fe2o3_ctx *ctx, int32_t peer_device) {
     return fe2o3_cuda_status(e, "cudaDeviceEnablePeerAccess");
 }
 
+// ---- peer-visible regions (CUDA IPC) ---------------------------------------------------
+struct fe2o3_peer_region {
+    fe2o3_ctx *ctx;
+    void *ptr;
+    uint64_t bytes;   // 0 for an imported mapping
+    bool imported;
+};
+static_assert(sizeof(cudaIpcMemHandle_t) == FE2O3_PEER_HANDLE_BYTES, "handle size");
+
+int32_t fe2o3_peer_region_create(fe2o3_ctx *ctx, uint64_t bytes, fe2o3_peer_region **out) {
+    if (!ctx || !out || bytes == 0) return FE2O3_ERR_INVALID_ARGUMENT;
+    *out = nullptr;
+    FE2O3_CUDA(cudaSetDevice(ctx->device));
+    void *ptr = nullptr;
+    FE2O3_CUDA(cudaMalloc(&ptr, bytes));
+    cudaError_t e = cudaMemset(ptr, 0, bytes);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) { cudaFree(ptr); return fe2o3_cuda_status(e, "zero-fill(peer region)"); }
+    *out = new (std::nothrow) fe2o3_peer_region{ctx, ptr, bytes, false};
+    if (!*out) { cudaFree(ptr); return FE2O3_ERR_SIZE_OVERFLOW; }
+    return FE2O3_OK;
+}
+int32_t fe2o3_peer_region_export(const fe2o3_peer_region *region, uint8_t handle[FE2O3_PEER_HANDLE_BYTES]) {
+    if (!region || !handle || region->imported) return FE2O3_ERR_INVALID_ARGUMENT;
+    cudaIpcMemHandle_t h;
+    FE2O3_CUDA(cudaIpcGetMemHandle(&h, region->ptr));
+    memcpy(handle, &h, sizeof h);
+    return FE2O3_OK;
+}
+int32_t fe2o3_peer_region_import(fe2o3_ctx *ctx, const uint8_t handle[FE2O3_PEER_HANDLE_BYTES], fe2o3_peer_region **out) {
+    if (!ctx || !handle || !out) return FE2O3_ERR_INVALID_ARGUMENT;
+    *out = nullptr;
+    FE2O3_CUDA(cudaSetDevice(ctx->device));
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof h);
+    void *ptr = nullptr;
+    FE2O3_CUDA(cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    *out = new (std::nothrow) fe2o3_peer_region{ctx, ptr, 0, true};
+    if (!*out) { cudaIpcCloseMemHandle(ptr); return FE2O3_ERR_SIZE_OVERFLOW; }
+    return FE2O3_OK;
+}
+uint64_t fe2o3_peer_region_ptr(const fe2o3_peer_region *region) { return region ? reinterpret_cast<uint64_t>(region->ptr) : 0; }
+uint64_t fe2o3_peer_region_bytes(const fe2o3_peer_region *region) { return region ? region->bytes : 0; }
+int32_t fe2o3_peer_region_destroy(fe2o3_peer_region *region) {
+    if (!region) return FE2O3_OK;
+    cudaSetDevice(region->ctx->device);
+    cudaError_t e = region->imported ? cudaIpcCloseMemHandle(region->ptr) : cudaFree(region->ptr);
+    delete region;
+    return fe2o3_cuda_status(e, "peer region release");
+}
+
 const char *fe2o3_status_string(int32_t s) {
     switch (s) {
         case FE2O3_OK: return "Ok";
@@ -1045,10 +1139,49 @@ int32_t fe2o3_moe_grouped_ffn_v1_prepare(fe2o3_ctx *ctx, const fe2o3_moe_grouped
     return FE2O3_OK;
 }
 
+int32_t fe2o3_moe_ep_ffn_v1_check(const fe2o3_moe_ep_ffn_v1_args *args) { return check_op(OP_MOE_EP_FFN, args); }
+int32_t fe2o3_moe_ep_ffn_v1_prepare(fe2o3_ctx *ctx, const fe2o3_moe_ep_ffn_v1_args *a, fe2o3_prepared **out) {
+    int32_t st = prepare_common(ctx, OP_MOE_EP_FFN, a, out);
+    if (st != FE2O3_OK) return st;
+    fe2o3_prepared *p = *out;
+    const uint32_t W = a->world, per = a->experts / W;
+    uint32_t *flags = reinterpret_cast<uint32_t *>(a->flags.ptr);
+    GemmEp ep{};
+    ep.pair_offsets = reinterpret_cast<const uint32_t *>(a->pair_offsets.ptr);
+    ep.world = W;
+    ep.rank = a->rank;
+    ep.epoch_counter = a->epoch_counter.len ? reinterpret_cast<const uint32_t *>(a->epoch_counter.ptr) : nullptr;
+    ep.epoch = a->epoch;
+    ep.spin_limit = a->spin_limit ? a->spin_limit : FE2O3_EP_DEFAULT_SPIN;
+    // first GEMM: waits per source for "rows complete"; GELU + bf16 hidden rows
+    GemmEp in = ep;
+    in.rows_flags = flags + FE2O3_EP_FLAG_ROWS(W);
+    st = gemm_tc_plan(ctx, &p->gemm[0], a->recv_x.ptr, a->w1.ptr, a->hidden.ptr, a->max_rows, a->d_ff, a->d_model,
+                      a->d_model, a->d_ff, a->d_ff, 1.f, 0.f, EPI_GELU_BF16, in.pair_offsets, per, 0, per, &in);
+    // second GEMM: every output row goes to its home rank's return buffer; the last CTA raises "outputs ready"
+    GemmEp outp = ep;
+    outp.row_meta = reinterpret_cast<const uint2 *>(a->recv_meta.ptr);
+    outp.peer_ret = reinterpret_cast<const uint64_t *>(a->peer_ret.ptr);
+    outp.ret_rows = 2u * a->tokens;
+    outp.peer_flags = reinterpret_cast<const uint64_t *>(a->peer_flags.ptr);
+    outp.done_counter = flags + FE2O3_EP_COUNTER_FFN(W);
+    if (st == FE2O3_OK)
+        st = gemm_tc_plan(ctx, &p->gemm[1], a->hidden.ptr, a->w2.ptr, 0, a->max_rows, a->d_model, a->d_ff, a->d_ff,
+                          a->d_model, a->d_model, 1.f, 0.f, EPI_SCATTER_PEER, outp.pair_offsets, per, 0, per, &outp);
+    if (st != FE2O3_OK) return fail_prepare(out, st);
+    gemm_tc_geometry(&p->gemm[0], &p->geo);
+    p->geo.launches = 2;
+    return FE2O3_OK;
+}
+
 // ---- launch ------------------------------------------------------------------------------------
 int32_t fe2o3_prepared_launch(fe2o3_prepared *p, fe2o3_stream *stream) {
     if (!p || !stream) return FE2O3_ERR_INVALID_ARGUMENT;
     if (stream->ctx != p->ctx) { fe2o3_set_error("WrongContext{role=stream}"); return FE2O3_ERR_DEVICE_MISMATCH; }
+    // the launch goes to the context's device whatever device the calling thread had current
+    int current = -1;
+    FE2O3_CUDA(cudaGetDevice(&current));
+    if (current != p->ctx->device) FE2O3_CUDA(cudaSetDevice(p->ctx->device));
     return launch_prepared(p, stream->s);
 }
 int32_t fe2o3_prepared_launch_and_wait(fe2o3_prepared *p, fe2o3_stream *stream, uint32_t timeout_ms,
@@ -1140,6 +1273,7 @@ int32_t fe2o3_launch_and_wait(fe2o3_executable *exe, uint32_t kernel_id, const v
         case OP_MOE_EXPERT_FFN: st = fe2o3_moe_expert_ffn_v1_prepare(exe->ctx, (const fe2o3_moe_expert_ffn_v1_args *)kernarg, &p); break;
         case OP_MOE_COMPACT: st = fe2o3_moe_compact_v1_prepare(exe->ctx, (const fe2o3_moe_compact_v1_args *)kernarg, &p); break;
         case OP_MOE_GROUPED_FFN: st = fe2o3_moe_grouped_ffn_v1_prepare(exe->ctx, (const fe2o3_moe_grouped_ffn_v1_args *)kernarg, &p); break;
+        case OP_MOE_EP_FFN: st = fe2o3_moe_ep_ffn_v1_prepare(exe->ctx, (const fe2o3_moe_ep_ffn_v1_args *)kernarg, &p); break;
         default:
             st = prepare_common(exe->ctx, kernel_id, kernarg, &p);
             if (st == FE2O3_OK) st = finish_simple(p);

@@ -595,11 +595,13 @@ int32_t attention_tc_plan(fe2o3_ctx *ctx, const fe2o3_flash_attention_v1_args *a
     return FE2O3_OK;
 }
 
+// Function attributes are per device: called by fe2o3_ctx_create with the context's device current.
+int32_t attention_tc_init_device() {
+    FE2O3_CUDA(cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTotal));
+    return FE2O3_OK;
+}
+
 int32_t attention_tc_launch(const AttnTcPlan *plan, cudaStream_t s) {
-    static std::once_flag once;
-    std::call_once(once, [] {
-        cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTotal);
-    });
     if (plan->grid == 0) return FE2O3_OK;
     attention_tc_kernel<<<plan->grid, kThreads, kSmemTotal, s>>>(plan->tmQ, plan->tmK, plan->tmV, plan->tmO, plan->p);
     fe2o3_count_launch(1);

@@ -47,6 +47,18 @@ int32_t fe2o3_cuda_status(cudaError_t e, const char *what);
 
 static inline uint32_t ceil_div_u32(uint64_t a, uint64_t b) { return (uint32_t)((a + b - 1) / b); }
 
+// Flag block of one rank of the expert-parallel layer, in u32 words (world = W):
+//   [0, W)    counts published by source rank s        [W, 2W)  rows complete from source rank s
+//   [2W, 3W)  outputs ready from owner rank o          3W, 3W+1, 3W+2  arrival counters of the
+//   dispatch kernel, the second FFN GEMM and the combine kernel (each re-armed by its last block)
+#define FE2O3_EP_FLAG_COUNTS(W) (0u)
+#define FE2O3_EP_FLAG_ROWS(W) (W)
+#define FE2O3_EP_FLAG_OUTPUTS(W) (2u * (W))
+#define FE2O3_EP_COUNTER_DISPATCH(W) (3u * (W))
+#define FE2O3_EP_COUNTER_FFN(W) (3u * (W) + 1u)
+#define FE2O3_EP_COUNTER_COMBINE(W) (3u * (W) + 2u)
+#define FE2O3_EP_DEFAULT_SPIN (1u << 24)
+
 // Capacity of the context's reduction scratch: partials followed by one counter.
 #define FE2O3_REDUCE_MAX_BLOCKS 4096u
 
@@ -71,6 +83,31 @@ __device__ __forceinline__ uint16_t f32_to_bf16_bits(float v) {
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+// ---- system-scope flags (expert-parallel exchange) -----------------------------
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Bounded wait until *flag has reached `epoch` (flags only grow; the comparison survives wrap-around).
+// Returns false after `limit` polls.
+__device__ __forceinline__ bool flag_wait(const uint32_t *flag, uint32_t epoch, uint32_t limit) {
+    uint32_t spins = 0;
+    while ((int32_t)(ld_acquire_sys(flag) - epoch) < 0) {
+        if (++spins > limit) return false;
+        __nanosleep(64);
+    }
+    return true;
+}
+// Orders this thread's earlier generic-proxy observations (a flag it acquired) before its later
+// asynchronous-proxy reads of global memory (bulk tensor loads of the rows that flag covers).
+__device__ __forceinline__ void fence_proxy_async_global() {
+    asm volatile("fence.proxy.async.global;" ::: "memory");
 }
 
 // ---- mbarrier -------------------------------------------------------------
@@ -140,6 +177,20 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
 // instruction (elect, __syncwarp, a collective TMEM load).
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t *bar, uint32_t parity) {
     return __all_sync(0xffffffffu, mbar_wait(bar, parity)) != 0;
+}
+// Waits of roles that depend on another role of the same CTA: when that role has given up (it sets
+// *abort), the pipeline will never advance, so the wait ends at its next look at the flag instead of
+// running out its own limit.  The flag is only read on the slow path.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t *bar, uint32_t parity, const volatile int *abort) {
+    bool done = mbar_test(bar, parity);
+    for (uint32_t i = 0; !done && i < FE2O3_SPIN_LIMIT; ++i) {
+        done = mbar_try_wait(bar, parity);
+        if (!done && i > 64) {
+            __nanosleep(32);
+            if ((i & 127u) == 127u && *abort) break;
+        }
+    }
+    return __all_sync(0xffffffffu, done) != 0;
 }
 // Arrival with a count: stands in for `n` parties at once.
 __device__ __forceinline__ void mbar_arrive_n(uint64_t *bar, uint32_t n) {

@@ -50,9 +50,12 @@ struct TileCoord {
 };
 
 // Static tile order.  Plain: bands of kGroupM m-tiles, m fastest inside a band.
-// Grouped: expert-major; inside an expert m fastest.
+// Grouped: expert-major; inside an expert m fastest.  Grouped with per-source waiting (first GEMM of
+// the expert-parallel FFN): inside an expert n fastest, and the m-tiles rotated so that the tile
+// holding this rank's own first row comes first: rows that never crossed NVLink are there at once,
+// the other sources' rows get the time of those tiles to arrive.
 __device__ __forceinline__ TileCoord decode_tile(uint32_t id, const GemmParams &p, uint32_t n_tiles,
-                                                 const uint32_t *s_off) {
+                                                 const uint32_t *s_off, const uint32_t *s_pair) {
     TileCoord t;
     t.valid = false;
     t.expert = 0;
@@ -77,8 +80,16 @@ __device__ __forceinline__ TileCoord decode_tile(uint32_t id, const GemmParams &
         const uint32_t cnt = mt * n_tiles;
         if (id < base + cnt) {
             const uint32_t local = id - base;
-            t.m0 = s_off[e] + (local % mt) * BM;
-            t.n0 = local / mt;
+            uint32_t mi;
+            if (p.ep.rows_flags) {
+                const uint32_t own = s_pair[e * p.ep.world + p.ep.rank] - s_off[e];   // this rank's first row in the segment
+                mi = (local / n_tiles + min(own / BM, mt - 1)) % mt;
+                t.n0 = local % n_tiles;
+            } else {
+                mi = local % mt;
+                t.n0 = local / mt;
+            }
+            t.m0 = s_off[e] + mi * BM;
             t.m_end = s_off[e + 1];
             t.expert = p.expert_mod ? e % p.expert_mod : e;   // index of the B matrix
             t.valid = true;
@@ -134,7 +145,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint64_t *tmem_full = empty + kStages;
     uint64_t *tmem_empty = tmem_full + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + 2);
-    __shared__ uint32_t s_off[33];
+    __shared__ uint32_t s_off[33];             // row segments of the groups
+    __shared__ uint32_t s_pair[33];            // expert-parallel: rows of (local expert, source) pairs
+    __shared__ unsigned long long s_peer[32];  // expert-parallel: return buffer of every rank
     __shared__ int s_abort;
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -142,7 +155,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const uint32_t num_kb = (p.K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
-        s_abort = 0;
+        // Expert-parallel passes chain kernels through flags on other ranks: once a kernel of the pass has
+        // reported a fault (a wait that ran out, a bad table), the later ones must not publish anything.
+        // They find the status word set and do nothing but their arrival counting.
+        s_abort = (p.ep.pair_offsets && p.status && __ldcg(p.status) != 0u) ? 1 : 0;
         for (int i = 0; i < kStages; ++i) {
             mbar_init(&full[i], 1);
             mbar_init(&empty[i], 1);
@@ -153,9 +169,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         mbar_fence_init();
     }
-    if (p.experts) {
-        for (uint32_t i = threadIdx.x; i <= p.experts; i += blockDim.x) s_off[i] = p.expert_offsets[i];
+    if (p.experts && threadIdx.x == 64) {
+        // The segment table is device data (in the expert-parallel layer it derives from other ranks'
+        // counts): it is made monotone and cut off at M here, so that no row index derived from it can
+        // leave A or C, and the fault is reported instead.
+        const uint32_t stride = p.ep.pair_offsets ? p.ep.world : 1u;
+        uint32_t prev = 0;
+        bool bad = false;
+        for (uint32_t i = 0; i <= p.experts; ++i) {
+            uint32_t v = p.expert_offsets[i * stride];
+            if (v < prev || v > p.M) { bad = true; v = v < prev ? prev : p.M; }
+            s_off[i] = v;
+            prev = v;
+        }
+        if (bad) kstatus_set(p.status, FE2O3_KSTATUS_SLOT_RANGE);
     }
+    if (p.ep.pair_offsets) {
+        const uint32_t pairs = p.experts * p.ep.world;   // at most 32
+        for (uint32_t i = threadIdx.x; i <= pairs; i += blockDim.x) s_pair[i] = min(p.ep.pair_offsets[i], p.M);
+        if (p.ep.peer_ret)
+            for (uint32_t i = threadIdx.x; i < p.ep.world; i += blockDim.x) s_peer[i] = p.ep.peer_ret[i];
+    }
+    const uint32_t ep_epoch = p.ep.epoch_counter ? __ldcg(p.ep.epoch_counter) + 1u : p.ep.epoch;
     if (warp == 1) {
         tmem_alloc(tmem_slot, 2 * BN);
         tmem_relinquish();
@@ -164,6 +199,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    const bool dead = s_abort != 0;   // uniform over the CTA: read after the barrier, before any role can set it
 
     if (warp == 0) {
         // ------------------------------------------------ TMA producer (warp converged, one elected lane issues)
@@ -173,12 +209,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         __syncwarp();
         uint32_t stage = 0, phase = 0, loaded = 0;
-        bool ok = true;
+        uint32_t seen = 0;   // sources whose "rows complete" flag this CTA has already acquired
+        bool ok = !dead;
         for (uint32_t id = blockIdx.x; ok; id += gridDim.x) {
-            TileCoord t = decode_tile(id, p, n_tiles, s_off);
+            TileCoord t = decode_tile(id, p, n_tiles, s_off, s_pair);
             if (!t.valid) break;
+            if (p.ep.rows_flags) {
+                // Sources with rows in this tile.  Their rows were written by the source ranks' SMs
+                // (generic proxy, then a system-scope release of the flag); this warp acquires the flag
+                // and orders that observation before its bulk tensor loads (asynchronous proxy) with a
+                // proxy fence.
+                const uint32_t hi = min(t.m0 + BM, t.m_end);
+                uint32_t need = 0;
+                if (lane < p.experts * p.ep.world && s_pair[lane] < hi && s_pair[lane + 1] > t.m0)
+                    need = 1u << (lane % p.ep.world);
+                need = __reduce_or_sync(0xffffffffu, need) & ~seen;
+                seen |= need;
+                while (need) {
+                    const uint32_t src = __ffs(need) - 1;
+                    need &= need - 1;
+                    if (!__all_sync(0xffffffffu, flag_wait(p.ep.rows_flags + src, ep_epoch, p.ep.spin_limit))) { ok = false; break; }
+                }
+                if (!ok) break;
+                fence_proxy_async_global();
+            }
             for (uint32_t kb = 0; kb < num_kb; ++kb, ++loaded) {
-                if (!mbar_wait_warp(&empty[stage], phase ^ 1)) { ok = false; break; }
+                if (!mbar_wait_warp(&empty[stage], phase ^ 1, &s_abort)) { ok = false; break; }
                 if (elect_one()) {
                     uint8_t *sa = smem + stage * L::kStageBytes;
                     uint8_t *sb = sa + L::kABytes;
@@ -210,18 +266,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // ------------------------------------------------ MMA issuer (warp converged, one elected lane issues)
         constexpr uint32_t idesc = umma_idesc(1u, BM, BN, 0u, 1u);
         uint32_t stage = 0, phase = 0, it = 0;
-        bool ok = true;
+        bool ok = !dead;
         const uint64_t desc_a0 = umma_smem_desc(smem_u32(smem), 16, 1024);
         const uint64_t desc_b0 = umma_smem_desc(smem_u32(smem) + L::kABytes, 8192, 1024);
         for (uint32_t id = blockIdx.x; ok; id += gridDim.x, ++it) {
-            TileCoord t = decode_tile(id, p, n_tiles, s_off);
+            TileCoord t = decode_tile(id, p, n_tiles, s_off, s_pair);
             if (!t.valid) break;
             const uint32_t buf = it & 1, acc_phase = (it >> 1) & 1;
-            if (!mbar_wait_warp(&tmem_empty[buf], acc_phase ^ 1)) { ok = false; break; }
+            if (!mbar_wait_warp(&tmem_empty[buf], acc_phase ^ 1, &s_abort)) { ok = false; break; }
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + buf * BN;
             for (uint32_t kb = 0; kb < num_kb; ++kb) {
-                if (!mbar_wait_warp(&full[stage], phase)) { ok = false; break; }
+                if (!mbar_wait_warp(&full[stage], phase, &s_abort)) { ok = false; break; }
                 tc_fence_after();
                 if (elect_one()) {
                     // only the 16-byte-unit start address field of the descriptors moves
@@ -258,13 +314,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         uint8_t *slice = smem + L::kStagingOffset + ew * 4096;
         const bool out_bf16 = p.epilogue == EPI_GELU_BF16;
         uint32_t it = 0;
-        bool ok = true;
+        bool ok = !dead;
         bool store_pending = false;
         for (uint32_t id = blockIdx.x; ok; id += gridDim.x, ++it) {
-            TileCoord t = decode_tile(id, p, n_tiles, s_off);
+            TileCoord t = decode_tile(id, p, n_tiles, s_off, s_pair);
             if (!t.valid) break;
             const uint32_t buf = it & 1, acc_phase = (it >> 1) & 1;
-            if (!mbar_wait_warp(&tmem_full[buf], acc_phase)) { ok = false; break; }
+            if (!mbar_wait_warp(&tmem_full[buf], acc_phase, &s_abort)) { ok = false; break; }
             tc_fence_after();
             const uint32_t row0 = t.m0 + quad * 32;
             const uint32_t row = row0 + lane;
@@ -272,6 +328,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const bool bulk = p.bulk_store && row0 + 32 <= t.m_end;   // warp-uniform
             const uint32_t col_base = t.n0 * BN + col_half * (BN / 2);
             const uint32_t taddr = tmem_base + buf * BN + col_half * (BN / 2) + ((quad * 32u) << 16);
+            // scatter epilogue: where this lane's row goes (0 = nowhere)
+            unsigned long long dst_row = 0;
+            if (p.epilogue == EPI_SCATTER_PEER && row_ok) {
+                const uint2 meta = __ldcg(p.ep.row_meta + row);   // (route id, home rank), written by the source rank
+                if (meta.y < p.ep.world && meta.x < p.ep.ret_rows)
+                    dst_row = s_peer[meta.y] + (unsigned long long)meta.x * p.N * sizeof(float);
+                else
+                    kstatus_set(p.status, FE2O3_KSTATUS_SLOT_RANGE);
+            }
             if (out_bf16) {
                 // ---- GELU, bf16 output: two chunks (64 columns) per 128-byte group
 #pragma unroll 1
@@ -336,7 +401,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     }
                     const uint32_t col = col_base + g * 32;
                     if (col >= p.N) continue;
-                    if (bulk && p.epilogue == EPI_STORE) {
+                    if (p.epilogue == EPI_SCATTER_PEER) {
+                        // Every row of the tile has its own destination (the return buffer of its home
+                        // rank, at its route id).  The chunk is transposed through the warp's slice of
+                        // shared memory so that each store instruction writes four whole 128-byte
+                        // segments: eight lanes per row, one 16-byte piece each.
+                        __syncwarp();   // the previous chunk has been read out of the slice
+#pragma unroll
+                        for (int k = 0; k < 8; ++k)
+                            *reinterpret_cast<uint4 *>(slice + lane * 128 + ((k ^ (lane & 7)) * 16)) =
+                                make_uint4(r[4 * k], r[4 * k + 1], r[4 * k + 2], r[4 * k + 3]);
+                        __syncwarp();
+                        const uint32_t piece = lane & 7;
+#pragma unroll
+                        for (int it = 0; it < 8; ++it) {
+                            const uint32_t rr = it * 4 + (lane >> 3);
+                            const uint4 v = *reinterpret_cast<const uint4 *>(slice + rr * 128 + ((piece ^ (rr & 7)) * 16));
+                            const unsigned long long dst = __shfl_sync(0xffffffffu, dst_row, rr);
+                            if (dst != 0 && col + piece * 4 < p.N)
+                                *reinterpret_cast<uint4 *>(dst + (unsigned long long)(col + piece * 4) * sizeof(float)) = v;
+                        }
+                    } else if (bulk && p.epilogue == EPI_STORE) {
                         if (store_pending) {
                             if (lane == 0) tma_store_wait_read();
                             __syncwarp();
@@ -375,6 +460,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         // the staging slice must stay intact until the last copy has read it
         if (store_pending && lane == 0) tma_store_wait_read();
+        // rows stored into other ranks' memory must be visible there before "outputs ready" is raised
+        if (p.epilogue == EPI_SCATTER_PEER) __threadfence_system();
         if (!ok && lane == 0) {
             kstatus_set(p.status, FE2O3_KSTATUS_WAIT_EXPIRED);
             atomicExch(&s_abort, 1);
@@ -385,6 +472,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, 2 * BN);
+    }
+    if (p.ep.done_counter && threadIdx.x == 0) {
+        // The last CTA of the grid to finish raises "outputs ready" on every rank, unless some CTA gave
+        // up on a wait (the pass is void then).  A failed CTA still arrives, so the counter is re-armed.
+        const bool failed = s_abort != 0;
+        const uint32_t old = atomicAdd(p.ep.done_counter, failed ? 0x10001u : 1u);
+        if ((old & 0xffffu) == gridDim.x - 1) {
+            atomicExch(p.ep.done_counter, 0u);
+            if (!failed && (old >> 16) == 0) {
+                __threadfence_system();
+                for (uint32_t w = 0; w < p.ep.world; ++w)
+                    st_release_sys(reinterpret_cast<uint32_t *>(p.ep.peer_flags[w]) + FE2O3_EP_FLAG_OUTPUTS(p.ep.world) + p.ep.rank,
+                                   ep_epoch);
+            }
+        }
     }
 }
 
@@ -453,7 +555,8 @@ bool gemm_tc_supported(uint64_t a, uint64_t b, uint32_t lda, uint32_t ldb, uint3
 // bound on rows (the capacity of A and C).
 int32_t gemm_tc_plan(fe2o3_ctx *ctx, GemmTcPlan *plan, uint64_t a, uint64_t b, uint64_t c, uint32_t M, uint32_t N,
                      uint32_t K, uint32_t lda, uint32_t ldb, uint32_t ldc, float alpha, float beta, uint32_t epilogue,
-                     const uint32_t *expert_offsets, uint32_t experts, uint32_t expert_mod, uint32_t b_matrices) {
+                     const uint32_t *expert_offsets, uint32_t experts, uint32_t expert_mod, uint32_t b_matrices,
+                     const GemmEp *ep) {
     plan->bn = (N > 128) ? 256 : 128;
     uint64_t dA[2] = {K, M}, sA[1] = {(uint64_t)lda * 2};
     uint32_t bA[2] = {BK, BM};
@@ -473,7 +576,8 @@ int32_t gemm_tc_plan(fe2o3_ctx *ctx, GemmTcPlan *plan, uint64_t a, uint64_t b, u
     const uint32_t esize = epilogue == EPI_GELU_BF16 ? 2u : 4u;
     uint32_t bulk = 0;
     plan->tmC = plan->tmA;   // a valid map when the bulk path is off (never used then)
-    if (epilogue != EPI_ALPHA_BETA && (c & 15u) == 0 && ((uint64_t)ldc * esize) % 16u == 0 && M > 0 && N > 0) {
+    if (epilogue != EPI_ALPHA_BETA && epilogue != EPI_SCATTER_PEER && (c & 15u) == 0 && ((uint64_t)ldc * esize) % 16u == 0 &&
+        M > 0 && N > 0) {
         uint64_t dC[2] = {N, M}, sC[1] = {(uint64_t)ldc * esize};
         uint32_t bC[2] = {128u / esize, 32};
         st = esize == 2 ? fe2o3_make_tmap_bf16(&plan->tmC, c, 2, dC, sC, bC) : fe2o3_make_tmap_f32(&plan->tmC, c, 2, dC, sC, bC);
@@ -481,7 +585,7 @@ int32_t gemm_tc_plan(fe2o3_ctx *ctx, GemmTcPlan *plan, uint64_t a, uint64_t b, u
         bulk = 1;
     }
     plan->p = GemmParams{reinterpret_cast<void *>(c), M, N, K, ldc, alpha, beta, epilogue, expert_offsets, experts,
-                         expert_mod, bulk, ctx->status_word};
+                         expert_mod, bulk, ctx->status_word, ep ? *ep : GemmEp{}};
     const uint32_t n_tiles = (N + plan->bn - 1) / plan->bn;
     const uint64_t m_tiles = (uint64_t)(M + BM - 1) / BM + experts;  // grouped: each expert may add a ragged tile
     uint64_t tiles = m_tiles * n_tiles;
@@ -490,14 +594,16 @@ int32_t gemm_tc_plan(fe2o3_ctx *ctx, GemmTcPlan *plan, uint64_t a, uint64_t b, u
     return FE2O3_OK;
 }
 
+// Function attributes are per device: called by fe2o3_ctx_create with the context's device current.
+int32_t gemm_tc_init_device() {
+    FE2O3_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    (int)SmemLayout<256>::kTotal));
+    FE2O3_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    (int)SmemLayout<128>::kTotal));
+    return FE2O3_OK;
+}
+
 int32_t gemm_tc_launch(const GemmTcPlan *plan, cudaStream_t s) {
-    static std::once_flag once;
-    std::call_once(once, [] {
-        cudaFuncSetAttribute(gemm_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)SmemLayout<256>::kTotal);
-        cudaFuncSetAttribute(gemm_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)SmemLayout<128>::kTotal);
-    });
     if (plan->p.M == 0 || plan->p.N == 0) return FE2O3_OK;
     if (plan->bn == 256)
         gemm_tc_kernel<256><<<plan->grid, kThreads, plan->smem, s>>>(plan->tmA, plan->tmB, plan->tmC, plan->p);

@@ -2,7 +2,27 @@
 #pragma once
 #include "common.cuh"
 
-enum GemmEpilogue : uint32_t { EPI_STORE = 0, EPI_ALPHA_BETA = 1, EPI_GELU_BF16 = 2 };
+enum GemmEpilogue : uint32_t { EPI_STORE = 0, EPI_ALPHA_BETA = 1, EPI_GELU_BF16 = 2, EPI_SCATTER_PEER = 3 };
+
+// Expert-parallel extensions of the grouped GEMM (all zero otherwise).  The rows of A are this rank's
+// receive buffer: `experts` contiguous segments (one per local expert), each made of `world` runs, one
+// per source rank; pair_offsets[le * world + s] is the first row of (local expert le, source s).
+struct GemmEp {
+    const uint32_t *pair_offsets;   // [experts * world + 1]; null = not expert-parallel
+    uint32_t world, rank;
+    const uint32_t *epoch_counter;  // pass number - 1 on the device, or null to use `epoch`
+    uint32_t epoch;
+    uint32_t spin_limit;            // polls before a flag wait gives up
+    // input side (first FFN GEMM): the producer waits for "rows complete" of a source right before the
+    // first tile that holds rows of that source; tiles are taken m-tile major starting at this rank's own rows
+    const uint32_t *rows_flags;     // this rank's flags, one per source; null = rows are already complete
+    // output side (EPI_SCATTER_PEER, second FFN GEMM): row r goes to ret[row_meta[r].y] + row_meta[r].x * N
+    const uint2 *row_meta;          // (route id, home rank) per row of A / C
+    const uint64_t *peer_ret;       // [world] base address of every rank's return buffer
+    uint32_t ret_rows;              // rows of a return buffer
+    const uint64_t *peer_flags;     // [world] base address of every rank's flag block
+    uint32_t *done_counter;         // this rank's arrival counter of the kernel's CTAs
+};
 
 struct GemmParams {
     void *c;                 // f32 (EPI_STORE / EPI_ALPHA_BETA) or bf16 bits (EPI_GELU_BF16)
@@ -17,6 +37,7 @@ struct GemmParams {
     uint32_t expert_mod;     // group g reads B matrix (g % expert_mod); 0 = identity
     uint32_t bulk_store;     // C is addressable by the copy engine (tensor map tmC is valid)
     uint32_t *status;
+    GemmEp ep;
 };
 
 struct GemmTcPlan {
@@ -34,6 +55,8 @@ int32_t fe2o3_make_tmap_f32(CUtensorMap *out, uint64_t base, uint32_t rank, cons
 bool gemm_tc_supported(uint64_t a, uint64_t b, uint32_t lda, uint32_t ldb, uint32_t K);
 int32_t gemm_tc_plan(fe2o3_ctx *ctx, GemmTcPlan *plan, uint64_t a, uint64_t b, uint64_t c, uint32_t M, uint32_t N,
                      uint32_t K, uint32_t lda, uint32_t ldb, uint32_t ldc, float alpha, float beta, uint32_t epilogue,
-                     const uint32_t *expert_offsets, uint32_t experts, uint32_t expert_mod = 0, uint32_t b_matrices = 0);
+                     const uint32_t *expert_offsets, uint32_t experts, uint32_t expert_mod = 0, uint32_t b_matrices = 0,
+                     const GemmEp *ep = nullptr);
 int32_t gemm_tc_launch(const GemmTcPlan *plan, cudaStream_t s);
+int32_t gemm_tc_init_device();
 void gemm_tc_geometry(const GemmTcPlan *plan, fe2o3_geometry *geo);

@@ -289,13 +289,18 @@ device_scan_kernel(const uint32_t *in, uint32_t *out, uint64_t n, uint32_t exclu
             }
             if (!ok) break;
             if (!mbar_wait_warp(&sh.agg_ready[st], ph)) { ok = false; break; }
+            // The stage's partial sums are read BEFORE the arrival below: that arrival lets the finish
+            // warps release the stage, after which the aggregate warps may overwrite sh.part[st].
+            uint32_t aggregate = 0;
+            if constexpr (!kFloat) {
+                for (int q = 0; q < kFinishWarps; ++q) aggregate += sh.part[st][q];
+            }
+            __syncwarp();
             if (lane == 0) {
                 sh.prefix[st] = prefix;
                 mbar_arrive(&sh.prefix_ready[st]);
             }
             if constexpr (!kFloat) {
-                uint32_t aggregate = 0;
-                for (int q = 0; q < kFinishWarps; ++q) aggregate += sh.part[st][q];
                 running = prefix + aggregate;
                 covered = tile + 1;
             }
@@ -396,10 +401,6 @@ int32_t launch_device_scan(fe2o3_ctx *ctx, cudaStream_t s, const void *args, fe2
     const uint32_t grid = tiles < sms ? (tiles ? tiles : 1u) : sms;
     if (geo) *geo = fe2o3_geometry{{grid, 1, 1}, {kScanThreads, 1, 1}, kSmemBytes, 1};
     if (plan_only || n == 0) return FE2O3_OK;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        cudaFuncSetAttribute(device_scan_kernel<kFloat>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
-    });
     // ticket at word 0, descriptors from byte 64
     uint32_t *ticket = ctx->scan_scratch;
     uint64_t *desc = reinterpret_cast<uint64_t *>(ctx->scan_scratch + 16);
@@ -409,6 +410,13 @@ int32_t launch_device_scan(fe2o3_ctx *ctx, cudaStream_t s, const void *args, fe2
                                                                       a->exclusive, ticket, desc, ctx->status_word);
     fe2o3_count_launch(1);
     return fe2o3_cuda_status(cudaGetLastError(), kFloat ? "device_scan_sum_f32" : "device_scan_sum_u32");
+}
+
+// Function attributes are per device: called by fe2o3_ctx_create with the context's device current.
+int32_t device_scan_init_device() {
+    FE2O3_CUDA(cudaFuncSetAttribute(device_scan_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+    FE2O3_CUDA(cudaFuncSetAttribute(device_scan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+    return FE2O3_OK;
 }
 
 int32_t launch_device_scan_u32(fe2o3_ctx *ctx, cudaStream_t s, const void *args, fe2o3_geometry *geo, bool plan_only) {

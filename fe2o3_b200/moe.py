@@ -6,22 +6,28 @@ rank order) with every stage a launch through the C ABI.
 
 Several GPUs (one process per GPU, `torch.distributed`): tokens are split
 across ranks and experts are block-partitioned.  Each rank routes its own
-tokens; rows bound for experts on other ranks travel in one all-to-all
-(dispatch), the owning rank runs the grouped FFN, and a second all-to-all
-(combine) brings the rows back to the token's home rank, where the weighted
-combine runs in rank order.  torch is used for device memory and NCCL plumbing
-only; every arithmetic stage is a kernel of libfe2o3_b200.so.
+tokens; rows bound for experts on other ranks are stored straight into the
+owners' receive buffers over NVLink by the dispatch kernel, the owning rank
+runs the grouped FFN, whose second GEMM stores every output row into the home
+rank's return buffer from its epilogue, and the home rank combines the two rows
+of each token in rank order from local memory (`exchange="peer"`, kernels of
+csrc/moe_ep.cu and csrc/gemm_tc.cu).  `exchange="nccl"` does the two transfers
+with NCCL all-to-alls instead and needs the host for its split sizes.  torch is
+used for device memory and process-group plumbing only; every arithmetic stage
+is a kernel of libfe2o3_b200.so.
 """
 import numpy as np
 
-from . import SCHEDULE_AUTO, prepare  # noqa: F401
+from . import SCHEDULE_AUTO, Fe2o3Error, PeerRegion, prepare  # noqa: F401
 
 DROP = 0xFFFFFFFF
 
 
 def split_plan(counts, rank, world):
-    """Pure host logic of the exchange, from the gathered per-(source rank,
-    expert) route counts `counts[world][experts]`.
+    """Pure host logic of the NCCL exchange, from the gathered per-(source rank,
+    expert) ADMITTED route counts `counts[world][experts]` (the rows that exist
+    in the senders' compact buffers: requests beyond an expert's capacity are
+    dropped before the exchange).
 
     Returns (send_rows, recv_rows, group_offsets): rows this rank sends to each
     destination, rows it receives from each source, and the exclusive scan of
@@ -38,11 +44,35 @@ def split_plan(counts, rank, world):
     return send_rows, recv_rows, group_offsets
 
 
+def pair_plan(counts, rank, world):
+    """Pure host statement of the peer exchange's row layout, from the same
+    admitted counts: on its owner, the rows of local expert `le` from source `s`
+    start at pair_offsets[le * world + s] (local-expert major, source minor), and
+    `bases[d][e]` is the first row of THIS rank's rows for expert e on e's owner d.
+    The dispatch kernel computes both on the device; tests compare against this."""
+    counts = np.asarray(counts, np.int64)
+    experts = counts.shape[1]
+    per = experts // world
+    mine = counts[:, rank * per:(rank + 1) * per]           # [source][local expert]
+    pair_offsets = np.zeros(experts + 1, np.uint32)
+    pair_offsets[1:] = np.cumsum(mine.T.reshape(-1))          # le-major, source-minor
+    bases = np.zeros(experts, np.int64)
+    for e in range(experts):
+        d, le = divmod(e, per)
+        bases[e] = counts[:, d * per:d * per + le].sum() + counts[:rank, e].sum()
+    return pair_offsets, bases
+
+
 class MoeTop2Layer:
-    def __init__(self, ctx, stream, tokens, d_model, d_ff, experts, rank=0, world=1, capacity=None, exchange="auto"):
+    def __init__(self, ctx, stream, tokens, d_model, d_ff, experts, rank=0, world=1, capacity=None, exchange="auto",
+                 spin_limit=0, peer_ptrs=None):
+        """`peer_ptrs` (optional, peer exchange only): {"recv_x" | "recv_meta" | "ret" | "counts" | "flags":
+        [address of rank p's buffer for p in range(world)]} when the caller has mapped the buffers itself
+        (sizes: `region_sizes`); by default the layer allocates and maps them."""
         import torch
         self.torch = torch
-        self.exchange = "none" if world == 1 else exchange
+        # a single rank runs the reference's host schedule unless the peer path is asked for by name
+        self.exchange = "none" if (world == 1 and exchange != "peer") else exchange
         assert experts % world == 0 and tokens % world == 0
         self.ctx, self.stream = ctx, stream
         self.rank, self.world = rank, world
@@ -63,22 +93,47 @@ class MoeTop2Layer:
         self.offsets = z(E + 1, torch.int32)
         self.weights = z(R, torch.float32)
         self.out = z(T * d, torch.float32)
-        # rows this rank may have to process: every route of every rank in the worst case
-        self.max_rows = R * world
-        self.compact_x = z(R * d, torch.bfloat16)            # local routes, expert-major
-        self.compact_out = z(R * d, torch.float32)           # FFN rows back in local slot order
-        if world > 1 and self.exchange in ("auto", "peer"):
+        # rows this rank may have to process: every admitted route of every rank in the worst case
+        self.max_rows = min(R, E * self.capacity) * world
+        if self.exchange in ("auto", "peer"):
             try:
-                self._setup_peer_buffers(dev)
+                self._setup_peer_buffers(dev, peer_ptrs)
                 self.exchange = "peer"
-            except Exception as err:  # symmetric memory unavailable: use the NCCL all-to-all path
+            except Exception as err:  # no peer mapping available: use the NCCL all-to-all path
                 if self.exchange == "peer":
                     raise
                 self.exchange, self.exchange_fallback_reason = "nccl", f"{type(err).__name__}: {err}"
-        if world > 1:
-            if self.exchange == "nccl":
-                self.recv_x = z(self.max_rows * d, torch.bfloat16)
-                self.ffn_out = z(self.max_rows * d, torch.float32)
+        P = lambda op, **kw: prepare(ctx, op, **kw)
+        self.k_gate = P("moe_gate_v1", x=self.x, wg=self.wg, logits=self.logits, tokens=T, d_model=d, experts=E)
+        self.k_top2 = P("moe_top2_v1", logits=self.logits, top2_experts=self.top2, requested_counts=self.requested,
+                        admitted_counts=self.admitted, expert_offsets=self.offsets, route_slots=self.slots,
+                        permutation=self.perm, inverse=self.inverse, tokens=T, experts=E, capacity=self.capacity)
+        self.k_weights = P("moe_route_weights_v1", logits=self.logits, top2_experts=self.top2,
+                           route_weights=self.weights, tokens=T, experts=E)
+        if self.exchange == "peer":
+            self.rows = self.max_rows
+            self.hidden = z(self.max_rows * f, torch.bfloat16)
+            self.pair_offsets = z(E + 1, torch.int32)
+            self.epoch_counter = z(1, torch.int32)  # pass number, advanced on the device: passes replay from a graph
+            me = rank
+            common = dict(pair_offsets=self.pair_offsets, peer_ret=self.peer_ret, peer_flags=self.peer_flags,
+                          epoch_counter=self.epoch_counter, tokens=T, d_model=d, experts=E, world=world, rank=rank,
+                          epoch=0, max_rows=self.max_rows, spin_limit=spin_limit)
+            self.k_phase = [P("moe_ep_exchange_v1", x=self.x, top2_experts=self.top2, permutation=self.perm,
+                              inverse=self.inverse, expert_offsets=self.offsets, admitted_counts=self.admitted,
+                              route_weights=self.weights, combined_output=self.out, peer_recv_x=self.peer_recv_x,
+                              peer_recv_meta=self.peer_recv_meta, peer_counts=self.peer_counts, phase=ph, **common)
+                            for ph in range(2)]
+            self.k_ffn = P("moe_ep_ffn_v1", recv_x=(self._ptrs["recv_x"][me], self.max_rows * d), w1=self.w1, w2=self.w2,
+                           hidden=self.hidden, recv_meta=(self._ptrs["recv_meta"][me], 2 * self.max_rows),
+                           flags=(self._ptrs["flags"][me], 3 * world + 3), d_ff=f, **common)
+            self.launches_per_step = 8
+            return
+        self.compact_x = z(R * d, torch.bfloat16)            # local routes, expert-major
+        self.compact_out = z(R * d, torch.float32)           # FFN rows back in local slot order
+        if world > 1:   # NCCL all-to-all path
+            self.recv_x = z(self.max_rows * d, torch.bfloat16)
+            self.ffn_out = z(self.max_rows * d, torch.float32)
             self.group_offsets = z(E + 1, torch.int32)
             self.counts_all = z(world * E, torch.int32)
             self.host_counts = torch.zeros(world * E, dtype=torch.int32).pin_memory()
@@ -88,13 +143,6 @@ class MoeTop2Layer:
             rows, ffn_in, ffn_res, ffn_off = R, self.compact_x, self.compact_out, self.offsets
         self.hidden = z(rows * f, torch.bfloat16)
         self.rows = rows
-        P = lambda op, **kw: prepare(ctx, op, **kw)
-        self.k_gate = P("moe_gate_v1", x=self.x, wg=self.wg, logits=self.logits, tokens=T, d_model=d, experts=E)
-        self.k_top2 = P("moe_top2_v1", logits=self.logits, top2_experts=self.top2, requested_counts=self.requested,
-                        admitted_counts=self.admitted, expert_offsets=self.offsets, route_slots=self.slots,
-                        permutation=self.perm, inverse=self.inverse, tokens=T, experts=E, capacity=self.capacity)
-        self.k_weights = P("moe_route_weights_v1", logits=self.logits, top2_experts=self.top2,
-                           route_weights=self.weights, tokens=T, experts=E)
         if world == 1:
             self.k_ffn = P("moe_expert_ffn_v1", x=self.x, w1=self.w1, w2=self.w2, permutation=self.perm,
                            expert_offsets=self.offsets, compact_x=self.compact_x, hidden=self.hidden,
@@ -107,39 +155,122 @@ class MoeTop2Layer:
                            experts_cycle=self.per)
         self.k_combine = P("moe_expert_combine_v1", compact_output=self.compact_out, inverse=self.inverse,
                            route_weights=self.weights, combined_output=self.out, tokens=T, width=d)
-        if self.exchange == "peer":
-            from ._lib import MoeEpExchangeArgs
-            self.remote_rows = z(R, torch.int32)
-            self.epoch_counter = z(1, torch.int32)  # pass number, advanced on the device: passes replay from a graph
-            self.k_phase = [P("moe_ep_exchange_v1", x=self.x, top2_experts=self.top2, permutation=self.perm,
-                              inverse=self.inverse, expert_offsets=self.offsets, requested_counts=self.requested,
-                              route_weights=self.weights, group_offsets=self.group_offsets,
-                              remote_rows=self.remote_rows, combined_output=self.out, peer_recv_x=self.peer_recv_x,
-                              peer_ffn_out=self.peer_ffn_out, peer_counts=self.peer_counts,
-                              peer_flags=self.peer_flags, epoch_counter=self.epoch_counter, tokens=T, d_model=d,
-                              experts=E, world=world, rank=rank, epoch=0, max_rows=self.max_rows, phase=ph)
-                            for ph in range(5)]
         self.launches_per_step = 7 if world == 1 else 8
 
-    def _setup_peer_buffers(self, dev):
-        """Receive buffer, expert-output buffer, counts table and flags in symmetric (peer-mapped) memory."""
+    # ---- peer-visible buffers ---------------------------------------------------------------
+    @staticmethod
+    def region_sizes(tokens, d_model, experts, world, capacity=None):
+        """Bytes of each peer-visible buffer of one rank (tokens = the whole batch)."""
+        R = 2 * (tokens // world)
+        max_rows = min(R, experts * (R if capacity is None else capacity)) * world
+        return {"recv_x": max_rows * d_model * 2, "recv_meta": max_rows * 8, "ret": R * d_model * 4,
+                "counts": world * experts * 4, "flags": 4096}
+
+    def _setup_peer_buffers(self, dev, peer_ptrs=None):
+        """Receive buffer, row records, return buffer, counts table and flags, mapped by every rank.
+
+        The regions are allocated and exported by the library (fe2o3_peer_region_*, CUDA IPC) and the
+        handles travel over the process group; when that is not possible on this system, torch's
+        symmetric memory provides the same mapping."""
+        t = self.torch
+        sizes = self.region_sizes(self.T * self.world, self.d, self.E, self.world, self.capacity)
+        self.peer_mapping = None
+        if peer_ptrs is not None:
+            self._ptrs = {k: [int(p) for p in peer_ptrs[k]] for k in sizes}
+            self.peer_mapping = "caller"
+        elif self.world == 1:
+            self._local = {k: t.zeros(n, dtype=t.uint8, device=dev) for k, n in sizes.items()}
+            self._ptrs = {k: [v.data_ptr()] for k, v in self._local.items()}
+            self.peer_mapping = "local"
+        else:
+            import torch.distributed as dist
+
+            def all_ok(ok):   # every rank must take the same branch: agree on the outcome of each step
+                flag = t.tensor([1 if ok else 0], dtype=t.int32, device=dev)
+                dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+                return int(flag.item()) == 1
+            reason = ""
+            try:
+                mine = self._create_regions_ipc(sizes)
+            except Fe2o3Error as err:
+                mine, reason = None, str(err)
+            mapped = False
+            if all_ok(mine is not None):
+                try:
+                    self._ptrs = self._import_regions_ipc(dev, sizes, mine)
+                    mapped = True
+                except Fe2o3Error as err:
+                    reason = str(err)
+                mapped = all_ok(mapped)
+            if mapped:
+                self.peer_mapping = "ipc"
+            else:
+                self.ipc_fallback_reason = reason or "another rank could not map the regions"
+                self._close_regions()
+                self._ptrs = self._map_regions_symm(dev, sizes)
+                self.peer_mapping = "symmetric_memory"
+            t.cuda.synchronize()
+            dist.barrier()
+        table = lambda k: t.tensor(self._ptrs[k], dtype=t.int64, device=dev)
+        self.peer_recv_x, self.peer_recv_meta, self.peer_ret = table("recv_x"), table("recv_meta"), table("ret")
+        self.peer_counts, self.peer_flags = table("counts"), table("flags")
+
+    def _create_regions_ipc(self, sizes):
+        self._regions = {k: PeerRegion.create(self.ctx, n) for k, n in sizes.items()}
+        self._imported = []
+        return b"".join(self._regions[k].export() for k in sizes)
+
+    def _import_regions_ipc(self, dev, sizes, mine):
+        import torch.distributed as dist
+        t, W, me = self.torch, self.world, self.rank
+        names = list(sizes)
+        local = t.tensor(list(mine), dtype=t.uint8, device=dev)
+        everyone = t.empty(W * len(mine), dtype=t.uint8, device=dev)
+        dist.all_gather_into_tensor(everyone, local)
+        blob = bytes(everyone.cpu().numpy())
+        ptrs = {k: [0] * W for k in names}
+        hb = PeerRegion.HANDLE_BYTES
+        for p in range(W):
+            for i, k in enumerate(names):
+                if p == me:
+                    ptrs[k][p] = self._regions[k].ptr
+                else:
+                    off = p * len(mine) + i * hb
+                    region = PeerRegion.open(self.ctx, blob[off:off + hb])
+                    self._imported.append(region)
+                    ptrs[k][p] = region.ptr
+        return ptrs
+
+    def _map_regions_symm(self, dev, sizes):
         import torch.distributed as dist
         import torch.distributed._symmetric_memory as symm_mem
         t = self.torch
-        d, E, W = self.d, self.E, self.world
-        sizes = [self.max_rows * d * 2, self.max_rows * d * 4, W * E * 4, 4096]
-        self._symm, ptrs = [], []
-        for nbytes in sizes:
+        self._symm, ptrs = [], {}
+        for k, nbytes in sizes.items():
             buf = symm_mem.empty(nbytes, dtype=t.uint8, device=dev)
             hdl = symm_mem.rendezvous(buf, dist.group.WORLD)
             buf.zero_()
             self._symm.append((buf, hdl))
-            ptrs.append(t.tensor([int(p) for p in hdl.buffer_ptrs], dtype=t.int64, device=dev))
-        self.peer_recv_x, self.peer_ffn_out, self.peer_counts, self.peer_flags = ptrs
-        self.recv_x = self._symm[0][0].view(t.bfloat16)
-        self.ffn_out = self._symm[1][0].view(t.float32)
-        t.cuda.synchronize()
-        dist.barrier()
+            ptrs[k] = [int(p) for p in hdl.buffer_ptrs]
+        return ptrs
+
+    def _close_regions(self):
+        for r in getattr(self, "_imported", []):
+            try:
+                r.close()
+            except Fe2o3Error:
+                pass
+        for r in getattr(self, "_regions", {}).values():
+            try:
+                r.close()
+            except Fe2o3Error:
+                pass
+        self._imported, self._regions = [], {}
+
+    def close(self):
+        """Unmaps the other ranks' regions and frees this rank's (call on every rank, after a barrier)."""
+        self.torch.cuda.synchronize()
+        self._close_regions()
 
     # ---- host-side loading -------------------------------------------------------------
     def load(self, x_bits, wg_bits, w1_bits, w2_bits):
@@ -151,7 +282,10 @@ class MoeTop2Layer:
     # ---- one step ------------------------------------------------------------------------
     def ffn_rows(self):
         """Rows the expert FFN of this rank processed in the last pass (device read; synchronises)."""
-        off = self.group_offsets if self.world > 1 else self.offsets
+        if self.exchange == "peer":
+            off = self.pair_offsets
+        else:
+            off = self.group_offsets if self.world > 1 else self.offsets
         return int(off[-1].item())
 
     def forward(self, stream=None):
@@ -160,16 +294,13 @@ class MoeTop2Layer:
         self.k_gate.launch(s)
         self.k_top2.launch(s)
         self.k_weights.launch(s)
-        if self.world == 1:
+        if self.exchange == "peer":
+            self.k_phase[0].launch(s)   # counts exchange + rows to their experts' ranks
+            self.k_ffn.launch(s)        # waits per source inside; returns rows to their home ranks
+            self.k_phase[1].launch(s)   # combine from the local return buffer, advance the pass number
+        elif self.world == 1:
             self.k_ffn.launch(s)
             self.k_combine.launch(s)
-        elif self.exchange == "peer":
-            self.k_phase[0].launch(s)   # counts exchange + rows to their experts' ranks
-            self.k_phase[1].launch(s)   # wait for every source's rows
-            self.k_ffn.launch(s)
-            self.k_phase[2].launch(s)   # expert outputs ready
-            self.k_phase[3].launch(s)   # pull and combine
-            self.k_phase[4].launch(s)   # advance the pass number
         else:
             self._exchange_forward()
             self.k_combine.launch(s)
@@ -198,7 +329,8 @@ class MoeTop2Layer:
         t, dist = self.torch, self.torch.distributed
         s, d = self.stream, self.d
         self.k_compact.launch(s)
-        dist.all_gather_into_tensor(self.counts_all, self.requested)
+        # the compact buffers hold ADMITTED rows only (expert_offsets is the scan of the admitted counts)
+        dist.all_gather_into_tensor(self.counts_all, self.admitted)
         self.host_counts.copy_(self.counts_all, non_blocking=True)
         t.cuda.current_stream().synchronize()
         counts = self.host_counts.numpy().reshape(self.world, self.E)

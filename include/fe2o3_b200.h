@@ -146,6 +146,24 @@ int32_t fe2o3_event_destroy(fe2o3_event *event);
 /* crates/fe2o3-core/src/peer_access.rs:24-60 */
 int32_t fe2o3_peer_access_enable(fe2o3_ctx *ctx, int32_t peer_device);
 
+/* Peer-visible device memory for one-process-per-GPU layouts (the capability of
+ * crates/fe2o3-core/src/peer_access.rs:24-60 across process boundaries).  The
+ * owner creates a zero-filled region and exports a 64-byte handle; it hands the
+ * handle to the other processes of the node over any host channel; each of
+ * them imports it and gets an address in its own address space through which
+ * its kernels load and store the owner's memory over NVLink (peer access to the
+ * owner's device is enabled on import).  Destroy closes an imported mapping or
+ * frees an owned region; the owner must outlive the importers' use. */
+typedef struct fe2o3_peer_region fe2o3_peer_region;
+#define FE2O3_PEER_HANDLE_BYTES 64
+int32_t fe2o3_peer_region_create(fe2o3_ctx *ctx, uint64_t bytes, fe2o3_peer_region **out);
+int32_t fe2o3_peer_region_export(const fe2o3_peer_region *region, uint8_t handle[FE2O3_PEER_HANDLE_BYTES]);
+int32_t fe2o3_peer_region_import(fe2o3_ctx *ctx, const uint8_t handle[FE2O3_PEER_HANDLE_BYTES],
+                                 fe2o3_peer_region **out);
+uint64_t fe2o3_peer_region_ptr(const fe2o3_peer_region *region);
+uint64_t fe2o3_peer_region_bytes(const fe2o3_peer_region *region); /* 0 for an imported mapping */
+int32_t fe2o3_peer_region_destroy(fe2o3_peer_region *region);
+
 const char *fe2o3_status_string(int32_t status);
 /* Human-readable detail of the calling thread's last failure (role, expected,
  * actual), mirroring the adapter error payloads. */
@@ -264,32 +282,62 @@ typedef struct fe2o3_moe_grouped_ffn_v1_args {
     uint32_t d_model, d_ff, groups, experts_cycle;
 } fe2o3_moe_grouped_ffn_v1_args;
 
-/* Expert-parallel exchange over peer memory (no counterpart in the reference,
+/* Expert-parallel layer over peer memory (no counterpart in the reference,
  * which is single-device).  One rank per GPU; rank r owns tokens/world tokens
- * and experts [r*experts/world, (r+1)*experts/world).  The peer_* slices are
- * device arrays of `world` u64 addresses, entry p being rank p's buffer, mapped
- * into this process: recv_x [max_rows][d_model] bf16, ffn_out
- * [max_rows][d_model] f32, counts [world][experts] u32, flags [3*world + 1] u32
- * (zero before the first pass).  The pass number ("epoch") must increase by one
- * per layer pass on every rank: either patch `epoch` before each pass
+ * and experts [r*per, (r+1)*per), per = experts/world.  The peer_* slices are
+ * device arrays of `world` u64 addresses, entry p being rank p's buffer mapped
+ * into this process (fe2o3_peer_region_* below, or any other peer mapping):
+ *   recv_x    [max_rows][d_model] bf16   rows routed to the rank's experts
+ *   recv_meta [max_rows] {u32 route id, u32 home rank}   where each row came from
+ *   ret       [2*tokens][d_model] f32    expert outputs by route id, on the home rank
+ *   counts    [world][experts] u32       admitted routes per (source rank, expert)
+ *   flags     [3*world + 3] u32, zero before the first pass
+ * Rows on the owner of expert e are ordered local-expert-major, source-rank-minor,
+ * so each expert's rows are one contiguous segment; pair_offsets[le*world + s]
+ * is the first row of (local expert le, source s), pair_offsets[experts] the
+ * row count.
+ *
+ * The pass number ("epoch") must increase by one per layer pass on every rank:
+ * either patch `epoch` in all three prepared blocks before each pass
  * (fe2o3_prepared_patch_kernarg) or give `epoch_counter`, one local u32 that
- * starts at 0 (the phases then use *epoch_counter + 1 and the ADVANCE phase,
- * launched last, increments it, which lets a whole pass be replayed from a CUDA
- * graph).  Phases, in stream order:
- * DISPATCH (counts exchange + rows to their expert's rank + group_offsets for
- * fe2o3_moe_grouped_ffn_v1 on recv_x), WAIT_ROWS, the FFN, FFN_DONE, COMBINE
- * (pull the two expert rows, weighted sum in rank order).  Waits are bounded. */
+ * starts at 0: the kernels then use *epoch_counter + 1 and the COMBINE phase
+ * increments it, so that a whole pass replays from one CUDA graph.
+ *
+ * One pass, in stream order:
+ *   moe_ep_exchange_v1, phase DISPATCH  publish counts, wait for every rank's
+ *       counts, write pair_offsets, store this rank's accepted rows and their
+ *       (route, home) records into the owners' receive buffers, raise
+ *       "rows complete" on every rank.
+ *   moe_ep_ffn_v1  GELU(x*W1)*W2 over the received rows as two grouped tcgen05
+ *       GEMMs.  The first waits per source rank, inside the kernel, for "rows
+ *       complete" right before it first loads rows of that source (tiles of this
+ *       rank's own rows come first); the second stores every output row straight
+ *       into the return buffer of the row's home rank from its epilogue and,
+ *       when its last tile is stored, raises "outputs ready" on every rank.
+ *   moe_ep_exchange_v1, phase COMBINE   wait for "outputs ready" of every rank,
+ *       then out[t] = w0*ret[2t] + w1*ret[2t+1] in rank order from local memory
+ *       (examples/moe_expert_v1/src/kernel.rs:104-157).
+ * Every device-side wait gives up after `spin_limit` polls (0 = the default of
+ * 2^24, about a second) and records FE2O3_KSTATUS_WAIT_EXPIRED; a pass that
+ * reports it is void on every rank. */
 #define FE2O3_MOE_EP_DISPATCH 0u
-#define FE2O3_MOE_EP_WAIT_ROWS 1u
-#define FE2O3_MOE_EP_FFN_DONE 2u
-#define FE2O3_MOE_EP_COMBINE 3u
-#define FE2O3_MOE_EP_ADVANCE 4u
+#define FE2O3_MOE_EP_COMBINE 1u
 typedef struct fe2o3_moe_ep_exchange_v1_args {
-    fe2o3_slice x, top2_experts, permutation, inverse, expert_offsets, requested_counts, route_weights,
-        group_offsets, remote_rows, combined_output, peer_recv_x, peer_ffn_out, peer_counts, peer_flags,
+    fe2o3_slice x, top2_experts, permutation, inverse, expert_offsets, admitted_counts, route_weights,
+        pair_offsets, combined_output, peer_recv_x, peer_recv_meta, peer_ret, peer_counts, peer_flags,
         epoch_counter;
-    uint32_t tokens, d_model, experts, world, rank, epoch, max_rows, phase;
+    uint32_t tokens, d_model, experts, world, rank, epoch, max_rows, phase, spin_limit, reserved;
 } fe2o3_moe_ep_exchange_v1_args;
+
+/* The expert FFN of one rank of the expert-parallel layer (see above): recv_x,
+ * recv_meta (two u32 per row) and flags are this rank's own buffers (the
+ * entries `rank` of the peer tables), w1 [per][d_model][d_ff] and
+ * w2 [per][d_ff][d_model] its experts, hidden [max_rows][d_ff] bf16 workspace.
+ * `tokens` is the per-rank token count (a return buffer has 2*tokens rows). */
+typedef struct fe2o3_moe_ep_ffn_v1_args {
+    fe2o3_slice recv_x, w1, w2, pair_offsets, hidden, recv_meta, flags, peer_ret, peer_flags, epoch_counter;
+    uint32_t tokens, d_model, d_ff, experts, world, rank, epoch, max_rows, spin_limit, reserved;
+} fe2o3_moe_ep_ffn_v1_args;
 
 /* examples/moe_expert_v1/src/kernel.rs:104-109
  * moe_expert_combine_f32_t8_k2_o16_v1(compact_output, inverse, route_weights,
@@ -389,6 +437,7 @@ int32_t fe2o3_moe_expert_combine_v1_check(const fe2o3_moe_expert_combine_v1_args
 int32_t fe2o3_moe_compact_v1_check(const fe2o3_moe_compact_v1_args *args);
 int32_t fe2o3_moe_grouped_ffn_v1_check(const fe2o3_moe_grouped_ffn_v1_args *args);
 int32_t fe2o3_moe_ep_exchange_v1_check(const fe2o3_moe_ep_exchange_v1_args *args);
+int32_t fe2o3_moe_ep_ffn_v1_check(const fe2o3_moe_ep_ffn_v1_args *args);
 int32_t fe2o3_masked_reduce_u32_check(const fe2o3_masked_reduce_u32_args *args);
 int32_t fe2o3_masked_reduce_u32_packed_check(const fe2o3_masked_reduce_u32_packed_args *args);
 int32_t fe2o3_device_scan_u32_check(const fe2o3_device_scan_u32_args *args);
@@ -424,6 +473,7 @@ int32_t fe2o3_moe_grouped_ffn_v1_prepare(fe2o3_ctx *ctx, const fe2o3_moe_grouped
                                          fe2o3_prepared **out);
 int32_t fe2o3_moe_ep_exchange_v1_prepare(fe2o3_ctx *ctx, const fe2o3_moe_ep_exchange_v1_args *args,
                                          fe2o3_prepared **out);
+int32_t fe2o3_moe_ep_ffn_v1_prepare(fe2o3_ctx *ctx, const fe2o3_moe_ep_ffn_v1_args *args, fe2o3_prepared **out);
 int32_t fe2o3_masked_reduce_u32_prepare(fe2o3_ctx *ctx, const fe2o3_masked_reduce_u32_args *args,
                                         fe2o3_prepared **out);
 int32_t fe2o3_masked_reduce_u32_packed_prepare(fe2o3_ctx *ctx, const fe2o3_masked_reduce_u32_packed_args *args,
