@@ -74,6 +74,10 @@ class Stream:
     def synchronize(self):
         check(lib.fe2o3_stream_sync(self._h), "Stream::synchronize")
 
+    def wait_event(self, event):
+        """Later work on this stream starts after `event` has completed (device-side ordering)."""
+        check(lib.fe2o3_stream_wait_event(self._h, event._h), "Stream::wait_event")
+
     @property
     def native(self):
         p = C.c_void_p()
@@ -119,6 +123,11 @@ class DeviceBuffer:
 
     def __len__(self):
         return int(lib.fe2o3_buf_len(self._h))
+
+    @property
+    def __cuda_array_interface__(self):
+        """Zero-copy view for array libraries (`torch.as_tensor(buf, device="cuda")`)."""
+        return {"shape": (len(self),), "typestr": self.dtype.str, "data": (self.as_device_ptr(), False), "version": 2}
 
     def as_device_ptr(self):
         return int(lib.fe2o3_buf_ptr(self._h))

@@ -129,7 +129,7 @@ EXPORTS = [
     "fe2o3_buf_from_host", "fe2o3_buf_to_host", "fe2o3_buf_copy_from_host_async", "fe2o3_buf_copy_to_host_async",
     "fe2o3_buf_free", "fe2o3_buf_quarantine", "fe2o3_buf_ptr", "fe2o3_buf_len", "fe2o3_buf_slice",
     "fe2o3_pinned_alloc", "fe2o3_pinned_free", "fe2o3_event_create", "fe2o3_event_record", "fe2o3_event_sync",
-    "fe2o3_event_query", "fe2o3_event_elapsed_ms", "fe2o3_event_destroy", "fe2o3_peer_access_enable",
+    "fe2o3_event_query", "fe2o3_event_elapsed_ms", "fe2o3_event_destroy", "fe2o3_stream_wait_event", "fe2o3_peer_access_enable",
     "fe2o3_status_string", "fe2o3_last_error", "fe2o3_prepared_launch", "fe2o3_prepared_launch_and_wait",
     "fe2o3_prepared_geometry", "fe2o3_prepared_kernarg", "fe2o3_prepared_patch_kernarg", "fe2o3_prepared_symbol", "fe2o3_prepared_destroy",
     "fe2o3_ctx_take_kernel_status", "fe2o3_load_executable", "fe2o3_resolve_kernel", "fe2o3_launch_and_wait",

@@ -908,6 +908,12 @@ int32_t fe2o3_event_elapsed_ms(fe2o3_event *start, fe2o3_event *end, float *ms) 
     FE2O3_CUDA(cudaEventElapsedTime(ms, start->e, end->e));
     return FE2O3_OK;
 }
+int32_t fe2o3_stream_wait_event(fe2o3_stream *stream, fe2o3_event *event) {
+    if (!stream || !event) return FE2O3_ERR_INVALID_ARGUMENT;
+    if (event->ctx != stream->ctx) { fe2o3_set_error("OperationDeviceMismatch"); return FE2O3_ERR_DEVICE_MISMATCH; }
+    FE2O3_CUDA(cudaStreamWaitEvent(stream->s, event->e, 0));
+    return FE2O3_OK;
+}
 int32_t fe2o3_event_destroy(fe2o3_event *event) {
     if (!event) return FE2O3_OK;
     cudaError_t e = cudaEventDestroy(event->e);

@@ -83,7 +83,12 @@ class MoeTop2Layer:
         dev = torch.device("cuda", torch.cuda.current_device())
         z = lambda n, dt: torch.zeros(n, dtype=dt, device=dev)
         T, d, f, E, R = self.T, d_model, d_ff, experts, self.R
-        self.x = z(T * d, torch.bfloat16)
+        # tokens in and combined output out are library-owned buffers (the host copies of an end-to-end step
+        # go through fe2o3_buf_copy_*_async); the torch tensors are views of the same memory
+        from . import DeviceBuffer
+        self.x_buf = DeviceBuffer.zeroed(stream, T * d, np.uint16)
+        self.out_buf = DeviceBuffer.zeroed(stream, T * d, np.float32)
+        self.x = torch.as_tensor(self.x_buf, device=dev).view(torch.bfloat16)
         self.wg = z(d * E, torch.bfloat16)
         self.w1 = z(self.per * d * f, torch.bfloat16)   # this rank's experts only
         self.w2 = z(self.per * f * d, torch.bfloat16)
@@ -92,7 +97,7 @@ class MoeTop2Layer:
         self.requested, self.admitted = z(E, torch.int32), z(E, torch.int32)
         self.offsets = z(E + 1, torch.int32)
         self.weights = z(R, torch.float32)
-        self.out = z(T * d, torch.float32)
+        self.out = torch.as_tensor(self.out_buf, device=dev)
         # rows this rank may have to process: every admitted route of every rank in the worst case
         self.max_rows = min(R, E * self.capacity) * world
         if self.exchange in ("auto", "peer"):
@@ -288,15 +293,20 @@ class MoeTop2Layer:
             off = self.group_offsets if self.world > 1 else self.offsets
         return int(off[-1].item())
 
-    def forward(self, stream=None):
-        """Enqueues one layer pass on `stream` (default: the layer's stream) and returns the output tensor."""
+    def forward(self, stream=None, ffn_marks=None):
+        """Enqueues one layer pass on `stream` (default: the layer's stream) and returns the output tensor.
+        `ffn_marks`: optional (begin, end) events recorded around the expert FFN of the peer exchange."""
         s = stream or self.stream
         self.k_gate.launch(s)
         self.k_top2.launch(s)
         self.k_weights.launch(s)
         if self.exchange == "peer":
             self.k_phase[0].launch(s)   # counts exchange + rows to their experts' ranks
+            if ffn_marks:
+                ffn_marks[0].record(s)
             self.k_ffn.launch(s)        # waits per source inside; returns rows to their home ranks
+            if ffn_marks:
+                ffn_marks[1].record(s)
             self.k_phase[1].launch(s)   # combine from the local return buffer, advance the pass number
         elif self.world == 1:
             self.k_ffn.launch(s)

@@ -141,6 +141,12 @@ int32_t fe2o3_event_sync(fe2o3_event *event);
 /* *done = 1 when complete, 0 when still running */
 int32_t fe2o3_event_query(fe2o3_event *event, int32_t *done);
 int32_t fe2o3_event_elapsed_ms(fe2o3_event *start, fe2o3_event *end, float *ms);
+/* Work enqueued on `stream` after this call starts only when `event` has completed (device-side
+ * ordering between two streams of one context; the host does not block).  The reference runs one
+ * stream per operation and names cross-stream ordering a caller obligation
+ * (crates/fe2o3-core/src/operation.rs:296-305); this is the call that discharges it when copies
+ * and kernels of consecutive steps overlap on separate streams. */
+int32_t fe2o3_stream_wait_event(fe2o3_stream *stream, fe2o3_event *event);
 int32_t fe2o3_event_destroy(fe2o3_event *event);
 
 /* crates/fe2o3-core/src/peer_access.rs:24-60 */

@@ -60,6 +60,25 @@ def set_threads(n):
     return int(lib().orc_get_max_threads())
 
 
+def synth_normal_bf16(seed, domain, n, sigma):
+    """The benchmark's N(0, sigma^2) bf16 stream (same bytes as fe2o3_b200.synth.normal_bf16)."""
+    out = np.empty(n, np.uint16)
+    lib().orc_synth_normal_bf16(u64(seed), u64(domain), u64(n), f32c(sigma), _p(out))
+    return out
+
+
+def synth_u32_below(seed, domain, n, bound):
+    out = np.empty(n, np.uint32)
+    lib().orc_synth_u32_below(u64(seed), u64(domain), u64(n), C.c_uint32(bound), _p(out))
+    return out
+
+
+def synth_bernoulli_flags(seed, domain, n, p, flag_value=7):
+    out = np.empty(n, np.uint32)
+    lib().orc_synth_bernoulli_flags(u64(seed), u64(domain), u64(n), f64c(p), C.c_uint32(flag_value), _p(out))
+    return out
+
+
 def mix64(v):
     return lib().orc_mix64(v & 0xFFFFFFFFFFFFFFFF)
 

@@ -103,6 +103,48 @@ uint64_t orc_splitmix64_next(uint64_t *state) {
 }
 
 /* ------------------------------------------------------------------ */
+/* Benchmark workload generators (not reference code).  The benchmark's */
+/* inputs are keyed SplitMix64 streams in the style of inputs.rs:54-79: */
+/* element i of stream (seed, domain) = mix64(seed ^ mix64(domain) ^    */
+/* i * odd).  Restated here so that the CPU reference arm can build its */
+/* inputs without loading the GPU library; a test holds the two         */
+/* generators equal byte for byte.                                      */
+/* ------------------------------------------------------------------ */
+
+static inline uint64_t synth_draw(uint64_t key, uint64_t i) { return orc_mix64(key ^ (i * 0xd6e8feb86659fd93ull)); }
+
+static inline double synth_normal01(uint64_t key, uint64_t i) {
+    /* Box-Muller in binary64 on two draws of the same index */
+    const uint64_t u1 = synth_draw(key, 2 * i), u2 = synth_draw(key, 2 * i + 1);
+    const double a = ((double)(u1 >> 11) + 1.0) * (1.0 / 9007199254740992.0);
+    const double b = (double)(u2 >> 11) * (1.0 / 9007199254740992.0);
+    return sqrt(-2.0 * log(a)) * cos(6.283185307179586476925 * b);
+}
+
+void orc_synth_normal_bf16(uint64_t seed, uint64_t domain, uint64_t n, float sigma, uint16_t *out) {
+    const uint64_t key = seed ^ orc_mix64(domain);
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < (int64_t)n; ++i)
+        out[i] = orc_bf16_from_f32((float)((double)sigma * synth_normal01(key, (uint64_t)i)));
+}
+
+void orc_synth_u32_below(uint64_t seed, uint64_t domain, uint64_t n, uint32_t bound, uint32_t *out) {
+    const uint64_t key = seed ^ orc_mix64(domain);
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < (int64_t)n; ++i)
+        out[i] = (uint32_t)(((synth_draw(key, (uint64_t)i) >> 32) * (uint64_t)bound) >> 32);
+}
+
+void orc_synth_bernoulli_flags(uint64_t seed, uint64_t domain, uint64_t n, double p, uint32_t flag_value,
+                               uint32_t *flags) {
+    const uint64_t key = seed ^ orc_mix64(domain);
+    const uint64_t threshold = (uint64_t)(p * 4294967296.0);
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < (int64_t)n; ++i)
+        flags[i] = (synth_draw(key, (uint64_t)i) >> 32) < threshold ? flag_value : 0u;
+}
+
+/* ------------------------------------------------------------------ */
 /* GEMM oracles                                                        */
 /* ------------------------------------------------------------------ */
 

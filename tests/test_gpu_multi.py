@@ -9,7 +9,7 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 
-def _rank_main(rank, world, port, shape, exchange, results):
+def _rank_main(rank, world, port, shape, exchange, capacity, results):
     import torch
     import torch.distributed as dist
     os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -23,7 +23,8 @@ def _rank_main(rank, world, port, shape, exchange, results):
         from fe2o3_b200.moe import MoeTop2Layer
         T, d, f, E = shape
         ctx = fe.GpuContext(rank)
-        layer = MoeTop2Layer(ctx, ctx.default_stream(), T, d, f, E, rank=rank, world=world, exchange=exchange)
+        layer = MoeTop2Layer(ctx, ctx.default_stream(), T, d, f, E, rank=rank, world=world, exchange=exchange,
+                             capacity=capacity)
         per, tl = E // world, T // world
         x = synth.normal_bf16(4, 1, T * d, 1.0)[rank * tl * d:(rank + 1) * tl * d]
         wg = synth.normal_bf16(4, 2, d * E, 0.02)
@@ -34,14 +35,19 @@ def _rank_main(rank, world, port, shape, exchange, results):
             out = layer.forward()
         torch.cuda.synchronize()
         assert ctx.take_kernel_status(ctx.default_stream()) == 0
-        results[rank] = (out.cpu().numpy(), layer.top2.cpu().numpy().view(np.uint32))
+        results[rank] = (out.cpu().numpy(), layer.top2.cpu().numpy().view(np.uint32), layer.capacity,
+                         getattr(layer, "peer_mapping", None))
+        dist.barrier()
+        if exchange == "peer":
+            layer.close()
     finally:
         dist.destroy_process_group()
 
 
 @pytest.mark.parametrize("exchange", ["peer", "nccl"])
-@pytest.mark.parametrize("shape", [(512, 256, 512, 8), (1024, 128, 256, 4)])
-def test_expert_parallel_moe_two_gpus(orc, shape, exchange):
+@pytest.mark.parametrize("shape,capacity", [((512, 256, 512, 8), None), ((1024, 128, 256, 4), None),
+                                            ((512, 128, 256, 8), 60)])   # the last one drops routes on every rank
+def test_expert_parallel_moe_two_gpus(orc, shape, capacity, exchange):
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
@@ -52,20 +58,26 @@ def test_expert_parallel_moe_two_gpus(orc, shape, exchange):
     port = 29600 + (os.getpid() % 1000)
     with mp.Manager() as m:
         results = m.dict()
-        mp.spawn(_rank_main, args=(world, port, shape, exchange, results), nprocs=world, join=True)
+        mp.spawn(_rank_main, args=(world, port, shape, exchange, capacity, results), nprocs=world, join=True)
         outs = [results[r] for r in range(world)]
-    out = np.concatenate([o[0] for o in outs]).reshape(T, d)
-    top2 = np.concatenate([o[1] for o in outs])
     x = synth.normal_bf16(4, 1, T * d, 1.0)
     wg = synth.normal_bf16(4, 2, d * E, 0.02)
     w1 = np.concatenate([synth.normal_bf16(4, 100 + e, d * f, 0.02) for e in range(E)])
     w2 = np.concatenate([synth.normal_bf16(4, 200 + e, f * d, 0.02) for e in range(E)])
-    logits = orc.moe_gate_logits(x, wg, T, d, E)
-    _, routing = orc.moe_top2_route(logits, T, E, 2 * T)
-    assert (top2 == routing["top2_experts"]).all()  # routing indices: bit-exact
-    w = orc.moe_route_weights(logits, routing["top2_experts"], T, E)
-    compact = orc.moe_expert_ffn(x, w1, w2, routing["top2_experts"], routing["inverse"], T, d, f, E)
-    _, want = orc.moe_combine(compact, routing["inverse"], w, T, d)
-    want = want.reshape(T, d)
-    limit = 2e-3 * np.abs(want).max() + 2e-2 * np.abs(want)  # BASELINE rel 2e-2 plus a stated absolute term
-    assert (np.abs(out - want) <= limit).all(), float(np.abs(out - want).max())
+    tl = T // world
+    for r in range(world):
+        # every rank routes its own tokens with its own capacity: the oracle of the rank's shard
+        out, top2, cap, mapping = outs[r]
+        xr = x[r * tl * d:(r + 1) * tl * d]
+        logits = orc.moe_gate_logits(xr, wg, tl, d, E)
+        _, routing = orc.moe_top2_route(logits, tl, E, cap)
+        assert (top2 == routing["top2_experts"]).all()  # routing indices: bit-exact
+        if capacity is not None:
+            assert (routing["requested_counts"] > routing["admitted_counts"]).any()   # the case does drop routes
+        w = orc.moe_route_weights(logits, routing["top2_experts"], tl, E)
+        compact = orc.moe_expert_ffn(xr, w1, w2, routing["top2_experts"], routing["inverse"], tl, d, f, E)
+        _, want = orc.moe_combine(compact, routing["inverse"], w, tl, d)
+        want = want.reshape(tl, d)
+        limit = 2e-3 * np.abs(want).max() + 2e-2 * np.abs(want)  # BASELINE rel 2e-2 plus a stated absolute term
+        got = out.reshape(tl, d)
+        assert (np.abs(got - want) <= limit).all(), (r, mapping, float(np.abs(got - want).max()))

@@ -11,7 +11,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from fe2o3_b200.moe import split_plan
+from fe2o3_b200.moe import pair_plan, split_plan
 
 EXPERTS, WIDTH = 4, 3
 
@@ -67,3 +67,45 @@ def test_split_plan_single_rank_is_identity():
     counts = np.array([[3, 0, 2, 5]])
     send, recv, off = split_plan(counts, 0, 1)
     assert send == [10] and recv == [10] and off.tolist() == [0, 3, 3, 5, 10]
+
+
+def test_split_plan_uses_admitted_rows_when_capacity_drops():
+    """With a capacity below demand the senders' compact buffers hold admitted rows only, so the plan
+    must be fed the admitted counts: the send sizes then add up to each sender's compact row count and
+    every receiver's segments tile its receive buffer."""
+    requested = np.array([[9, 2, 7, 4], [1, 8, 3, 6]])
+    capacity = 5
+    admitted = np.minimum(requested, capacity)
+    world = 2
+    plans = [split_plan(admitted, r, world) for r in range(world)]
+    for r, (send, recv, off) in enumerate(plans):
+        assert sum(send) == admitted[r].sum()
+        assert off[-1] == sum(recv) and (np.diff(off.astype(np.int64)) >= 0).all()
+    for src in range(world):
+        for dst in range(world):
+            assert plans[src][0][dst] == plans[dst][1][src]   # what one sends the other expects
+
+
+def test_pair_plan_layout():
+    """Row layout of the peer exchange: on its owner every expert's rows are one contiguous segment made
+    of one run per source rank, and the runs of all (owner, expert, source) triples tile the owners'
+    buffers without gaps or overlaps."""
+    rng = np.random.default_rng(7)
+    world, experts = 4, 8
+    per = experts // world
+    counts = rng.integers(0, 9, (world, experts))
+    counts[2, 3] = 0
+    covered = [np.zeros(int(counts[:, d * per:(d + 1) * per].sum()), np.int32) for d in range(world)]
+    for r in range(world):
+        pairs, bases = pair_plan(counts, r, world)
+        assert pairs[0] == 0 and pairs[-1] == counts[:, r * per:(r + 1) * per].sum()
+        for le in range(per):
+            for s in range(world):
+                assert pairs[le * world + s + 1] - pairs[le * world + s] == counts[s, r * per + le]
+        for e in range(experts):
+            d = e // per
+            covered[d][bases[e]:bases[e] + counts[r, e]] += 1
+            # the sender's base agrees with the owner's pair table
+            owner_pairs, _ = pair_plan(counts, d, world)
+            assert bases[e] == owner_pairs[(e % per) * world + r]
+    assert all((c == 1).all() for c in covered)

@@ -412,3 +412,16 @@ def test_scan_sum_f32_reference_is_the_exact_prefix_and_magnitude(orc):
     exc, emag = orc.scan_sum_f32(v, exclusive=True)
     assert exc.tolist() == [0.0] + inc[:-1].tolist() and emag.tolist() == [0.0] + mag[:-1].tolist()
     assert orc.scan_sum_f32(np.zeros(0, np.float32))[0].size == 0
+
+
+def test_benchmark_generators_agree_with_the_library(orc):
+    """The CPU reference arm builds its inputs with the oracle's restatement of the benchmark's keyed
+    SplitMix64 streams; the GPU arm uses the library's host generators.  Same (seed, domain, n) must give
+    the same bytes, or the two arms would not measure the same workload."""
+    from fe2o3_b200 import synth
+    n = 70001
+    assert (orc.synth_normal_bf16(4, 1, n, 1.0) == synth.normal_bf16(4, 1, n, 1.0)).all()
+    assert (orc.synth_normal_bf16(4, 107, n, 0.02) == synth.normal_bf16(4, 107, n, 0.02)).all()
+    assert (orc.synth_u32_below(1, 1, n, 1 << 16) == synth.u32_below(1, 1, n, 1 << 16)).all()
+    flags, _ = synth.bernoulli(1, 2, n, 0.75, flag_value=7, packed=False)
+    assert (orc.synth_bernoulli_flags(1, 2, n, 0.75, 7) == flags).all()
