@@ -572,14 +572,13 @@ def wl_moe(h, steps, warmup, cpu=True, **shape):
         x_rows = np.ascontiguousarray(x.reshape(t_local, d)[idx])
         top2_rows = layer.top2.cpu().numpy().view(np.uint32).reshape(t_local, 2)[idx]
         if h.world > 1:
-            def gather(a, dt):
-                loc = torch.from_numpy(np.ascontiguousarray(a).view(dt)).cuda()
-                allr = torch.empty((h.world,) + tuple(loc.shape), dtype=loc.dtype, device="cuda")
-                torch.distributed.all_gather_into_tensor(allr.view(-1), loc.view(-1))
-                return allr.cpu().numpy()
-            out_all = gather(out_rows, np.float32)
-            x_all = gather(x_rows.view(np.int16), np.int16).view(np.uint16)
-            top2_all = gather(top2_rows.view(np.int32), np.int32).view(np.uint32)
+            def gather(a):   # bytes travel (NCCL has no 16-bit integer type); rank-major result in a's dtype
+                a = np.ascontiguousarray(a)
+                loc = torch.from_numpy(a.view(np.uint8).reshape(-1)).cuda()
+                allr = torch.empty(h.world * loc.numel(), dtype=torch.uint8, device="cuda")
+                torch.distributed.all_gather_into_tensor(allr, loc)
+                return allr.cpu().numpy().view(a.dtype).reshape((h.world,) + a.shape)
+            out_all, x_all, top2_all = gather(out_rows), gather(x_rows), gather(top2_rows)
         else:
             out_all, x_all, top2_all = out_rows[None], x_rows[None], top2_rows[None]
         if h.rank == 0:

@@ -56,7 +56,7 @@ MoeGroupedFfnArgs = _struct("MoeGroupedFfnArgs", ["compact_x", "w1", "w2", "grou
 MoeEpExchangeArgs = _struct("MoeEpExchangeArgs",
                             ["x", "top2_experts", "permutation", "inverse", "expert_offsets", "admitted_counts",
                              "route_weights", "pair_offsets", "combined_output", "peer_recv_x", "peer_recv_meta",
-                             "peer_ret", "peer_counts", "peer_flags", "epoch_counter"],
+                             "peer_ret", "peer_counts", "peer_flags", "epoch_counter", "logits"],
                             [("tokens", u32), ("d_model", u32), ("experts", u32), ("world", u32), ("rank", u32),
                              ("epoch", u32), ("max_rows", u32), ("phase", u32), ("spin_limit", u32), ("reserved", u32)])
 MoeEpFfnArgs = _struct("MoeEpFfnArgs",
@@ -108,7 +108,7 @@ OPS = {
     "moe_expert_combine_v1": (MoeCombineArgs, 72, False),
     "moe_compact_v1": (MoeCompactArgs, 56, False),
     "moe_grouped_ffn_v1": (MoeGroupedFfnArgs, 112, False),
-    "moe_ep_exchange_v1": (MoeEpExchangeArgs, 280, False),
+    "moe_ep_exchange_v1": (MoeEpExchangeArgs, 296, False),
     "moe_ep_ffn_v1": (MoeEpFfnArgs, 200, False),
     "masked_reduce_u32": (MaskedReduceArgs, 48, False),
     "masked_reduce_u32_packed": (MaskedReducePackedArgs, 48, False),

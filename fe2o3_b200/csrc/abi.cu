@@ -377,9 +377,13 @@ int regions_for(uint32_t op, const void *args, Region *r, int32_t *status) {
             r[11] = RGN("PeerFlags", a->peer_flags, a->world, 8, false);
             r[12] = RGN("PairOffsets", a->pair_offsets, a->experts + 1, 4, true);
             r[13] = RGN("CombinedOutput", a->combined_output, (uint64_t)a->tokens * a->d_model, 4, true);
-            if (a->epoch_counter.ptr == 0 && a->epoch_counter.len == 0) return 14;
-            r[14] = RGN("EpochCounter", a->epoch_counter, 1, 4, true);
-            return 15;
+            int n = 14;
+            if (a->epoch_counter.ptr != 0 || a->epoch_counter.len != 0) r[n++] = RGN("EpochCounter", a->epoch_counter, 1, 4, true);
+            if (a->logits.ptr != 0 || a->logits.len != 0) {
+                r[n++] = RGN("Logits", a->logits, (uint64_t)a->tokens * a->experts, 4, false);
+                r[6].output = a->phase == FE2O3_MOE_EP_DISPATCH;   // the dispatch phase writes the route weights then
+            }
+            return n;
         }
         case OP_MOE_EP_FFN: {
             const fe2o3_moe_ep_ffn_v1_args *a = static_cast<const fe2o3_moe_ep_ffn_v1_args *>(args);

@@ -20,11 +20,14 @@
 // (warp 1 owns the TMEM allocation), 3 idle, 4-7 = softmax for tile 0, 8-11 =
 // softmax for tile 1.  A softmax thread owns one query row (one TMEM lane): it
 // reads its 128 scores once into registers and releases S at once, so the next
-// Q*K^T overlaps the exponentials.  (HALVES = 2 splits every row between two
-// threads, 64 keys and 32 output columns each, with the row maximum exchanged
-// through shared memory; measured on B200 it is slower, 495 against 566 TFLOP/s
-// at the benchmark shape, because the extra exchange lengthens each warp's
-// chain more than the second warp per scheduler shortens the exponentials.)
+// Q*K^T overlaps the exponentials.  (Splitting every row between two threads, 64
+// keys and 32 output columns each, with the row maximum exchanged through
+// shared memory, was measured on B200 and is slower, 495 against 566 TFLOP/s at
+// the benchmark shape: the extra exchange lengthens each warp's chain more than
+// the second warp per scheduler shortens the exponentials.)  Registers are
+// re-balanced at the start: the warpgroup of the producer and the issuers gives
+// most of its registers up, the two softmax warpgroups take them, so that a
+// softmax thread keeps its 128 scores and 64 packed probabilities in registers.
 // The exponent offset is a per-row reference
 // maximum that is only moved (and O and l rescaled through TMEM) when the block
 // maximum exceeds it by more than 2^8; the final quotient O / l is independent
@@ -44,12 +47,18 @@ constexpr int D = 64;            // head dimension handled by this kernel
 constexpr int BQ = 128;          // query rows per tile
 constexpr int BKV = 128;         // keys per block
 constexpr int QT = 2;            // query tiles per unit
-constexpr int HALVES = 1;        // softmax threads per query row (1 or 2; see above)
 constexpr int Q_STAGES = 2;
-constexpr int KV_STAGES = HALVES == 2 ? 3 : 4;   // the second output slices take the room of one stage
-constexpr uint32_t kTileParties = 1 + 4 * HALVES;    // per tile: its issuer and its softmax warps (output staging)
+constexpr int KV_STAGES = 4;
+constexpr uint32_t kTileParties = 1 + 4;             // per tile: its issuer and its four softmax warps (output staging)
 constexpr uint32_t kQEmptyParties = QT * kTileParties;
-constexpr int kSoftmaxWarps = 4 * HALVES * QT;
+constexpr int kSoftmaxWarps = 4 * QT;
+#ifndef FE2O3_ATTN_REGS_CONTROL
+#define FE2O3_ATTN_REGS_CONTROL 48
+#define FE2O3_ATTN_REGS_SOFTMAX 224
+#endif
+constexpr int kRegsControl = FE2O3_ATTN_REGS_CONTROL;   // registers per thread of warps 0-3 after the re-balance
+constexpr int kRegsSoftmax = FE2O3_ATTN_REGS_SOFTMAX;   // and of the softmax warps: 128 * 48 + 256 * 224 = 63488 <= 65536
+static_assert(128 * kRegsControl + 256 * kRegsSoftmax <= 65536, "register file");
 constexpr int kThreads = 32 * (4 + kSoftmaxWarps);
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 constexpr float kTruncGain = 1.001953125f;           // 1 + 2^-9: half a bf16 ulp, relative
@@ -60,9 +69,7 @@ constexpr uint32_t kOffQ = 0;
 constexpr uint32_t kOffK = kOffQ + Q_STAGES * QT * kTileBytes;
 constexpr uint32_t kOffV = kOffK + KV_STAGES * kTileBytes;
 constexpr uint32_t kOffBar = kOffV + KV_STAGES * kTileBytes;
-constexpr uint32_t kOffX = kOffBar + 512;                                  // row maxima / sums exchanged between halves
-constexpr uint32_t kOffStage = (kOffX + QT * HALVES * BQ * 4 + 1023) & ~1023u;  // output slices of the second warp of a row pair
-constexpr uint32_t kSmemTotal = kOffStage + (HALVES == 2 ? QT * 4 * 4096 : 0) + 1024;
+constexpr uint32_t kSmemTotal = kOffBar + 512 + 1024;   // + alignment slack
 
 // TMEM columns: S tile t at t*128 (128 f32 columns), O tile t at 256 + t*64 (64 f32 columns),
 // P tile t at 384 + t*64 (128 bf16 per row = 64 columns).
@@ -104,10 +111,11 @@ __device__ __forceinline__ bool unit_at(const AttnParams &p, uint32_t i, Unit &u
     return true;
 }
 
-// Named barrier for the two warps that share a TMEM lane quadrant of one tile.
-__device__ __forceinline__ void pair_barrier(uint32_t id) {
-    asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory");
-}
+// Register re-balance between warpgroups (all four warps of a warpgroup execute it).
+template <int N>
+__device__ __forceinline__ void regs_release() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void regs_take() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
 
 __global__ void __launch_bounds__(kThreads, 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -127,7 +135,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     uint64_t *pv_done = p_ready + QT;
     uint64_t *stagger = pv_done + QT;              // 1: tile 0 finished its first exponential phase
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(stagger + 1);
-    float *xchg = reinterpret_cast<float *>(smem + kOffX);   // [QT][HALVES][BQ]
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -144,11 +151,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
         for (int t = 0; t < QT; ++t) {
             mbar_init(&s_full[t], 1);
-            mbar_init(&s_empty[t], 4 * HALVES);
-            mbar_init(&p_ready[t], 4 * HALVES);
+            mbar_init(&s_empty[t], 4);
+            mbar_init(&p_ready[t], 4);
             mbar_init(&pv_done[t], 1);
         }
-        mbar_init(stagger, 4 * HALVES);
+        mbar_init(stagger, 4);
         mbar_fence_init();
     }
     if (warp == 1) {
@@ -159,7 +166,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-
+    // Each branch below opens with its own register re-balance, so that the code of a role is compiled
+    // against that role's register count (a re-balance ahead of the branches would hold every role to
+    // the smaller count).
+    if (warp < 4) {
+    regs_release<kRegsControl>();
     if (warp == 0) {
         // ---------------------------------------------------------- TMA producer
         // The whole warp runs the loop converged; one elected lane issues the copies.
@@ -294,33 +305,25 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
         if (ok && pending) issue_pv();
         if (!ok && lane == 0) kstatus_set(p.status, FE2O3_KSTATUS_WAIT_EXPIRED);
-    } else if (warp == 3) {
-        // idle: keeps the softmax warps at four per scheduler and their TMEM quadrant equal to warp % 4
+    }
+    // warp 3 idles: it keeps the softmax warps at four per scheduler and their TMEM quadrant equal to warp % 4
     } else {
+        regs_take<kRegsSoftmax>();
         // ---------------------------------------------------------- softmax warps
-        constexpr int NCH = BKV / HALVES / 32;              // 32-column chunks of the score row per thread
-        constexpr int OCOLS = D / HALVES;                   // output columns per thread
+        constexpr int NCH = BKV / 32;                       // 32-column chunks of the score row
+        constexpr int OCOLS = D;                            // output columns per thread
         const uint32_t sw = warp - 4;                       // 0 .. kSoftmaxWarps-1
-        const uint32_t t = sw / (4 * HALVES);               // query tile of this warp
+        const uint32_t t = sw / 4;                          // query tile of this warp
         const uint32_t quad = warp & 3;                     // TMEM lane quadrant this warp may access
-        const uint32_t h = (sw % (4 * HALVES)) >> 2;        // which part of the row's keys and output columns
         const uint32_t r = quad * 32 + lane;                // row inside the tile
         const uint32_t lane_addr = (quad * 32u) << 16;
-        const uint32_t tS = tmem_base + t * BKV + h * (NCH * 32) + lane_addr;
-        const uint32_t tO = tmem_base + kColO + t * D + h * OCOLS + lane_addr;
-        const uint32_t tP = tmem_base + kColP + t * (BKV / 2) + h * (NCH * 16) + lane_addr;
-        float *my_x = xchg + (t * HALVES + h) * BQ + r;
-        const float *peer_x = xchg + (t * HALVES + (h ^ (HALVES - 1))) * BQ + r;
-        const uint32_t bar_id = 1 + t * 4 + quad;           // named barrier of the two warps sharing (tile, quadrant)
-        constexpr uint32_t kPairBarsPerBlock = HALVES == 2 ? 2 : 0, kPairBarsPerUnit = HALVES == 2 ? 1 : 0;
+        const uint32_t tS = tmem_base + t * BKV + lane_addr;
+        const uint32_t tO = tmem_base + kColO + t * D + lane_addr;
+        const uint32_t tP = tmem_base + kColP + t * (BKV / 2) + lane_addr;
         const float c = p.scale_log2;
-        // The named barrier has no time limit, so both warps of a pair must execute the same number of
-        // them whatever happens: every wait is warp-uniform, and a warp that gives up still arrives at
-        // every remaining pair barrier (2 per key block and 1 per unit) before it leaves.
         bool ok = true;
         uint32_t gt = 0;             // key blocks this tile has processed, over all units
         uint32_t n = 0;              // units with keys seen so far (selects the Q stage)
-        uint32_t pair_bars_owed = 0; // pair barriers of the current unit not yet executed when a wait gave up
         uint32_t ui = 0;
         Unit u;
         for (; ok && unit_at(p, ui, u); ++ui) {
@@ -332,7 +335,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             float m_ref = -INFINITY;   // exponent offset, in raw score units (identical in both halves)
             float l = 0.0f;            // this thread's share of the denominator
             bool s_early = false;      // s_full of the coming block was seen complete by the early probe
-            pair_bars_owed = kPairBarsPerBlock * u.nkv + kPairBarsPerUnit;
 
             for (uint32_t j = 0; j < u.nkv; ++j, ++gt) {
                 // A probe of a barrier takes about 200 cycles even when the phase is complete, so the two
@@ -351,7 +353,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&s_empty[t]);
 
-                const uint32_t key0 = j * BKV + h * (NCH * 32);
+                const uint32_t key0 = j * BKV;
                 const bool need_mask = (j * BKV + BKV > p.seq) || (p.causal && j * BKV + BKV - 1 > u.q0 + t * BQ);
                 if (need_mask) {
 #pragma unroll
@@ -374,15 +376,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                             mx[q] = max3(mx[q], __uint_as_float(s[ch][i + 2 * q]), __uint_as_float(s[ch][i + 2 * q + 1]));
                     }
                 }
-                float rowmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-                if constexpr (HALVES == 2) {
-                    // both halves of the row must use the same maximum
-                    *my_x = rowmax;
-                    pair_barrier(bar_id);
-                    rowmax = fmaxf(rowmax, *peer_x);
-                    pair_barrier(bar_id);   // the slot is rewritten in the next block of keys
-                    pair_bars_owed -= 2;
-                }
+                const float rowmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
                 // move the reference only when the block maximum outgrows it by more than the threshold
                 const bool move = (rowmax - m_ref) * c > kRescaleThreshold;  // true for the first admitted key (m_ref = -inf)
                 const float factor = move ? ex2_approx((m_ref - rowmax) * c) : 1.0f;  // 0 when m_ref = -inf
@@ -465,24 +459,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             if (!ok) break;
             if (!mbar_wait_warp(&pv_done[t], (gt - 1) & 1)) { ok = false; break; }
             tc_fence_after();
-            float l_row = l;
-            if constexpr (HALVES == 2) {
-                // the row's denominator is the sum of the two halves' shares
-                *my_x = l;
-                pair_barrier(bar_id);
-                l_row = l + *peer_x;
-            }
-            pair_bars_owed = 0;
+            const float l_row = l;
             // Output.  The unit's Q tile is dead once its last Q*K^T has completed (the s_full wait above
             // proved that), so the warp stages its 32 rows, 32 columns at a time, in a 4 KiB slice
             // (128-byte swizzle, so the 16-byte writes of a warp spread over all banks) and hands them to
-            // the copy engine: full-line writes that do not hold the warp.  The first warp of a row pair
-            // uses its slice of the Q tile, the second a slice of its own.  The Q stage is given back to
+            // the copy engine: full-line writes that do not hold the warp.  The Q stage is given back to
             // the producer when the copies have read the slices.
             const float inv = kTruncGain / l_row;   // the sums carry the gain of the truncation bias
             bool finite = isfinite(l_row) && l_row > 0.0f;
-            uint8_t *slice = (HALVES == 1 || h == 0) ? smem + kOffQ + (qs * QT + t) * kTileBytes + quad * 4096
-                                                     : smem + kOffStage + (t * 4 + quad) * 4096;
+            uint8_t *slice = smem + kOffQ + (qs * QT + t) * kTileBytes + quad * 4096;
             const uint32_t row0 = u.q0 + t * BQ + quad * 32;   // first query row of this warp
 #pragma unroll
             for (int g = 0; g < OCOLS / 32; ++g) {
@@ -506,7 +491,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0 && row0 < p.seq) {   // rows beyond seq are clipped by the copy engine
-                    tma_store_3d(&tmO, slice, (int32_t)(h * OCOLS + g * 32), (int32_t)row0, (int32_t)u.head);
+                    tma_store_3d(&tmO, slice, (int32_t)(g * 32), (int32_t)row0, (int32_t)u.head);
                     tma_store_commit();
                 }
             }
@@ -520,17 +505,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             tc_fence_before();
             __syncwarp();
         }
-        if (!ok) {
-            if (lane == 0) kstatus_set(p.status, FE2O3_KSTATUS_WAIT_EXPIRED);
-            if constexpr (HALVES == 2) {
-                // settle the pair barriers of the unit that was abandoned and of every unit after it
-                for (uint32_t b = 0; b < pair_bars_owed; ++b) pair_barrier(bar_id);
-                for (++ui; unit_at(p, ui, u); ++ui) {
-                    if (u.nkv == 0 || t >= u.nt) continue;
-                    for (uint32_t b = 0; b < 2 * u.nkv + 1; ++b) pair_barrier(bar_id);
-                }
-            }
-        }
+        if (!ok && lane == 0) kstatus_set(p.status, FE2O3_KSTATUS_WAIT_EXPIRED);
     }
     tc_fence_before();
     __syncthreads();

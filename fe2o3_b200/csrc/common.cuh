@@ -85,6 +85,15 @@ __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return (uint32_t)__cvta_generic_to_shared(p);
 }
 
+// Route weights of one token (softmax over the experts renormalised over the two winners = softmax
+// over the two winning logits): e1 = exp(l1 - l0) <= 1, w0 = 1 / (1 + e1) in [1/2, 1], w1 = 1 - w0,
+// which is exact, so w0 + w1 == 1.0f as examples/moe_expert_v1/src/contract.rs:34 requires.
+__device__ __forceinline__ void route_weight_pair(float l0, float l1, float &w0, float &w1) {
+    const float e1 = expf(l1 - l0);
+    w0 = __fdiv_rn(1.0f, __fadd_rn(1.0f, e1));
+    w1 = __fsub_rn(1.0f, w0);
+}
+
 // ---- system-scope flags (expert-parallel exchange) -----------------------------
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
     uint32_t v;

@@ -390,6 +390,141 @@ moe_gate_warp_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict_
     }
 }
 
+// ---- gate logits: Wg resident in shared memory, x through an asynchronous copy ring ---------
+// Same arithmetic and order again (each logit one sequential chain of separately rounded products
+// and sums over k), laid out for what bounds the gate: the latency of that chain (2048 dependent
+// additions per output whatever the token count) when there are few tokens, instruction issue and
+// the HBM stream of x when there are many.
+//   Wg is widened to f32 once per block into shared memory ([k][E], E * d_model * 4 bytes) and stays
+//     there: the k loop stages no weights.
+//   lane = (token, group of EPL experts).  Each warp streams the rows of its own tokens, 64 k values
+//     at a time, into a private ring of STAGES shared-memory stages with 16-byte asynchronous copies
+//     (no registers and no scoreboard are held while they fly, so the ring really is STAGES - 1
+//     chunks deep; a ring of prefetched registers is not: the hardware tracks outstanding loads of a
+//     warp with a handful of counters, and waiting for the oldest load waits for the youngest that
+//     shares its counter).  The warp synchronises with itself only; there is no block barrier in
+//     the loop.  Rows are padded by 16 bytes so that the 16-byte reads of eight tokens do not
+//     collide on banks.
+//   The EPL logits of a lane advance as EPL / 2 packed f32x2 products and sums per k (each half
+//     rounded exactly like the scalar instruction).  EPL = 2 spreads a token over E / 2 lanes, so a
+//     rank's 2048 tokens of an expert-parallel layer still make 256 warps, each running at the pace
+//     of the dependent additions; EPL = 4 halves the instructions per multiply-add for large batches.
+// Needs E in {4, 8, 16}, d_model a multiple of 64 with E * d_model * 4 bytes of shared memory
+// available, 16-byte aligned x and Wg.
+constexpr int kGateKC2 = 64;                       // k values per stage
+constexpr int kGateRowBytes = kGateKC2 * 2 + 16;   // one token's stage row, padded
+
+__device__ __forceinline__ void cp_async_16(void *dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <int E, int EPL, int WARPS, int STAGES>
+__global__ void __launch_bounds__(32 * WARPS)
+moe_gate_lanes_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict__ wg, float *__restrict__ logits,
+                      uint32_t tokens, uint32_t d_model) {
+    extern __shared__ __align__(16) uint8_t gate_lanes_smem[];
+    constexpr int LPT = E / EPL;        // lanes per token
+    constexpr int TPW = 32 / LPT;       // tokens per warp
+    constexpr int NP = EPL / 2;         // packed accumulators per lane
+    constexpr int kStageBytes = TPW * kGateRowBytes;
+    constexpr int kGranules = TPW * 8;  // 16-byte pieces per stage
+    float *gate_w = reinterpret_cast<float *>(gate_lanes_smem);                 // [d_model][E]
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    uint8_t *ring = gate_lanes_smem + (size_t)d_model * E * 4 + (size_t)warp * STAGES * kStageBytes;
+    const uint32_t tok0 = (blockIdx.x * WARPS + warp) * TPW;
+    const uint32_t nchunks = d_model / kGateKC2;
+    auto copy_chunk = [&](uint32_t chunk) {
+        if (chunk < nchunks) {
+            uint8_t *stage = ring + (chunk % STAGES) * kStageBytes;
+#pragma unroll
+            for (int g0 = 0; g0 < kGranules; g0 += 32) {
+                const uint32_t g = g0 + lane;
+                if (kGranules >= 32 || g < (uint32_t)kGranules) {
+                    const uint32_t tk = g >> 3, piece = g & 7;
+                    const uint32_t token = min(tok0 + tk, tokens - 1);   // rows beyond the batch re-read the last row
+                    cp_async_16(stage + tk * kGateRowBytes + piece * 16,
+                                x + (uint64_t)token * d_model + chunk * kGateKC2 + piece * 8);
+                }
+            }
+        }
+        cp_async_commit();   // an empty group keeps the group count uniform at the tail
+    };
+    // the first chunks are on their way while the block widens Wg
+#pragma unroll
+    for (int c = 0; c < STAGES - 1; ++c) copy_chunk(c);
+    for (uint32_t v = tid; v < d_model * E / 8; v += 32 * WARPS) {
+        const uint4 w = __ldg(reinterpret_cast<const uint4 *>(wg) + v);
+        float4 *dst = reinterpret_cast<float4 *>(gate_w + v * 8);
+        dst[0] = make_float4(__uint_as_float(w.x << 16), __uint_as_float(w.x & 0xffff0000u), __uint_as_float(w.y << 16),
+                             __uint_as_float(w.y & 0xffff0000u));
+        dst[1] = make_float4(__uint_as_float(w.z << 16), __uint_as_float(w.z & 0xffff0000u), __uint_as_float(w.w << 16),
+                             __uint_as_float(w.w & 0xffff0000u));
+    }
+    __syncthreads();
+    const uint32_t tt = lane / LPT, e0 = (lane % LPT) * EPL;
+    uint64_t acc[NP];
+#pragma unroll
+    for (int q = 0; q < NP; ++q) acc[q] = 0ull;   // {+0.0f, +0.0f}
+    for (uint32_t c = 0; c < nchunks; ++c) {
+        cp_async_wait<STAGES - 2>();   // this lane's pieces of chunk c have landed
+        __syncwarp();                  // every lane's have, and nobody still reads the stage refilled next
+        copy_chunk(c + STAGES - 1);
+        const uint4 *xrow = reinterpret_cast<const uint4 *>(ring + (c % STAGES) * kStageBytes + tt * kGateRowBytes);
+        const float *wk = gate_w + (uint64_t)c * kGateKC2 * E + e0;
+#pragma unroll
+        for (int v = 0; v < kGateKC2 / 8; ++v) {
+            const uint4 xv = xrow[v];
+            const uint32_t words[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const float xf = __uint_as_float(h ? (words[i] & 0xffff0000u) : (words[i] << 16));
+                    const uint64_t xx = pack_f32x2(xf, xf);
+                    const float *w = wk + (v * 8 + 2 * i + h) * E;
+                    if constexpr (EPL == 2) {
+                        const float2 a = *reinterpret_cast<const float2 *>(w);
+                        acc[0] = add_f32x2(acc[0], mul_f32x2(xx, pack_f32x2(a.x, a.y)));
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < EPL / 4; ++q) {
+                            const float4 a = *reinterpret_cast<const float4 *>(w + 4 * q);
+                            acc[2 * q] = add_f32x2(acc[2 * q], mul_f32x2(xx, pack_f32x2(a.x, a.y)));
+                            acc[2 * q + 1] = add_f32x2(acc[2 * q + 1], mul_f32x2(xx, pack_f32x2(a.z, a.w)));
+                        }
+                    }
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+    if (tok0 + tt < tokens) {
+#pragma unroll
+        for (int q = 0; q < NP; ++q) {
+            float lo, hi;
+            unpack_f32x2(acc[q], lo, hi);
+            *reinterpret_cast<float2 *>(logits + (uint64_t)(tok0 + tt) * E + e0 + 2 * q) = make_float2(lo, hi);
+        }
+    }
+}
+
+template <int E, int EPL, int WARPS, int STAGES>
+static cudaError_t launch_gate_lanes(cudaStream_t s, const uint16_t *x, const uint16_t *wg, float *lg, uint32_t tokens,
+                                     uint32_t d_model, fe2o3_geometry *geo) {
+    constexpr uint32_t tokens_per_block = WARPS * (32 / (E / EPL));
+    const uint32_t grid = ceil_div_u32(tokens, tokens_per_block);
+    const uint32_t smem = d_model * E * 4 + WARPS * STAGES * (32 / (E / EPL)) * kGateRowBytes;
+    if (geo) { *geo = fe2o3_geometry{{grid, 1, 1}, {32 * WARPS, 1, 1}, smem, 1}; return cudaSuccess; }
+    // the attribute is per device and cheap to set: set it on every launch for the current device
+    cudaError_t e = cudaFuncSetAttribute(moe_gate_lanes_kernel<E, EPL, WARPS, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    moe_gate_lanes_kernel<E, EPL, WARPS, STAGES><<<grid, 32 * WARPS, smem, s>>>(x, wg, lg, tokens, d_model);
+    return cudaSuccess;
+}
+
 // ---- top-2 routing over many blocks --------------------------------------------
 // Same result as moe_top2_kernel.  Block b owns tokens [256 b, 256 b + 256).
 // Pass 1 counts, per block and expert, the routes the block requests and checks
@@ -573,20 +708,17 @@ moe_route_place_kernel(fe2o3_moe_top2_v1_args a, const uint32_t *scratch) {
 }
 
 // ---- route weights ------------------------------------------------------------
-// Softmax over the experts renormalised over the two winners equals a softmax
-// over the two winning logits: e1 = exp(l1 - l0) <= 1, w0 = 1/(1+e1) in
-// [1/2, 1], w1 = 1 - w0, which is exact, so w0 + w1 == 1.0f as
-// examples/moe_expert_v1/src/contract.rs:34 requires.
+// One thread per token; the arithmetic is route_weight_pair (common.cuh).
 __global__ void moe_route_weights_kernel(const float *__restrict__ logits, const uint32_t *__restrict__ top2,
                                          float *__restrict__ weights, uint32_t tokens, uint32_t experts) {
     const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= tokens) return;
     const float l0 = logits[(uint64_t)t * experts + top2[2ull * t]];
     const float l1 = logits[(uint64_t)t * experts + top2[2ull * t + 1]];
-    const float e1 = expf(l1 - l0);
-    const float w0 = __fdiv_rn(1.0f, __fadd_rn(1.0f, e1));
+    float w0, w1;
+    route_weight_pair(l0, l1, w0, w1);
     weights[2ull * t] = w0;
-    weights[2ull * t + 1] = __fsub_rn(1.0f, w0);
+    weights[2ull * t + 1] = w1;
 }
 
 // ---- compaction ---------------------------------------------------------------
@@ -668,18 +800,37 @@ int32_t launch_moe_gate(fe2o3_ctx *, cudaStream_t s, const void *args, fe2o3_geo
     const uint32_t smem = (tpb * (kGateKC + 1) + kGateKC * E) * sizeof(float);
     const bool per_token = E == 4 || E == 8 || E == 16;
     if (per_token) {
-        // FE2O3_GATE_BLOCK=1 selects the 32-token block kernel even where the warp kernel applies
-        static const bool force_block = getenv("FE2O3_GATE_BLOCK") != nullptr;
-        // measured on B200 with d_model 2048, 8 experts: 2048 tokens 26 us against 34 us for the block
-        // kernel, 16384 tokens 80 us against 50 us, so the warp kernel serves the small token counts
-        // that one rank of an expert-parallel layer sees
-        const bool warp_ok = !force_block && a->tokens <= 4096u && a->d_model % 64u == 0 && a->d_model >= 64u &&
-                             ((a->x.ptr | a->wg.ptr) & 15u) == 0;
+        // FE2O3_GATE_KERNEL=block | warp selects one of the two older kernels where the pairs kernel applies
+        static const char *force = getenv("FE2O3_GATE_KERNEL");
+        const bool aligned = ((a->x.ptr | a->wg.ptr) & 15u) == 0;
+        const bool lanes_ok = !force && aligned && a->d_model % 64u == 0 && a->d_model >= 64u && (a->logits.ptr & 7u) == 0 &&
+                              (uint64_t)a->d_model * E * 4u <= 96u * 1024u && a->tokens > 0;
+        const uint16_t *x = reinterpret_cast<const uint16_t *>(a->x.ptr), *wg = reinterpret_cast<const uint16_t *>(a->wg.ptr);
+        float *lg = reinterpret_cast<float *>(a->logits.ptr);
+        if (lanes_ok) {
+            // few tokens: two experts per lane (most warps, pace of the dependent sums); many: four per lane
+            const bool wide = a->tokens > 4096u;
+#define FE2O3_GATE_LANES(EE, g)                                                                                            \
+    (wide ? launch_gate_lanes<EE, 4, 8, 6>(s, x, wg, lg, a->tokens, a->d_model, g)                                         \
+          : launch_gate_lanes<EE, 2, 4, 8>(s, x, wg, lg, a->tokens, a->d_model, g))
+            fe2o3_geometry g{};
+            cudaError_t e = E == 4 ? FE2O3_GATE_LANES(4, &g) : E == 8 ? FE2O3_GATE_LANES(8, &g) : FE2O3_GATE_LANES(16, &g);
+            if (geo) *geo = g;
+            if (plan_only) return FE2O3_OK;
+            e = E == 4 ? FE2O3_GATE_LANES(4, nullptr) : E == 8 ? FE2O3_GATE_LANES(8, nullptr) : FE2O3_GATE_LANES(16, nullptr);
+#undef FE2O3_GATE_LANES
+            if (e != cudaSuccess) return fe2o3_cuda_status(e, "moe_gate_v1");
+            fe2o3_count_launch(1);
+            return fe2o3_cuda_status(cudaGetLastError(), "moe_gate_v1");
+        }
+        const bool force_block = force && force[0] == 'b';
+        // other shapes: up to 4096 tokens the warp-per-eight-tokens kernel (measured on B200 with d_model
+        // 2048, 8 experts: 26 us against 34 us for the block kernel at 2048 tokens, 80 against 50 us at
+        // 16384), beyond that the 32-token block kernel
+        const bool warp_ok = !force_block && a->tokens <= 4096u && a->d_model % 64u == 0 && a->d_model >= 64u && aligned;
         const uint32_t g2 = ceil_div_u32(a->tokens, warp_ok ? 8u : (uint32_t)kGate2Tokens), thr = warp_ok ? 32u : 32 * (E / 4);
         if (geo) *geo = fe2o3_geometry{{g2, 1, 1}, {thr, 1, 1}, 0, 1};
         if (plan_only || a->tokens == 0) return FE2O3_OK;
-        const uint16_t *x = reinterpret_cast<const uint16_t *>(a->x.ptr), *wg = reinterpret_cast<const uint16_t *>(a->wg.ptr);
-        float *lg = reinterpret_cast<float *>(a->logits.ptr);
         if (warp_ok) {
             if (E == 4) moe_gate_warp_kernel<4><<<g2, 32, 0, s>>>(x, wg, lg, a->tokens, a->d_model);
             else if (E == 8) moe_gate_warp_kernel<8><<<g2, 32, 0, s>>>(x, wg, lg, a->tokens, a->d_model);

@@ -76,6 +76,21 @@ moe_ep_dispatch_kernel(fe2o3_moe_ep_exchange_v1_args a, uint32_t *status) {
         for (uint32_t p = threadIdx.x; p < W; p += kThreads)
             st_release_sys(reinterpret_cast<uint32_t *>(peer_flags[p]) + FE2O3_EP_FLAG_COUNTS(W) + me, epoch);
     }
+    if (a.logits.len && !dead) {
+        // Route weights of this rank's tokens, one token per thread of the grid, computed while the counts
+        // of the other ranks are still on their way (the combine phase reads them).
+        const float *logits = reinterpret_cast<const float *>(a.logits.ptr);
+        const uint32_t *top2 = reinterpret_cast<const uint32_t *>(a.top2_experts.ptr);
+        float *weights = reinterpret_cast<float *>(a.route_weights.ptr);
+        for (uint32_t t = blockIdx.x * kThreads + threadIdx.x; t < a.tokens; t += gridDim.x * kThreads) {
+            const uint32_t e0 = top2[2ull * t], e1 = top2[2ull * t + 1];
+            if (e0 >= E || e1 >= E) { kstatus_set(status, FE2O3_KSTATUS_SLOT_RANGE); continue; }
+            float w0, w1;
+            route_weight_pair(logits[(uint64_t)t * E + e0], logits[(uint64_t)t * E + e1], w0, w1);
+            weights[2ull * t] = w0;
+            weights[2ull * t + 1] = w1;
+        }
+    }
     // every block waits for the counts of every source (thread s polls source s: local memory)
     int ok = dead ? 0 : (threadIdx.x < W ? (flag_wait(my_flags + FE2O3_EP_FLAG_COUNTS(W) + threadIdx.x, epoch, limit) ? 1 : 0) : 1);
     ok = __syncthreads_and(ok);

@@ -127,12 +127,13 @@ class MoeTop2Layer:
             self.k_phase = [P("moe_ep_exchange_v1", x=self.x, top2_experts=self.top2, permutation=self.perm,
                               inverse=self.inverse, expert_offsets=self.offsets, admitted_counts=self.admitted,
                               route_weights=self.weights, combined_output=self.out, peer_recv_x=self.peer_recv_x,
-                              peer_recv_meta=self.peer_recv_meta, peer_counts=self.peer_counts, phase=ph, **common)
+                              peer_recv_meta=self.peer_recv_meta, peer_counts=self.peer_counts, phase=ph,
+                              logits=self.logits if ph == 0 else None, **common)   # dispatch also writes the route weights
                             for ph in range(2)]
             self.k_ffn = P("moe_ep_ffn_v1", recv_x=(self._ptrs["recv_x"][me], self.max_rows * d), w1=self.w1, w2=self.w2,
                            hidden=self.hidden, recv_meta=(self._ptrs["recv_meta"][me], 2 * self.max_rows),
                            flags=(self._ptrs["flags"][me], 3 * world + 3), d_ff=f, **common)
-            self.launches_per_step = 8
+            self.launches_per_step = 7
             return
         self.compact_x = z(R * d, torch.bfloat16)            # local routes, expert-major
         self.compact_out = z(R * d, torch.float32)           # FFN rows back in local slot order
@@ -299,9 +300,10 @@ class MoeTop2Layer:
         s = stream or self.stream
         self.k_gate.launch(s)
         self.k_top2.launch(s)
-        self.k_weights.launch(s)
+        if self.exchange != "peer":
+            self.k_weights.launch(s)
         if self.exchange == "peer":
-            self.k_phase[0].launch(s)   # counts exchange + rows to their experts' ranks
+            self.k_phase[0].launch(s)   # counts exchange + route weights + rows to their experts' ranks
             if ffn_marks:
                 ffn_marks[0].record(s)
             self.k_ffn.launch(s)        # waits per source inside; returns rows to their home ranks

@@ -310,7 +310,9 @@ typedef struct fe2o3_moe_grouped_ffn_v1_args {
  * increments it, so that a whole pass replays from one CUDA graph.
  *
  * One pass, in stream order:
- *   moe_ep_exchange_v1, phase DISPATCH  publish counts, wait for every rank's
+ *   moe_ep_exchange_v1, phase DISPATCH  publish counts; when `logits`
+ *       ([tokens][experts] f32, optional) is given, write route_weights from it as
+ *       fe2o3_moe_route_weights_v1 does, while the counts travel; wait for every rank's
  *       counts, write pair_offsets, store this rank's accepted rows and their
  *       (route, home) records into the owners' receive buffers, raise
  *       "rows complete" on every rank.
@@ -331,7 +333,7 @@ typedef struct fe2o3_moe_grouped_ffn_v1_args {
 typedef struct fe2o3_moe_ep_exchange_v1_args {
     fe2o3_slice x, top2_experts, permutation, inverse, expert_offsets, admitted_counts, route_weights,
         pair_offsets, combined_output, peer_recv_x, peer_recv_meta, peer_ret, peer_counts, peer_flags,
-        epoch_counter;
+        epoch_counter, logits;
     uint32_t tokens, d_model, experts, world, rank, epoch, max_rows, phase, spin_limit, reserved;
 } fe2o3_moe_ep_exchange_v1_args;
 

@@ -105,8 +105,7 @@ class VirtualRanks:
         self.epoch += 1
         for layer in self.layers:
             layer.k_gate.launch(s)
-            layer.k_top2.launch(s)
-            layer.k_weights.launch(s)
+            layer.k_top2.launch(s)   # the route weights are written by the dispatch kernel
         # what the dispatch kernels' first blocks would exchange: every rank's admitted counts in every
         # rank's table, and the "counts published" flags at this pass's epoch
         counts = t.stack([layer.admitted for layer in self.layers]).reshape(-1)            # [W][E] int32

@@ -443,9 +443,12 @@ print("ok")
     assert r.returncode == 0 and "ok" in r.stdout, r.stdout + r.stderr
 
 
-# up to 4096 tokens with d_model % 64 == 0 take the warp-per-eight-tokens kernel, more tokens the 32-token block kernel
+# d_model % 256 == 0 with 4, 8 or 16 experts takes the one-warp-per-block pairs kernel; otherwise up to 4096 tokens with
+# d_model % 64 == 0 the warp-per-eight-tokens kernel, more tokens the 32-token block kernel, other expert counts the
+# generic kernel
 @pytest.mark.parametrize("T,d,E", [(100, 64, 8), (300, 200, 4), (257, 2048, 8), (64, 136, 16), (50, 96, 5), (33, 70, 8),
-                                   (4500, 128, 8), (4200, 192, 16), (1000, 256, 4)])
+                                   (4500, 128, 8), (4200, 192, 16), (1000, 256, 4), (2048, 2048, 8), (101, 512, 16),
+                                   (70, 768, 4), (5000, 256, 8)])
 def test_moe_gate_logits_bit_exact(gpu, orc, T, d, E):
     fe, ctx, stream = gpu
     from fe2o3_b200 import synth
