@@ -38,6 +38,10 @@ int32_t launch_gemm_exact(cudaStream_t, uint32_t dtype, bool epilogue, uint64_t 
                           fe2o3_geometry *, bool);
 int32_t launch_attention_simt(fe2o3_ctx *, cudaStream_t, const fe2o3_flash_attention_v1_args *, fe2o3_geometry *, bool);
 
+bool gemm_split_supported(uint64_t a, uint64_t b, uint32_t N, uint32_t K);
+int32_t gemm_split_launch(cudaStream_t s, const float *a, const float *b, uint16_t *a3, uint16_t *b3, uint32_t M, uint32_t N,
+                          uint32_t K);
+
 struct AttnTcPlan;
 bool attention_tc_supported(const fe2o3_flash_attention_v1_args *);
 int32_t attention_tc_plan(fe2o3_ctx *, const fe2o3_flash_attention_v1_args *, AttnTcPlan **);
@@ -124,6 +128,7 @@ struct fe2o3_prepared {
     uint32_t schedule;   // GEMM: resolved schedule
     GemmTcPlan gemm[2];  // tcgen05 plans (FFN uses both)
     AttnTcPlan *attn;
+    void *scratch[2];    // device workspace owned by the prepared object (split bf16 operands of the f32 GEMM)
     fe2o3_geometry geo;
 };
 
@@ -237,8 +242,11 @@ int regions_for(uint32_t op, const void *args, Region *r, int32_t *status) {
         }
         case OP_TILED_GEMM_GENERAL: {
             const fe2o3_tiled_gemm_general_v1_args *a = static_cast<const fe2o3_tiled_gemm_general_v1_args *>(args);
-            if (a->lda < a->k || a->ldb < a->n || a->ldc < a->n) {
-                *status = unsupported("StrideTooSmall: lda >= k, ldb >= n, ldc >= n required");
+            // an operand without rows or columns has no stride rule (general_plan.rs:406-425 checked_extent)
+            const bool a_bad = a->m && a->k && a->lda < a->k, b_bad = a->k && a->n && a->ldb < a->n,
+                       c_bad = a->m && a->n && a->ldc < a->n;
+            if (a_bad || b_bad || c_bad) {
+                *status = unsupported("StrideTooSmall: lda >= k, ldb >= n, ldc >= n required for nonempty operands");
                 return 0;
             }
             if ((uint64_t)a->m * a->n == 0) return 0;
@@ -501,10 +509,30 @@ int32_t check_op(uint32_t op, const void *args) {
 int32_t resolve_gemm(fe2o3_prepared *p, uint32_t schedule, uint32_t dtype, uint64_t a, uint64_t b, uint64_t c,
                      uint32_t M, uint32_t N, uint32_t K, uint32_t lda, uint32_t ldb, uint32_t ldc, float alpha,
                      float beta, bool epilogue) {
+    if (schedule > FE2O3_GEMM_SCHEDULE_AUTO) { fe2o3_set_error("unknown schedule"); return FE2O3_ERR_INVALID_ARGUMENT; }
+    if (dtype == FE2O3_DTYPE_F32) {
+        // f32 operands: the exact-order schedule unless the tensor-core one is asked for by name; that one splits
+        // each operand into bf16 terms (gemm_split.cu) and is specified by a bound, not bit-exact
+        if (schedule != FE2O3_GEMM_SCHEDULE_TCGEN05) {
+            p->schedule = FE2O3_GEMM_SCHEDULE_EXACT_ORDER;
+            return launch_gemm_exact(nullptr, dtype, epilogue, a, b, c, M, N, K, lda, ldb, ldc, alpha, beta, &p->geo, true);
+        }
+        if (epilogue || lda != K || ldb != N || !gemm_split_supported(a, b, N, K))
+            return unsupported("tcgen05 schedule for f32 operands needs packed A and B, 16-byte aligned, K and N multiples of 8");
+        p->schedule = FE2O3_GEMM_SCHEDULE_TCGEN05;
+        FE2O3_CUDA(cudaSetDevice(p->ctx->device));
+        FE2O3_CUDA(cudaMalloc(&p->scratch[0], (size_t)M * 3 * K * 2));
+        FE2O3_CUDA(cudaMalloc(&p->scratch[1], (size_t)3 * K * N * 2));
+        int32_t st = gemm_tc_plan(p->ctx, &p->gemm[0], reinterpret_cast<uint64_t>(p->scratch[0]), reinterpret_cast<uint64_t>(p->scratch[1]),
+                                  c, M, N, 3 * K, 3 * K, N, ldc, 1.f, 0.f, 0u, nullptr, 0);
+        if (st != FE2O3_OK) return st;
+        gemm_tc_geometry(&p->gemm[0], &p->geo);
+        p->geo.launches = 3;
+        return FE2O3_OK;
+    }
     const bool tc_ok = dtype == FE2O3_DTYPE_BF16 && gemm_tc_supported(a, b, lda, ldb, K);
     if (schedule == FE2O3_GEMM_SCHEDULE_TCGEN05 && !tc_ok)
         return unsupported("tcgen05 schedule needs bf16 operands, K > 0, 16-byte aligned bases, lda and ldb multiples of 8");
-    if (schedule > FE2O3_GEMM_SCHEDULE_AUTO) { fe2o3_set_error("unknown schedule"); return FE2O3_ERR_INVALID_ARGUMENT; }
     if (schedule == FE2O3_GEMM_SCHEDULE_AUTO)
         schedule = (tc_ok && (uint64_t)M * N * K >= (1ull << 21)) ? FE2O3_GEMM_SCHEDULE_TCGEN05 : FE2O3_GEMM_SCHEDULE_EXACT_ORDER;
     p->schedule = schedule;
@@ -532,6 +560,7 @@ int32_t prepare_common(fe2o3_ctx *ctx, uint32_t op, const void *args, fe2o3_prep
     p->ctx = ctx;
     p->op = op;
     p->attn = nullptr;
+    p->scratch[0] = p->scratch[1] = nullptr;
     p->schedule = 0;
     memset(p->kernarg, 0, sizeof p->kernarg);
     memcpy(p->kernarg, args, kOps[op].kernarg_bytes);
@@ -550,6 +579,13 @@ int32_t launch_prepared(fe2o3_prepared *p, cudaStream_t s) {
         case OP_SCALAR_GEMM:
         case OP_TILED_GEMM: {
             const fe2o3_scalar_gemm_v1_args *a = reinterpret_cast<const fe2o3_scalar_gemm_v1_args *>(p->kernarg);
+            if (p->schedule == FE2O3_GEMM_SCHEDULE_TCGEN05 && p->op == OP_SCALAR_GEMM) {
+                int32_t st = gemm_split_launch(s, reinterpret_cast<const float *>(a->a.ptr), reinterpret_cast<const float *>(a->b.ptr),
+                                               static_cast<uint16_t *>(p->scratch[0]), static_cast<uint16_t *>(p->scratch[1]), a->m,
+                                               a->n, a->k);
+                if (st != FE2O3_OK) return st;
+                return gemm_tc_launch(&p->gemm[0], s);
+            }
             if (p->schedule == FE2O3_GEMM_SCHEDULE_TCGEN05) return gemm_tc_launch(&p->gemm[0], s);
             return launch_gemm_exact(s, p->op == OP_SCALAR_GEMM ? FE2O3_DTYPE_F32 : FE2O3_DTYPE_BF16, false, a->a.ptr,
                                      a->b.ptr, a->c.ptr, a->m, a->n, a->k, a->k, a->n, a->n, 1.f, 0.f, nullptr, false);
@@ -1239,6 +1275,9 @@ const char *fe2o3_prepared_symbol(const fe2o3_prepared *p) { return p ? kOps[p->
 int32_t fe2o3_prepared_destroy(fe2o3_prepared *p) {
     if (!p) return FE2O3_OK;
     if (p->attn) attention_tc_free(p->attn);
+    // the workspace may still be read by a launch in flight: freeing synchronises with the device (cudaFree does)
+    for (void *w : p->scratch)
+        if (w) cudaFree(w);
     delete p;
     return FE2O3_OK;
 }

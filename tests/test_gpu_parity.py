@@ -321,6 +321,82 @@ def test_gemm_general_tcgen05_alpha_beta_strides(gpu, orc):
             assert (bits(got[r * ldc:r * ldc + n]) == bits(want[r * n:(r + 1) * n])).all(), (schedule, r)
 
 
+# The reference's hardware matrix: seven shape / stride / coefficient profiles, each run by both of its schedules
+# (examples/tiled_gemm_general_v1/hardware-harness/src/lib.rs:139-253), on its integer-pattern inputs (:372-386,
+# 1640-1648) with NaN-poisoned padding between rows (:69-75).  Here each profile runs on the exact-order schedule
+# and, where the copy engine can address the operands (16-byte rows), on the tcgen05 schedule as well.
+HARDWARE_CASES = [("packed", (16, 16, 16), (16, 16, 16), 1.0, 0.0),
+                  ("strided-all-tails", (17, 19, 18), (23, 29, 31), 0.5, -1.0),
+                  ("multi-wg-multi-phase", (33, 35, 33), (37, 41, 43), 2.0, 0.25),
+                  ("m-tail", (17, 16, 16), (16, 16, 16), -1.0, 1.0),
+                  ("n-tail", (16, 17, 16), (16, 19, 23), 1.5, -0.5),
+                  ("k-tail", (16, 16, 17), (21, 19, 16), -0.5, 2.0),
+                  ("zero-k", (17, 19, 0), (0, 0, 23), 7.0, 0.5)]
+
+
+def _pattern(rows, cols, rf, cf, modulus):
+    r, c = np.meshgrid(np.arange(rows), np.arange(cols), indexing="ij")
+    return ((r * rf + c * cf) % modulus).astype(np.float32) - np.float32(modulus // 2)
+
+
+@pytest.mark.parametrize("name,shape,strides,alpha,beta", HARDWARE_CASES, ids=[c[0] for c in HARDWARE_CASES])
+def test_gemm_general_reference_hardware_matrix(gpu, orc, name, shape, strides, alpha, beta):
+    fe, ctx, stream = gpu
+    (m, n, k), (lda, ldb, ldc) = shape, strides
+    ext = lambda rows, cols, ld: (rows - 1) * ld + cols if rows and cols else 0
+    a = np.full(ext(m, k, lda), 0x7fc1, np.uint16)                            # poisoned padding: a NaN pattern
+    b = np.full(ext(k, n, ldb), 0x7fd1, np.uint16)
+    c = np.full(ext(m, n, ldc), 0x7fc0c001, np.uint32).view(np.float32)
+    pa, pb, pc = _pattern(m, k, 3, 5, 7), _pattern(k, n, 2, 3, 5), _pattern(m, n, 7, 11, 13)
+    for r in range(m):
+        a[r * lda:r * lda + k] = (pa[r].view(np.uint32) >> 16).astype(np.uint16)   # small integers: exact in bf16
+        c[r * ldc:r * ldc + n] = pc[r]
+    for r in range(k):
+        b[r * ldb:r * ldb + n] = (pb[r].view(np.uint32) >> 16).astype(np.uint16)
+    want = orc.gemm_bf16(m, n, k, a, b, lda=lda, ldb=ldb, ldc=ldc, alpha=alpha, beta=beta, c=c)
+    ran = []
+    for schedule in (fe.SCHEDULE_EXACT_ORDER, fe.SCHEDULE_TCGEN05):
+        A, B, Cb = Guarded(fe, stream, a), Guarded(fe, stream, b), Guarded(fe, stream, c)
+        try:
+            p = fe.prepare(ctx, "tiled_gemm_general_v1", schedule=schedule, a=A.slice, b=B.slice, c=Cb.slice, m=m, n=n, k=k,
+                           lda=lda, ldb=ldb, ldc=ldc, alpha=alpha, beta=beta)
+        except fe.Fe2o3Error as err:
+            # the tensor-core schedule admits 16-byte aligned operands with 16-byte row pitches and K > 0 only
+            assert schedule == fe.SCHEDULE_TCGEN05 and err.status == -10, err
+            continue
+        assert len(p.kernarg) == 80   # the reference's explicit argument block (lib.rs:578-593)
+        p.launch_and_wait(stream, 20000)
+        got = Cb.read()
+        for r in range(m):
+            assert (bits(got[r * ldc:r * ldc + n]) == bits(want[r * n:(r + 1) * n])).all(), (name, schedule, r)
+            pad = got[r * ldc + n:(r + 1) * ldc] if r + 1 < m else got[:0]
+            assert (pad.view(np.uint32) == 0x7fc0c001).all(), (name, schedule, "padding of C was written")
+        A.unchanged(); B.unchanged()
+        ran.append(schedule)
+    assert fe.SCHEDULE_EXACT_ORDER in ran
+    if name == "packed":
+        assert fe.SCHEDULE_TCGEN05 in ran   # every operand row is 16-byte aligned there
+
+
+@pytest.mark.parametrize("m,n,k,rows", [(512, 512, 512, 512), (4096, 4096, 4096, 96), (136, 264, 72, 136)])
+def test_scalar_gemm_f32_tcgen05_split_within_bound(gpu, orc, m, n, k, rows):
+    """f32 operands on the tensor cores (split into two bf16 terms each, three products): the stated bound is
+    |C - A*B| <= 2^-14 * (|A|*|B|) elementwise, plus the f32 accumulation term K * 2^-24 * (|A|*|B|)."""
+    fe, ctx, stream = gpu
+    from fe2o3_b200 import synth
+    a, b = synth.uniform_f32(0, 1, m * k), synth.uniform_f32(0, 2, k * n)
+    A, B = Guarded(fe, stream, a), Guarded(fe, stream, b)
+    Cb = Guarded(fe, stream, np.full(m * n, np.nan, np.float32))
+    p = run(fe, ctx, stream, "scalar_gemm_v1", schedule=fe.SCHEDULE_TCGEN05, a=A.slice, b=B.slice, c=Cb.slice, m=m, n=n, k=k)
+    assert p.geometry.launches == 3
+    got = Cb.read().reshape(m, n)[:rows].astype(np.float64)
+    a64, b64 = a.reshape(m, k)[:rows].astype(np.float64), b.reshape(k, n).astype(np.float64)
+    exact, mag = a64 @ b64, np.abs(a64) @ np.abs(b64)
+    bound = (2.0 ** -14 + k * 2.0 ** -24) * mag
+    assert (np.abs(got - exact) <= bound).all(), float((np.abs(got - exact) / mag).max())
+    A.unchanged(); B.unchanged()
+
+
 def test_gemm_empty_and_zero_k(gpu, orc):
     fe, ctx, stream = gpu
     assert fe.prepare(ctx, "tiled_gemm_v1", a=(0, 0), b=(0, 0), c=(0, 0), m=0, n=16, k=16) is None  # NoDispatch
