@@ -7,7 +7,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libfe2o3_b200.so")
+# FE2O3_B200_LIB names another build of the same library (for instance one compiled with diagnostics)
+LIB_PATH = os.environ.get("FE2O3_B200_LIB") or os.path.join(_HERE, "libfe2o3_b200.so")
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(

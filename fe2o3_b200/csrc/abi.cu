@@ -1199,6 +1199,7 @@ int32_t fe2o3_moe_ep_ffn_v1_prepare(fe2o3_ctx *ctx, const fe2o3_moe_ep_ffn_v1_ar
     ep.epoch_counter = a->epoch_counter.len ? reinterpret_cast<const uint32_t *>(a->epoch_counter.ptr) : nullptr;
     ep.epoch = a->epoch;
     ep.spin_limit = a->spin_limit ? a->spin_limit : FE2O3_EP_DEFAULT_SPIN;
+    ep.trace_flags = flags;
     // first GEMM: waits per source for "rows complete"; GELU + bf16 hidden rows
     GemmEp in = ep;
     in.rows_flags = flags + FE2O3_EP_FLAG_ROWS(W);

@@ -58,6 +58,16 @@ static inline uint32_t ceil_div_u32(uint64_t a, uint64_t b) { return (uint32_t)(
 #define FE2O3_EP_COUNTER_FFN(W) (3u * (W) + 1u)
 #define FE2O3_EP_COUNTER_COMBINE(W) (3u * (W) + 2u)
 #define FE2O3_EP_DEFAULT_SPIN (1u << 24)
+// Diagnostic build (-DFE2O3_EP_TRACE): the kernels of the expert-parallel layer stamp the global
+// nanosecond timer into 64-bit slots at byte 2048 of the rank's flag block (which must then be at
+// least 4096 bytes), one slot per event, overwritten every pass.
+#define FE2O3_EP_TRACE_WORD 512u
+enum {
+    FE2O3_EP_T_DISPATCH_BEGIN = 0, FE2O3_EP_T_COUNTS_HERE = 1, FE2O3_EP_T_ROWS_SENT = 2, FE2O3_EP_T_FFN1_BEGIN = 3,
+    FE2O3_EP_T_FFN1_FIRST_WAIT_DONE = 4, FE2O3_EP_T_FFN1_LAST_WAIT_DONE = 5, FE2O3_EP_T_FFN1_END = 6,
+    FE2O3_EP_T_FFN2_BEGIN = 7, FE2O3_EP_T_FFN2_END = 8, FE2O3_EP_T_COMBINE_BEGIN = 9, FE2O3_EP_T_OUTPUTS_HERE = 10,
+    FE2O3_EP_T_COMBINE_END = 11
+};
 
 // Capacity of the context's reduction scratch: partials followed by one counter.
 #define FE2O3_REDUCE_MAX_BLOCKS 4096u
@@ -113,6 +123,15 @@ __device__ __forceinline__ bool flag_wait(const uint32_t *flag, uint32_t epoch, 
     }
     return true;
 }
+#ifdef FE2O3_EP_TRACE
+__device__ __forceinline__ void ep_trace(uint32_t *flags, uint32_t slot) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    reinterpret_cast<unsigned long long *>(flags + FE2O3_EP_TRACE_WORD)[slot] = t;
+}
+#else
+__device__ __forceinline__ void ep_trace(uint32_t *, uint32_t) {}
+#endif
 // Orders this thread's earlier generic-proxy observations (a flag it acquired) before its later
 // asynchronous-proxy reads of global memory (bulk tensor loads of the rows that flag covers).
 __device__ __forceinline__ void fence_proxy_async_global() {

@@ -191,6 +191,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             for (uint32_t i = threadIdx.x; i < p.ep.world; i += blockDim.x) s_peer[i] = p.ep.peer_ret[i];
     }
     const uint32_t ep_epoch = p.ep.epoch_counter ? __ldcg(p.ep.epoch_counter) + 1u : p.ep.epoch;
+#ifdef FE2O3_EP_TRACE
+    if (p.ep.trace_flags && blockIdx.x == 0 && threadIdx.x == 0)
+        ep_trace(p.ep.trace_flags, p.ep.rows_flags ? FE2O3_EP_T_FFN1_BEGIN : FE2O3_EP_T_FFN2_BEGIN);
+#endif
     if (warp == 1) {
         tmem_alloc(tmem_slot, 2 * BN);
         tmem_relinquish();
@@ -232,6 +236,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 }
                 if (!ok) break;
                 fence_proxy_async_global();
+#ifdef FE2O3_EP_TRACE
+                if (blockIdx.x == 0 && lane == 0 && p.ep.trace_flags) {
+                    if (id == blockIdx.x) ep_trace(p.ep.trace_flags, FE2O3_EP_T_FFN1_FIRST_WAIT_DONE);
+                    if (seen == (1u << p.ep.world) - 1u) ep_trace(p.ep.trace_flags, FE2O3_EP_T_FFN1_LAST_WAIT_DONE);
+                }
+#endif
             }
             for (uint32_t kb = 0; kb < num_kb; ++kb, ++loaded) {
                 if (!mbar_wait_warp(&empty[stage], phase ^ 1, &s_abort)) { ok = false; break; }
@@ -473,6 +483,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         tc_fence_after();
         tmem_dealloc(tmem_base, 2 * BN);
     }
+#ifdef FE2O3_EP_TRACE
+    if (p.ep.trace_flags && blockIdx.x == gridDim.x - 1 && threadIdx.x == 0)
+        ep_trace(p.ep.trace_flags, p.ep.rows_flags ? FE2O3_EP_T_FFN1_END : FE2O3_EP_T_FFN2_END);
+#endif
     if (p.ep.done_counter && threadIdx.x == 0) {
         // The last CTA of the grid to finish raises "outputs ready" on every rank, unless some CTA gave
         // up on a wait (the pass is void then).  A failed CTA still arrives, so the counter is re-armed.

@@ -22,6 +22,7 @@ struct GemmEp {
     uint32_t ret_rows;              // rows of a return buffer
     const uint64_t *peer_flags;     // [world] base address of every rank's flag block
     uint32_t *done_counter;         // this rank's arrival counter of the kernel's CTAs
+    uint32_t *trace_flags;          // this rank's flag block (diagnostic time stamps, FE2O3_EP_TRACE builds only)
 };
 
 struct GemmParams {

@@ -64,6 +64,7 @@ moe_ep_dispatch_kernel(fe2o3_moe_ep_exchange_v1_args a, uint32_t *status) {
 
     // routing that reported a fault (non-finite logits) leaves no table to dispatch: the pass is void
     const bool dead = status && __ldcg(status) != 0u;
+    if (blockIdx.x == 0 && threadIdx.x == 0) ep_trace(my_flags, FE2O3_EP_T_DISPATCH_BEGIN);
     if (blockIdx.x == 0 && !dead) {
         // publish this rank's admitted counts into every rank's table, then the flag
         const uint32_t *admitted = reinterpret_cast<const uint32_t *>(a.admitted_counts.ptr);
@@ -94,6 +95,7 @@ moe_ep_dispatch_kernel(fe2o3_moe_ep_exchange_v1_args a, uint32_t *status) {
     // every block waits for the counts of every source (thread s polls source s: local memory)
     int ok = dead ? 0 : (threadIdx.x < W ? (flag_wait(my_flags + FE2O3_EP_FLAG_COUNTS(W) + threadIdx.x, epoch, limit) ? 1 : 0) : 1);
     ok = __syncthreads_and(ok);
+    if (blockIdx.x == 0 && threadIdx.x == 0) ep_trace(my_flags, FE2O3_EP_T_COUNTS_HERE);
     if (ok) {
         for (uint32_t i = threadIdx.x; i < W * E; i += kThreads) s_counts[i] = __ldcg(my_counts + i);
         for (uint32_t i = threadIdx.x; i <= E; i += kThreads)
@@ -176,6 +178,7 @@ moe_ep_dispatch_kernel(fe2o3_moe_ep_exchange_v1_args a, uint32_t *status) {
         for (uint32_t p = threadIdx.x; p < W; p += kThreads)
             st_release_sys(reinterpret_cast<uint32_t *>(peer_flags[p]) + FE2O3_EP_FLAG_ROWS(W) + me, epoch);
     }
+    if (s_last && threadIdx.x == 0) ep_trace(my_flags, FE2O3_EP_T_ROWS_SENT);
 }
 
 // One block per token.  The two rows of a token were stored into this rank's return buffer, indexed by
@@ -190,10 +193,12 @@ moe_ep_combine_kernel(fe2o3_moe_ep_exchange_v1_args a, uint32_t *status) {
     const uint64_t *peer_ret = reinterpret_cast<const uint64_t *>(a.peer_ret.ptr);
     uint32_t *my_flags = reinterpret_cast<uint32_t *>(peer_flags[me]);
     const uint32_t t = blockIdx.x;
+    if (blockIdx.x == 0 && threadIdx.x == 0) ep_trace(my_flags, FE2O3_EP_T_COMBINE_BEGIN);
     // a pass in which an earlier kernel reported a fault is void: write nothing
     const bool dead = status && __ldcg(status) != 0u;
     int ok = (!dead && threadIdx.x < W) ? (flag_wait(my_flags + FE2O3_EP_FLAG_OUTPUTS(W) + threadIdx.x, epoch, limit) ? 1 : 0) : 1;
     ok = __syncthreads_and(ok);
+    if (blockIdx.x == 0 && threadIdx.x == 0) ep_trace(my_flags, FE2O3_EP_T_OUTPUTS_HERE);
     if (!ok) {
         if (threadIdx.x == 0) kstatus_set(status, FE2O3_KSTATUS_WAIT_EXPIRED);
     } else if (!dead && t < a.tokens) {
@@ -241,6 +246,7 @@ moe_ep_combine_kernel(fe2o3_moe_ep_exchange_v1_args a, uint32_t *status) {
     if (threadIdx.x == 0) {
         const uint32_t old = atomicAdd(my_flags + FE2O3_EP_COUNTER_COMBINE(W), 1u);
         if (old == gridDim.x - 1) {
+            ep_trace(my_flags, FE2O3_EP_T_COMBINE_END);
             atomicExch(my_flags + FE2O3_EP_COUNTER_COMBINE(W), 0u);
             if (a.epoch_counter.len) *reinterpret_cast<uint32_t *>(a.epoch_counter.ptr) += 1u;
         }
