@@ -7,8 +7,11 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <dlfcn.h>
+
 #include <atomic>
 #include <chrono>
+#include <mutex>
 #include <new>
 #include <thread>
 
@@ -134,7 +137,112 @@ struct fe2o3_prepared {
 
 struct fe2o3_executable {
     fe2o3_ctx *ctx;
+    uint8_t digest[32];   // of the image the caller presented (and this library is)
 };
+
+// ---- kernel registry (symbol -> device function), filled by file-scope objects of the kernel sources ----
+namespace {
+struct KernelEntry {
+    const char *symbol;
+    const void *entry;
+};
+constexpr int kMaxKernelEntries = 64;
+KernelEntry *kernel_table(int **count) {
+    static KernelEntry table[kMaxKernelEntries];   // function-local: usable from other sources' static initialisers
+    static int n = 0;
+    *count = &n;
+    return table;
+}
+}  // namespace
+void fe2o3_register_kernel(const char *symbol, const void *entry) {
+    int *n;
+    KernelEntry *t = kernel_table(&n);
+    if (*n < kMaxKernelEntries) t[(*n)++] = KernelEntry{symbol, entry};
+}
+
+// ---- SHA-256 (FIPS 180-4), for the image digest of load_executable ----------------------------
+namespace {
+struct Sha256 {
+    uint32_t h[8];
+    uint8_t block[64];
+    uint64_t total;
+    uint32_t fill;
+    Sha256() : total(0), fill(0) {
+        static const uint32_t init[8] = {0x6a09e667u, 0xbb67ae85u, 0x3c6ef372u, 0xa54ff53au,
+                                         0x510e527fu, 0x9b05688cu, 0x1f83d9abu, 0x5be0cd19u};
+        memcpy(h, init, sizeof h);
+    }
+    static uint32_t rotr(uint32_t v, int r) { return (v >> r) | (v << (32 - r)); }
+    void compress(const uint8_t *p) {
+        static const uint32_t K[64] = {
+            0x428a2f98u, 0x71374491u, 0xb5c0fbcfu, 0xe9b5dba5u, 0x3956c25bu, 0x59f111f1u, 0x923f82a4u, 0xab1c5ed5u,
+            0xd807aa98u, 0x12835b01u, 0x243185beu, 0x550c7dc3u, 0x72be5d74u, 0x80deb1feu, 0x9bdc06a7u, 0xc19bf174u,
+            0xe49b69c1u, 0xefbe4786u, 0x0fc19dc6u, 0x240ca1ccu, 0x2de92c6fu, 0x4a7484aau, 0x5cb0a9dcu, 0x76f988dau,
+            0x983e5152u, 0xa831c66du, 0xb00327c8u, 0xbf597fc7u, 0xc6e00bf3u, 0xd5a79147u, 0x06ca6351u, 0x14292967u,
+            0x27b70a85u, 0x2e1b2138u, 0x4d2c6dfcu, 0x53380d13u, 0x650a7354u, 0x766a0abbu, 0x81c2c92eu, 0x92722c85u,
+            0xa2bfe8a1u, 0xa81a664bu, 0xc24b8b70u, 0xc76c51a3u, 0xd192e819u, 0xd6990624u, 0xf40e3585u, 0x106aa070u,
+            0x19a4c116u, 0x1e376c08u, 0x2748774cu, 0x34b0bcb5u, 0x391c0cb3u, 0x4ed8aa4au, 0x5b9cca4fu, 0x682e6ff3u,
+            0x748f82eeu, 0x78a5636fu, 0x84c87814u, 0x8cc70208u, 0x90befffau, 0xa4506cebu, 0xbef9a3f7u, 0xc67178f2u};
+        uint32_t w[64];
+        for (int i = 0; i < 16; ++i)
+            w[i] = ((uint32_t)p[4 * i] << 24) | ((uint32_t)p[4 * i + 1] << 16) | ((uint32_t)p[4 * i + 2] << 8) | p[4 * i + 3];
+        for (int i = 16; i < 64; ++i) {
+            const uint32_t s0 = rotr(w[i - 15], 7) ^ rotr(w[i - 15], 18) ^ (w[i - 15] >> 3);
+            const uint32_t s1 = rotr(w[i - 2], 17) ^ rotr(w[i - 2], 19) ^ (w[i - 2] >> 10);
+            w[i] = w[i - 16] + s0 + w[i - 7] + s1;
+        }
+        uint32_t a = h[0], b = h[1], c = h[2], d = h[3], e = h[4], f = h[5], g = h[6], hh = h[7];
+        for (int i = 0; i < 64; ++i) {
+            const uint32_t t1 = hh + (rotr(e, 6) ^ rotr(e, 11) ^ rotr(e, 25)) + ((e & f) ^ (~e & g)) + K[i] + w[i];
+            const uint32_t t2 = (rotr(a, 2) ^ rotr(a, 13) ^ rotr(a, 22)) + ((a & b) ^ (a & c) ^ (b & c));
+            hh = g; g = f; f = e; e = d + t1; d = c; c = b; b = a; a = t1 + t2;
+        }
+        h[0] += a; h[1] += b; h[2] += c; h[3] += d; h[4] += e; h[5] += f; h[6] += g; h[7] += hh;
+    }
+    void update(const uint8_t *p, uint64_t n) {
+        total += n;
+        while (n) {
+            const uint32_t take = (uint32_t)((64 - fill) < n ? (64 - fill) : n);
+            memcpy(block + fill, p, take);
+            fill += take; p += take; n -= take;
+            if (fill == 64) { compress(block); fill = 0; }
+        }
+    }
+    void finish(uint8_t out[32]) {
+        const uint64_t bits = total * 8;
+        const uint8_t one = 0x80, zero = 0;
+        update(&one, 1);
+        while (fill != 56) update(&zero, 1);
+        uint8_t len[8];
+        for (int i = 0; i < 8; ++i) len[i] = (uint8_t)(bits >> (56 - 8 * i));
+        update(len, 8);
+        for (int i = 0; i < 8; ++i)
+            for (int j = 0; j < 4; ++j) out[4 * i + j] = (uint8_t)(h[i] >> (24 - 8 * j));
+    }
+};
+
+// SHA-256 of this shared library's file, as found on disk at first use.  false when it cannot be read.
+bool own_image_digest(uint8_t out[32]) {
+    static std::once_flag once;
+    static bool ok = false;
+    static uint8_t digest[32];
+    std::call_once(once, [] {
+        Dl_info info;
+        if (!dladdr(reinterpret_cast<const void *>(&fe2o3_register_kernel), &info) || !info.dli_fname) return;
+        FILE *f = fopen(info.dli_fname, "rb");
+        if (!f) return;
+        Sha256 sha;
+        static uint8_t buf[1 << 16];
+        size_t n;
+        while ((n = fread(buf, 1, sizeof buf, f)) > 0) sha.update(buf, n);
+        fclose(f);
+        sha.finish(digest);
+        ok = true;
+    });
+    if (ok) memcpy(out, digest, 32);
+    return ok;
+}
+}  // namespace
 
 // ---- region checks ---------------------------------------------------------------
 namespace {
@@ -410,7 +518,7 @@ int regions_for(uint32_t op, const void *args, Region *r, int32_t *status) {
             r[5] = RGN("PeerRet", a->peer_ret, a->world, 8, false);
             r[6] = RGN("PeerFlags", a->peer_flags, a->world, 8, false);
             r[7] = RGN("Hidden", a->hidden, (uint64_t)a->max_rows * a->d_ff, 2, true);
-            r[8] = RGN("Flags", a->flags, 3ull * a->world + 3, 4, true);
+            r[8] = RGN("Flags", a->flags, FE2O3_EP_FLAG_WORDS((uint64_t)a->world), 4, true);
             if (a->epoch_counter.ptr == 0 && a->epoch_counter.len == 0) return 9;
             r[9] = RGN("EpochCounter", a->epoch_counter, 1, 4, false);
             return 10;
@@ -1041,6 +1149,7 @@ const char *fe2o3_status_string(int32_t s) {
         case FE2O3_ERR_UNKNOWN_SYMBOL: return "UnknownSymbol";
         case FE2O3_ERR_NOT_SM100: return "NotSm100";
         case FE2O3_ERR_NONFINITE: return "NonFinite";
+        case FE2O3_ERR_EXECUTABLE_REJECTED: return "ExecutableRejected";
         case FE2O3_ERR_NO_DISPATCH: return "NoDispatch";
         default: return s > 0 ? "CudaError" : "Unknown";
     }
@@ -1203,6 +1312,7 @@ int32_t fe2o3_moe_ep_ffn_v1_prepare(fe2o3_ctx *ctx, const fe2o3_moe_ep_ffn_v1_ar
     // first GEMM: waits per source for "rows complete"; GELU + bf16 hidden rows
     GemmEp in = ep;
     in.rows_flags = flags + FE2O3_EP_FLAG_ROWS(W);
+    in.table_flag = flags + FE2O3_EP_FLAG_TABLE(W);
     st = gemm_tc_plan(ctx, &p->gemm[0], a->recv_x.ptr, a->w1.ptr, a->hidden.ptr, a->max_rows, a->d_ff, a->d_model,
                       a->d_model, a->d_ff, a->d_ff, 1.f, 0.f, EPI_GELU_BF16, in.pair_offsets, per, 0, per, &in);
     // second GEMM: every output row goes to its home rank's return buffer; the last CTA raises "outputs ready"
@@ -1216,6 +1326,7 @@ int32_t fe2o3_moe_ep_ffn_v1_prepare(fe2o3_ctx *ctx, const fe2o3_moe_ep_ffn_v1_ar
         st = gemm_tc_plan(ctx, &p->gemm[1], a->hidden.ptr, a->w2.ptr, 0, a->max_rows, a->d_model, a->d_ff, a->d_ff,
                           a->d_model, a->d_model, 1.f, 0.f, EPI_SCATTER_PEER, outp.pair_offsets, per, 0, per, &outp);
     if (st != FE2O3_OK) return fail_prepare(out, st);
+    p->gemm[0].overlap_previous = 1;   // may start beside the dispatch kernel launched just before it
     gemm_tc_geometry(&p->gemm[0], &p->geo);
     p->geo.launches = 2;
     return FE2O3_OK;
@@ -1288,10 +1399,59 @@ int32_t fe2o3_ctx_take_kernel_status(fe2o3_ctx *ctx, fe2o3_stream *stream, uint3
 }
 
 // ---- runtime adapter ---------------------------------------------------------------------------
-int32_t fe2o3_load_executable(fe2o3_ctx *ctx, fe2o3_executable **out) {
-    if (!ctx || !out) return FE2O3_ERR_INVALID_ARGUMENT;
-    *out = new (std::nothrow) fe2o3_executable{ctx};
-    return *out ? FE2O3_OK : FE2O3_ERR_SIZE_OVERFLOW;
+int32_t fe2o3_image_digest(uint8_t digest[32]) {
+    if (!digest) return FE2O3_ERR_INVALID_ARGUMENT;
+    if (!own_image_digest(digest)) {
+        fe2o3_set_error("the library image could not be read back from disk");
+        return FE2O3_ERR_EXECUTABLE_REJECTED;
+    }
+    return FE2O3_OK;
+}
+int32_t fe2o3_load_executable(fe2o3_ctx *ctx, const void *bytes, uint64_t len, const uint8_t digest[32],
+                              fe2o3_executable **out) {
+    if (!ctx || !out || !digest || (!bytes && len)) return FE2O3_ERR_INVALID_ARGUMENT;
+    *out = nullptr;
+    // the digest must be the digest of the bytes presented ...
+    Sha256 sha;
+    sha.update(static_cast<const uint8_t *>(bytes), len);
+    uint8_t got[32];
+    sha.finish(got);
+    if (memcmp(got, digest, 32) != 0) {
+        fe2o3_set_error("ExecutableRejected: the digest is not the SHA-256 of the %llu bytes presented", (unsigned long long)len);
+        return FE2O3_ERR_EXECUTABLE_REJECTED;
+    }
+    // ... and those bytes must be the image that will run: this library's own file
+    uint8_t mine[32];
+    if (!own_image_digest(mine) || memcmp(mine, digest, 32) != 0) {
+        fe2o3_set_error("ExecutableRejected: the artifact is not the sm_100a image loaded in this process");
+        return FE2O3_ERR_EXECUTABLE_REJECTED;
+    }
+    fe2o3_executable *exe = new (std::nothrow) fe2o3_executable();
+    if (!exe) return FE2O3_ERR_SIZE_OVERFLOW;
+    exe->ctx = ctx;
+    memcpy(exe->digest, digest, 32);
+    *out = exe;
+    return FE2O3_OK;
+}
+int32_t fe2o3_observe_kernel_resources(fe2o3_executable *exe, uint32_t kernel_id, fe2o3_kernel_resources *out) {
+    if (!exe || !out || kernel_id >= OP_COUNT) return FE2O3_ERR_INVALID_ARGUMENT;
+    int *n;
+    KernelEntry *t = kernel_table(&n);
+    for (int i = 0; i < *n; ++i) {
+        if (strcmp(t[i].symbol, kOps[kernel_id].symbol) != 0) continue;
+        FE2O3_CUDA(cudaSetDevice(exe->ctx->device));
+        cudaFuncAttributes a;
+        FE2O3_CUDA(cudaFuncGetAttributes(&a, t[i].entry));
+        out->registers_per_thread = (uint32_t)a.numRegs;
+        out->static_shared_bytes = (uint32_t)a.sharedSizeBytes;
+        out->max_dynamic_shared_bytes = (uint32_t)a.maxDynamicSharedSizeBytes;
+        out->max_threads_per_block = (uint32_t)a.maxThreadsPerBlock;
+        out->local_bytes_per_thread = (uint32_t)a.localSizeBytes;
+        out->const_bytes = (uint32_t)a.constSizeBytes;
+        return FE2O3_OK;
+    }
+    fe2o3_set_error("UnknownSymbol: no device function registered for %s", kOps[kernel_id].symbol);
+    return FE2O3_ERR_UNKNOWN_SYMBOL;
 }
 int32_t fe2o3_resolve_kernel(fe2o3_executable *exe, const char *symbol, uint32_t *kernel_id, uint64_t *kernarg_bytes) {
     if (!exe || !symbol || !kernel_id) return FE2O3_ERR_INVALID_ARGUMENT;
@@ -1305,8 +1465,8 @@ int32_t fe2o3_resolve_kernel(fe2o3_executable *exe, const char *symbol, uint32_t
     fe2o3_set_error("UnknownSymbol: %s", symbol);
     return FE2O3_ERR_UNKNOWN_SYMBOL;
 }
-int32_t fe2o3_launch_and_wait(fe2o3_executable *exe, uint32_t kernel_id, const void *kernarg, uint64_t kernarg_bytes,
-                              fe2o3_stream *stream, uint32_t timeout_ms, uint32_t *kernel_status) {
+int32_t fe2o3_launch_and_wait(fe2o3_executable *exe, uint32_t kernel_id, const fe2o3_geometry *geometry, const void *kernarg,
+                              uint64_t kernarg_bytes, fe2o3_stream *stream, uint32_t timeout_ms, uint32_t *kernel_status) {
     if (!exe || !kernarg || !stream || kernel_id >= OP_COUNT) return FE2O3_ERR_INVALID_ARGUMENT;
     if (kernarg_bytes != kOps[kernel_id].kernarg_bytes) {
         fe2o3_set_error("Length{role=kernarg, expected=%llu, actual=%llu}",
@@ -1330,6 +1490,20 @@ int32_t fe2o3_launch_and_wait(fe2o3_executable *exe, uint32_t kernel_id, const v
     }
     if (st == FE2O3_ERR_NO_DISPATCH) return FE2O3_OK;
     if (st != FE2O3_OK) return st;
+    if (geometry) {
+        // the caller's launch geometry must be the one this argument block plans to (the launch is rejected
+        // before anything is submitted, like every other adapter failure)
+        const fe2o3_geometry &g = p->geo;
+        if (memcmp(geometry->grid, g.grid, sizeof g.grid) != 0 || memcmp(geometry->workgroup, g.workgroup, sizeof g.workgroup) != 0 ||
+            geometry->dynamic_shared_bytes != g.dynamic_shared_bytes) {
+            fe2o3_set_error("GeometryMismatch: caller grid %ux%ux%u block %ux%ux%u shared %u, plan grid %ux%ux%u block %ux%ux%u shared %u",
+                            geometry->grid[0], geometry->grid[1], geometry->grid[2], geometry->workgroup[0], geometry->workgroup[1],
+                            geometry->workgroup[2], geometry->dynamic_shared_bytes, g.grid[0], g.grid[1], g.grid[2],
+                            g.workgroup[0], g.workgroup[1], g.workgroup[2], g.dynamic_shared_bytes);
+            fe2o3_prepared_destroy(p);
+            return FE2O3_ERR_INVALID_ARGUMENT;
+        }
+    }
     st = fe2o3_prepared_launch_and_wait(p, stream, timeout_ms, kernel_status);
     fe2o3_prepared_destroy(p);
     return st;

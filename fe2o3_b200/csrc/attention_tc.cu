@@ -588,3 +588,5 @@ void attention_tc_geometry(const AttnTcPlan *plan, fe2o3_geometry *geo) {
 }
 
 void attention_tc_free(AttnTcPlan *plan) { delete plan; }
+
+static Fe2o3KernelRegistration reg_attention("flash_attention_v1", reinterpret_cast<const void *>(attention_tc_kernel));

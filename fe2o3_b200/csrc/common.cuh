@@ -36,6 +36,12 @@ struct fe2o3_stream {
 };
 
 void fe2o3_set_error(const char *fmt, ...);
+// Names the device function that carries a kernel symbol of the runtime adapter, for
+// fe2o3_observe_kernel_resources.  Each source registers its kernels with a file-scope object.
+void fe2o3_register_kernel(const char *symbol, const void *entry);
+struct Fe2o3KernelRegistration {
+    Fe2o3KernelRegistration(const char *symbol, const void *entry) { fe2o3_register_kernel(symbol, entry); }
+};
 void fe2o3_count_launch(uint32_t n);
 int32_t fe2o3_cuda_status(cudaError_t e, const char *what);
 
@@ -49,14 +55,19 @@ static inline uint32_t ceil_div_u32(uint64_t a, uint64_t b) { return (uint32_t)(
 
 // Flag block of one rank of the expert-parallel layer, in u32 words (world = W):
 //   [0, W)    counts published by source rank s        [W, 2W)  rows complete from source rank s
-//   [2W, 3W)  outputs ready from owner rank o          3W, 3W+1, 3W+2  arrival counters of the
-//   dispatch kernel, the second FFN GEMM and the combine kernel (each re-armed by its last block)
+//   [2W, 3W)  outputs ready from owner rank o          3W+1, 3W+2  arrival counters of the second FFN
+//   GEMM and the combine kernel (each re-armed by its last block)   3W+3  "row table written" (local:
+//   the dispatch kernel to the FFN kernel that may already be running beside it)
+//   [3W+4, 5W+4)  rows stored so far per destination rank, two sets used by alternate passes (the set of
+//   the next pass is cleared by the dispatch kernel of this one)
 #define FE2O3_EP_FLAG_COUNTS(W) (0u)
 #define FE2O3_EP_FLAG_ROWS(W) (W)
 #define FE2O3_EP_FLAG_OUTPUTS(W) (2u * (W))
-#define FE2O3_EP_COUNTER_DISPATCH(W) (3u * (W))
 #define FE2O3_EP_COUNTER_FFN(W) (3u * (W) + 1u)
 #define FE2O3_EP_COUNTER_COMBINE(W) (3u * (W) + 2u)
+#define FE2O3_EP_FLAG_TABLE(W) (3u * (W) + 3u)
+#define FE2O3_EP_ROWS_DONE(W, parity) (3u * (W) + 4u + (parity) * (W))
+#define FE2O3_EP_FLAG_WORDS(W) (5u * (W) + 4u)
 #define FE2O3_EP_DEFAULT_SPIN (1u << 24)
 // Diagnostic build (-DFE2O3_EP_TRACE): the kernels of the expert-parallel layer stamp the global
 // nanosecond timer into 64-bit slots at byte 2048 of the rank's flag block (which must then be at
@@ -132,6 +143,10 @@ __device__ __forceinline__ void ep_trace(uint32_t *flags, uint32_t slot) {
 #else
 __device__ __forceinline__ void ep_trace(uint32_t *, uint32_t) {}
 #endif
+// Programmatic dependent launch: lets the next kernel of the stream, if it was launched with programmatic
+// stream serialization, start once every block of this grid has executed this (or exited).  That kernel
+// sees none of this grid's memory effects unless it synchronises by other means (flags, here).
+__device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 // Orders this thread's earlier generic-proxy observations (a flag it acquired) before its later
 // asynchronous-proxy reads of global memory (bulk tensor loads of the rows that flag covers).
 __device__ __forceinline__ void fence_proxy_async_global() {

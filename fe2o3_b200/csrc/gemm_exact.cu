@@ -110,3 +110,5 @@ int32_t launch_gemm_exact(cudaStream_t s, uint32_t dtype, bool epilogue, uint64_
     fe2o3_count_launch(1);
     return fe2o3_cuda_status(cudaGetLastError(), "gemm_exact");
 }
+
+static Fe2o3KernelRegistration reg_scalar("scalar_gemm_v1", reinterpret_cast<const void *>(gemm_exact_kernel<float, false>));

@@ -51,9 +51,9 @@ struct TileCoord {
 
 // Static tile order.  Plain: bands of kGroupM m-tiles, m fastest inside a band.
 // Grouped: expert-major; inside an expert m fastest.  Grouped with per-source waiting (first GEMM of
-// the expert-parallel FFN): inside an expert n fastest, and the m-tiles rotated so that the tile
-// holding this rank's own first row comes first: rows that never crossed NVLink are there at once,
-// the other sources' rows get the time of those tiles to arrive.
+// the expert-parallel FFN): by the source rank of the tile's first row, this rank's own rows first
+// (they never cross NVLink), then ranks +1, +2, ... which is the order in which the other ranks send
+// to this one; inside a source by local expert, then m, n fastest.
 __device__ __forceinline__ TileCoord decode_tile(uint32_t id, const GemmParams &p, uint32_t n_tiles,
                                                  const uint32_t *s_off, const uint32_t *s_pair) {
     TileCoord t;
@@ -73,29 +73,44 @@ __device__ __forceinline__ TileCoord decode_tile(uint32_t id, const GemmParams &
         t.valid = true;
         return t;
     }
-    uint32_t base = 0;
-    for (uint32_t e = 0; e < p.experts; ++e) {
-        const uint32_t rows = s_off[e + 1] - s_off[e];
-        const uint32_t mt = (rows + BM - 1) / BM;
-        const uint32_t cnt = mt * n_tiles;
-        if (id < base + cnt) {
-            const uint32_t local = id - base;
-            uint32_t mi;
-            if (p.ep.rows_flags) {
-                const uint32_t own = s_pair[e * p.ep.world + p.ep.rank] - s_off[e];   // this rank's first row in the segment
-                mi = (local / n_tiles + min(own / BM, mt - 1)) % mt;
+    if (p.ep.rows_flags) {
+        // groups = (rotation step j, local expert le): the tiles whose first row belongs to source (rank + j) mod W
+        const uint32_t W = p.ep.world;
+        uint32_t base = 0;
+        for (uint32_t g = 0; g < W * p.experts; ++g) {
+            const uint32_t j = g / p.experts, le = g % p.experts;
+            const uint32_t src = (p.ep.rank + j) % W, pi = le * W + src;
+            const uint32_t seg = s_off[le], lo = s_pair[pi] - seg, hi = s_pair[pi + 1] - seg;
+            const uint32_t i0 = (lo + BM - 1) / BM, i1 = (hi + BM - 1) / BM;   // tile starts seg + i * BM in [lo, hi)
+            const uint32_t cnt = hi > lo ? (i1 - i0) * n_tiles : 0u;
+            if (id < base + cnt) {
+                const uint32_t local = id - base;
+                t.m0 = seg + (i0 + local / n_tiles) * BM;
                 t.n0 = local % n_tiles;
-            } else {
-                mi = local % mt;
-                t.n0 = local / mt;
+                t.m_end = s_off[le + 1];
+                t.expert = le;
+                t.valid = true;
+                break;
             }
-            t.m0 = s_off[e] + mi * BM;
-            t.m_end = s_off[e + 1];
-            t.expert = p.expert_mod ? e % p.expert_mod : e;   // index of the B matrix
-            t.valid = true;
-            break;
+            base += cnt;
         }
-        base += cnt;
+    } else {
+        uint32_t base = 0;
+        for (uint32_t e = 0; e < p.experts; ++e) {
+            const uint32_t rows = s_off[e + 1] - s_off[e];
+            const uint32_t mt = (rows + BM - 1) / BM;
+            const uint32_t cnt = mt * n_tiles;
+            if (id < base + cnt) {
+                const uint32_t local = id - base;
+                t.m0 = s_off[e] + (local % mt) * BM;
+                t.n0 = local / mt;
+                t.m_end = s_off[e + 1];
+                t.expert = p.expert_mod ? e % p.expert_mod : e;   // index of the B matrix
+                t.valid = true;
+                break;
+            }
+            base += cnt;
+        }
     }
     // The offsets come from shared memory, which the compiler must treat as lane-varying.  Every lane
     // of the (converged) calling warp holds the same values; taking them from lane 0 lets the TMA
@@ -169,7 +184,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         mbar_fence_init();
     }
+    __shared__ int s_table_bad;
+    const uint32_t ep_epoch = p.ep.epoch_counter ? __ldcg(p.ep.epoch_counter) + 1u : p.ep.epoch;
     if (p.experts && threadIdx.x == 64) {
+        // The dispatch kernel that writes the table may still be running beside this kernel: wait for its
+        // "table written" flag before reading (bounded like every wait).
+        s_table_bad = 0;
+        if (p.ep.table_flag && !flag_wait(p.ep.table_flag, ep_epoch, p.ep.spin_limit)) {
+            s_table_bad = 1;
+            kstatus_set(p.status, FE2O3_KSTATUS_WAIT_EXPIRED);
+        }
         // The segment table is device data (in the expert-parallel layer it derives from other ranks'
         // counts): it is made monotone and cut off at M here, so that no row index derived from it can
         // leave A or C, and the fault is reported instead.
@@ -177,20 +201,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         uint32_t prev = 0;
         bool bad = false;
         for (uint32_t i = 0; i <= p.experts; ++i) {
-            uint32_t v = p.expert_offsets[i * stride];
+            uint32_t v = __ldcg(p.expert_offsets + i * stride);
             if (v < prev || v > p.M) { bad = true; v = v < prev ? prev : p.M; }
             s_off[i] = v;
             prev = v;
         }
         if (bad) kstatus_set(p.status, FE2O3_KSTATUS_SLOT_RANGE);
     }
-    if (p.ep.pair_offsets) {
+    if (p.ep.pair_offsets && threadIdx.x == 64) {   // the thread that has waited for the table
         const uint32_t pairs = p.experts * p.ep.world;   // at most 32
-        for (uint32_t i = threadIdx.x; i <= pairs; i += blockDim.x) s_pair[i] = min(p.ep.pair_offsets[i], p.M);
-        if (p.ep.peer_ret)
-            for (uint32_t i = threadIdx.x; i < p.ep.world; i += blockDim.x) s_peer[i] = p.ep.peer_ret[i];
+        uint32_t prev = 0;
+        for (uint32_t i = 0; i <= pairs; ++i) {   // monotone and inside A, like the segment table
+            uint32_t v = __ldcg(p.ep.pair_offsets + i);
+            v = v < prev ? prev : (v > p.M ? p.M : v);
+            s_pair[i] = v;
+            prev = v;
+        }
     }
-    const uint32_t ep_epoch = p.ep.epoch_counter ? __ldcg(p.ep.epoch_counter) + 1u : p.ep.epoch;
+    if (p.ep.peer_ret)
+        for (uint32_t i = threadIdx.x; i < p.ep.world; i += blockDim.x) s_peer[i] = p.ep.peer_ret[i];
 #ifdef FE2O3_EP_TRACE
     if (p.ep.trace_flags && blockIdx.x == 0 && threadIdx.x == 0)
         ep_trace(p.ep.trace_flags, p.ep.rows_flags ? FE2O3_EP_T_FFN1_BEGIN : FE2O3_EP_T_FFN2_BEGIN);
@@ -203,7 +232,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const bool dead = s_abort != 0;   // uniform over the CTA: read after the barrier, before any role can set it
+    const bool dead = s_abort != 0 || (p.experts && s_table_bad);   // uniform over the CTA: read after the barrier, before any role can set it
 
     if (warp == 0) {
         // ------------------------------------------------ TMA producer (warp converged, one elected lane issues)
@@ -605,6 +634,7 @@ int32_t gemm_tc_plan(fe2o3_ctx *ctx, GemmTcPlan *plan, uint64_t a, uint64_t b, u
     uint64_t tiles = m_tiles * n_tiles;
     plan->grid = (uint32_t)(tiles < (uint64_t)ctx->sm_count ? (tiles ? tiles : 1) : (uint64_t)ctx->sm_count);
     plan->smem = plan->bn == 256 ? SmemLayout<256>::kTotal : SmemLayout<128>::kTotal;
+    plan->overlap_previous = 0;
     return FE2O3_OK;
 }
 
@@ -619,14 +649,33 @@ int32_t gemm_tc_init_device() {
 
 int32_t gemm_tc_launch(const GemmTcPlan *plan, cudaStream_t s) {
     if (plan->p.M == 0 || plan->p.N == 0) return FE2O3_OK;
-    if (plan->bn == 256)
-        gemm_tc_kernel<256><<<plan->grid, kThreads, plan->smem, s>>>(plan->tmA, plan->tmB, plan->tmC, plan->p);
-    else
-        gemm_tc_kernel<128><<<plan->grid, kThreads, plan->smem, s>>>(plan->tmA, plan->tmB, plan->tmC, plan->p);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(plan->grid, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = plan->smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    if (plan->overlap_previous) {
+        // programmatic dependent launch: the kernel may start while the kernel before it in the stream (the
+        // expert-parallel dispatch, which says when) is still running; the two synchronise through flags
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    cudaError_t e = plan->bn == 256 ? cudaLaunchKernelEx(&cfg, gemm_tc_kernel<256>, plan->tmA, plan->tmB, plan->tmC, plan->p)
+                                    : cudaLaunchKernelEx(&cfg, gemm_tc_kernel<128>, plan->tmA, plan->tmB, plan->tmC, plan->p);
     fe2o3_count_launch(1);
-    return fe2o3_cuda_status(cudaGetLastError(), "gemm_tc");
+    return fe2o3_cuda_status(e, "gemm_tc");
 }
 
 void gemm_tc_geometry(const GemmTcPlan *plan, fe2o3_geometry *geo) {
     *geo = fe2o3_geometry{{plan->grid, 1, 1}, {kThreads, 1, 1}, plan->smem, 1};
 }
+
+// kernel symbols of the runtime adapter carried by this source (the schedule a large launch resolves to)
+static Fe2o3KernelRegistration reg_tiled("tiled_gemm_lds_slice1", reinterpret_cast<const void *>(gemm_tc_kernel<256>));
+static Fe2o3KernelRegistration reg_general("tiled_gemm_general_v1", reinterpret_cast<const void *>(gemm_tc_kernel<256>));
+static Fe2o3KernelRegistration reg_ffn("moe_expert_ffn_v1", reinterpret_cast<const void *>(gemm_tc_kernel<256>));
+static Fe2o3KernelRegistration reg_gffn("moe_grouped_ffn_v1", reinterpret_cast<const void *>(gemm_tc_kernel<256>));
+static Fe2o3KernelRegistration reg_epffn("moe_ep_ffn_v1", reinterpret_cast<const void *>(gemm_tc_kernel<256>));

@@ -16,6 +16,7 @@ struct GemmEp {
     // input side (first FFN GEMM): the producer waits for "rows complete" of a source right before the
     // first tile that holds rows of that source; tiles are taken m-tile major starting at this rank's own rows
     const uint32_t *rows_flags;     // this rank's flags, one per source; null = rows are already complete
+    const uint32_t *table_flag;     // "pair_offsets written" flag of the dispatch kernel this GEMM may run beside
     // output side (EPI_SCATTER_PEER, second FFN GEMM): row r goes to ret[row_meta[r].y] + row_meta[r].x * N
     const uint2 *row_meta;          // (route id, home rank) per row of A / C
     const uint64_t *peer_ret;       // [world] base address of every rank's return buffer
@@ -47,6 +48,7 @@ struct GemmTcPlan {
     uint32_t bn;
     uint32_t grid;
     uint32_t smem;
+    uint32_t overlap_previous;   // launch with programmatic stream serialization: may start beside the kernel before it
 };
 
 int32_t fe2o3_make_tmap_bf16(CUtensorMap *out, uint64_t base, uint32_t rank, const uint64_t *dims,

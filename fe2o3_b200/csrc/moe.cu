@@ -912,3 +912,9 @@ int32_t launch_moe_combine(fe2o3_ctx *ctx, cudaStream_t s, const void *args, fe2
     fe2o3_count_launch(1);
     return fe2o3_cuda_status(cudaGetLastError(), "moe_expert_combine_v1");
 }
+
+static Fe2o3KernelRegistration reg_top2("moe_top2_v1", reinterpret_cast<const void *>(moe_route_place_kernel));
+static Fe2o3KernelRegistration reg_gate("moe_gate_v1", reinterpret_cast<const void *>(moe_gate_lanes_kernel<8, 4, 8, 6>));
+static Fe2o3KernelRegistration reg_weights("moe_route_weights_v1", reinterpret_cast<const void *>(moe_route_weights_kernel));
+static Fe2o3KernelRegistration reg_compact("moe_compact_v1", reinterpret_cast<const void *>(moe_compact_kernel));
+static Fe2o3KernelRegistration reg_combine("moe_expert_combine_v1", reinterpret_cast<const void *>(moe_combine_kernel));

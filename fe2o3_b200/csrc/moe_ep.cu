@@ -14,7 +14,8 @@
 //             copy x rows straight from the token array into the owners'
 //             receive buffers together with a (route id, home rank) record per
 //             row (compaction and dispatch in one pass), then raise "rows
-//             complete" on every rank.
+//             complete" on each rank as soon as the last row for it is stored.  The kernel
+//             lets the FFN kernel start beside it (programmatic dependent launch).
 //   expert FFN  (gemm_tc.cu) the first grouped GEMM waits for "rows complete"
 //             per source inside the kernel; the second stores each output row
 //             into the home rank's return buffer from its epilogue and raises
@@ -31,27 +32,34 @@
 // buffers and counts of pass p; and a rank's return buffer is written in pass
 // p+1 only with rows that this rank itself dispatched after that combine.
 // Every wait is bounded and records FE2O3_KSTATUS_WAIT_EXPIRED instead of
-// hanging; a block whose wait ran out still takes part in the arrival counting,
-// so the counters are re-armed for the next pass.  One rank per GPU.
+// hanging; the arrival counters are re-armed even then (a block that gave up
+// still arrives; the per-destination row counters alternate between two sets,
+// each cleared a pass ahead).  One rank per GPU.
 #include "common.cuh"
 
 namespace {
 
 constexpr uint32_t kDrop = 0xffffffffu;
 constexpr int kThreads = 256;
-constexpr uint32_t kFailedTicket = 0x10001u;   // arrival of a block whose wait expired (high half marks the failure)
+// The dispatch kernel shares every SM with one block of the GEMM that follows it (320 threads x 168 registers,
+// nearly all of the shared memory): 192 threads x 56 registers fit the register file beside it.
+constexpr int kDispatchThreads = 192;
 
 // the pass number: from the device counter when one is given, else the scalar in the argument block
 __device__ __forceinline__ uint32_t current_epoch(const fe2o3_moe_ep_exchange_v1_args &a) {
     return a.epoch_counter.len ? __ldcg(reinterpret_cast<const uint32_t *>(a.epoch_counter.ptr)) + 1u : a.epoch;
 }
 
-__global__ void __launch_bounds__(kThreads)
+// One block per SM, few registers and almost no shared memory: the first GEMM of the expert FFN is
+// launched right behind this kernel with programmatic stream serialization and runs beside it on the same
+// SMs (one GEMM block and one block of this kernel fit an SM together), computing on the rows that have
+// arrived while the others still travel.  Rows go out destination by destination, this rank's own first,
+// then ranks me-1, me-2, ... so that every rank receives from me+1 first, then me+2, ... which is the order
+// in which its GEMM takes the tiles; "rows complete" is raised per destination as soon as the last row for
+// it has been stored.
+__global__ void __launch_bounds__(kDispatchThreads, 6)
 moe_ep_dispatch_kernel(fe2o3_moe_ep_exchange_v1_args a, uint32_t *status) {
-    __shared__ uint32_t s_counts[32 * 32];   // [world][experts], world * experts <= 1024
-    __shared__ uint32_t s_base[32];          // first row of this rank's segment for expert e on e's owner
-    __shared__ uint32_t s_off[33];           // local expert_offsets
-    __shared__ bool s_last, s_clean;
+    launch_dependents();
     const uint32_t E = a.experts, W = a.world, me = a.rank, per = E / W;
     const uint32_t epoch = current_epoch(a);
     const uint32_t limit = a.spin_limit ? a.spin_limit : FE2O3_EP_DEFAULT_SPIN;
@@ -61,6 +69,7 @@ moe_ep_dispatch_kernel(fe2o3_moe_ep_exchange_v1_args a, uint32_t *status) {
     const uint64_t *peer_meta = reinterpret_cast<const uint64_t *>(a.peer_recv_meta.ptr);
     uint32_t *my_flags = reinterpret_cast<uint32_t *>(peer_flags[me]);
     const uint32_t *my_counts = reinterpret_cast<const uint32_t *>(peer_counts[me]);
+    uint32_t *rows_done = my_flags + FE2O3_EP_ROWS_DONE(W, epoch & 1u);
 
     // routing that reported a fault (non-finite logits) leaves no table to dispatch: the pass is void
     const bool dead = status && __ldcg(status) != 0u;
@@ -68,14 +77,16 @@ moe_ep_dispatch_kernel(fe2o3_moe_ep_exchange_v1_args a, uint32_t *status) {
     if (blockIdx.x == 0 && !dead) {
         // publish this rank's admitted counts into every rank's table, then the flag
         const uint32_t *admitted = reinterpret_cast<const uint32_t *>(a.admitted_counts.ptr);
-        for (uint32_t i = threadIdx.x; i < W * E; i += kThreads) {
+        for (uint32_t i = threadIdx.x; i < W * E; i += kDispatchThreads) {
             const uint32_t p = i / E, e = i % E;
             reinterpret_cast<uint32_t *>(peer_counts[p])[me * E + e] = admitted[e];
         }
         __threadfence_system();
         __syncthreads();
-        for (uint32_t p = threadIdx.x; p < W; p += kThreads)
+        for (uint32_t p = threadIdx.x; p < W; p += kDispatchThreads)
             st_release_sys(reinterpret_cast<uint32_t *>(peer_flags[p]) + FE2O3_EP_FLAG_COUNTS(W) + me, epoch);
+        // the per-destination row counters of the NEXT pass (nobody touches that set during this one)
+        for (uint32_t p = threadIdx.x; p < W; p += kDispatchThreads) my_flags[FE2O3_EP_ROWS_DONE(W, (epoch & 1u) ^ 1u) + p] = 0u;
     }
     if (a.logits.len && !dead) {
         // Route weights of this rank's tokens, one token per thread of the grid, computed while the counts
@@ -83,7 +94,7 @@ moe_ep_dispatch_kernel(fe2o3_moe_ep_exchange_v1_args a, uint32_t *status) {
         const float *logits = reinterpret_cast<const float *>(a.logits.ptr);
         const uint32_t *top2 = reinterpret_cast<const uint32_t *>(a.top2_experts.ptr);
         float *weights = reinterpret_cast<float *>(a.route_weights.ptr);
-        for (uint32_t t = blockIdx.x * kThreads + threadIdx.x; t < a.tokens; t += gridDim.x * kThreads) {
+        for (uint32_t t = blockIdx.x * kDispatchThreads + threadIdx.x; t < a.tokens; t += gridDim.x * kDispatchThreads) {
             const uint32_t e0 = top2[2ull * t], e1 = top2[2ull * t + 1];
             if (e0 >= E || e1 >= E) { kstatus_set(status, FE2O3_KSTATUS_SLOT_RANGE); continue; }
             float w0, w1;
@@ -96,89 +107,108 @@ moe_ep_dispatch_kernel(fe2o3_moe_ep_exchange_v1_args a, uint32_t *status) {
     int ok = dead ? 0 : (threadIdx.x < W ? (flag_wait(my_flags + FE2O3_EP_FLAG_COUNTS(W) + threadIdx.x, epoch, limit) ? 1 : 0) : 1);
     ok = __syncthreads_and(ok);
     if (blockIdx.x == 0 && threadIdx.x == 0) ep_trace(my_flags, FE2O3_EP_T_COUNTS_HERE);
-    if (ok) {
-        for (uint32_t i = threadIdx.x; i < W * E; i += kThreads) s_counts[i] = __ldcg(my_counts + i);
-        for (uint32_t i = threadIdx.x; i <= E; i += kThreads)
-            s_off[i] = reinterpret_cast<const uint32_t *>(a.expert_offsets.ptr)[i];
-        __syncthreads();
-        if (threadIdx.x < E) {
-            // on expert e's owner: whole segments of the owner's earlier experts, then the rows of earlier sources
-            const uint32_t e = threadIdx.x, d = e / per, le = e % per;
-            uint32_t base = 0;
-            for (uint32_t l2 = 0; l2 < le; ++l2)
-                for (uint32_t s = 0; s < W; ++s) base += s_counts[s * E + d * per + l2];
-            for (uint32_t s = 0; s < me; ++s) base += s_counts[s * E + e];
-            s_base[e] = base;
+    if (!ok) {
+        // nothing is sent and no flag is raised: the other ranks' waits run out in turn
+        if (threadIdx.x == 0) kstatus_set(status, FE2O3_KSTATUS_WAIT_EXPIRED);
+        return;
+    }
+    // Every warp keeps the small tables it needs in registers, one entry per lane (this kernel shares its
+    // SMs with the GEMM that follows it, which leaves it no shared memory to speak of):
+    //   lane e < E: off_lo/off_hi = local slots of expert e, base = first row of this rank's rows for e on e's owner
+    //   lane j < W: the j-th destination in sending order, rank (me - j) mod W: v_lo/v_hi = its rows in that order
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t *offsets = reinterpret_cast<const uint32_t *>(a.expert_offsets.ptr);
+    const uint32_t off_lo = lane < E ? offsets[lane] : 0u, off_hi = lane < E ? offsets[lane + 1] : 0u;
+    const uint32_t accepted = offsets[E];
+    uint32_t base = 0;
+    if (lane < E) {
+        // on expert e's owner: whole segments of the owner's earlier experts, then the rows of earlier sources
+        const uint32_t e = lane, d = e / per, le = e % per;
+        for (uint32_t l2 = 0; l2 < le; ++l2)
+            for (uint32_t s = 0; s < W; ++s) base += __ldcg(my_counts + s * E + d * per + l2);
+        for (uint32_t s = 0; s < me; ++s) base += __ldcg(my_counts + s * E + e);
+    }
+    uint32_t v_lo = 0, v_hi = 0;
+    if (lane < W) {
+        for (uint32_t j = 0; j <= lane; ++j) {
+            const uint32_t d = (me + W - j) % W;
+            v_lo = v_hi;
+            v_hi += offsets[(d + 1) * per] - offsets[d * per];
         }
-        if (blockIdx.x == 0 && threadIdx.x == 0) {
-            // row partition of what this rank receives: pair (local expert, source)
-            uint32_t *pair_offsets = reinterpret_cast<uint32_t *>(a.pair_offsets.ptr);
-            uint32_t run = 0;
-            pair_offsets[0] = 0;
-            for (uint32_t le = 0; le < per; ++le)
-                for (uint32_t s = 0; s < W; ++s) {
-                    run += s_counts[s * E + me * per + le];
-                    // a table that overruns the receive buffer is cut off: the FFN must never index past it
-                    pair_offsets[le * W + s + 1] = run < a.max_rows ? run : a.max_rows;
-                }
-            if (run > a.max_rows) kstatus_set(status, FE2O3_KSTATUS_SLOT_RANGE);
-        }
-        __syncthreads();
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 32) {
+        // row partition of what this rank receives: pair (local expert, source); then tell the FFN kernel,
+        // which may already be running on this GPU, that the table is there
+        uint32_t *pair_offsets = reinterpret_cast<uint32_t *>(a.pair_offsets.ptr);
+        uint32_t run = 0;
+        pair_offsets[0] = 0;
+        for (uint32_t le = 0; le < per; ++le)
+            for (uint32_t s = 0; s < W; ++s) {
+                run += __ldcg(my_counts + s * E + me * per + le);
+                // a table that overruns the receive buffer is cut off: the FFN must never index past it
+                pair_offsets[le * W + s + 1] = run < a.max_rows ? run : a.max_rows;
+            }
+        if (run > a.max_rows) kstatus_set(status, FE2O3_KSTATUS_SLOT_RANGE);
+        __threadfence();
+        st_release_sys(my_flags + FE2O3_EP_FLAG_TABLE(W), epoch);
+    }
+    if (blockIdx.x == 0 && threadIdx.x < W && v_hi == v_lo)   // nothing to send there: complete at once
+        st_release_sys(reinterpret_cast<uint32_t *>(peer_flags[(me + W - threadIdx.x) % W]) + FE2O3_EP_FLAG_ROWS(W) + me, epoch);
 
-        // rows: one warp per accepted local slot; a lane keeps up to eight 16-byte loads in flight before the peer stores
-        const uint32_t accepted = s_off[E];
-        const uint32_t *perm = reinterpret_cast<const uint32_t *>(a.permutation.ptr);
-        const uint32_t vec_per_row = a.d_model / 8;
-        const uint4 *x = reinterpret_cast<const uint4 *>(a.x.ptr);
-        const uint32_t lane = threadIdx.x & 31;
-        const uint32_t gwarp = blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5), nwarps = gridDim.x * (kThreads / 32);
-        for (uint32_t slot = gwarp; slot < accepted; slot += nwarps) {
-            // the slot's expert = number of expert segments that end at or before it
-            const uint32_t e = __popc(__ballot_sync(0xffffffffu, lane < E && slot >= s_off[lane + 1]));
-            const uint32_t route = perm[slot];
-            if (e >= E || route == kDrop || (route >> 1) >= a.tokens) {
-                if (lane == 0) kstatus_set(status, FE2O3_KSTATUS_SLOT_RANGE);
-                continue;
-            }
-            const uint32_t dst_rank = e / per;
-            const uint32_t dst_row = s_base[e] + (slot - s_off[e]);
-            if (dst_row >= a.max_rows) {
-                if (lane == 0) kstatus_set(status, FE2O3_KSTATUS_SLOT_RANGE);
-                continue;
-            }
-            if (lane == 0) reinterpret_cast<uint2 *>(peer_meta[dst_rank])[dst_row] = make_uint2(route, me);
-            const uint4 *src = x + (uint64_t)(route >> 1) * vec_per_row;
-            uint4 *dst = reinterpret_cast<uint4 *>(peer_recv[dst_rank]) + (uint64_t)dst_row * vec_per_row;
-            for (uint32_t i0 = lane; i0 < vec_per_row; i0 += 32 * 8) {
-                uint4 v[8];
-#pragma unroll
-                for (int u = 0; u < 8; ++u)
-                    if (i0 + 32 * u < vec_per_row) v[u] = __ldg(src + i0 + 32 * u);
-#pragma unroll
-                for (int u = 0; u < 8; ++u)
-                    if (i0 + 32 * u < vec_per_row) dst[i0 + 32 * u] = v[u];
+    // rows: one warp per accepted local slot, four 16-byte loads in flight per lane before the peer stores
+    const uint32_t *perm = reinterpret_cast<const uint32_t *>(a.permutation.ptr);
+    const uint32_t vec_per_row = a.d_model / 8;
+    const uint4 *x = reinterpret_cast<const uint4 *>(a.x.ptr);
+    const uint32_t gwarp = blockIdx.x * (kDispatchThreads / 32) + (threadIdx.x >> 5), nwarps = gridDim.x * (kDispatchThreads / 32);
+    uint32_t cur_j = W, cur_cnt = 0;   // rows stored for the cur_j-th destination and not yet accounted for
+    auto account = [&]() {
+        // every lane's stores are ordered before the counter update; whoever completes the destination's
+        // count raises "rows complete" there
+        __threadfence_system();
+        __syncwarp();
+        const uint32_t total = __shfl_sync(0xffffffffu, v_hi - v_lo, cur_j);
+        if (lane == 0 && cur_cnt) {
+            const uint32_t d = (me + W - cur_j) % W;
+            const uint32_t done = atomicAdd(rows_done + d, cur_cnt) + cur_cnt;
+            if (done == total) {
+                __threadfence_system();
+                st_release_sys(reinterpret_cast<uint32_t *>(peer_flags[d]) + FE2O3_EP_FLAG_ROWS(W) + me, epoch);
             }
         }
-    } else if (threadIdx.x == 0) {
-        kstatus_set(status, FE2O3_KSTATUS_WAIT_EXPIRED);
+        cur_cnt = 0;
+    };
+    for (uint32_t v = gwarp; v < accepted; v += nwarps) {
+        // v-th row in sending order: which destination, which local slot, which expert
+        const uint32_t j = __popc(__ballot_sync(0xffffffffu, lane < W && v >= v_hi));
+        if (j != cur_j) {
+            if (cur_cnt) account();
+            cur_j = j;
+        }
+        ++cur_cnt;   // counted even when the row is refused below: the destination must not wait for it
+        const uint32_t dst_rank = (me + W - j) % W;
+        const uint32_t slot = offsets[dst_rank * per] + (v - __shfl_sync(0xffffffffu, v_lo, j));
+        const uint32_t e = __popc(__ballot_sync(0xffffffffu, lane < E && slot >= off_hi));
+        const uint32_t route = perm[slot];
+        const uint32_t dst_row = __shfl_sync(0xffffffffu, base, e & 31) + (slot - __shfl_sync(0xffffffffu, off_lo, e & 31));
+        if (e >= E || route == kDrop || (route >> 1) >= a.tokens || dst_row >= a.max_rows) {
+            if (lane == 0) kstatus_set(status, FE2O3_KSTATUS_SLOT_RANGE);
+            continue;
+        }
+        if (lane == 0) reinterpret_cast<uint2 *>(peer_meta[dst_rank])[dst_row] = make_uint2(route, me);
+        const uint4 *src = x + (uint64_t)(route >> 1) * vec_per_row;
+        uint4 *dst = reinterpret_cast<uint4 *>(peer_recv[dst_rank]) + (uint64_t)dst_row * vec_per_row;
+        for (uint32_t i0 = lane; i0 < vec_per_row; i0 += 32 * 4) {
+            uint4 q[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (i0 + 32 * u < vec_per_row) q[u] = __ldg(src + i0 + 32 * u);
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (i0 + 32 * u < vec_per_row) dst[i0 + 32 * u] = q[u];
+        }
     }
-    // all of this block's rows are written; the last block to arrive raises "rows complete" everywhere,
-    // unless some block's wait ran out (the pass is void then, and the peers' waits expire in turn)
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const uint32_t old = atomicAdd(my_flags + FE2O3_EP_COUNTER_DISPATCH(W), ok ? 1u : kFailedTicket);
-        s_last = (old & 0xffffu) == gridDim.x - 1;
-        s_clean = ok && (old >> 16) == 0;
-        if (s_last) atomicExch(my_flags + FE2O3_EP_COUNTER_DISPATCH(W), 0u);   // re-arm for the next pass
-    }
-    __syncthreads();
-    if (s_last && s_clean) {
-        __threadfence_system();
-        for (uint32_t p = threadIdx.x; p < W; p += kThreads)
-            st_release_sys(reinterpret_cast<uint32_t *>(peer_flags[p]) + FE2O3_EP_FLAG_ROWS(W) + me, epoch);
-    }
-    if (s_last && threadIdx.x == 0) ep_trace(my_flags, FE2O3_EP_T_ROWS_SENT);
+    if (cur_cnt) account();
+    if (blockIdx.x == 0 && threadIdx.x == 0) ep_trace(my_flags, FE2O3_EP_T_ROWS_SENT);
 }
 
 // One block per token.  The two rows of a token were stored into this rank's return buffer, indexed by
@@ -259,10 +289,15 @@ int32_t launch_moe_ep_exchange(fe2o3_ctx *ctx, cudaStream_t s, const void *args,
     const fe2o3_moe_ep_exchange_v1_args *a = static_cast<const fe2o3_moe_ep_exchange_v1_args *>(args);
     switch (a->phase) {
         case FE2O3_MOE_EP_DISPATCH: {
-            const uint32_t grid = (uint32_t)ctx->sm_count * 4u;
-            if (geo) *geo = fe2o3_geometry{{grid, 1, 1}, {kThreads, 1, 1}, 0, 1};
+            const uint32_t grid = (uint32_t)ctx->sm_count;
+            if (geo) *geo = fe2o3_geometry{{grid, 1, 1}, {kDispatchThreads, 1, 1}, 0, 1};
             if (plan_only) return FE2O3_OK;
-            moe_ep_dispatch_kernel<<<grid, kThreads, 0, s>>>(*a, ctx->status_word);
+            // The GEMM that is to run beside this kernel needs nearly all of an SM's shared memory; an SM
+            // changes its split between L1 and shared memory only when idle, so this kernel asks for the
+            // largest shared-memory split although it uses none (per device, cheap: set at every launch).
+            cudaFuncSetAttribute(moe_ep_dispatch_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                 (int)cudaSharedmemCarveoutMaxShared);
+            moe_ep_dispatch_kernel<<<grid, kDispatchThreads, 0, s>>>(*a, ctx->status_word);
             break;
         }
         case FE2O3_MOE_EP_COMBINE: {
@@ -279,3 +314,5 @@ int32_t launch_moe_ep_exchange(fe2o3_ctx *ctx, cudaStream_t s, const void *args,
     fe2o3_count_launch(1);
     return fe2o3_cuda_status(cudaGetLastError(), "moe_ep_exchange_v1");
 }
+
+static Fe2o3KernelRegistration reg_exchange("moe_ep_exchange_v1", reinterpret_cast<const void *>(moe_ep_dispatch_kernel));

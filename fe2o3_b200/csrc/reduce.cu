@@ -430,3 +430,11 @@ extern "C" int32_t fe2o3_masked_reduce_u32_noalloc(const uint32_t *values, const
     fe2o3_count_launch(1);
     return fe2o3_cuda_status(cudaGetLastError(), "masked_reduce_u32_noalloc");
 }
+
+static Fe2o3KernelRegistration reg_reduce("masked_reduce_sum_u32", reinterpret_cast<const void *>(masked_reduce_u32_kernel));
+static Fe2o3KernelRegistration reg_reduce_packed("masked_reduce_sum_u32_packed", reinterpret_cast<const void *>(masked_reduce_u32_packed_kernel));
+static Fe2o3KernelRegistration reg_wave_lds("gfx942_wave_lds_v1_hw", reinterpret_cast<const void *>(wave_lds_v1_kernel));
+static Fe2o3KernelRegistration reg_wave64("wave64_collectives_v1", reinterpret_cast<const void *>(wave64_collectives_kernel));
+static Fe2o3KernelRegistration reg_wave64_seg("wave64_collectives_segmented", reinterpret_cast<const void *>(wave64_collectives_kernel));
+static Fe2o3KernelRegistration reg_lds_i32("lds_publish_read_reduce_i32_v1", reinterpret_cast<const void *>(lds_publish_read_reduce_i32_kernel));
+static Fe2o3KernelRegistration reg_atomic("scoped_atomic_add_u32_v1", reinterpret_cast<const void *>(scoped_atomic_add_u32_kernel));

@@ -425,3 +425,6 @@ int32_t launch_device_scan_u32(fe2o3_ctx *ctx, cudaStream_t s, const void *args,
 int32_t launch_device_scan_f32(fe2o3_ctx *ctx, cudaStream_t s, const void *args, fe2o3_geometry *geo, bool plan_only) {
     return launch_device_scan<true>(ctx, s, args, geo, plan_only);
 }
+
+static Fe2o3KernelRegistration reg_scan_u32("device_scan_sum_u32", reinterpret_cast<const void *>(device_scan_kernel<false>));
+static Fe2o3KernelRegistration reg_scan_f32("device_scan_sum_f32", reinterpret_cast<const void *>(device_scan_kernel<true>));

@@ -203,3 +203,5 @@ int32_t launch_row_softmax(fe2o3_ctx *ctx, cudaStream_t s, const void *args, fe2
     fe2o3_count_launch(1);
     return fe2o3_cuda_status(cudaGetLastError(), "row_softmax_v1");
 }
+
+static Fe2o3KernelRegistration reg_softmax("row_softmax_v1", reinterpret_cast<const void *>(row_softmax_warp_kernel<8, false>));

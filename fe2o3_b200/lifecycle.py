@@ -501,9 +501,10 @@ class Unloaded:
 # ------------------------------------------------------------ the CUDA adapter
 class CudaRuntimeAdapter(RuntimeAdapter):
     """The adapter over libfe2o3_b200.so: fe2o3_ctx_observe_environment, fe2o3_load_executable,
-    fe2o3_resolve_kernel, fe2o3_launch_and_wait, fe2o3_unload_executable.  The image is the library
-    itself, so `load_executable` checks that the receipt's bytes are the bytes of the library that is
-    loaded in this process before it asks the library for its executable."""
+    fe2o3_resolve_kernel, fe2o3_observe_kernel_resources, fe2o3_launch_and_wait,
+    fe2o3_unload_executable.  The image is the library itself: `load_executable` hands the receipt's
+    bytes and digest to the library, which rejects them unless they are the bytes of the image that is
+    loaded in this process."""
 
     def __init__(self, ctx, stream, timeout_ms=5000):
         from . import _lib
@@ -520,11 +521,10 @@ class CudaRuntimeAdapter(RuntimeAdapter):
         return EnvironmentObservation(target, self.ctx.device, self._instance, int(self.ctx._h.value))
 
     def load_executable(self, artifact_bytes, digest):
-        with open(self._lib.LIB_PATH, "rb") as f:
-            if hashlib.sha256(f.read()).digest() != digest:
-                raise RuntimeError("the receipt does not describe the loaded library image")
         exe = C.c_void_p()
-        self._check(self._lib.lib.fe2o3_load_executable(self.ctx._h, C.byref(exe)), "load_executable")
+        dig = (C.c_uint8 * 32).from_buffer_copy(digest)
+        self._check(self._lib.lib.fe2o3_load_executable(self.ctx._h, artifact_bytes, C.c_uint64(len(artifact_bytes)), dig,
+                                                        C.byref(exe)), "load_executable")
         obj = hashlib.sha256(b"exe" + self._instance + int(exe.value).to_bytes(8, "little")).digest()
         return (exe, obj), LoadObservation(digest, len(artifact_bytes), self._instance, int(self.ctx._h.value), obj)
 
@@ -536,7 +536,12 @@ class CudaRuntimeAdapter(RuntimeAdapter):
         return _CudaKernel(kid.value, kobj), ResolutionObservation(obj, symbol, kobj, int(nbytes.value), KERNARG_ALIGNMENT)
 
     def observe_kernel_resources(self, executable, kernel):
-        # shared memory and stack are the kernel's own and are fixed at build time: nothing is requested
+        res = self._lib.KernelResources()
+        self._check(self._lib.lib.fe2o3_observe_kernel_resources(executable[0], C.c_uint32(kernel.kernel_id), C.byref(res)),
+                    "observe_kernel_resources")
+        self.last_resources = res
+        # what the lifecycle compares is what the LAUNCH must provide beyond the kernel's own compiled needs:
+        # shared memory and stack are fixed at build time, nothing is requested of the caller
         return ResourceObservation(executable[1], kernel.object, 0, 0)
 
     def initialize_implicit_kernarg(self, executable, kernel, geometry, explicit_byte_len, implicit_byte_offset,
@@ -547,7 +552,10 @@ class CudaRuntimeAdapter(RuntimeAdapter):
 
     def launch_and_wait(self, executable, kernel, geometry, kernarg):
         status = C.c_uint32()
-        rc = self._lib.lib.fe2o3_launch_and_wait(executable[0], C.c_uint32(kernel.kernel_id), kernarg,
+        geo = self._lib.Geometry()
+        geo.grid[:], geo.workgroup[:] = geometry.grid, geometry.workgroup
+        geo.dynamic_shared_bytes = geometry.dynamic_shared_bytes
+        rc = self._lib.lib.fe2o3_launch_and_wait(executable[0], C.c_uint32(kernel.kernel_id), C.byref(geo), kernarg,
                                                  C.c_uint64(len(kernarg)), self.stream._h,
                                                  C.c_uint32(self.timeout_ms), C.byref(status))
         self._check(rc, "launch_and_wait")

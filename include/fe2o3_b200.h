@@ -44,6 +44,7 @@ extern "C" {
 #define FE2O3_ERR_UNKNOWN_SYMBOL -13
 #define FE2O3_ERR_NOT_SM100 -14           /* target check: device is not sm_100 */
 #define FE2O3_ERR_NONFINITE -15           /* finite-input policy violated */
+#define FE2O3_ERR_EXECUTABLE_REJECTED -16 /* load_executable: digest or image mismatch */
 #define FE2O3_ERR_NO_DISPATCH 1000        /* not an error: plan says "nothing to launch" */
 
 /* Device-side status words written instead of trapping
@@ -297,7 +298,7 @@ typedef struct fe2o3_moe_grouped_ffn_v1_args {
  *   recv_meta [max_rows] {u32 route id, u32 home rank}   where each row came from
  *   ret       [2*tokens][d_model] f32    expert outputs by route id, on the home rank
  *   counts    [world][experts] u32       admitted routes per (source rank, expert)
- *   flags     [3*world + 3] u32, zero before the first pass
+ *   flags     [5*world + 4] u32, zero before the first pass
  * Rows on the owner of expert e are ordered local-expert-major, source-rank-minor,
  * so each expert's rows are one contiguous segment; pair_offsets[le*world + s]
  * is the first row of (local expert le, source s), pair_offsets[experts] the
@@ -317,9 +318,12 @@ typedef struct fe2o3_moe_grouped_ffn_v1_args {
  *       (route, home) records into the owners' receive buffers, raise
  *       "rows complete" on every rank.
  *   moe_ep_ffn_v1  GELU(x*W1)*W2 over the received rows as two grouped tcgen05
- *       GEMMs.  The first waits per source rank, inside the kernel, for "rows
- *       complete" right before it first loads rows of that source (tiles of this
- *       rank's own rows come first); the second stores every output row straight
+ *       GEMMs.  The first is launched so that it may start while the dispatch
+ *       kernel before it in the stream is still sending (programmatic dependent
+ *       launch); it waits per source rank, inside the kernel, for "rows complete"
+ *       right before it first loads rows of that source, and takes the tiles in the
+ *       order the rows arrive (this rank's own first, then ranks +1, +2, ...: every
+ *       rank sends to rank-1 first, then rank-2, ...); the second stores every output row straight
  *       into the return buffer of the row's home rank from its epilogue and,
  *       when its last tile is stored, raises "outputs ready" on every rank.
  *   moe_ep_exchange_v1, phase COMBINE   wait for "outputs ready" of every rank,
@@ -535,18 +539,46 @@ int32_t fe2o3_prepared_destroy(fe2o3_prepared *prepared);
 int32_t fe2o3_ctx_take_kernel_status(fe2o3_ctx *ctx, fe2o3_stream *stream, uint32_t *status);
 
 /* ---- runtime adapter ---------------------------------------------------- */
-/* The five entry points of ReviewedHsaExecutableLifecycleAdapterV1
- * (crates/fe2o3-host/src/hsa_executable_lifecycle.rs:963-1035) over the
- * library's built-in sm_100a image: load, resolve by kernel symbol, launch with
- * a packed argument block and bounded wait, unload.  Native shape:
- * crates/fe2o3-hsa-runtime/native/runtime.h:82-122. */
+/* The entry points of ReviewedHsaExecutableLifecycleAdapterV1
+ * (crates/fe2o3-host/src/hsa_executable_lifecycle.rs:963-1071) over the
+ * library's built-in sm_100a image; native shape:
+ * crates/fe2o3-hsa-runtime/native/runtime.h:82-122.
+ *
+ * load_executable(bytes, digest) (hsa_executable_lifecycle.rs:977-990): the
+ * artifact of this backend is the shared library file itself (the device code is
+ * embedded in it).  The caller presents the bytes it holds a receipt for and
+ * their SHA-256; the call fails with FE2O3_ERR_EXECUTABLE_REJECTED unless the
+ * digest is the digest of those bytes AND of the library image loaded in this
+ * process (fe2o3_image_digest), so a receipt for any other build cannot launch.
+ * Nothing native stays live after a failed load.
+ * resolve_kernel(exe, symbol) (:992-1003): the reference kernel function names.
+ * observe_kernel_resources(exe, kernel) (:1005-1016): the compiled resources of
+ * the device function that carries the symbol (the schedule large launches
+ * resolve to, where an op has several).
+ * launch_and_wait(exe, kernel, geometry, kernarg) (:1038-1060, geometry record
+ * :823-853): `geometry` may be NULL; when given it must equal the geometry the
+ * argument block plans to, else FE2O3_ERR_INVALID_ARGUMENT before submission.
+ * initialize_implicit_kernarg has no counterpart: CUDA kernels take no hidden
+ * arguments. */
 typedef struct fe2o3_executable fe2o3_executable;
-int32_t fe2o3_load_executable(fe2o3_ctx *ctx, fe2o3_executable **out);
+typedef struct fe2o3_kernel_resources {
+    uint32_t registers_per_thread;
+    uint32_t static_shared_bytes;
+    uint32_t max_dynamic_shared_bytes;
+    uint32_t max_threads_per_block;
+    uint32_t local_bytes_per_thread; /* stack / spill space */
+    uint32_t const_bytes;
+} fe2o3_kernel_resources;
+int32_t fe2o3_image_digest(uint8_t digest[32]);
+int32_t fe2o3_load_executable(fe2o3_ctx *ctx, const void *bytes, uint64_t len, const uint8_t digest[32],
+                              fe2o3_executable **out);
 int32_t fe2o3_resolve_kernel(fe2o3_executable *exe, const char *symbol, uint32_t *kernel_id,
                              uint64_t *kernarg_bytes);
-int32_t fe2o3_launch_and_wait(fe2o3_executable *exe, uint32_t kernel_id, const void *kernarg,
-                              uint64_t kernarg_bytes, fe2o3_stream *stream, uint32_t timeout_ms,
-                              uint32_t *kernel_status);
+int32_t fe2o3_observe_kernel_resources(fe2o3_executable *exe, uint32_t kernel_id, fe2o3_kernel_resources *out);
+struct fe2o3_geometry;
+int32_t fe2o3_launch_and_wait(fe2o3_executable *exe, uint32_t kernel_id, const struct fe2o3_geometry *geometry,
+                              const void *kernarg, uint64_t kernarg_bytes, fe2o3_stream *stream,
+                              uint32_t timeout_ms, uint32_t *kernel_status);
 int32_t fe2o3_unload_executable(fe2o3_executable *exe);
 
 /* ---- deterministic synthetic inputs (host side) ------------------------- */

@@ -618,23 +618,52 @@ def test_moe_end_to_end_small(gpu, orc, T, d, f, E, cap):
 
 def test_runtime_adapter_resolves_reference_symbols(gpu, orc):
     import ctypes as C
+    import hashlib
     fe, ctx, stream = gpu
-    from fe2o3_b200._lib import lib, RowSoftmaxArgs
+    from fe2o3_b200._lib import lib, LIB_PATH, Geometry, KernelResources
+    image = open(LIB_PATH, "rb").read()
+    digest = hashlib.sha256(image).digest()
+    dig = lambda b: (C.c_uint8 * 32).from_buffer_copy(b)
+    mine = (C.c_uint8 * 32)()
+    fe.check(lib.fe2o3_image_digest(mine))
+    assert bytes(mine) == digest                                   # the library's own SHA-256 agrees with hashlib
     exe = C.c_void_p()
-    fe.check(lib.fe2o3_load_executable(ctx._h, C.byref(exe)))
+    # load_executable(bytes, digest): a digest that is not the digest of the bytes, and bytes that are not the
+    # loaded image, are both refused and leave nothing loaded (hsa_executable_lifecycle.rs:977-990)
+    assert lib.fe2o3_load_executable(ctx._h, image, C.c_uint64(len(image)), dig(bytes(32)), C.byref(exe)) == -16
+    other = b"not the image"
+    assert lib.fe2o3_load_executable(ctx._h, other, C.c_uint64(len(other)), dig(hashlib.sha256(other).digest()), C.byref(exe)) == -16
+    assert not exe.value
+    fe.check(lib.fe2o3_load_executable(ctx._h, image, C.c_uint64(len(image)), dig(digest), C.byref(exe)))
     kid, nbytes = C.c_uint32(), C.c_uint64()
+    res = KernelResources()
     for sym in ("tiled_gemm_lds_slice1", "tiled_gemm_general_v1", "scalar_gemm_v1", "flash_attention_v1", "row_softmax_v1",
                 "moe_top2_v1", "moe_expert_combine_v1", "wave64_collectives_v1", "gfx942_wave_lds_v1_hw",
                 "lds_publish_read_reduce_i32_v1", "scoped_atomic_add_u32_v1"):
         fe.check(lib.fe2o3_resolve_kernel(exe, sym.encode(), C.byref(kid), C.byref(nbytes)), sym)
+        fe.check(lib.fe2o3_observe_kernel_resources(exe, kid, C.byref(res)), sym)
+        assert 0 < res.registers_per_thread <= 255 and 32 <= res.max_threads_per_block <= 1024, sym
+    fe.check(lib.fe2o3_resolve_kernel(exe, b"flash_attention_v1", C.byref(kid), C.byref(nbytes)))
+    fe.check(lib.fe2o3_observe_kernel_resources(exe, kid, C.byref(res)))
+    assert res.max_dynamic_shared_bytes > 100 * 1024              # the tensor-core kernel's opted-in shared memory
     assert lib.fe2o3_resolve_kernel(exe, b"no_such_kernel", C.byref(kid), C.byref(nbytes)) == -13
     fe.check(lib.fe2o3_resolve_kernel(exe, b"row_softmax_v1", C.byref(kid), C.byref(nbytes)))
     x = np.linspace(-3, 3, 64, dtype=np.float32)
     i, o = Guarded(fe, stream, x), Guarded(fe, stream, np.zeros(64, np.float32))
     args = fe.make_args("row_softmax_v1", input=i.slice, output=o.slice, rows=1, cols=64)
     ks = C.c_uint32()
-    fe.check(lib.fe2o3_launch_and_wait(exe, kid, C.byref(args), nbytes, stream._h, C.c_uint32(5000), C.byref(ks)))
+    # a geometry that is not the one the argument block plans to is refused before anything is submitted
+    plan = fe.prepare(ctx, "row_softmax_v1", input=i.slice, output=o.slice, rows=1, cols=64).geometry
+    wrong = Geometry()
+    wrong.grid[:], wrong.workgroup[:] = (plan.grid[0] + 1, 1, 1), tuple(plan.workgroup)
+    assert lib.fe2o3_launch_and_wait(exe, kid, C.byref(wrong), C.byref(args), nbytes, stream._h, C.c_uint32(5000), C.byref(ks)) == -2
+    assert (o.read() == 0).all()
+    fe.check(lib.fe2o3_launch_and_wait(exe, kid, C.byref(plan), C.byref(args), nbytes, stream._h, C.c_uint32(5000), C.byref(ks)))
     assert np.abs(o.read() - orc.row_softmax(x)[1]).max() < 1e-7
+    o2 = Guarded(fe, stream, np.zeros(64, np.float32))
+    args2 = fe.make_args("row_softmax_v1", input=i.slice, output=o2.slice, rows=1, cols=64)
+    fe.check(lib.fe2o3_launch_and_wait(exe, kid, None, C.byref(args2), nbytes, stream._h, C.c_uint32(5000), C.byref(ks)))  # no geometry given
+    assert np.abs(o2.read() - orc.row_softmax(x)[1]).max() < 1e-7
     fe.check(lib.fe2o3_unload_executable(exe))
     props = ctx.observe_environment()
     assert props.compute_major == 10 and props.multiprocessors > 100

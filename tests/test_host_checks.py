@@ -144,3 +144,14 @@ def test_synthetic_generators_are_deterministic_and_match_the_reference_recipe(o
     x = synth.normal_bf16(4, 3, 4096, 1.0)
     assert (x == orc.bf16_from_f32(synth.normal_f32(4, 3, 4096, 1.0))).all()
     assert _lib.lib.fe2o3_bf16_from_f32(1.0) == 0x3F80
+
+
+def test_image_digest_is_sha256_of_the_library_file():
+    """load_executable(bytes, digest) compares the presented digest with the SHA-256 of the library's own
+    file, computed by the library (no CUDA call): it must agree with an independent SHA-256."""
+    import ctypes as C
+    import hashlib
+    from fe2o3_b200._lib import LIB_PATH, lib
+    out = (C.c_uint8 * 32)()
+    assert lib.fe2o3_image_digest(out) == 0
+    assert bytes(out) == hashlib.sha256(open(LIB_PATH, "rb").read()).digest()
