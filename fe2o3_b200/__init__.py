@@ -171,6 +171,56 @@ class Event:
         return ms.value
 
 
+class Operation:
+    """A submitted operation that owns its buffers until completion is established
+    (crates/fe2o3-core/src/operation.rs:272-420 OwnedDeviceOperation)."""
+
+    def __init__(self, handle, keep):
+        self._h, self._keep = handle, keep   # the host arrays of the copies must outlive the operation
+
+    @classmethod
+    def submit(cls, stream, prepared=None, buffers=(), copies_in=(), copies_out=()):
+        """copies_in / copies_out: (DeviceBuffer, host array) pairs, host -> device before the launch and
+        device -> host after it."""
+        def pack(pairs):
+            arr = (_lib.HostCopy * max(1, len(pairs)))()
+            for i, (buf, host) in enumerate(pairs):
+                arr[i].buffer, arr[i].host, arr[i].elements = buf._h, host.ctypes.data, host.size
+            return arr
+        bufs = (C.c_void_p * max(1, len(buffers)))(*[b._h for b in buffers])
+        h = C.c_void_p()
+        st = lib.fe2o3_operation_submit(stream._h, prepared._h if prepared else None, bufs, C.c_uint32(len(buffers)),
+                                        pack(copies_in), C.c_uint32(len(copies_in)), pack(copies_out),
+                                        C.c_uint32(len(copies_out)), C.byref(h))
+        op = cls(h, (copies_in, copies_out)) if h.value else None
+        if st != 0:
+            if op:   # work may be pending: establish quiescence before reporting the submission error
+                op.abandon()
+            check(st, "Operation::submit")
+        return op
+
+    def is_complete(self):
+        d = C.c_int32()
+        check(lib.fe2o3_operation_is_complete(self._h, C.byref(d)), "Operation::is_complete")
+        return bool(d.value)
+
+    def wait(self, timeout_ms=5000):
+        """Returns the kernel status word.  A deadline that passes raises Fe2o3Error(StillRunning, -18) and
+        leaves the operation submitted; any other outcome consumes it."""
+        ks = C.c_uint32()
+        st = lib.fe2o3_operation_wait(self._h, C.c_uint32(timeout_ms), C.byref(ks))
+        if st == -18:
+            check(st, "Operation::wait")
+        self._h = None
+        check(st, "Operation::wait")
+        return ks.value
+
+    def abandon(self):
+        if self._h:
+            lib.fe2o3_operation_abandon(self._h)
+            self._h = None
+
+
 class PeerRegion:
     """Device memory that the other processes of the node can map
     (crates/fe2o3-core/src/peer_access.rs:24-60 across processes)."""

@@ -89,6 +89,10 @@ class Geometry(C.Structure):
     _fields_ = [("grid", u32 * 3), ("workgroup", u32 * 3), ("dynamic_shared_bytes", u32), ("launches", u32)]
 
 
+class HostCopy(C.Structure):
+    _fields_ = [("buffer", vp), ("host", vp), ("elements", u64)]
+
+
 class KernelResources(C.Structure):
     _fields_ = [("registers_per_thread", u32), ("static_shared_bytes", u32), ("max_dynamic_shared_bytes", u32),
                 ("max_threads_per_block", u32), ("local_bytes_per_thread", u32), ("const_bytes", u32)]
@@ -139,7 +143,8 @@ EXPORTS = [
     "fe2o3_status_string", "fe2o3_last_error", "fe2o3_prepared_launch", "fe2o3_prepared_launch_and_wait",
     "fe2o3_prepared_geometry", "fe2o3_prepared_kernarg", "fe2o3_prepared_patch_kernarg", "fe2o3_prepared_symbol", "fe2o3_prepared_destroy",
     "fe2o3_ctx_take_kernel_status", "fe2o3_load_executable", "fe2o3_resolve_kernel", "fe2o3_launch_and_wait",
-    "fe2o3_image_digest", "fe2o3_observe_kernel_resources",
+    "fe2o3_image_digest", "fe2o3_observe_kernel_resources", "fe2o3_operation_submit", "fe2o3_operation_is_complete",
+    "fe2o3_operation_wait", "fe2o3_operation_abandon",
     "fe2o3_unload_executable", "fe2o3_synth_uniform_f32", "fe2o3_synth_normal_f32", "fe2o3_synth_normal_bf16",
     "fe2o3_synth_uniform_bf16", "fe2o3_synth_u32_below", "fe2o3_synth_bernoulli", "fe2o3_synth_gemm_inputs_v1",
     "fe2o3_bf16_from_f32", "fe2o3_launch_count", "fe2o3_masked_reduce_u32_noalloc",

@@ -78,6 +78,7 @@ struct fe2o3_buf {
     uint64_t elements;
     uint32_t element_bytes;
     bool quarantined;
+    uint32_t owners;   // submitted operations that own the buffer
 };
 struct fe2o3_event {
     fe2o3_ctx *ctx;
@@ -952,7 +953,7 @@ int32_t fe2o3_buf_alloc_zeroed(fe2o3_stream *stream, uint64_t elements, uint32_t
         if (e == cudaSuccess) e = cudaStreamSynchronize(stream->s);
         if (e != cudaSuccess) { cudaFree(ptr); return fe2o3_cuda_status(e, "zero-fill"); }
     }
-    fe2o3_buf *b = new (std::nothrow) fe2o3_buf{stream->ctx, ptr, elements, element_bytes, false};
+    fe2o3_buf *b = new (std::nothrow) fe2o3_buf{stream->ctx, ptr, elements, element_bytes, false, 0};
     if (!b) { cudaFree(ptr); return FE2O3_ERR_SIZE_OVERFLOW; }
     *out = b;
     return FE2O3_OK;
@@ -993,6 +994,10 @@ int32_t fe2o3_buf_quarantine(fe2o3_buf *buf) {
 }
 int32_t fe2o3_buf_free(fe2o3_buf *buf) {
     if (!buf) return FE2O3_OK;
+    if (buf->owners) {
+        fe2o3_set_error("Busy: the buffer is owned by %u submitted operation(s)", buf->owners);
+        return FE2O3_ERR_BUSY;
+    }
     int32_t st = FE2O3_OK;
     if (buf->ptr && !buf->quarantined) st = fe2o3_cuda_status(cudaFree(buf->ptr), "cudaFree");
     delete buf;
@@ -1009,6 +1014,119 @@ int32_t fe2o3_buf_slice(const fe2o3_buf *buf, uint64_t start, uint64_t len, fe2o
     }
     out->ptr = reinterpret_cast<uint64_t>(buf->ptr) + start * buf->element_bytes;
     out->len = len;
+    return FE2O3_OK;
+}
+
+// ---- owned asynchronous operations ----------------------------------------------------------
+struct fe2o3_operation {
+    fe2o3_ctx *ctx;
+    cudaStream_t stream;
+    cudaEvent_t done;
+    fe2o3_buf **buffers;
+    uint32_t n_buffers;
+    bool launched_kernel;
+};
+static void operation_release(fe2o3_operation *op, bool quarantine) {
+    for (uint32_t i = 0; i < op->n_buffers; ++i) {
+        if (op->buffers[i]->owners) op->buffers[i]->owners -= 1;
+        if (quarantine) op->buffers[i]->quarantined = true;
+    }
+    if (!quarantine) cudaEventDestroy(op->done);   // an event whose completion is unknown is leaked with its buffers
+    delete[] op->buffers;
+    delete op;
+}
+int32_t fe2o3_operation_submit(fe2o3_stream *stream, fe2o3_prepared *prepared, fe2o3_buf *const *buffers, uint32_t n_buffers,
+                               const fe2o3_host_copy *copies_in, uint32_t n_in, const fe2o3_host_copy *copies_out,
+                               uint32_t n_out, fe2o3_operation **out) {
+    if (!stream || !out || (n_buffers && !buffers) || (n_in && !copies_in) || (n_out && !copies_out))
+        return FE2O3_ERR_INVALID_ARGUMENT;
+    *out = nullptr;
+    if (prepared && prepared->ctx != stream->ctx) { fe2o3_set_error("WrongContext{role=stream}"); return FE2O3_ERR_DEVICE_MISMATCH; }
+    const uint32_t total = n_buffers + n_in + n_out;
+    fe2o3_operation *op = new (std::nothrow) fe2o3_operation{stream->ctx, stream->s, nullptr, nullptr, 0, prepared != nullptr};
+    if (!op) return FE2O3_ERR_SIZE_OVERFLOW;
+    op->buffers = new (std::nothrow) fe2o3_buf *[total ? total : 1];
+    if (!op->buffers) { delete op; return FE2O3_ERR_SIZE_OVERFLOW; }
+    auto own = [&](fe2o3_buf *b) -> bool {
+        if (!b || b->ctx != stream->ctx) return false;
+        b->owners += 1;
+        op->buffers[op->n_buffers++] = b;
+        return true;
+    };
+    bool ok = true;
+    for (uint32_t i = 0; ok && i < n_buffers; ++i) ok = own(buffers[i]);
+    for (uint32_t i = 0; ok && i < n_in; ++i) ok = own(copies_in[i].buffer) && copies_in[i].elements <= copies_in[i].buffer->elements;
+    for (uint32_t i = 0; ok && i < n_out; ++i) ok = own(copies_out[i].buffer) && copies_out[i].elements <= copies_out[i].buffer->elements;
+    cudaError_t e = cudaSuccess;
+    if (ok) e = cudaSetDevice(stream->ctx->device);
+    if (ok && e == cudaSuccess) e = cudaEventCreateWithFlags(&op->done, cudaEventDisableTiming);
+    if (!ok || e != cudaSuccess) {
+        // nothing has been submitted: hand everything back (Err before submission)
+        for (uint32_t i = 0; i < op->n_buffers; ++i) op->buffers[i]->owners -= 1;
+        delete[] op->buffers;
+        delete op;
+        if (!ok) { fe2o3_set_error("OperationDeviceMismatch or copy exceeds buffer"); return FE2O3_ERR_DEVICE_MISMATCH; }
+        return fe2o3_cuda_status(e, "operation submit");
+    }
+    // From here on work may be pending: on any error the operation is still returned so that the caller
+    // can establish quiescence through it (operation.rs:296-305), together with the error.
+    int32_t st = FE2O3_OK;
+    for (uint32_t i = 0; st == FE2O3_OK && i < n_in; ++i)
+        st = fe2o3_cuda_status(cudaMemcpyAsync(copies_in[i].buffer->ptr, copies_in[i].host,
+                                               copies_in[i].elements * copies_in[i].buffer->element_bytes, cudaMemcpyHostToDevice,
+                                               stream->s), "operation copy in");
+    if (st == FE2O3_OK && prepared) st = launch_prepared(prepared, stream->s);
+    for (uint32_t i = 0; st == FE2O3_OK && i < n_out; ++i)
+        st = fe2o3_cuda_status(cudaMemcpyAsync(copies_out[i].host, copies_out[i].buffer->ptr,
+                                               copies_out[i].elements * copies_out[i].buffer->element_bytes, cudaMemcpyDeviceToHost,
+                                               stream->s), "operation copy out");
+    cudaEventRecord(op->done, stream->s);
+    *out = op;
+    return st;
+}
+int32_t fe2o3_operation_is_complete(fe2o3_operation *op, int32_t *done) {
+    if (!op || !done) return FE2O3_ERR_INVALID_ARGUMENT;
+    cudaError_t e = cudaEventQuery(op->done);
+    if (e == cudaErrorNotReady) { *done = 0; return FE2O3_OK; }
+    *done = e == cudaSuccess ? 1 : 0;
+    return fe2o3_cuda_status(e, "cudaEventQuery");
+}
+int32_t fe2o3_operation_wait(fe2o3_operation *op, uint32_t timeout_ms, uint32_t *kernel_status) {
+    if (!op) return FE2O3_ERR_INVALID_ARGUMENT;
+    if (kernel_status) *kernel_status = 0;
+    const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms);
+    cudaError_t e;
+    for (;;) {
+        e = cudaEventQuery(op->done);
+        if (e != cudaErrorNotReady) break;
+        if (std::chrono::steady_clock::now() >= deadline) {
+            fe2o3_set_error("StillRunning: not complete after %u ms; the operation keeps its buffers", timeout_ms);
+            return FE2O3_ERR_STILL_RUNNING;
+        }
+        std::this_thread::sleep_for(std::chrono::microseconds(50));
+    }
+    if (e == cudaSuccess) {
+        int32_t st = FE2O3_OK;
+        uint32_t ks = 0;
+        if (op->launched_kernel) st = take_status(op->ctx, op->stream, &ks);
+        if (kernel_status) *kernel_status = ks;
+        operation_release(op, false);
+        if (st == FE2O3_OK && ks != 0) { fe2o3_set_error("kernel reported status word %u", ks); return FE2O3_ERR_KERNEL_STATUS; }
+        return st;
+    }
+    // the event reported an execution error: quiescence of the whole stream decides
+    const int32_t event_error = fe2o3_cuda_status(e, "operation event");
+    if (cudaStreamSynchronize(op->stream) == cudaSuccess) {
+        operation_release(op, false);
+        return event_error;
+    }
+    operation_release(op, true);
+    fe2o3_set_error("AmbiguousCompletion: neither the event nor the stream could establish completion; buffers are quarantined");
+    return FE2O3_ERR_AMBIGUOUS_COMPLETION;
+}
+int32_t fe2o3_operation_abandon(fe2o3_operation *op) {
+    if (!op) return FE2O3_OK;
+    operation_release(op, true);
     return FE2O3_OK;
 }
 
@@ -1150,6 +1268,8 @@ const char *fe2o3_status_string(int32_t s) {
         case FE2O3_ERR_NOT_SM100: return "NotSm100";
         case FE2O3_ERR_NONFINITE: return "NonFinite";
         case FE2O3_ERR_EXECUTABLE_REJECTED: return "ExecutableRejected";
+        case FE2O3_ERR_BUSY: return "Busy";
+        case FE2O3_ERR_STILL_RUNNING: return "StillRunning";
         case FE2O3_ERR_NO_DISPATCH: return "NoDispatch";
         default: return s > 0 ? "CudaError" : "Unknown";
     }

@@ -131,6 +131,42 @@ uint64_t fe2o3_buf_len(const fe2o3_buf *buf);
  * sub-slice: FE2O3_ERR_INVALID_REGION when [start, start+len) leaves the buffer. */
 int32_t fe2o3_buf_slice(const fe2o3_buf *buf, uint64_t start, uint64_t len, fe2o3_slice *out);
 
+/* ---- owned asynchronous operations -------------------------------------- */
+/* crates/fe2o3-core/src/operation.rs:272-420 OwnedDeviceOperation: a submitted
+ * operation owns every buffer it may touch until completion has been
+ * established.  In Rust the buffers move into the operation; here submit marks
+ * them as owned: fe2o3_buf_free on an owned buffer fails with FE2O3_ERR_BUSY and
+ * frees nothing.  The work is a prepared launch (optional) preceded by
+ * host-to-device copies and followed by device-to-host copies (both optional),
+ * all asynchronous on `stream`.
+ *   is_complete (operation.rs:318-324): non-blocking; errors leave it submitted.
+ *   wait (:326-360): the completion event is polled up to timeout_ms; on completion
+ *     the buffers are released, the kernel status word is read and the operation is
+ *     destroyed.  If the event reports an error the whole stream is synchronised
+ *     instead: when that succeeds the buffers are released and the event's error is
+ *     returned; when both fail, completion is unknown: every buffer is quarantined
+ *     (its free becomes a deliberate leak, crates/fe2o3-core/src/memory.rs:129-161),
+ *     the operation is destroyed and FE2O3_ERR_AMBIGUOUS_COMPLETION is returned.
+ *     When the deadline passes with the work still running the call returns
+ *     FE2O3_ERR_STILL_RUNNING and the operation STAYS submitted and owning (wait
+ *     again, or abandon); every other return value has consumed the operation.
+ *   abandon: quarantines the buffers and destroys the operation without waiting
+ *     (the Quiescent/Ambiguous policy of crates/fe2o3-completion/src/lib.rs:46-60). */
+#define FE2O3_ERR_BUSY -17          /* the buffer is owned by a submitted operation */
+#define FE2O3_ERR_STILL_RUNNING -18 /* operation wait: deadline passed, the operation stays submitted */
+typedef struct fe2o3_operation fe2o3_operation;
+typedef struct fe2o3_host_copy {
+    fe2o3_buf *buffer;  /* owned by the operation until completion */
+    void *host;         /* pinned for real overlap; must stay valid until completion */
+    uint64_t elements;
+} fe2o3_host_copy;
+int32_t fe2o3_operation_submit(fe2o3_stream *stream, fe2o3_prepared *prepared, fe2o3_buf *const *buffers,
+                               uint32_t n_buffers, const fe2o3_host_copy *copies_in, uint32_t n_in,
+                               const fe2o3_host_copy *copies_out, uint32_t n_out, fe2o3_operation **out);
+int32_t fe2o3_operation_is_complete(fe2o3_operation *op, int32_t *done);
+int32_t fe2o3_operation_wait(fe2o3_operation *op, uint32_t timeout_ms, uint32_t *kernel_status);
+int32_t fe2o3_operation_abandon(fe2o3_operation *op);
+
 /* crates/fe2o3-core/src/pinned_memory.rs */
 int32_t fe2o3_pinned_alloc(fe2o3_ctx *ctx, uint64_t bytes, void **out);
 int32_t fe2o3_pinned_free(fe2o3_ctx *ctx, void *ptr);
