@@ -77,7 +77,7 @@ enum {
     FE2O3_EP_T_DISPATCH_BEGIN = 0, FE2O3_EP_T_COUNTS_HERE = 1, FE2O3_EP_T_ROWS_SENT = 2, FE2O3_EP_T_FFN1_BEGIN = 3,
     FE2O3_EP_T_FFN1_FIRST_WAIT_DONE = 4, FE2O3_EP_T_FFN1_LAST_WAIT_DONE = 5, FE2O3_EP_T_FFN1_END = 6,
     FE2O3_EP_T_FFN2_BEGIN = 7, FE2O3_EP_T_FFN2_END = 8, FE2O3_EP_T_COMBINE_BEGIN = 9, FE2O3_EP_T_OUTPUTS_HERE = 10,
-    FE2O3_EP_T_COMBINE_END = 11
+    FE2O3_EP_T_COMBINE_END = 11, FE2O3_EP_T_OWN_ROWS_DONE = 12, FE2O3_EP_T_FFN1_TABLE_HERE = 13
 };
 
 // Capacity of the context's reduction scratch: partials followed by one counter.

@@ -147,8 +147,11 @@ __device__ __forceinline__ uint32_t cvt_bf16x2(float lo, float hi) {
     return d;
 }
 
-template <int BN>
-__global__ void __launch_bounds__(kThreads, 1)
+// REGS = 168 is what the block's 320 threads can have; REGS = 128 (still no spills) is for the GEMM that runs
+// beside the expert-parallel dispatch kernel: registers are handed out to four warps at a time, so the ten
+// warps count as twelve, and 12 x 32 x 128 leaves room for one block of that kernel on the same SM.
+template <int BN, int REGS>
+__global__ void __maxnreg__(REGS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, GemmParams p) {
     using L = SmemLayout<BN>;
@@ -194,6 +197,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             s_table_bad = 1;
             kstatus_set(p.status, FE2O3_KSTATUS_WAIT_EXPIRED);
         }
+#ifdef FE2O3_EP_TRACE
+        if (p.ep.trace_flags && p.ep.table_flag && blockIdx.x == 0) ep_trace(p.ep.trace_flags, FE2O3_EP_T_FFN1_TABLE_HERE);
+#endif
         // The segment table is device data (in the expert-parallel layer it derives from other ranks'
         // counts): it is made monotone and cut off at M here, so that no row index derived from it can
         // leave A or C, and the fault is reported instead.
@@ -640,9 +646,13 @@ int32_t gemm_tc_plan(fe2o3_ctx *ctx, GemmTcPlan *plan, uint64_t a, uint64_t b, u
 
 // Function attributes are per device: called by fe2o3_ctx_create with the context's device current.
 int32_t gemm_tc_init_device() {
-    FE2O3_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    FE2O3_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<256, 168>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     (int)SmemLayout<256>::kTotal));
-    FE2O3_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    FE2O3_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<128, 168>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    (int)SmemLayout<128>::kTotal));
+    FE2O3_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<256, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    (int)SmemLayout<256>::kTotal));
+    FE2O3_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<128, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     (int)SmemLayout<128>::kTotal));
     return FE2O3_OK;
 }
@@ -663,8 +673,13 @@ int32_t gemm_tc_launch(const GemmTcPlan *plan, cudaStream_t s) {
         cfg.attrs = attr;
         cfg.numAttrs = 1;
     }
-    cudaError_t e = plan->bn == 256 ? cudaLaunchKernelEx(&cfg, gemm_tc_kernel<256>, plan->tmA, plan->tmB, plan->tmC, plan->p)
-                                    : cudaLaunchKernelEx(&cfg, gemm_tc_kernel<128>, plan->tmA, plan->tmB, plan->tmC, plan->p);
+    cudaError_t e;
+    if (plan->overlap_previous)
+        e = plan->bn == 256 ? cudaLaunchKernelEx(&cfg, gemm_tc_kernel<256, 128>, plan->tmA, plan->tmB, plan->tmC, plan->p)
+                            : cudaLaunchKernelEx(&cfg, gemm_tc_kernel<128, 128>, plan->tmA, plan->tmB, plan->tmC, plan->p);
+    else
+        e = plan->bn == 256 ? cudaLaunchKernelEx(&cfg, gemm_tc_kernel<256, 168>, plan->tmA, plan->tmB, plan->tmC, plan->p)
+                            : cudaLaunchKernelEx(&cfg, gemm_tc_kernel<128, 168>, plan->tmA, plan->tmB, plan->tmC, plan->p);
     fe2o3_count_launch(1);
     return fe2o3_cuda_status(e, "gemm_tc");
 }
@@ -674,8 +689,8 @@ void gemm_tc_geometry(const GemmTcPlan *plan, fe2o3_geometry *geo) {
 }
 
 // kernel symbols of the runtime adapter carried by this source (the schedule a large launch resolves to)
-static Fe2o3KernelRegistration reg_tiled("tiled_gemm_lds_slice1", reinterpret_cast<const void *>(gemm_tc_kernel<256>));
-static Fe2o3KernelRegistration reg_general("tiled_gemm_general_v1", reinterpret_cast<const void *>(gemm_tc_kernel<256>));
-static Fe2o3KernelRegistration reg_ffn("moe_expert_ffn_v1", reinterpret_cast<const void *>(gemm_tc_kernel<256>));
-static Fe2o3KernelRegistration reg_gffn("moe_grouped_ffn_v1", reinterpret_cast<const void *>(gemm_tc_kernel<256>));
-static Fe2o3KernelRegistration reg_epffn("moe_ep_ffn_v1", reinterpret_cast<const void *>(gemm_tc_kernel<256>));
+static Fe2o3KernelRegistration reg_tiled("tiled_gemm_lds_slice1", reinterpret_cast<const void *>(gemm_tc_kernel<256, 168>));
+static Fe2o3KernelRegistration reg_general("tiled_gemm_general_v1", reinterpret_cast<const void *>(gemm_tc_kernel<256, 168>));
+static Fe2o3KernelRegistration reg_ffn("moe_expert_ffn_v1", reinterpret_cast<const void *>(gemm_tc_kernel<256, 168>));
+static Fe2o3KernelRegistration reg_gffn("moe_grouped_ffn_v1", reinterpret_cast<const void *>(gemm_tc_kernel<256, 168>));
+static Fe2o3KernelRegistration reg_epffn("moe_ep_ffn_v1", reinterpret_cast<const void *>(gemm_tc_kernel<256, 168>));

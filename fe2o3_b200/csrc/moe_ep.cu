@@ -159,7 +159,16 @@ moe_ep_dispatch_kernel(fe2o3_moe_ep_exchange_v1_args a, uint32_t *status) {
     const uint32_t *perm = reinterpret_cast<const uint32_t *>(a.permutation.ptr);
     const uint32_t vec_per_row = a.d_model / 8;
     const uint4 *x = reinterpret_cast<const uint4 *>(a.x.ptr);
-    const uint32_t gwarp = blockIdx.x * (kDispatchThreads / 32) + (threadIdx.x >> 5), nwarps = gridDim.x * (kDispatchThreads / 32);
+    // The first 1/W of the blocks copy this rank's own rows (memory-bound, quick, and what the GEMM beside this
+    // kernel starts on), the others send the rows of the other ranks (NVLink-bound): otherwise the own rows of the
+    // slowest warp would only be complete near the end of the kernel.
+    const uint32_t own_rows = __shfl_sync(0xffffffffu, v_hi, 0);
+    const uint32_t own_blocks = W == 1 ? gridDim.x : max(1u, gridDim.x / W);
+    const bool own_part = blockIdx.x < own_blocks;
+    const uint32_t warps_per_block = kDispatchThreads / 32;
+    const uint32_t nwarps = (own_part ? own_blocks : gridDim.x - own_blocks) * warps_per_block;
+    const uint32_t first = (own_part ? blockIdx.x : blockIdx.x - own_blocks) * warps_per_block + (threadIdx.x >> 5);
+    const uint32_t v_begin = own_part ? 0u : own_rows, v_end = own_part ? own_rows : accepted;
     uint32_t cur_j = W, cur_cnt = 0;   // rows stored for the cur_j-th destination and not yet accounted for
     auto account = [&]() {
         // every lane's stores are ordered before the counter update; whoever completes the destination's
@@ -173,11 +182,12 @@ moe_ep_dispatch_kernel(fe2o3_moe_ep_exchange_v1_args a, uint32_t *status) {
             if (done == total) {
                 __threadfence_system();
                 st_release_sys(reinterpret_cast<uint32_t *>(peer_flags[d]) + FE2O3_EP_FLAG_ROWS(W) + me, epoch);
+                if (d == me) ep_trace(my_flags, FE2O3_EP_T_OWN_ROWS_DONE);
             }
         }
         cur_cnt = 0;
     };
-    for (uint32_t v = gwarp; v < accepted; v += nwarps) {
+    for (uint32_t v = v_begin + first; v < v_end; v += nwarps) {
         // v-th row in sending order: which destination, which local slot, which expert
         const uint32_t j = __popc(__ballot_sync(0xffffffffu, lane < W && v >= v_hi));
         if (j != cur_j) {
