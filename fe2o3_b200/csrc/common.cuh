@@ -67,7 +67,10 @@ static inline uint32_t ceil_div_u32(uint64_t a, uint64_t b) { return (uint32_t)(
 #define FE2O3_EP_COUNTER_COMBINE(W) (3u * (W) + 2u)
 #define FE2O3_EP_FLAG_TABLE(W) (3u * (W) + 3u)
 #define FE2O3_EP_ROWS_DONE(W, parity) (3u * (W) + 4u + (parity) * (W))
-#define FE2O3_EP_FLAG_WORDS(W) (5u * (W) + 4u)
+//   5W+4, 5W+5  blocks of the dispatch kernel that have stored their share of this rank's own rows (two
+//   alternating counters like the row counters)
+#define FE2O3_EP_OWN_BLOCKS(W, parity) (5u * (W) + 4u + (parity))
+#define FE2O3_EP_FLAG_WORDS(W) (5u * (W) + 6u)
 #define FE2O3_EP_DEFAULT_SPIN (1u << 24)
 // Diagnostic build (-DFE2O3_EP_TRACE): the kernels of the expert-parallel layer stamp the global
 // nanosecond timer into 64-bit slots at byte 2048 of the rank's flag block (which must then be at

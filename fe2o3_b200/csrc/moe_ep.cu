@@ -42,8 +42,12 @@ namespace {
 constexpr uint32_t kDrop = 0xffffffffu;
 constexpr int kThreads = 256;
 // The dispatch kernel shares every SM with one block of the GEMM that follows it (320 threads x 168 registers,
-// nearly all of the shared memory): 192 threads x 56 registers fit the register file beside it.
+// nearly all of the shared memory): 192 threads x 64 registers fit the register file beside it (registers go out to four warps at a time: 8 x 32 x 64 beside the 12 x 32 x 128 of the GEMM).
 constexpr int kDispatchThreads = 192;
+#ifndef FE2O3_DISPATCH_INFLIGHT
+#define FE2O3_DISPATCH_INFLIGHT 4
+#endif
+constexpr int kInFlight = FE2O3_DISPATCH_INFLIGHT;   // 16-byte loads a lane issues before the matching stores
 
 // the pass number: from the device counter when one is given, else the scalar in the argument block
 __device__ __forceinline__ uint32_t current_epoch(const fe2o3_moe_ep_exchange_v1_args &a) {
@@ -57,7 +61,7 @@ __device__ __forceinline__ uint32_t current_epoch(const fe2o3_moe_ep_exchange_v1
 // then ranks me-1, me-2, ... so that every rank receives from me+1 first, then me+2, ... which is the order
 // in which its GEMM takes the tiles; "rows complete" is raised per destination as soon as the last row for
 // it has been stored.
-__global__ void __launch_bounds__(kDispatchThreads, 6)
+__global__ void __launch_bounds__(kDispatchThreads, 5)
 moe_ep_dispatch_kernel(fe2o3_moe_ep_exchange_v1_args a, uint32_t *status) {
     launch_dependents();
     const uint32_t E = a.experts, W = a.world, me = a.rank, per = E / W;
@@ -87,6 +91,7 @@ moe_ep_dispatch_kernel(fe2o3_moe_ep_exchange_v1_args a, uint32_t *status) {
             st_release_sys(reinterpret_cast<uint32_t *>(peer_flags[p]) + FE2O3_EP_FLAG_COUNTS(W) + me, epoch);
         // the per-destination row counters of the NEXT pass (nobody touches that set during this one)
         for (uint32_t p = threadIdx.x; p < W; p += kDispatchThreads) my_flags[FE2O3_EP_ROWS_DONE(W, (epoch & 1u) ^ 1u) + p] = 0u;
+        if (threadIdx.x == 0) my_flags[FE2O3_EP_OWN_BLOCKS(W, (epoch & 1u) ^ 1u)] = 0u;
     }
     if (a.logits.len && !dead) {
         // Route weights of this rank's tokens, one token per thread of the grid, computed while the counts
@@ -155,20 +160,12 @@ moe_ep_dispatch_kernel(fe2o3_moe_ep_exchange_v1_args a, uint32_t *status) {
     if (blockIdx.x == 0 && threadIdx.x < W && v_hi == v_lo)   // nothing to send there: complete at once
         st_release_sys(reinterpret_cast<uint32_t *>(peer_flags[(me + W - threadIdx.x) % W]) + FE2O3_EP_FLAG_ROWS(W) + me, epoch);
 
-    // rows: one warp per accepted local slot, four 16-byte loads in flight per lane before the peer stores
+    // rows: one warp per accepted local slot, kInFlight 16-byte loads in flight per lane before the peer stores
     const uint32_t *perm = reinterpret_cast<const uint32_t *>(a.permutation.ptr);
     const uint32_t vec_per_row = a.d_model / 8;
     const uint4 *x = reinterpret_cast<const uint4 *>(a.x.ptr);
-    // The first 1/W of the blocks copy this rank's own rows (memory-bound, quick, and what the GEMM beside this
-    // kernel starts on), the others send the rows of the other ranks (NVLink-bound): otherwise the own rows of the
-    // slowest warp would only be complete near the end of the kernel.
     const uint32_t own_rows = __shfl_sync(0xffffffffu, v_hi, 0);
-    const uint32_t own_blocks = W == 1 ? gridDim.x : max(1u, gridDim.x / W);
-    const bool own_part = blockIdx.x < own_blocks;
-    const uint32_t warps_per_block = kDispatchThreads / 32;
-    const uint32_t nwarps = (own_part ? own_blocks : gridDim.x - own_blocks) * warps_per_block;
-    const uint32_t first = (own_part ? blockIdx.x : blockIdx.x - own_blocks) * warps_per_block + (threadIdx.x >> 5);
-    const uint32_t v_begin = own_part ? 0u : own_rows, v_end = own_part ? own_rows : accepted;
+    const uint32_t gwarp = blockIdx.x * (kDispatchThreads / 32) + (threadIdx.x >> 5), nwarps = gridDim.x * (kDispatchThreads / 32);
     uint32_t cur_j = W, cur_cnt = 0;   // rows stored for the cur_j-th destination and not yet accounted for
     auto account = [&]() {
         // every lane's stores are ordered before the counter update; whoever completes the destination's
@@ -187,7 +184,7 @@ moe_ep_dispatch_kernel(fe2o3_moe_ep_exchange_v1_args a, uint32_t *status) {
         }
         cur_cnt = 0;
     };
-    for (uint32_t v = v_begin + first; v < v_end; v += nwarps) {
+    auto send_row = [&](uint32_t v) {
         // v-th row in sending order: which destination, which local slot, which expert
         const uint32_t j = __popc(__ballot_sync(0xffffffffu, lane < W && v >= v_hi));
         if (j != cur_j) {
@@ -202,21 +199,40 @@ moe_ep_dispatch_kernel(fe2o3_moe_ep_exchange_v1_args a, uint32_t *status) {
         const uint32_t dst_row = __shfl_sync(0xffffffffu, base, e & 31) + (slot - __shfl_sync(0xffffffffu, off_lo, e & 31));
         if (e >= E || route == kDrop || (route >> 1) >= a.tokens || dst_row >= a.max_rows) {
             if (lane == 0) kstatus_set(status, FE2O3_KSTATUS_SLOT_RANGE);
-            continue;
+            return;
         }
         if (lane == 0) reinterpret_cast<uint2 *>(peer_meta[dst_rank])[dst_row] = make_uint2(route, me);
         const uint4 *src = x + (uint64_t)(route >> 1) * vec_per_row;
         uint4 *dst = reinterpret_cast<uint4 *>(peer_recv[dst_rank]) + (uint64_t)dst_row * vec_per_row;
-        for (uint32_t i0 = lane; i0 < vec_per_row; i0 += 32 * 4) {
-            uint4 q[4];
+        for (uint32_t i0 = lane; i0 < vec_per_row; i0 += 32 * kInFlight) {
+            uint4 q[kInFlight];
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
+            for (int u = 0; u < kInFlight; ++u)
                 if (i0 + 32 * u < vec_per_row) q[u] = __ldg(src + i0 + 32 * u);
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
+            for (int u = 0; u < kInFlight; ++u)
                 if (i0 + 32 * u < vec_per_row) dst[i0 + 32 * u] = q[u];
         }
+        };
+    // Phase 1: this rank's own rows, by all blocks.  They are what the GEMM beside this kernel starts on, and
+    // they copy at memory speed as long as nothing else is in the way: rows to other ranks leave at NVLink
+    // speed and hold up everything behind them in the memory system, so no block starts on those before every
+    // block is through with its own rows (all blocks of this grid are resident at once, one per SM).
+    for (uint32_t v = gwarp; v < own_rows; v += nwarps) send_row(v);
+    if (cur_cnt) account();
+    if (W > 1) {
+        uint32_t *own_blocks = my_flags + FE2O3_EP_OWN_BLOCKS(W, epoch & 1u);
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            atomicAdd(own_blocks, 1u);
+            uint32_t spins = 0;
+            while (*reinterpret_cast<volatile uint32_t *>(own_blocks) < gridDim.x && ++spins < limit) __nanosleep(64);
+            // a wait that runs out only costs the ordering: the rows below are still sent
+        }
+        __syncthreads();
     }
+    // Phase 2: the other ranks' rows, in sending order
+    for (uint32_t v = own_rows + gwarp; v < accepted; v += nwarps) send_row(v);
     if (cur_cnt) account();
     if (blockIdx.x == 0 && threadIdx.x == 0) ep_trace(my_flags, FE2O3_EP_T_ROWS_SENT);
 }

@@ -132,7 +132,7 @@ class MoeTop2Layer:
                             for ph in range(2)]
             self.k_ffn = P("moe_ep_ffn_v1", recv_x=(self._ptrs["recv_x"][me], self.max_rows * d), w1=self.w1, w2=self.w2,
                            hidden=self.hidden, recv_meta=(self._ptrs["recv_meta"][me], 2 * self.max_rows),
-                           flags=(self._ptrs["flags"][me], 5 * world + 4), d_ff=f, **common)
+                           flags=(self._ptrs["flags"][me], 5 * world + 6), d_ff=f, **common)
             self.launches_per_step = 7
             return
         self.compact_x = z(R * d, torch.bfloat16)            # local routes, expert-major

@@ -334,7 +334,7 @@ typedef struct fe2o3_moe_grouped_ffn_v1_args {
  *   recv_meta [max_rows] {u32 route id, u32 home rank}   where each row came from
  *   ret       [2*tokens][d_model] f32    expert outputs by route id, on the home rank
  *   counts    [world][experts] u32       admitted routes per (source rank, expert)
- *   flags     [5*world + 4] u32, zero before the first pass
+ *   flags     [5*world + 6] u32, zero before the first pass
  * Rows on the owner of expert e are ordered local-expert-major, source-rank-minor,
  * so each expert's rows are one contiguous segment; pair_offsets[le*world + s]
  * is the first row of (local expert le, source s), pair_offsets[experts] the
