@@ -1434,7 +1434,7 @@ int32_t fe2o3_moe_ep_ffn_v1_prepare(fe2o3_ctx *ctx, const fe2o3_moe_ep_ffn_v1_ar
     in.rows_flags = flags + FE2O3_EP_FLAG_ROWS(W);
     in.table_flag = flags + FE2O3_EP_FLAG_TABLE(W);
     st = gemm_tc_plan(ctx, &p->gemm[0], a->recv_x.ptr, a->w1.ptr, a->hidden.ptr, a->max_rows, a->d_ff, a->d_model,
-                      a->d_model, a->d_ff, a->d_ff, 1.f, 0.f, EPI_GELU_BF16, in.pair_offsets, per, 0, per, &in);
+                      a->d_model, a->d_ff, a->d_ff, 1.f, 0.f, EPI_GELU_BF16, in.pair_offsets, per, 0, per, &in, 2u * a->tokens);
     // second GEMM: every output row goes to its home rank's return buffer; the last CTA raises "outputs ready"
     GemmEp outp = ep;
     outp.row_meta = reinterpret_cast<const uint2 *>(a->recv_meta.ptr);
@@ -1444,7 +1444,7 @@ int32_t fe2o3_moe_ep_ffn_v1_prepare(fe2o3_ctx *ctx, const fe2o3_moe_ep_ffn_v1_ar
     outp.done_counter = flags + FE2O3_EP_COUNTER_FFN(W);
     if (st == FE2O3_OK)
         st = gemm_tc_plan(ctx, &p->gemm[1], a->hidden.ptr, a->w2.ptr, 0, a->max_rows, a->d_model, a->d_ff, a->d_ff,
-                          a->d_model, a->d_model, 1.f, 0.f, EPI_SCATTER_PEER, outp.pair_offsets, per, 0, per, &outp);
+                          a->d_model, a->d_model, 1.f, 0.f, EPI_SCATTER_PEER, outp.pair_offsets, per, 0, per, &outp, 2u * a->tokens);
     if (st != FE2O3_OK) return fail_prepare(out, st);
     p->gemm[0].overlap_previous = 1;   // may start beside the dispatch kernel launched just before it
     gemm_tc_geometry(&p->gemm[0], &p->geo);

@@ -605,8 +605,13 @@ bool gemm_tc_supported(uint64_t a, uint64_t b, uint32_t lda, uint32_t ldb, uint3
 int32_t gemm_tc_plan(fe2o3_ctx *ctx, GemmTcPlan *plan, uint64_t a, uint64_t b, uint64_t c, uint32_t M, uint32_t N,
                      uint32_t K, uint32_t lda, uint32_t ldb, uint32_t ldc, float alpha, float beta, uint32_t epilogue,
                      const uint32_t *expert_offsets, uint32_t experts, uint32_t expert_mod, uint32_t b_matrices,
-                     const GemmEp *ep) {
+                     const GemmEp *ep, uint32_t expected_rows) {
+    // 256-wide tiles whenever N allows.  Half-width tiles would fill the last round of SMs better when a rank
+    // has few row tiles (512 tiles on 148 SMs are 4 rounds, 1024 half tiles 7 half rounds), but they re-read A
+    // twice as often and were measured slower, not faster, on 4096 and 8192 rows (passes of 530 against 481 us
+    // and 686 against 590 us).
     plan->bn = (N > 128) ? 256 : 128;
+    (void)expected_rows;
     uint64_t dA[2] = {K, M}, sA[1] = {(uint64_t)lda * 2};
     uint32_t bA[2] = {BK, BM};
     int32_t st = fe2o3_make_tmap_bf16(&plan->tmA, a, 2, dA, sA, bA);

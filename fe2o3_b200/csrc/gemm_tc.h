@@ -59,7 +59,7 @@ bool gemm_tc_supported(uint64_t a, uint64_t b, uint32_t lda, uint32_t ldb, uint3
 int32_t gemm_tc_plan(fe2o3_ctx *ctx, GemmTcPlan *plan, uint64_t a, uint64_t b, uint64_t c, uint32_t M, uint32_t N,
                      uint32_t K, uint32_t lda, uint32_t ldb, uint32_t ldc, float alpha, float beta, uint32_t epilogue,
                      const uint32_t *expert_offsets, uint32_t experts, uint32_t expert_mod = 0, uint32_t b_matrices = 0,
-                     const GemmEp *ep = nullptr);
+                     const GemmEp *ep = nullptr, uint32_t expected_rows = 0);
 int32_t gemm_tc_launch(const GemmTcPlan *plan, cudaStream_t s);
 int32_t gemm_tc_init_device();
 void gemm_tc_geometry(const GemmTcPlan *plan, fe2o3_geometry *geo);
