@@ -62,7 +62,7 @@ MoeEpExchangeArgs = _struct("MoeEpExchangeArgs",
                              ("epoch", u32), ("max_rows", u32), ("phase", u32), ("spin_limit", u32), ("reserved", u32)])
 MoeEpFfnArgs = _struct("MoeEpFfnArgs",
                        ["recv_x", "w1", "w2", "pair_offsets", "hidden", "recv_meta", "flags", "peer_ret", "peer_flags",
-                        "epoch_counter"],
+                        "epoch_counter", "progress"],
                        [("tokens", u32), ("d_model", u32), ("d_ff", u32), ("experts", u32), ("world", u32), ("rank", u32),
                         ("epoch", u32), ("max_rows", u32), ("spin_limit", u32), ("reserved", u32)])
 MaskedReduceArgs = _struct("MaskedReduceArgs", ["values", "active", "output"])
@@ -119,7 +119,7 @@ OPS = {
     "moe_compact_v1": (MoeCompactArgs, 56, False),
     "moe_grouped_ffn_v1": (MoeGroupedFfnArgs, 112, False),
     "moe_ep_exchange_v1": (MoeEpExchangeArgs, 296, False),
-    "moe_ep_ffn_v1": (MoeEpFfnArgs, 200, False),
+    "moe_ep_ffn_v1": (MoeEpFfnArgs, 216, False),
     "masked_reduce_u32": (MaskedReduceArgs, 48, False),
     "masked_reduce_u32_packed": (MaskedReducePackedArgs, 48, False),
     "device_scan_u32": (DeviceScanArgs, 40, False),

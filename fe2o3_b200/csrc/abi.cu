@@ -520,9 +520,11 @@ int regions_for(uint32_t op, const void *args, Region *r, int32_t *status) {
             r[6] = RGN("PeerFlags", a->peer_flags, a->world, 8, false);
             r[7] = RGN("Hidden", a->hidden, (uint64_t)a->max_rows * a->d_ff, 2, true);
             r[8] = RGN("Flags", a->flags, FE2O3_EP_FLAG_WORDS((uint64_t)a->world), 4, true);
-            if (a->epoch_counter.ptr == 0 && a->epoch_counter.len == 0) return 9;
-            r[9] = RGN("EpochCounter", a->epoch_counter, 1, 4, false);
-            return 10;
+            int n = 9;
+            if (a->epoch_counter.ptr != 0 || a->epoch_counter.len != 0) r[n++] = RGN("EpochCounter", a->epoch_counter, 1, 4, false);
+            if (a->progress.ptr != 0 || a->progress.len != 0)
+                r[n++] = RGN("Progress", a->progress, 2 * ((uint64_t)a->max_rows / 128 + per + 1), 4, true);
+            return n;
         }
         case OP_MOE_COMBINE: {
             const fe2o3_moe_expert_combine_v1_args *a = static_cast<const fe2o3_moe_expert_combine_v1_args *>(args);
@@ -1429,8 +1431,15 @@ int32_t fe2o3_moe_ep_ffn_v1_prepare(fe2o3_ctx *ctx, const fe2o3_moe_ep_ffn_v1_ar
     ep.epoch = a->epoch;
     ep.spin_limit = a->spin_limit ? a->spin_limit : FE2O3_EP_DEFAULT_SPIN;
     ep.trace_flags = flags;
+    const bool handover = a->progress.len != 0;
+    uint32_t *progress = reinterpret_cast<uint32_t *>(a->progress.ptr);
     // first GEMM: waits per source for "rows complete"; GELU + bf16 hidden rows
     GemmEp in = ep;
+    if (handover) {
+        in.progress = progress;
+        in.progress_mode = 1;
+        in.progress_len = (uint32_t)(a->progress.len / 2);
+    }
     in.rows_flags = flags + FE2O3_EP_FLAG_ROWS(W);
     in.table_flag = flags + FE2O3_EP_FLAG_TABLE(W);
     st = gemm_tc_plan(ctx, &p->gemm[0], a->recv_x.ptr, a->w1.ptr, a->hidden.ptr, a->max_rows, a->d_ff, a->d_model,
@@ -1442,11 +1451,19 @@ int32_t fe2o3_moe_ep_ffn_v1_prepare(fe2o3_ctx *ctx, const fe2o3_moe_ep_ffn_v1_ar
     outp.ret_rows = 2u * a->tokens;
     outp.peer_flags = reinterpret_cast<const uint64_t *>(a->peer_flags.ptr);
     outp.done_counter = flags + FE2O3_EP_COUNTER_FFN(W);
+    if (handover) {
+        outp.progress = progress;
+        outp.progress_mode = 2;
+        outp.table_flag = flags + FE2O3_EP_FLAG_TABLE(W);   // started early, it may run ahead of the dispatch kernel too
+        outp.progress_len = (uint32_t)(a->progress.len / 2);
+        outp.progress_target = ((a->d_ff + 255u) / 256u) * 8u;   // tiles across d_ff x epilogue warps of the first GEMM
+    }
     if (st == FE2O3_OK)
         st = gemm_tc_plan(ctx, &p->gemm[1], a->hidden.ptr, a->w2.ptr, 0, a->max_rows, a->d_model, a->d_ff, a->d_ff,
                           a->d_model, a->d_model, 1.f, 0.f, EPI_SCATTER_PEER, outp.pair_offsets, per, 0, per, &outp, 2u * a->tokens);
     if (st != FE2O3_OK) return fail_prepare(out, st);
     p->gemm[0].overlap_previous = 1;   // may start beside the dispatch kernel launched just before it
+    p->gemm[1].overlap_previous = handover ? 1 : 0;   // may take over SMs as the first GEMM leaves them
     gemm_tc_geometry(&p->gemm[0], &p->geo);
     p->geo.launches = 2;
     return FE2O3_OK;

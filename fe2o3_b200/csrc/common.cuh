@@ -271,6 +271,8 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap *m, const void *s
                  : "memory");
 }
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Waits until the committed bulk stores of this thread are complete (their writes performed).
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // Waits until the committed bulk stores of this thread have finished READING shared memory.
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *m, uint64_t *bar, int32_t x, int32_t y) {

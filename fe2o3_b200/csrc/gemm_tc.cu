@@ -46,6 +46,7 @@ struct SmemLayout {
 
 struct TileCoord {
     uint32_t m0, n0, m_end, expert;
+    uint32_t mt_index;   // running index of the 128-row tile over all groups (expert-parallel hand-over counters)
     bool valid;
 };
 
@@ -59,7 +60,7 @@ __device__ __forceinline__ TileCoord decode_tile(uint32_t id, const GemmParams &
     TileCoord t;
     t.valid = false;
     t.expert = 0;
-    t.m0 = t.n0 = t.m_end = 0;
+    t.m0 = t.n0 = t.m_end = t.mt_index = 0;
     if (p.experts == 0) {
         const uint32_t m_tiles = (p.M + BM - 1) / BM;
         if (id >= m_tiles * n_tiles) return t;
@@ -73,7 +74,7 @@ __device__ __forceinline__ TileCoord decode_tile(uint32_t id, const GemmParams &
         t.valid = true;
         return t;
     }
-    if (p.ep.rows_flags) {
+    if (p.ep.rows_flags || p.ep.progress_mode) {
         // groups = (rotation step j, local expert le): the tiles whose first row belongs to source (rank + j) mod W
         const uint32_t W = p.ep.world;
         uint32_t base = 0;
@@ -85,10 +86,13 @@ __device__ __forceinline__ TileCoord decode_tile(uint32_t id, const GemmParams &
             const uint32_t cnt = hi > lo ? (i1 - i0) * n_tiles : 0u;
             if (id < base + cnt) {
                 const uint32_t local = id - base;
-                t.m0 = seg + (i0 + local / n_tiles) * BM;
+                const uint32_t mi = i0 + local / n_tiles;
+                t.m0 = seg + mi * BM;
                 t.n0 = local % n_tiles;
                 t.m_end = s_off[le + 1];
                 t.expert = le;
+                t.mt_index = mi;
+                for (uint32_t l2 = 0; l2 < le; ++l2) t.mt_index += (s_off[l2 + 1] - s_off[l2] + BM - 1) / BM;
                 t.valid = true;
                 break;
             }
@@ -120,6 +124,7 @@ __device__ __forceinline__ TileCoord decode_tile(uint32_t id, const GemmParams &
     t.n0 = __shfl_sync(0xffffffffu, t.n0, 0);
     t.m_end = __shfl_sync(0xffffffffu, t.m_end, 0);
     t.expert = __shfl_sync(0xffffffffu, t.expert, 0);
+    t.mt_index = __shfl_sync(0xffffffffu, t.mt_index, 0);
     t.valid = __shfl_sync(0xffffffffu, (uint32_t)t.valid, 0) != 0;
     return t;
 }
@@ -171,6 +176,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t n_tiles = (p.N + BN - 1) / BN;
     const uint32_t num_kb = (p.K + BK - 1) / BK;
+    // the second GEMM of the expert FFN may take over each SM as this kernel's CTA leaves it
+    if (p.ep.progress_mode == 1) launch_dependents();
 
     if (threadIdx.x == 0) {
         // Expert-parallel passes chain kernels through flags on other ranks: once a kernel of the pass has
@@ -189,6 +196,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     __shared__ int s_table_bad;
     const uint32_t ep_epoch = p.ep.epoch_counter ? __ldcg(p.ep.epoch_counter) + 1u : p.ep.epoch;
+    // hand-over counters: two sets used by alternate passes; this pass's set was cleared during the previous one
+    uint32_t *const progress = p.ep.progress ? p.ep.progress + (ep_epoch & 1u) * p.ep.progress_len : nullptr;
     if (p.experts && threadIdx.x == 64) {
         // The dispatch kernel that writes the table may still be running beside this kernel: wait for its
         // "table written" flag before reading (bounded like every wait).
@@ -198,7 +207,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             kstatus_set(p.status, FE2O3_KSTATUS_WAIT_EXPIRED);
         }
 #ifdef FE2O3_EP_TRACE
-        if (p.ep.trace_flags && p.ep.table_flag && blockIdx.x == 0) ep_trace(p.ep.trace_flags, FE2O3_EP_T_FFN1_TABLE_HERE);
+        if (p.ep.trace_flags && p.ep.table_flag && p.ep.progress_mode != 2 && blockIdx.x == 0) ep_trace(p.ep.trace_flags, FE2O3_EP_T_FFN1_TABLE_HERE);
 #endif
         // The segment table is device data (in the expert-parallel layer it derives from other ranks'
         // counts): it is made monotone and cut off at M here, so that no row index derived from it can
@@ -277,6 +286,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     if (seen == (1u << p.ep.world) - 1u) ep_trace(p.ep.trace_flags, FE2O3_EP_T_FFN1_LAST_WAIT_DONE);
                 }
 #endif
+            }
+            if (p.ep.progress_mode == 2) {
+                // The rows of this tile are the first GEMM's output, stored by the copy engine (asynchronous
+                // proxy) and announced through a counter: acquire the count, then order it before the bulk
+                // tensor loads below.
+                if (t.mt_index >= p.ep.progress_len ||
+                    !__all_sync(0xffffffffu, flag_wait(progress + t.mt_index, p.ep.progress_target, p.ep.spin_limit))) {
+                    ok = false;
+                    break;
+                }
+                fence_proxy_async_global();
             }
             for (uint32_t kb = 0; kb < num_kb; ++kb, ++loaded) {
                 if (!mbar_wait_warp(&empty[stage], phase ^ 1, &s_abort)) { ok = false; break; }
@@ -502,6 +522,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     }
                 }
             }
+            if (p.ep.progress_mode == 1) {
+                // this warp's part of the hidden rows of the tile is in memory: bulk stores complete (not merely
+                // read out of shared memory), direct stores fenced; then one count per warp
+                if (store_pending) {
+                    if (lane == 0) tma_store_wait_all();
+                    store_pending = false;
+                }
+                __threadfence();
+                __syncwarp();
+                fence_proxy_async_global();
+                if (lane == 0 && t.mt_index < p.ep.progress_len) atomicAdd(progress + t.mt_index, 1u);
+            }
         }
         // the staging slice must stay intact until the last copy has read it
         if (store_pending && lane == 0) tma_store_wait_read();
@@ -529,6 +561,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const uint32_t old = atomicAdd(p.ep.done_counter, failed ? 0x10001u : 1u);
         if ((old & 0xffffu) == gridDim.x - 1) {
             atomicExch(p.ep.done_counter, 0u);
+            if (p.ep.progress_mode == 2)   // the other set of hand-over counters, for the next pass (nobody uses it during this one)
+                for (uint32_t i = 0; i < p.ep.progress_len; ++i) p.ep.progress[((ep_epoch & 1u) ^ 1u) * p.ep.progress_len + i] = 0u;
             if (!failed && (old >> 16) == 0) {
                 __threadfence_system();
                 for (uint32_t w = 0; w < p.ep.world; ++w)

@@ -24,6 +24,14 @@ struct GemmEp {
     const uint64_t *peer_flags;     // [world] base address of every rank's flag block
     uint32_t *done_counter;         // this rank's arrival counter of the kernel's CTAs
     uint32_t *trace_flags;          // this rank's flag block (diagnostic time stamps, FE2O3_EP_TRACE builds only)
+    // Row-tile hand-over between the two GEMMs of the expert FFN, so that the second can start on the SMs the
+    // first one leaves idle in its last round: one counter per 128-row tile of the hidden activations.
+    //   mode 1 (producer, first GEMM): every epilogue warp adds one when its part of a tile is in memory;
+    //   mode 2 (consumer, second GEMM): the TMA producer waits until a row tile's counter has reached
+    //   progress_target (tiles across d_ff x epilogue warps) before its first load of those rows, takes the
+    //   tiles in the first GEMM's order, and the last CTA of the grid clears the counters for the next pass.
+    uint32_t *progress;
+    uint32_t progress_mode, progress_target, progress_len;
 };
 
 struct GemmParams {

@@ -65,8 +65,11 @@ def pair_plan(counts, rank, world):
 
 class MoeTop2Layer:
     def __init__(self, ctx, stream, tokens, d_model, d_ff, experts, rank=0, world=1, capacity=None, exchange="auto",
-                 spin_limit=0, peer_ptrs=None):
-        """`peer_ptrs` (optional, peer exchange only): {"recv_x" | "recv_meta" | "ret" | "counts" | "flags":
+                 spin_limit=0, peer_ptrs=None, io_sets=1):
+        """`io_sets`: how many (input, output) buffer pairs the layer owns (`x_bufs[i]`, `out_bufs[i]`); a pass
+        names the pair it reads and writes (`forward(io=i)`), so a host can fill the next pass's input and
+        drain the previous pass's output on copy streams while this one computes.
+        `peer_ptrs` (optional, peer exchange only): {"recv_x" | "recv_meta" | "ret" | "counts" | "flags":
         [address of rank p's buffer for p in range(world)]} when the caller has mapped the buffers itself
         (sizes: `region_sizes`); by default the layer allocates and maps them."""
         import torch
@@ -86,9 +89,11 @@ class MoeTop2Layer:
         # tokens in and combined output out are library-owned buffers (the host copies of an end-to-end step
         # go through fe2o3_buf_copy_*_async); the torch tensors are views of the same memory
         from . import DeviceBuffer
-        self.x_buf = DeviceBuffer.zeroed(stream, T * d, np.uint16)
-        self.out_buf = DeviceBuffer.zeroed(stream, T * d, np.float32)
-        self.x = torch.as_tensor(self.x_buf, device=dev).view(torch.bfloat16)
+        self.x_bufs = [DeviceBuffer.zeroed(stream, T * d, np.uint16) for _ in range(io_sets)]
+        self.out_bufs = [DeviceBuffer.zeroed(stream, T * d, np.float32) for _ in range(io_sets)]
+        self.xs = [torch.as_tensor(b, device=dev).view(torch.bfloat16) for b in self.x_bufs]
+        self.outs = [torch.as_tensor(b, device=dev) for b in self.out_bufs]
+        self.x_buf, self.out_buf, self.x, self.out = self.x_bufs[0], self.out_bufs[0], self.xs[0], self.outs[0]
         self.wg = z(d * E, torch.bfloat16)
         self.w1 = z(self.per * d * f, torch.bfloat16)   # this rank's experts only
         self.w2 = z(self.per * f * d, torch.bfloat16)
@@ -97,7 +102,6 @@ class MoeTop2Layer:
         self.requested, self.admitted = z(E, torch.int32), z(E, torch.int32)
         self.offsets = z(E + 1, torch.int32)
         self.weights = z(R, torch.float32)
-        self.out = torch.as_tensor(self.out_buf, device=dev)
         # rows this rank may have to process: every admitted route of every rank in the worst case
         self.max_rows = min(R, E * self.capacity) * world
         if self.exchange in ("auto", "peer"):
@@ -109,7 +113,10 @@ class MoeTop2Layer:
                     raise
                 self.exchange, self.exchange_fallback_reason = "nccl", f"{type(err).__name__}: {err}"
         P = lambda op, **kw: prepare(ctx, op, **kw)
-        self.k_gate = P("moe_gate_v1", x=self.x, wg=self.wg, logits=self.logits, tokens=T, d_model=d, experts=E)
+        # kernels that read the tokens or write the output exist once per buffer pair
+        self.k_gates = [P("moe_gate_v1", x=x, wg=self.wg, logits=self.logits, tokens=T, d_model=d, experts=E)
+                        for x in self.xs]
+        self.k_gate = self.k_gates[0]
         self.k_top2 = P("moe_top2_v1", logits=self.logits, top2_experts=self.top2, requested_counts=self.requested,
                         admitted_counts=self.admitted, expert_offsets=self.offsets, route_slots=self.slots,
                         permutation=self.perm, inverse=self.inverse, tokens=T, experts=E, capacity=self.capacity)
@@ -120,19 +127,21 @@ class MoeTop2Layer:
             self.hidden = z(self.max_rows * f, torch.bfloat16)
             self.pair_offsets = z(E + 1, torch.int32)
             self.epoch_counter = z(1, torch.int32)  # pass number, advanced on the device: passes replay from a graph
+            self.progress = z(2 * (self.max_rows // 128 + self.per + 1), torch.int32)   # row-tile hand-over between the FFN GEMMs
             me = rank
             common = dict(pair_offsets=self.pair_offsets, peer_ret=self.peer_ret, peer_flags=self.peer_flags,
                           epoch_counter=self.epoch_counter, tokens=T, d_model=d, experts=E, world=world, rank=rank,
                           epoch=0, max_rows=self.max_rows, spin_limit=spin_limit)
-            self.k_phase = [P("moe_ep_exchange_v1", x=self.x, top2_experts=self.top2, permutation=self.perm,
-                              inverse=self.inverse, expert_offsets=self.offsets, admitted_counts=self.admitted,
-                              route_weights=self.weights, combined_output=self.out, peer_recv_x=self.peer_recv_x,
-                              peer_recv_meta=self.peer_recv_meta, peer_counts=self.peer_counts, phase=ph,
-                              logits=self.logits if ph == 0 else None, **common)   # dispatch also writes the route weights
-                            for ph in range(2)]
+            self.k_phases = [[P("moe_ep_exchange_v1", x=x, top2_experts=self.top2, permutation=self.perm,
+                                inverse=self.inverse, expert_offsets=self.offsets, admitted_counts=self.admitted,
+                                route_weights=self.weights, combined_output=out, peer_recv_x=self.peer_recv_x,
+                                peer_recv_meta=self.peer_recv_meta, peer_counts=self.peer_counts, phase=ph,
+                                logits=self.logits if ph == 0 else None, **common)   # dispatch also writes the route weights
+                              for ph in range(2)] for x, out in zip(self.xs, self.outs)]
+            self.k_phase = self.k_phases[0]
             self.k_ffn = P("moe_ep_ffn_v1", recv_x=(self._ptrs["recv_x"][me], self.max_rows * d), w1=self.w1, w2=self.w2,
                            hidden=self.hidden, recv_meta=(self._ptrs["recv_meta"][me], 2 * self.max_rows),
-                           flags=(self._ptrs["flags"][me], 5 * world + 6), d_ff=f, **common)
+                           flags=(self._ptrs["flags"][me], 5 * world + 6), progress=self.progress, d_ff=f, **common)
             self.launches_per_step = 7
             return
         self.compact_x = z(R * d, torch.bfloat16)            # local routes, expert-major
@@ -150,17 +159,19 @@ class MoeTop2Layer:
         self.hidden = z(rows * f, torch.bfloat16)
         self.rows = rows
         if world == 1:
-            self.k_ffn = P("moe_expert_ffn_v1", x=self.x, w1=self.w1, w2=self.w2, permutation=self.perm,
-                           expert_offsets=self.offsets, compact_x=self.compact_x, hidden=self.hidden,
-                           compact_output=self.compact_out, tokens=T, d_model=d, d_ff=f, experts=E)
+            self.k_ffns = [P("moe_expert_ffn_v1", x=x, w1=self.w1, w2=self.w2, permutation=self.perm,
+                             expert_offsets=self.offsets, compact_x=self.compact_x, hidden=self.hidden,
+                             compact_output=self.compact_out, tokens=T, d_model=d, d_ff=f, experts=E) for x in self.xs]
+            self.k_ffn = self.k_ffns[0]
         else:
-            self.k_compact = P("moe_compact_v1", x=self.x, permutation=self.perm, compact_x=self.compact_x,
-                               tokens=T, d_model=d)
+            self.k_compacts = [P("moe_compact_v1", x=x, permutation=self.perm, compact_x=self.compact_x,
+                                 tokens=T, d_model=d) for x in self.xs]
             self.k_ffn = P("moe_grouped_ffn_v1", compact_x=ffn_in, w1=self.w1, w2=self.w2, group_offsets=ffn_off,
                            hidden=self.hidden, compact_output=ffn_res, d_model=d, d_ff=f, groups=E,
                            experts_cycle=self.per)
-        self.k_combine = P("moe_expert_combine_v1", compact_output=self.compact_out, inverse=self.inverse,
-                           route_weights=self.weights, combined_output=self.out, tokens=T, width=d)
+        self.k_combines = [P("moe_expert_combine_v1", compact_output=self.compact_out, inverse=self.inverse,
+                             route_weights=self.weights, combined_output=out, tokens=T, width=d) for out in self.outs]
+        self.k_combine = self.k_combines[0]
         self.launches_per_step = 7 if world == 1 else 8
 
     # ---- peer-visible buffers ---------------------------------------------------------------
@@ -294,29 +305,30 @@ class MoeTop2Layer:
             off = self.group_offsets if self.world > 1 else self.offsets
         return int(off[-1].item())
 
-    def forward(self, stream=None, ffn_marks=None):
-        """Enqueues one layer pass on `stream` (default: the layer's stream) and returns the output tensor.
-        `ffn_marks`: optional (begin, end) events recorded around the expert FFN of the peer exchange."""
+    def forward(self, stream=None, ffn_marks=None, io=0):
+        """Enqueues one layer pass on `stream` (default: the layer's stream) over buffer pair `io` and returns
+        the output tensor.  `ffn_marks`: optional (begin, end) events recorded around the expert FFN of the
+        peer exchange."""
         s = stream or self.stream
-        self.k_gate.launch(s)
+        self.k_gates[io].launch(s)
         self.k_top2.launch(s)
         if self.exchange != "peer":
             self.k_weights.launch(s)
         if self.exchange == "peer":
-            self.k_phase[0].launch(s)   # counts exchange + route weights + rows to their experts' ranks
+            self.k_phases[io][0].launch(s)   # counts exchange + route weights + rows to their experts' ranks
             if ffn_marks:
                 ffn_marks[0].record(s)
             self.k_ffn.launch(s)        # waits per source inside; returns rows to their home ranks
             if ffn_marks:
                 ffn_marks[1].record(s)
-            self.k_phase[1].launch(s)   # combine from the local return buffer, advance the pass number
+            self.k_phases[io][1].launch(s)   # combine from the local return buffer, advance the pass number
         elif self.world == 1:
-            self.k_ffn.launch(s)
-            self.k_combine.launch(s)
+            self.k_ffns[io].launch(s)
+            self.k_combines[io].launch(s)
         else:
-            self._exchange_forward()
-            self.k_combine.launch(s)
-        return self.out
+            self._exchange_forward(io)
+            self.k_combines[io].launch(s)
+        return self.outs[io]
 
     # ---- CUDA graph of one pass ---------------------------------------------------------
     def capture(self):
@@ -327,20 +339,23 @@ class MoeTop2Layer:
         t = self.torch
         self._side = t.cuda.Stream()
         self._side_stream = self.ctx.wrap_stream(self._side.cuda_stream)
-        self._graph = t.cuda.CUDAGraph()
-        t.cuda.synchronize()
-        with t.cuda.graph(self._graph, stream=self._side):
-            self.forward(self._side_stream)
+        self._graphs = []
+        for io in range(len(self.xs)):   # one graph per buffer pair
+            g = t.cuda.CUDAGraph()
+            t.cuda.synchronize()
+            with t.cuda.graph(g, stream=self._side):
+                self.forward(self._side_stream, io=io)
+            self._graphs.append(g)
         return True
 
-    def replay(self):
-        self._graph.replay()
-        return self.out
+    def replay(self, io=0):
+        self._graphs[io].replay()
+        return self.outs[io]
 
-    def _exchange_forward(self):
+    def _exchange_forward(self, io=0):
         t, dist = self.torch, self.torch.distributed
         s, d = self.stream, self.d
-        self.k_compact.launch(s)
+        self.k_compacts[io].launch(s)
         # the compact buffers hold ADMITTED rows only (expert_offsets is the scan of the admitted counts)
         dist.all_gather_into_tensor(self.counts_all, self.admitted)
         self.host_counts.copy_(self.counts_all, non_blocking=True)

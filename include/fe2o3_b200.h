@@ -381,9 +381,15 @@ typedef struct fe2o3_moe_ep_exchange_v1_args {
  * recv_meta (two u32 per row) and flags are this rank's own buffers (the
  * entries `rank` of the peer tables), w1 [per][d_model][d_ff] and
  * w2 [per][d_ff][d_model] its experts, hidden [max_rows][d_ff] bf16 workspace.
- * `tokens` is the per-rank token count (a return buffer has 2*tokens rows). */
+ * `tokens` is the per-rank token count (a return buffer has 2*tokens rows).
+ * `progress` (optional): 2 * (max_rows/128 + experts/world + 1) u32 of this rank,
+ * zero before the first pass: one counter per 128-row tile of `hidden` (two sets,
+ * used by alternate passes), through which
+ * the first GEMM hands finished row tiles to the second, which is then launched
+ * so that it takes over each SM as the first GEMM's block leaves it instead of
+ * waiting for the whole first GEMM (it clears the other set for the next pass). */
 typedef struct fe2o3_moe_ep_ffn_v1_args {
-    fe2o3_slice recv_x, w1, w2, pair_offsets, hidden, recv_meta, flags, peer_ret, peer_flags, epoch_counter;
+    fe2o3_slice recv_x, w1, w2, pair_offsets, hidden, recv_meta, flags, peer_ret, peer_flags, epoch_counter, progress;
     uint32_t tokens, d_model, d_ff, experts, world, rank, epoch, max_rows, spin_limit, reserved;
 } fe2o3_moe_ep_ffn_v1_args;
 

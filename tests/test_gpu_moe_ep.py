@@ -158,7 +158,7 @@ def test_waits_run_out_and_the_next_pass_works(gpu, orc):
     from fe2o3_b200.moe import MoeTop2Layer
     T, d, f, E = 256, 128, 256, 8
     x, wg, w1, w2 = _inputs(T, d, f, E)
-    layer = MoeTop2Layer(ctx, stream, T, d, f, E, exchange="peer", spin_limit=200)
+    layer = MoeTop2Layer(ctx, stream, T, d, f, E, exchange="peer", spin_limit=20000)
     layer.load(x, wg, w1, w2)
     _, want = _oracle_rank(orc, x, wg, w1, w2, T, d, f, E, layer.capacity)
     out = layer.forward().cpu().numpy().reshape(T, d)

@@ -42,6 +42,16 @@ def test_noalloc_masked_sum_matches_prepared_entry_point_twice(orc):
         got = int(new_out.to_host_vec(stream)[0])
         assert got == want == orc.masked_sum_u32(values, flags), (call, got, want)  # integers: bit-exact
 
+    # the same on a stream of the caller's own (not the default stream): the call is asynchronous on it
+    own = ctx.create_stream()
+    n = 300007
+    values, flags = synth.u32_below(21, 1, n, 1 << 16), synth.bernoulli(21, 2, n, 0.75, packed=False)[0]
+    v, a = fe.DeviceBuffer.from_host(own, values), fe.DeviceBuffer.from_host(own, flags)
+    out = fe.DeviceBuffer.from_host(own, np.full(1, 0xDEADBEEF, np.uint32))
+    assert fn(v.as_device_ptr(), a.as_device_ptr(), n, out.as_device_ptr(), own.native) == 0, lib.fe2o3_last_error()
+    own.synchronize()
+    assert int(out.to_host_vec(own)[0]) == orc.masked_sum_u32(values, flags)
+
     # sizes beyond the stated maximum are rejected before anything is launched
     one = fe.DeviceBuffer.zeroed(stream, 4, np.uint32)
     st = fn(one.as_device_ptr(), one.as_device_ptr(), (1 << 31) + 1, one.as_device_ptr(), None)
