@@ -475,14 +475,14 @@ def moe_oracle_tokens(oracle, x_rows, wg, w1_all, w2_all, n, d, f, E):
     return routing["top2_experts"], want.reshape(n, d)
 
 
-def wl_moe(h, steps, warmup, cpu=True, **shape):
+def wl_moe(h, steps, warmup, cpu=True, exchange="auto", **shape):
     fe = h.fe
     from fe2o3_b200.moe import MoeTop2Layer
     shape = {**MOE_SHAPE, **shape}
     T, d, f, E = shape["tokens"], shape["d_model"], shape["d_ff"], shape["experts"]
     peaks = measured_peaks()
     torch = h.torch
-    layer = MoeTop2Layer(h.ctx, h.stream, T, d, f, E, rank=h.rank, world=h.world, io_sets=2)
+    layer = MoeTop2Layer(h.ctx, h.stream, T, d, f, E, rank=h.rank, world=h.world, io_sets=2, exchange=exchange)
     x, wg, w1, w2 = moe_inputs(h.rank, h.world, T, d, f, E)
     layer.load(x, wg, w1, w2)
     l0 = fe.launch_count()
@@ -503,7 +503,7 @@ def wl_moe(h, steps, warmup, cpu=True, **shape):
     # eager passes (its first GEMM waits in the kernel for the other ranks' rows and its second one
     # stores rows into their memory, so it cannot run outside a pass); waiting time is included.
     n_ffn = max(3, min(steps, 10))
-    if h.world == 1:
+    if layer.exchange == "none":
         ffn = fe.prepare(h.ctx, "moe_grouped_ffn_v1", compact_x=layer.compact_x, w1=layer.w1, w2=layer.w2,
                          group_offsets=layer.offsets, hidden=layer.hidden, compact_output=layer.compact_out, d_model=d,
                          d_ff=f, groups=E, experts_cycle=E)
@@ -525,7 +525,7 @@ def wl_moe(h, steps, warmup, cpu=True, **shape):
                                    traffic=NCU_TRAFFIC.get(("moe_top2_v1", (T, d, f, E))) if h.world == 1 else None,
                                    peak_source=peaks["source"]),
                         "kernel": "gemm_tc_kernel<256>, the two grouped FFN GEMMs (two launches" +
-                                  (", timed alone)" if h.world == 1 else ", timed inside eager passes, waits for other ranks included)"),
+                                  (", timed alone)" if layer.exchange == "none" else ", timed inside eager passes, waits for other ranks included)"),
                         "rows": ffn_rows, "ms_per_pair": ffn_ms,
                         "whole_pass": {"achieved": flops / (step_ms * 1e-3) / 1e12 / h.world,
                                        "peak": peaks["bf16_tflops_sustained"],
@@ -809,6 +809,9 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary ops in the `ops` object")
     ap.add_argument("--small", action="store_true", help="reduced sizes (profiler captures)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-oracle leg (profiler captures)")
+    ap.add_argument("--exchange", default="auto", choices=("auto", "peer", "nccl"),
+                    help="moe_top2_v1: exchange between ranks; 'peer' on one GPU runs the expert-parallel kernels "
+                         "(dispatch, flag-waiting FFN, scatter epilogue, combine) over the rank's own buffers")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     # stdout carries exactly one line, the JSON result: anything a library prints to file descriptor 1
@@ -839,6 +842,8 @@ def main():
               "moe_top2_v1": {"tokens": 2048}}.get(args.workload, {})
     if args.no_cpu:
         kw["cpu"] = False
+    if args.workload == "moe_top2_v1" and args.exchange != "auto":
+        kw["exchange"] = args.exchange
     clocks = ClockSampler(local_rank)
     h.clocks = clocks
     res = WORKLOADS[args.workload](h, args.steps, args.warmup, **kw)

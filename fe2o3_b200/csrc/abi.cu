@@ -1463,7 +1463,7 @@ int32_t fe2o3_moe_ep_ffn_v1_prepare(fe2o3_ctx *ctx, const fe2o3_moe_ep_ffn_v1_ar
                           a->d_model, a->d_model, 1.f, 0.f, EPI_SCATTER_PEER, outp.pair_offsets, per, 0, per, &outp, 2u * a->tokens);
     if (st != FE2O3_OK) return fail_prepare(out, st);
     p->gemm[0].overlap_previous = 1;   // may start beside the dispatch kernel launched just before it
-    p->gemm[1].overlap_previous = handover ? 1 : 0;   // may take over SMs as the first GEMM leaves them
+    p->gemm[1].overlap_previous = handover ? 2 : 0;   // takes over SMs as the first GEMM leaves them
     gemm_tc_geometry(&p->gemm[0], &p->geo);
     p->geo.launches = 2;
     return FE2O3_OK;

@@ -713,7 +713,7 @@ int32_t gemm_tc_launch(const GemmTcPlan *plan, cudaStream_t s) {
         cfg.numAttrs = 1;
     }
     cudaError_t e;
-    if (plan->overlap_previous)
+    if (plan->overlap_previous == 1)   // shares the SMs with the small blocks of the kernel before it: the 128-register build
         e = plan->bn == 256 ? cudaLaunchKernelEx(&cfg, gemm_tc_kernel<256, 128>, plan->tmA, plan->tmB, plan->tmC, plan->p)
                             : cudaLaunchKernelEx(&cfg, gemm_tc_kernel<128, 128>, plan->tmA, plan->tmB, plan->tmC, plan->p);
     else

@@ -56,7 +56,8 @@ struct GemmTcPlan {
     uint32_t bn;
     uint32_t grid;
     uint32_t smem;
-    uint32_t overlap_previous;   // launch with programmatic stream serialization: may start beside the kernel before it
+    uint32_t overlap_previous;   // launch with programmatic stream serialization: 1 = may run beside the (small) blocks of the
+                                 // kernel before it on the same SMs, 2 = takes over SMs as blocks of the kernel before it exit
 };
 
 int32_t fe2o3_make_tmap_bf16(CUtensorMap *out, uint64_t base, uint32_t rank, const uint64_t *dims,
