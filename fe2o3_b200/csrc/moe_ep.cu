@@ -125,37 +125,53 @@ moe_ep_dispatch_kernel(fe2o3_moe_ep_exchange_v1_args a, uint32_t *status) {
     const uint32_t *offsets = reinterpret_cast<const uint32_t *>(a.expert_offsets.ptr);
     const uint32_t off_lo = lane < E ? offsets[lane] : 0u, off_hi = lane < E ? offsets[lane + 1] : 0u;
     const uint32_t accepted = offsets[E];
+    // (the loops below are unrolled so that their loads, which are independent, are in flight together: a
+    // chain of dependent round trips to L2 here delays the first row of the pass by microseconds)
     uint32_t base = 0;
     if (lane < E) {
         // on expert e's owner: whole segments of the owner's earlier experts, then the rows of earlier sources
         const uint32_t e = lane, d = e / per, le = e % per;
-        for (uint32_t l2 = 0; l2 < le; ++l2)
+        for (uint32_t l2 = 0; l2 < le; ++l2) {
+#pragma unroll 8
             for (uint32_t s = 0; s < W; ++s) base += __ldcg(my_counts + s * E + d * per + l2);
+        }
+#pragma unroll 8
         for (uint32_t s = 0; s < me; ++s) base += __ldcg(my_counts + s * E + e);
     }
     uint32_t v_lo = 0, v_hi = 0;
     if (lane < W) {
+#pragma unroll 8
         for (uint32_t j = 0; j <= lane; ++j) {
             const uint32_t d = (me + W - j) % W;
             v_lo = v_hi;
             v_hi += offsets[(d + 1) * per] - offsets[d * per];
         }
     }
-    if (blockIdx.x == 0 && threadIdx.x == 32) {
-        // row partition of what this rank receives: pair (local expert, source); then tell the FFN kernel,
-        // which may already be running on this GPU, that the table is there
+    if (blockIdx.x == 0 && (threadIdx.x >> 5) == 1) {
+        // Row partition of what this rank receives: pair (local expert, source), a running sum of the counts
+        // in that order, made by one warp (one count per lane, a shuffle scan, 32 pairs at a time); then
+        // tell the FFN kernel, which may already be running on this GPU, that the table is there.
         uint32_t *pair_offsets = reinterpret_cast<uint32_t *>(a.pair_offsets.ptr);
+        const uint32_t pairs = per * W;
         uint32_t run = 0;
-        pair_offsets[0] = 0;
-        for (uint32_t le = 0; le < per; ++le)
-            for (uint32_t s = 0; s < W; ++s) {
-                run += __ldcg(my_counts + s * E + me * per + le);
-                // a table that overruns the receive buffer is cut off: the FFN must never index past it
-                pair_offsets[le * W + s + 1] = run < a.max_rows ? run : a.max_rows;
+        if (lane == 0) pair_offsets[0] = 0;
+        for (uint32_t i0 = 0; i0 < pairs; i0 += 32) {
+            const uint32_t i = i0 + lane, le = i / W, src = i % W;
+            uint32_t c = i < pairs ? __ldcg(my_counts + src * E + me * per + le) : 0u;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t up = __shfl_up_sync(0xffffffffu, c, o);
+                if (lane >= (uint32_t)o) c += up;
             }
-        if (run > a.max_rows) kstatus_set(status, FE2O3_KSTATUS_SLOT_RANGE);
+            const uint32_t total = run + c;   // inclusive sum up to pair i
+            // a table that overruns the receive buffer is cut off: the FFN must never index past it
+            if (i < pairs) pair_offsets[i + 1] = total < a.max_rows ? total : a.max_rows;
+            run = __shfl_sync(0xffffffffu, total, 31);
+        }
+        if (lane == 0 && run > a.max_rows) kstatus_set(status, FE2O3_KSTATUS_SLOT_RANGE);
         __threadfence();
-        st_release_sys(my_flags + FE2O3_EP_FLAG_TABLE(W), epoch);
+        __syncwarp();
+        if (lane == 0) st_release_sys(my_flags + FE2O3_EP_FLAG_TABLE(W), epoch);
     }
     if (blockIdx.x == 0 && threadIdx.x < W && v_hi == v_lo)   // nothing to send there: complete at once
         st_release_sys(reinterpret_cast<uint32_t *>(peer_flags[(me + W - threadIdx.x) % W]) + FE2O3_EP_FLAG_ROWS(W) + me, epoch);
@@ -166,32 +182,32 @@ moe_ep_dispatch_kernel(fe2o3_moe_ep_exchange_v1_args a, uint32_t *status) {
     const uint4 *x = reinterpret_cast<const uint4 *>(a.x.ptr);
     const uint32_t own_rows = __shfl_sync(0xffffffffu, v_hi, 0);
     const uint32_t gwarp = blockIdx.x * (kDispatchThreads / 32) + (threadIdx.x >> 5), nwarps = gridDim.x * (kDispatchThreads / 32);
-    uint32_t cur_j = W, cur_cnt = 0;   // rows stored for the cur_j-th destination and not yet accounted for
+    // Rows this warp has stored and not yet accounted for, per destination: lane j counts the j-th destination
+    // in sending order.  A warp accounts once per phase, after ALL its rows of the phase: the fence that must
+    // precede the counter update waits for the stores to be acknowledged from the other GPU (microseconds),
+    // which a warp that paid it per destination would pay seven times in a row at eight ranks.
+    uint32_t pending = 0;
     auto account = [&]() {
-        // every lane's stores are ordered before the counter update; whoever completes the destination's
-        // count raises "rows complete" there
+        // every lane's stores are ordered before the counter updates; whoever completes a destination's
+        // count raises "rows complete" there (lane j for destination j, all destinations at once)
         __threadfence_system();
         __syncwarp();
-        const uint32_t total = __shfl_sync(0xffffffffu, v_hi - v_lo, cur_j);
-        if (lane == 0 && cur_cnt) {
-            const uint32_t d = (me + W - cur_j) % W;
-            const uint32_t done = atomicAdd(rows_done + d, cur_cnt) + cur_cnt;
-            if (done == total) {
+        if (lane < W && pending) {
+            const uint32_t d = (me + W - lane) % W;
+            const uint32_t done = atomicAdd(rows_done + d, pending) + pending;
+            if (done == v_hi - v_lo) {
                 __threadfence_system();
                 st_release_sys(reinterpret_cast<uint32_t *>(peer_flags[d]) + FE2O3_EP_FLAG_ROWS(W) + me, epoch);
                 if (d == me) ep_trace(my_flags, FE2O3_EP_T_OWN_ROWS_DONE);
             }
         }
-        cur_cnt = 0;
+        pending = 0;
+        __syncwarp();
     };
     auto send_row = [&](uint32_t v) {
         // v-th row in sending order: which destination, which local slot, which expert
         const uint32_t j = __popc(__ballot_sync(0xffffffffu, lane < W && v >= v_hi));
-        if (j != cur_j) {
-            if (cur_cnt) account();
-            cur_j = j;
-        }
-        ++cur_cnt;   // counted even when the row is refused below: the destination must not wait for it
+        if (lane == j) ++pending;   // counted even when the row is refused below: the destination must not wait for it
         const uint32_t dst_rank = (me + W - j) % W;
         const uint32_t slot = offsets[dst_rank * per] + (v - __shfl_sync(0xffffffffu, v_lo, j));
         const uint32_t e = __popc(__ballot_sync(0xffffffffu, lane < E && slot >= off_hi));
@@ -219,7 +235,7 @@ moe_ep_dispatch_kernel(fe2o3_moe_ep_exchange_v1_args a, uint32_t *status) {
     // speed and hold up everything behind them in the memory system, so no block starts on those before every
     // block is through with its own rows (all blocks of this grid are resident at once, one per SM).
     for (uint32_t v = gwarp; v < own_rows; v += nwarps) send_row(v);
-    if (cur_cnt) account();
+    if (__any_sync(0xffffffffu, pending != 0u)) account();
     if (W > 1) {
         uint32_t *own_blocks = my_flags + FE2O3_EP_OWN_BLOCKS(W, epoch & 1u);
         __syncthreads();
@@ -233,7 +249,7 @@ moe_ep_dispatch_kernel(fe2o3_moe_ep_exchange_v1_args a, uint32_t *status) {
     }
     // Phase 2: the other ranks' rows, in sending order
     for (uint32_t v = own_rows + gwarp; v < accepted; v += nwarps) send_row(v);
-    if (cur_cnt) account();
+    if (__any_sync(0xffffffffu, pending != 0u)) account();
     if (blockIdx.x == 0 && threadIdx.x == 0) ep_trace(my_flags, FE2O3_EP_T_ROWS_SENT);
 }
 
