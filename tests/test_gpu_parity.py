@@ -431,7 +431,12 @@ def test_attention_reference_profile_vectors(gpu, orc):
 
 
 @pytest.mark.parametrize("B,H,S,D,causal", [(1, 2, 128, 64, False), (2, 2, 256, 64, False), (1, 1, 384, 64, True),
-                                            (1, 1, 96, 32, False), (1, 2, 512, 128, False)])
+                                            (1, 1, 96, 32, False), (1, 2, 512, 128, False),
+                                            # 208 two-tile units on 148 CTAs: one full round of the persistent
+                                            # schedule, then a last round split into 120 single tiles
+                                            (2, 13, 2048, 64, False), (2, 13, 2048, 64, True),
+                                            # rows and keys that end inside a tile, several rounds
+                                            (1, 5, 1000, 64, True), (3, 7, 1900, 64, False)])
 def test_attention_bf16_vs_f64_oracle(gpu, orc, B, H, S, D, causal):
     fe = gpu[0]
     from fe2o3_b200 import synth
