@@ -75,12 +75,13 @@ __device__ __forceinline__ TileCoord decode_tile(uint32_t id, const GemmParams &
         return t;
     }
     if (p.ep.rows_flags || p.ep.progress_mode) {
-        // groups = (rotation step j, local expert le): the tiles whose first row belongs to source (rank + j) mod W
+        // groups = (run j, local expert le): the tiles whose first row belongs to source (rank + j) mod W; inside
+        // an expert's segment the runs lie in exactly that order (the owner's own rows first)
         const uint32_t W = p.ep.world;
         uint32_t base = 0;
         for (uint32_t g = 0; g < W * p.experts; ++g) {
             const uint32_t j = g / p.experts, le = g % p.experts;
-            const uint32_t src = (p.ep.rank + j) % W, pi = le * W + src;
+            const uint32_t pi = le * W + j;
             const uint32_t seg = s_off[le], lo = s_pair[pi] - seg, hi = s_pair[pi + 1] - seg;
             const uint32_t i0 = (lo + BM - 1) / BM, i1 = (hi + BM - 1) / BM;   // tile starts seg + i * BM in [lo, hi)
             const uint32_t cnt = hi > lo ? (i1 - i0) * n_tiles : 0u;
@@ -273,8 +274,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     need = 1u << (lane % p.ep.world);
                 need = __reduce_or_sync(0xffffffffu, need) & ~seen;
                 seen |= need;
-                while (need) {
-                    const uint32_t src = __ffs(need) - 1;
+                while (need) {   // bit k = run k of a segment = source (rank + k) mod W
+                    const uint32_t src = (p.ep.rank + __ffs(need) - 1) % p.ep.world;
                     need &= need - 1;
                     if (!__all_sync(0xffffffffu, flag_wait(p.ep.rows_flags + src, ep_epoch, p.ep.spin_limit))) { ok = false; break; }
                 }

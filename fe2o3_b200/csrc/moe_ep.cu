@@ -108,36 +108,16 @@ moe_ep_dispatch_kernel(fe2o3_moe_ep_exchange_v1_args a, uint32_t *status) {
             weights[2ull * t + 1] = w1;
         }
     }
-    // every block waits for the counts of every source (thread s polls source s: local memory)
-    int ok = dead ? 0 : (threadIdx.x < W ? (flag_wait(my_flags + FE2O3_EP_FLAG_COUNTS(W) + threadIdx.x, epoch, limit) ? 1 : 0) : 1);
-    ok = __syncthreads_and(ok);
-    if (blockIdx.x == 0 && threadIdx.x == 0) ep_trace(my_flags, FE2O3_EP_T_COUNTS_HERE);
-    if (!ok) {
-        // nothing is sent and no flag is raised: the other ranks' waits run out in turn
-        if (threadIdx.x == 0) kstatus_set(status, FE2O3_KSTATUS_WAIT_EXPIRED);
-        return;
-    }
     // Every warp keeps the small tables it needs in registers, one entry per lane (this kernel shares its
     // SMs with the GEMM that follows it, which leaves it no shared memory to speak of):
     //   lane e < E: off_lo/off_hi = local slots of expert e, base = first row of this rank's rows for e on e's owner
     //   lane j < W: the j-th destination in sending order, rank (me - j) mod W: v_lo/v_hi = its rows in that order
+    // (the loops below are unrolled so that their loads, which are independent, are in flight together: a
+    // chain of dependent round trips to L2 here delays the first row of the pass by microseconds)
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t *offsets = reinterpret_cast<const uint32_t *>(a.expert_offsets.ptr);
     const uint32_t off_lo = lane < E ? offsets[lane] : 0u, off_hi = lane < E ? offsets[lane + 1] : 0u;
-    const uint32_t accepted = offsets[E];
-    // (the loops below are unrolled so that their loads, which are independent, are in flight together: a
-    // chain of dependent round trips to L2 here delays the first row of the pass by microseconds)
-    uint32_t base = 0;
-    if (lane < E) {
-        // on expert e's owner: whole segments of the owner's earlier experts, then the rows of earlier sources
-        const uint32_t e = lane, d = e / per, le = e % per;
-        for (uint32_t l2 = 0; l2 < le; ++l2) {
-#pragma unroll 8
-            for (uint32_t s = 0; s < W; ++s) base += __ldcg(my_counts + s * E + d * per + l2);
-        }
-#pragma unroll 8
-        for (uint32_t s = 0; s < me; ++s) base += __ldcg(my_counts + s * E + e);
-    }
+    const uint32_t accepted = dead ? 0u : offsets[E];
     uint32_t v_lo = 0, v_hi = 0;
     if (lane < W) {
 #pragma unroll 8
@@ -147,34 +127,7 @@ moe_ep_dispatch_kernel(fe2o3_moe_ep_exchange_v1_args a, uint32_t *status) {
             v_hi += offsets[(d + 1) * per] - offsets[d * per];
         }
     }
-    if (blockIdx.x == 0 && (threadIdx.x >> 5) == 1) {
-        // Row partition of what this rank receives: pair (local expert, source), a running sum of the counts
-        // in that order, made by one warp (one count per lane, a shuffle scan, 32 pairs at a time); then
-        // tell the FFN kernel, which may already be running on this GPU, that the table is there.
-        uint32_t *pair_offsets = reinterpret_cast<uint32_t *>(a.pair_offsets.ptr);
-        const uint32_t pairs = per * W;
-        uint32_t run = 0;
-        if (lane == 0) pair_offsets[0] = 0;
-        for (uint32_t i0 = 0; i0 < pairs; i0 += 32) {
-            const uint32_t i = i0 + lane, le = i / W, src = i % W;
-            uint32_t c = i < pairs ? __ldcg(my_counts + src * E + me * per + le) : 0u;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const uint32_t up = __shfl_up_sync(0xffffffffu, c, o);
-                if (lane >= (uint32_t)o) c += up;
-            }
-            const uint32_t total = run + c;   // inclusive sum up to pair i
-            // a table that overruns the receive buffer is cut off: the FFN must never index past it
-            if (i < pairs) pair_offsets[i + 1] = total < a.max_rows ? total : a.max_rows;
-            run = __shfl_sync(0xffffffffu, total, 31);
-        }
-        if (lane == 0 && run > a.max_rows) kstatus_set(status, FE2O3_KSTATUS_SLOT_RANGE);
-        __threadfence();
-        __syncwarp();
-        if (lane == 0) st_release_sys(my_flags + FE2O3_EP_FLAG_TABLE(W), epoch);
-    }
-    if (blockIdx.x == 0 && threadIdx.x < W && v_hi == v_lo)   // nothing to send there: complete at once
-        st_release_sys(reinterpret_cast<uint32_t *>(peer_flags[(me + W - threadIdx.x) % W]) + FE2O3_EP_FLAG_ROWS(W) + me, epoch);
+    uint32_t base = 0;   // all zero until the counts are here: correct for the one expert whose rows go before that
 
     // rows: one warp per accepted local slot, kInFlight 16-byte loads in flight per lane before the peer stores
     const uint32_t *perm = reinterpret_cast<const uint32_t *>(a.permutation.ptr);
@@ -229,12 +182,71 @@ moe_ep_dispatch_kernel(fe2o3_moe_ep_exchange_v1_args a, uint32_t *status) {
             for (int u = 0; u < kInFlight; ++u)
                 if (i0 + 32 * u < vec_per_row) dst[i0 + 32 * u] = q[u];
         }
-        };
-    // Phase 1: this rank's own rows, by all blocks.  They are what the GEMM beside this kernel starts on, and
-    // they copy at memory speed as long as nothing else is in the way: rows to other ranks leave at NVLink
-    // speed and hold up everything behind them in the memory system, so no block starts on those before every
-    // block is through with its own rows (all blocks of this grid are resident at once, one per SM).
-    for (uint32_t v = gwarp; v < own_rows; v += nwarps) send_row(v);
+    };
+    // Phase A, while the counts of the other ranks are still on their way: this rank's own rows for its first
+    // local expert.  On its owner an expert's segment opens with the owner's own rows and the first local
+    // expert's segment opens the buffer, so these rows start at row 0 whatever the other ranks send.  They are
+    // what the GEMM beside this kernel starts on.
+    const uint32_t first_own = (accepted && per) ? offsets[me * per + 1] - offsets[me * per] : 0u;
+    for (uint32_t v = gwarp; v < first_own; v += nwarps) send_row(v);
+
+    // every block waits for the counts of every source (thread s polls source s: local memory)
+    int ok = dead ? 0 : (threadIdx.x < W ? (flag_wait(my_flags + FE2O3_EP_FLAG_COUNTS(W) + threadIdx.x, epoch, limit) ? 1 : 0) : 1);
+    ok = __syncthreads_and(ok);
+    if (blockIdx.x == 0 && threadIdx.x == 0) ep_trace(my_flags, FE2O3_EP_T_COUNTS_HERE);
+    if (!ok) {
+        // nothing more is sent and no flag is raised: the other ranks' waits run out in turn
+        if (threadIdx.x == 0) kstatus_set(status, FE2O3_KSTATUS_WAIT_EXPIRED);
+        return;
+    }
+    if (lane < E) {
+        // On expert e's owner d: whole segments of the owner's earlier experts, then the runs of the sources
+        // that come before this rank in the owner's order d, d+1, ... (mod W).
+        const uint32_t e = lane, d = e / per, le = e % per, k_me = (me + W - d) % W;
+        for (uint32_t l2 = 0; l2 < le; ++l2) {
+#pragma unroll 8
+            for (uint32_t s = 0; s < W; ++s) base += __ldcg(my_counts + s * E + d * per + l2);
+        }
+#pragma unroll 8
+        for (uint32_t k = 0; k < k_me; ++k) base += __ldcg(my_counts + ((d + k) % W) * E + e);
+    }
+    if (blockIdx.x == 0 && (threadIdx.x >> 5) == 1) {
+        // Row partition of what this rank receives: pair (local expert, run k = source (me + k) mod W), a
+        // running sum of the counts in that order, made by one warp (one count per lane, a shuffle scan, 32
+        // pairs at a time); then tell the FFN kernel, which may already be running on this GPU, that the
+        // table is there.
+        uint32_t *pair_offsets = reinterpret_cast<uint32_t *>(a.pair_offsets.ptr);
+        const uint32_t pairs = per * W;
+        uint32_t run = 0;
+        if (lane == 0) pair_offsets[0] = 0;
+        for (uint32_t i0 = 0; i0 < pairs; i0 += 32) {
+            const uint32_t i = i0 + lane, le = i / W, src = (me + i % W) % W;
+            uint32_t c = i < pairs ? __ldcg(my_counts + src * E + me * per + le) : 0u;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t up = __shfl_up_sync(0xffffffffu, c, o);
+                if (lane >= (uint32_t)o) c += up;
+            }
+            const uint32_t total = run + c;   // inclusive sum up to pair i
+            // a table that overruns the receive buffer is cut off: the FFN must never index past it
+            if (i < pairs) pair_offsets[i + 1] = total < a.max_rows ? total : a.max_rows;
+            run = __shfl_sync(0xffffffffu, total, 31);
+        }
+        if (lane == 0 && run > a.max_rows) kstatus_set(status, FE2O3_KSTATUS_SLOT_RANGE);
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) st_release_sys(my_flags + FE2O3_EP_FLAG_TABLE(W), epoch);
+    }
+    if (blockIdx.x == 0 && threadIdx.x < W && v_hi == v_lo)   // nothing to send there: complete at once
+        st_release_sys(reinterpret_cast<uint32_t *>(peer_flags[(me + W - threadIdx.x) % W]) + FE2O3_EP_FLAG_ROWS(W) + me, epoch);
+
+    // Phase B1: the rest of this rank's own rows (its other local experts), by all blocks, accounted together
+    // with phase A.  They copy at memory speed as long as nothing else is in the way: rows to other ranks
+    // leave at NVLink speed and hold up everything behind them in the memory system (the flag polls of the
+    // GEMM block on the same SM included), so no block starts on those before every block is through with
+    // its own rows and block 0 has published the row table (all blocks of this grid are resident at once,
+    // one per SM).
+    for (uint32_t v = first_own + gwarp; v < own_rows; v += nwarps) send_row(v);
     if (__any_sync(0xffffffffu, pending != 0u)) account();
     if (W > 1) {
         uint32_t *own_blocks = my_flags + FE2O3_EP_OWN_BLOCKS(W, epoch & 1u);

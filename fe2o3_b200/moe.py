@@ -46,20 +46,26 @@ def split_plan(counts, rank, world):
 
 def pair_plan(counts, rank, world):
     """Pure host statement of the peer exchange's row layout, from the same
-    admitted counts: on its owner, the rows of local expert `le` from source `s`
-    start at pair_offsets[le * world + s] (local-expert major, source minor), and
-    `bases[d][e]` is the first row of THIS rank's rows for expert e on e's owner d.
-    The dispatch kernel computes both on the device; tests compare against this."""
+    admitted counts: on its owner `o`, the rows of local expert `le` are one
+    segment made of one run per source, the owner's own rows first, then the
+    sources o+1, o+2, ... (mod world): run k (source (o + k) % world) starts at
+    pair_offsets[le * world + k].  `bases[e]` is the first row of THIS rank's rows
+    for expert e on e's owner.  A rank's own rows for its first local expert start
+    at row 0 whatever the other ranks send, which is why the dispatch kernel can
+    store them before the counts have been exchanged.  The dispatch kernel computes
+    both tables on the device; tests compare against this."""
     counts = np.asarray(counts, np.int64)
     experts = counts.shape[1]
     per = experts // world
-    mine = counts[:, rank * per:(rank + 1) * per]           # [source][local expert]
+    order = [(rank + k) % world for k in range(world)]
+    mine = counts[order][:, rank * per:(rank + 1) * per]     # [run k][local expert]
     pair_offsets = np.zeros(experts + 1, np.uint32)
-    pair_offsets[1:] = np.cumsum(mine.T.reshape(-1))          # le-major, source-minor
+    pair_offsets[1:] = np.cumsum(mine.T.reshape(-1))          # le-major, run-minor
     bases = np.zeros(experts, np.int64)
     for e in range(experts):
         d, le = divmod(e, per)
-        bases[e] = counts[:, d * per:d * per + le].sum() + counts[:rank, e].sum()
+        k_me = (rank - d) % world
+        bases[e] = counts[:, d * per:d * per + le].sum() + sum(counts[(d + k) % world, e] for k in range(k_me))
     return pair_offsets, bases
 
 

@@ -335,10 +335,11 @@ typedef struct fe2o3_moe_grouped_ffn_v1_args {
  *   ret       [2*tokens][d_model] f32    expert outputs by route id, on the home rank
  *   counts    [world][experts] u32       admitted routes per (source rank, expert)
  *   flags     [5*world + 6] u32, zero before the first pass
- * Rows on the owner of expert e are ordered local-expert-major, source-rank-minor,
- * so each expert's rows are one contiguous segment; pair_offsets[le*world + s]
- * is the first row of (local expert le, source s), pair_offsets[experts] the
- * row count.
+ * Rows on the owner o of an expert are ordered local-expert-major, and inside an
+ * expert's segment by source in the order o, o+1, ... (mod world): the owner's own
+ * rows first.  Each expert's rows are one contiguous segment; pair_offsets[le*world + k]
+ * is the first row of (local expert le, source (o + k) mod world),
+ * pair_offsets[experts] the row count.
  *
  * The pass number ("epoch") must increase by one per layer pass on every rank:
  * either patch `epoch` in all three prepared blocks before each pass

@@ -100,12 +100,13 @@ def test_pair_plan_layout():
         pairs, bases = pair_plan(counts, r, world)
         assert pairs[0] == 0 and pairs[-1] == counts[:, r * per:(r + 1) * per].sum()
         for le in range(per):
-            for s in range(world):
-                assert pairs[le * world + s + 1] - pairs[le * world + s] == counts[s, r * per + le]
+            for k in range(world):   # run k of a segment holds the rows of source (owner + k) % world
+                assert pairs[le * world + k + 1] - pairs[le * world + k] == counts[(r + k) % world, r * per + le]
+        assert bases[r * per] == 0   # own rows of the first local expert: placed without knowing any other rank's counts
         for e in range(experts):
             d = e // per
             covered[d][bases[e]:bases[e] + counts[r, e]] += 1
             # the sender's base agrees with the owner's pair table
             owner_pairs, _ = pair_plan(counts, d, world)
-            assert bases[e] == owner_pairs[(e % per) * world + r]
+            assert bases[e] == owner_pairs[(e % per) * world + (r - d) % world]
     assert all((c == 1).all() for c in covered)
