@@ -715,7 +715,9 @@ int32_t launch_prepared(fe2o3_prepared *p, cudaStream_t s) {
         case OP_MOE_EXPERT_FFN: {
             const fe2o3_moe_expert_ffn_v1_args *a = reinterpret_cast<const fe2o3_moe_expert_ffn_v1_args *>(p->kernarg);
             const uint32_t rows = (uint32_t)(a->compact_output.len / a->d_model);
-            int32_t st = launch_moe_compact(s, a->x.ptr, a->permutation.ptr, a->compact_x.ptr, rows, a->d_model, a->tokens);
+            int32_t st = FE2O3_OK;
+            if (!p->gemm[0].p.gather_perm)   // the first GEMM reads compact_x: fill it (otherwise it gathers the rows of x itself)
+                st = launch_moe_compact(s, a->x.ptr, a->permutation.ptr, a->compact_x.ptr, rows, a->d_model, a->tokens);
             if (st != FE2O3_OK) return st;
             st = gemm_tc_launch(&p->gemm[0], s);
             if (st != FE2O3_OK) return st;
@@ -1382,8 +1384,15 @@ int32_t fe2o3_moe_expert_ffn_v1_prepare(fe2o3_ctx *ctx, const fe2o3_moe_expert_f
         st = gemm_tc_plan(ctx, &p->gemm[1], a->hidden.ptr, a->w2.ptr, a->compact_output.ptr, rows, a->d_model, a->d_ff,
                           a->d_ff, a->d_model, a->d_model, 1.f, 0.f, 0u, off, a->experts);
     if (st != FE2O3_OK) return fail_prepare(out, st);
+    // The first GEMM fetches its rows of x through `permutation` itself when the row length allows it, which
+    // saves the compaction pass (compact_x is then left untouched); FE2O3_FFN_GATHER=0 keeps the compaction.
+    const char *gather_env = getenv("FE2O3_FFN_GATHER");
+    bool gathered = false;
+    if (!(gather_env && gather_env[0] == '0'))
+        gathered = gemm_tc_set_gather(&p->gemm[0], reinterpret_cast<const uint32_t *>(a->permutation.ptr),
+                                      reinterpret_cast<const void *>(a->x.ptr), a->tokens);
     gemm_tc_geometry(&p->gemm[0], &p->geo);
-    p->geo.launches = 3;
+    p->geo.launches = gathered ? 2 : 3;
     return FE2O3_OK;
 }
 

@@ -32,6 +32,8 @@ constexpr int UMMA_K = 16;
 constexpr int kStages = 4;
 constexpr int kEpilogueWarps = 8;
 constexpr int kThreads = 32 * (2 + kEpilogueWarps);
+constexpr int kGatherThreads = 64;   // two more warps when A is gathered row by row (they fit the block's register allocation,
+                                     // which is made for twelve warps anyway: registers go out to four warps at a time)
 constexpr int kGroupM = 16;     // m-tiles per rasterisation band (keeps a wave's A and B panels in L2)
 
 template <int BN>
@@ -186,7 +188,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // They find the status word set and do nothing but their arrival counting.
         s_abort = (p.ep.pair_offsets && p.status && __ldcg(p.status) != 0u) ? 1 : 0;
         for (int i = 0; i < kStages; ++i) {
-            mbar_init(&full[i], 1);
+            mbar_init(&full[i], p.gather_perm ? 1 + kGatherThreads : 1);   // the producer's expect-tx arrival + every loader thread
             mbar_init(&empty[i], 1);
         }
         for (int i = 0; i < 2; ++i) {
@@ -304,8 +306,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 if (elect_one()) {
                     uint8_t *sa = smem + stage * L::kStageBytes;
                     uint8_t *sb = sa + L::kABytes;
-                    mbar_arrive_expect_tx(&full[stage], L::kStageBytes);
-                    tma_load_2d(sa, &tmA, &full[stage], (int32_t)(kb * BK), (int32_t)t.m0);
+                    mbar_arrive_expect_tx(&full[stage], p.gather_perm ? L::kBBytes : L::kStageBytes);
+                    if (!p.gather_perm) tma_load_2d(sa, &tmA, &full[stage], (int32_t)(kb * BK), (int32_t)t.m0);
 #pragma unroll
                     for (int j = 0; j < BN / 64; ++j) {
                         if (p.experts)
@@ -344,6 +346,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const uint32_t d_tmem = tmem_base + buf * BN;
             for (uint32_t kb = 0; kb < num_kb; ++kb) {
                 if (!mbar_wait_warp(&full[stage], phase, &s_abort)) { ok = false; break; }
+                // gathered A rows were written by cp.async (generic proxy): order them before the tensor core's reads
+                if (p.gather_perm) fence_proxy_async_smem();
                 tc_fence_after();
                 if (elect_one()) {
                     // only the 16-byte-unit start address field of the descriptors moves
@@ -362,6 +366,47 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 if (++stage == kStages) { stage = 0; phase ^= 1; }
             }
         }
+        if (!ok && lane == 0) {
+            kstatus_set(p.status, FE2O3_KSTATUS_WAIT_EXPIRED);
+            atomicExch(&s_abort, 1);
+        }
+    } else if (warp >= 2 + kEpilogueWarps) {
+        // ------------------------------------------------ gather loaders (blocks launched with them only)
+        // 64 threads fetch the tile's 128 rows of A for every K block: thread = (row mod 8, 16-byte chunk of
+        // the row's 128 bytes), sixteen rows each, so that eight neighbouring lanes read one whole line.  The
+        // rows go straight into the 128-byte-swizzled stage the tensor core reads; a row that is not a route
+        // (past the group's end, or a dropped slot) is filled with zeros.  Completion is signalled to the
+        // stage's barrier by the copies themselves.
+        const uint32_t lt = threadIdx.x - 32 * (2 + kEpilogueWarps);
+        const uint32_t chunk = lt & 7, r0 = lt >> 3;
+        const uint8_t *src_base = reinterpret_cast<const uint8_t *>(p.gather_src);
+        uint32_t stage = 0, phase = 0;
+        bool ok = !dead;
+        for (uint32_t id = blockIdx.x; ok; id += gridDim.x) {
+            TileCoord t = decode_tile(id, p, n_tiles, s_off, s_pair);
+            if (!t.valid) break;
+            uint32_t tok[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const uint32_t row = t.m0 + r0 + 8 * i;
+                const uint32_t route = row < t.m_end ? __ldg(p.gather_perm + row) : 0xffffffffu;
+                tok[i] = (route == 0xffffffffu || (route >> 1) >= p.gather_tokens) ? 0xffffffffu : (route >> 1);
+            }
+            for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                if (!mbar_wait_warp(&empty[stage], phase ^ 1, &s_abort)) { ok = false; break; }
+                const uint32_t sa = smem_u32(smem + stage * L::kStageBytes) + r0 * 128 + ((chunk ^ (r0 & 7)) << 4);
+                const uint64_t col = (uint64_t)kb * (BK * 2) + chunk * 16;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const bool live = tok[i] != 0xffffffffu;
+                    const uint8_t *src = live ? src_base + (uint64_t)tok[i] * p.K * 2 + col : src_base;
+                    asm volatile("cp.async.cg.shared.global.L2::256B [%0], [%1], 16, %2;" ::"r"(sa + i * 1024), "l"(src), "r"(live ? 16 : 0) : "memory");
+                }
+                asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&full[stage])) : "memory");
+                if (++stage == kStages) { stage = 0; phase ^= 1; }
+            }
+        }
+        asm volatile("cp.async.wait_all;" ::: "memory");   // no copy may be in flight when the block exits
         if (!ok && lane == 0) {
             kstatus_set(p.status, FE2O3_KSTATUS_WAIT_EXPIRED);
             atomicExch(&s_abort, 1);
@@ -674,7 +719,7 @@ int32_t gemm_tc_plan(fe2o3_ctx *ctx, GemmTcPlan *plan, uint64_t a, uint64_t b, u
         bulk = 1;
     }
     plan->p = GemmParams{reinterpret_cast<void *>(c), M, N, K, ldc, alpha, beta, epilogue, expert_offsets, experts,
-                         expert_mod, bulk, ctx->status_word, ep ? *ep : GemmEp{}};
+                         expert_mod, bulk, ctx->status_word, ep ? *ep : GemmEp{}, nullptr, nullptr, 0u};
     const uint32_t n_tiles = (N + plan->bn - 1) / plan->bn;
     const uint64_t m_tiles = (uint64_t)(M + BM - 1) / BM + experts;  // grouped: each expert may add a ragged tile
     uint64_t tiles = m_tiles * n_tiles;
@@ -701,7 +746,7 @@ int32_t gemm_tc_launch(const GemmTcPlan *plan, cudaStream_t s) {
     if (plan->p.M == 0 || plan->p.N == 0) return FE2O3_OK;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(plan->grid, 1, 1);
-    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.blockDim = dim3(kThreads + (plan->p.gather_perm ? kGatherThreads : 0), 1, 1);
     cfg.dynamicSmemBytes = plan->smem;
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
@@ -724,8 +769,17 @@ int32_t gemm_tc_launch(const GemmTcPlan *plan, cudaStream_t s) {
     return fe2o3_cuda_status(e, "gemm_tc");
 }
 
+// Makes the plan's A operand a gather: row r of A = row (perm[r] >> 1) of src.  Needs whole 64-column K blocks.
+bool gemm_tc_set_gather(GemmTcPlan *plan, const uint32_t *perm, const void *src, uint32_t tokens) {
+    if (plan->p.K % BK != 0 || (reinterpret_cast<uintptr_t>(src) & 15u) != 0) return false;
+    plan->p.gather_perm = perm;
+    plan->p.gather_src = src;
+    plan->p.gather_tokens = tokens;
+    return true;
+}
+
 void gemm_tc_geometry(const GemmTcPlan *plan, fe2o3_geometry *geo) {
-    *geo = fe2o3_geometry{{plan->grid, 1, 1}, {kThreads, 1, 1}, plan->smem, 1};
+    *geo = fe2o3_geometry{{plan->grid, 1, 1}, {(uint32_t)(kThreads + (plan->p.gather_perm ? kGatherThreads : 0)), 1, 1}, plan->smem, 1};
 }
 
 // kernel symbols of the runtime adapter carried by this source (the schedule a large launch resolves to)

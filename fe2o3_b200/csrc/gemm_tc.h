@@ -48,6 +48,12 @@ struct GemmParams {
     uint32_t bulk_store;     // C is addressable by the copy engine (tensor map tmC is valid)
     uint32_t *status;
     GemmEp ep;
+    // Gathered A (first GEMM of the single-GPU expert FFN): row r of A is row (gather_perm[r] >> 1) of
+    // gather_src ([gather_tokens][K] bf16), or zero when gather_perm[r] names no route; the block is then
+    // launched with two loader warps more, which fetch the rows straight into the swizzled A stage.
+    const uint32_t *gather_perm;
+    const void *gather_src;
+    uint32_t gather_tokens;
 };
 
 struct GemmTcPlan {
@@ -71,4 +77,5 @@ int32_t gemm_tc_plan(fe2o3_ctx *ctx, GemmTcPlan *plan, uint64_t a, uint64_t b, u
                      const GemmEp *ep = nullptr, uint32_t expected_rows = 0);
 int32_t gemm_tc_launch(const GemmTcPlan *plan, cudaStream_t s);
 int32_t gemm_tc_init_device();
+bool gemm_tc_set_gather(GemmTcPlan *plan, const uint32_t *perm, const void *src, uint32_t tokens);
 void gemm_tc_geometry(const GemmTcPlan *plan, fe2o3_geometry *geo);

@@ -301,7 +301,10 @@ typedef struct fe2o3_moe_route_weights_v1_args {
  * w2 [E][d_ff][d_model] bf16, permutation/expert_offsets from routing;
  * compact_x [rows][d_model] bf16 and hidden [rows][d_ff] bf16 are
  * caller-provided workspace; compact_output [rows][d_model] f32.
- * rows = compact_output.len / d_model. */
+ * rows = compact_output.len / d_model.  When d_model is a multiple of 64 the
+ * first GEMM gathers the rows of x through `permutation` itself and compact_x
+ * is left untouched (two launches instead of three; the prepared geometry says
+ * which); the results are the same bits either way. */
 typedef struct fe2o3_moe_expert_ffn_v1_args {
     fe2o3_slice x, w1, w2, permutation, expert_offsets, compact_x, hidden, compact_output;
     uint32_t tokens, d_model, d_ff, experts;

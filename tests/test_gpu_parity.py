@@ -611,12 +611,50 @@ def moe_pipeline(gpu, orc, T, d, f, E, capacity, seed=4):
     return compact, want_compact, out, want_out, int(want["expert_offsets"][E])
 
 
-@pytest.mark.parametrize("T,d,f,E,cap", [(64, 128, 256, 4, 128), (300, 256, 512, 8, 600), (256, 128, 256, 8, 40)])
+@pytest.mark.parametrize("T,d,f,E,cap", [(64, 128, 256, 4, 128), (300, 256, 512, 8, 600), (256, 128, 256, 8, 40),
+                                         # a row length that is not whole 64-column blocks: the expert FFN
+                                         # compacts the rows first instead of gathering them in its first GEMM
+                                         (100, 136, 256, 4, 200),
+                                         # ragged groups over several row tiles, some routes dropped
+                                         (1500, 192, 320, 8, 300)])
 def test_moe_end_to_end_small(gpu, orc, T, d, f, E, cap):
     compact, want_compact, out, want_out, accepted = moe_pipeline(gpu, orc, T, d, f, E, cap)
     # BASELINE tolerance: outputs rel 2e-2, plus an absolute term of 2e-3 of the largest output
     assert_close(out, want_out, 2e-2, 2e-3, "combined output")
     assert_close(compact[: accepted * d], want_compact[: accepted * d], 2e-2, 2e-3, "compact expert output")
+
+
+def test_expert_ffn_gathered_rows_equal_compacted_rows(gpu, orc, monkeypatch):
+    """The expert FFN's first GEMM either reads rows that a compaction pass has laid out, or gathers the
+    rows of x through the permutation itself (loader warps, cp.async into the swizzled stage).  Both feed the
+    tensor core the same operands in the same order, so the two outputs are the same bits, on several
+    thousand row tiles, launch after launch."""
+    fe, ctx, stream = gpu
+    from fe2o3_b200 import synth
+    T, d, f, E = 6000, 512, 768, 8
+    R = 2 * T
+    x = synth.normal_bf16(6, 1, T * d, 1.0)
+    w1, w2 = synth.normal_bf16(6, 2, E * d * f, 0.05), synth.normal_bf16(6, 3, E * f * d, 0.05)
+    logits = synth.normal_bf16(6, 4, T * E, 1.0).astype(np.float32) / 256.0
+    _, routing = orc.moe_top2_route(logits, T, E, 1400)   # capacity below demand: dropped slots in every group
+    B = lambda a: fe.DeviceBuffer.from_host(stream, a)
+    X, W1, W2 = B(x), B(w1), B(w2)
+    PERM, OFF = B(routing["permutation"]), B(routing["expert_offsets"])
+    outs = {}
+    for mode in ("0", "1"):
+        monkeypatch.setenv("FE2O3_FFN_GATHER", mode)
+        CX, HID, CO = (fe.DeviceBuffer.zeroed(stream, n, t) for n, t in ((R * d, np.uint16), (R * f, np.uint16), (R * d, np.float32)))
+        p = fe.prepare(ctx, "moe_expert_ffn_v1", x=X, w1=W1, w2=W2, permutation=PERM, expert_offsets=OFF, compact_x=CX,
+                       hidden=HID, compact_output=CO, tokens=T, d_model=d, d_ff=f, experts=E)
+        assert p.geometry.launches == (2 if mode == "1" else 3)
+        res = []
+        for _ in range(3):
+            p.launch_and_wait(stream, 20000)
+            res.append(CO.to_host_vec(stream).copy())
+        assert all((bits(r) == bits(res[0])).all() for r in res)
+        outs[mode] = res[0]
+    accepted = int(routing["expert_offsets"][E]) * d
+    assert accepted > 0 and (bits(outs["0"][:accepted]) == bits(outs["1"][:accepted])).all()
 
 
 # ------------------------------------------------------------ adapter surface
