@@ -32,8 +32,11 @@ constexpr int UMMA_K = 16;
 constexpr int kStages = 4;
 constexpr int kEpilogueWarps = 8;
 constexpr int kThreads = 32 * (2 + kEpilogueWarps);
-constexpr int kGatherThreads = 64;   // two more warps when A is gathered row by row (they fit the block's register allocation,
-                                     // which is made for twelve warps anyway: registers go out to four warps at a time)
+constexpr int kGatherThreads = 128;  // four more warps when A is gathered row by row: fourteen warps count as sixteen in
+                                     // the register file (registers go out to four warps at a time), which the
+                                     // 128-register build of the kernel fills exactly; with two loader warps on the
+                                     // 168-register build the gathered GEMM was 6 % slower than the one fed by TMA
+                                     // and gained 11-18 us per MoE pass against the compaction pass, with four 40 us
 constexpr int kGroupM = 16;     // m-tiles per rasterisation band (keeps a wave's A and B panels in L2)
 
 template <int BN>
@@ -372,23 +375,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
     } else if (warp >= 2 + kEpilogueWarps) {
         // ------------------------------------------------ gather loaders (blocks launched with them only)
-        // 64 threads fetch the tile's 128 rows of A for every K block: thread = (row mod 8, 16-byte chunk of
-        // the row's 128 bytes), sixteen rows each, so that eight neighbouring lanes read one whole line.  The
+        // 128 threads fetch the tile's 128 rows of A for every K block: thread = (row mod 16, 16-byte chunk of
+        // the row's 128 bytes), eight rows each, so that eight neighbouring lanes read one whole line.  The
         // rows go straight into the 128-byte-swizzled stage the tensor core reads; a row that is not a route
         // (past the group's end, or a dropped slot) is filled with zeros.  Completion is signalled to the
         // stage's barrier by the copies themselves.
         const uint32_t lt = threadIdx.x - 32 * (2 + kEpilogueWarps);
-        const uint32_t chunk = lt & 7, r0 = lt >> 3;
+        const uint32_t chunk = lt & 7, r0 = lt >> 3;   // r0 in 0..15
         const uint8_t *src_base = reinterpret_cast<const uint8_t *>(p.gather_src);
         uint32_t stage = 0, phase = 0;
         bool ok = !dead;
         for (uint32_t id = blockIdx.x; ok; id += gridDim.x) {
             TileCoord t = decode_tile(id, p, n_tiles, s_off, s_pair);
             if (!t.valid) break;
-            uint32_t tok[16];
+            constexpr int kRowsPerThread = 128 * 8 / kGatherThreads;
+            uint32_t tok[kRowsPerThread];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const uint32_t row = t.m0 + r0 + 8 * i;
+            for (int i = 0; i < kRowsPerThread; ++i) {
+                const uint32_t row = t.m0 + r0 + (kGatherThreads / 8) * i;
                 const uint32_t route = row < t.m_end ? __ldg(p.gather_perm + row) : 0xffffffffu;
                 tok[i] = (route == 0xffffffffu || (route >> 1) >= p.gather_tokens) ? 0xffffffffu : (route >> 1);
             }
@@ -397,10 +401,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 const uint32_t sa = smem_u32(smem + stage * L::kStageBytes) + r0 * 128 + ((chunk ^ (r0 & 7)) << 4);
                 const uint64_t col = (uint64_t)kb * (BK * 2) + chunk * 16;
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
+                for (int i = 0; i < kRowsPerThread; ++i) {
                     const bool live = tok[i] != 0xffffffffu;
                     const uint8_t *src = live ? src_base + (uint64_t)tok[i] * p.K * 2 + col : src_base;
-                    asm volatile("cp.async.cg.shared.global.L2::256B [%0], [%1], 16, %2;" ::"r"(sa + i * 1024), "l"(src), "r"(live ? 16 : 0) : "memory");
+                    asm volatile("cp.async.cg.shared.global.L2::256B [%0], [%1], 16, %2;" ::"r"(sa + i * (kGatherThreads / 8) * 128), "l"(src), "r"(live ? 16 : 0) : "memory");
                 }
                 asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&full[stage])) : "memory");
                 if (++stage == kStages) { stage = 0; phase ^= 1; }
@@ -759,7 +763,9 @@ int32_t gemm_tc_launch(const GemmTcPlan *plan, cudaStream_t s) {
         cfg.numAttrs = 1;
     }
     cudaError_t e;
-    if (plan->overlap_previous == 1)   // shares the SMs with the small blocks of the kernel before it: the 128-register build
+    // the 128-register build: for a block that shares its SM with the small blocks of the kernel before it, and for
+    // one that carries the loader warps of a gathered A
+    if (plan->overlap_previous == 1 || plan->p.gather_perm)
         e = plan->bn == 256 ? cudaLaunchKernelEx(&cfg, gemm_tc_kernel<256, 128>, plan->tmA, plan->tmB, plan->tmC, plan->p)
                             : cudaLaunchKernelEx(&cfg, gemm_tc_kernel<128, 128>, plan->tmA, plan->tmB, plan->tmC, plan->p);
     else

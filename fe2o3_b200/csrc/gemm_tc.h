@@ -50,7 +50,7 @@ struct GemmParams {
     GemmEp ep;
     // Gathered A (first GEMM of the single-GPU expert FFN): row r of A is row (gather_perm[r] >> 1) of
     // gather_src ([gather_tokens][K] bf16), or zero when gather_perm[r] names no route; the block is then
-    // launched with two loader warps more, which fetch the rows straight into the swizzled A stage.
+    // launched with four loader warps more, which fetch the rows straight into the swizzled A stage.
     const uint32_t *gather_perm;
     const void *gather_src;
     uint32_t gather_tokens;
