@@ -145,8 +145,9 @@ NCU_TRAFFIC = {
     ("device_scan_u32", 1 << 28): 1074060800 + 1014678784,
     ("tiled_gemm_v1", (8192, 8192, 8192)): 1046762752 + 250886400,
     ("flash_attention_v1", (4, 16, 2048, 64)): 50588160 + 2605312,
-    # grouped FFN GEMMs of one pass, average of the two launches (GEMM-1 501 MB, GEMM-2 880 MB)
-    ("moe_top2_v1", (16384, 2048, 4096, 8)): (268686848 + 232546560 + 642772480 + 236861952) // 2,
+    # grouped FFN GEMMs of one pass, average of the two launches (GEMM-1, which gathers its rows of x, 483 MB;
+    # GEMM-2 897 MB)
+    ("moe_top2_v1", (16384, 2048, 4096, 8)): (250602496 + 232169472 + 659651072 + 237435904) // 2,
 }
 
 
@@ -504,10 +505,9 @@ def wl_moe(h, steps, warmup, cpu=True, exchange="auto", **shape):
     # stores rows into their memory, so it cannot run outside a pass); waiting time is included.
     n_ffn = max(3, min(steps, 10))
     if layer.exchange == "none":
-        ffn = fe.prepare(h.ctx, "moe_grouped_ffn_v1", compact_x=layer.compact_x, w1=layer.w1, w2=layer.w2,
-                         group_offsets=layer.offsets, hidden=layer.hidden, compact_output=layer.compact_out, d_model=d,
-                         d_ff=f, groups=E, experts_cycle=E)
-        ffn_ms = float(np.mean(h.time_steps(lambda: ffn.launch(h.stream), n_ffn, 3, flush=False)))
+        # the layer's own prepared expert FFN (its first GEMM gathers the rows of x through the permutation of
+        # the pass just run), launched alone
+        ffn_ms = float(np.mean(h.time_steps(lambda: layer.k_ffn.launch(h.stream), n_ffn, 3, flush=False)))
     else:
         marks = [(fe.Event(h.ctx), fe.Event(h.ctx)) for _ in range(n_ffn + 3)]
         h.barrier()
@@ -524,7 +524,7 @@ def wl_moe(h, steps, warmup, cpu=True, exchange="auto", **shape):
            "roofline": {**roofline("tensor", ffn_tf, peaks["bf16_tflops"], "TFLOP/s",
                                    traffic=NCU_TRAFFIC.get(("moe_top2_v1", (T, d, f, E))) if h.world == 1 else None,
                                    peak_source=peaks["source"]),
-                        "kernel": "gemm_tc_kernel<256>, the two grouped FFN GEMMs (two launches" +
+                        "kernel": "gemm_tc_kernel<256>, the two grouped FFN GEMMs of the pass (two launches" +
                                   (", timed alone)" if layer.exchange == "none" else ", timed inside eager passes, waits for other ranks included)"),
                         "rows": ffn_rows, "ms_per_pair": ffn_ms,
                         "whole_pass": {"achieved": flops / (step_ms * 1e-3) / 1e12 / h.world,
