@@ -145,9 +145,9 @@ NCU_TRAFFIC = {
     ("device_scan_u32", 1 << 28): 1074060800 + 1014678784,
     ("tiled_gemm_v1", (8192, 8192, 8192)): 1046762752 + 250886400,
     ("flash_attention_v1", (4, 16, 2048, 64)): 50588160 + 2605312,
-    # grouped FFN GEMMs of one pass, average of the two launches (GEMM-1, which gathers its rows of x, 483 MB;
-    # GEMM-2 897 MB)
-    ("moe_top2_v1", (16384, 2048, 4096, 8)): (250602496 + 232169472 + 659651072 + 237435904) // 2,
+    # grouped FFN GEMMs of one pass, average of the two launches (GEMM-1, which gathers its rows of x and clears
+    # the output, 629 MB; GEMM-2, which adds the weighted rows into the output, 1056 MB)
+    ("moe_top2_v1", (16384, 2048, 4096, 8)): (263091712 + 365496064 + 826510336 + 229486592) // 2,
 }
 
 
@@ -524,7 +524,7 @@ def wl_moe(h, steps, warmup, cpu=True, exchange="auto", **shape):
            "roofline": {**roofline("tensor", ffn_tf, peaks["bf16_tflops"], "TFLOP/s",
                                    traffic=NCU_TRAFFIC.get(("moe_top2_v1", (T, d, f, E))) if h.world == 1 else None,
                                    peak_source=peaks["source"]),
-                        "kernel": "gemm_tc_kernel<256>, the two grouped FFN GEMMs of the pass (two launches" +
+                        "kernel": "gemm_tc_kernel<256>, the two grouped FFN GEMMs of the pass, combine included (two launches" +
                                   (", timed alone)" if layer.exchange == "none" else ", timed inside eager passes, waits for other ranks included)"),
                         "rows": ffn_rows, "ms_per_pair": ffn_ms,
                         "whole_pass": {"achieved": flops / (step_ms * 1e-3) / 1e12 / h.world,

@@ -51,6 +51,9 @@ MoeExpertFfnArgs = _struct("MoeExpertFfnArgs", ["x", "w1", "w2", "permutation", 
                            [("tokens", u32), ("d_model", u32), ("d_ff", u32), ("experts", u32)])
 MoeCombineArgs = _struct("MoeCombineArgs", ["compact_output", "inverse", "route_weights", "combined_output"],
                          [("tokens", u32), ("width", u32)])
+MoeExpertFfnCombineArgs = _struct("MoeExpertFfnCombineArgs", ["x", "w1", "w2", "permutation", "expert_offsets",
+                                                              "route_weights", "hidden", "combined_output"],
+                                  [("tokens", u32), ("d_model", u32), ("d_ff", u32), ("experts", u32)])
 MoeCompactArgs = _struct("MoeCompactArgs", ["x", "permutation", "compact_x"], [("tokens", u32), ("d_model", u32)])
 MoeGroupedFfnArgs = _struct("MoeGroupedFfnArgs", ["compact_x", "w1", "w2", "group_offsets", "hidden", "compact_output"],
                             [("d_model", u32), ("d_ff", u32), ("groups", u32), ("experts_cycle", u32)])
@@ -118,6 +121,7 @@ OPS = {
     "moe_expert_combine_v1": (MoeCombineArgs, 72, False),
     "moe_compact_v1": (MoeCompactArgs, 56, False),
     "moe_grouped_ffn_v1": (MoeGroupedFfnArgs, 112, False),
+    "moe_expert_ffn_combine_v1": (MoeExpertFfnCombineArgs, 144, False),
     "moe_ep_exchange_v1": (MoeEpExchangeArgs, 296, False),
     "moe_ep_ffn_v1": (MoeEpFfnArgs, 216, False),
     "masked_reduce_u32": (MaskedReduceArgs, 48, False),

@@ -90,7 +90,7 @@ enum OpId : uint32_t {
     OP_MOE_GATE, OP_MOE_ROUTE_WEIGHTS, OP_MOE_EXPERT_FFN, OP_MOE_COMBINE, OP_MASKED_REDUCE, OP_MASKED_REDUCE_PACKED,
     OP_WAVE_LDS, OP_WAVE64_COLLECTIVES, OP_WAVE64_SEGMENTED, OP_LDS_REDUCE_I32, OP_SCOPED_ATOMIC_ADD,
     OP_MOE_COMPACT, OP_MOE_GROUPED_FFN, OP_MOE_EP_EXCHANGE, OP_DEVICE_SCAN_U32, OP_DEVICE_SCAN_F32, OP_MOE_EP_FFN,
-    OP_COUNT
+    OP_MOE_FFN_COMBINE, OP_COUNT
 };
 
 struct OpInfo {
@@ -123,6 +123,7 @@ static const OpInfo kOps[OP_COUNT] = {
     {"device_scan_sum_u32", sizeof(fe2o3_device_scan_u32_args), launch_device_scan_u32},
     {"device_scan_sum_f32", sizeof(fe2o3_device_scan_f32_args), launch_device_scan_f32},
     {"moe_ep_ffn_v1", sizeof(fe2o3_moe_ep_ffn_v1_args), nullptr},
+    {"moe_expert_ffn_combine_v1", sizeof(fe2o3_moe_expert_ffn_combine_v1_args), nullptr},
 };
 
 struct fe2o3_prepared {
@@ -446,6 +447,23 @@ int regions_for(uint32_t op, const void *args, Region *r, int32_t *status) {
             r[7] = RGN("CompactOutput", a->compact_output, rows * a->d_model, 4, true);
             return 8;
         }
+        case OP_MOE_FFN_COMBINE: {
+            const fe2o3_moe_expert_ffn_combine_v1_args *a = static_cast<const fe2o3_moe_expert_ffn_combine_v1_args *>(args);
+            if (a->d_model == 0 || a->d_ff == 0 || (a->d_model % 64) || (a->d_ff % 8) || a->experts < 1 || a->experts > 32) {
+                *status = unsupported("d_model a positive multiple of 64, d_ff of 8; 1 <= experts <= 32");
+                return 0;
+            }
+            const uint64_t rows = a->permutation.len;
+            r[0] = RGN("X", a->x, (uint64_t)a->tokens * a->d_model, 2, false);
+            r[1] = RGN("W1", a->w1, (uint64_t)a->experts * a->d_model * a->d_ff, 2, false);
+            r[2] = RGN("W2", a->w2, (uint64_t)a->experts * a->d_ff * a->d_model, 2, false);
+            r[3] = RGN("Permutation", a->permutation, rows, 4, false);
+            r[4] = RGN("ExpertOffsets", a->expert_offsets, a->experts + 1, 4, false);
+            r[5] = RGN("RouteWeights", a->route_weights, 2ull * a->tokens, 4, false);
+            r[6] = RGN("Hidden", a->hidden, rows * a->d_ff, 2, true);
+            r[7] = RGN("CombinedOutput", a->combined_output, (uint64_t)a->tokens * a->d_model, 4, true);
+            return 8;
+        }
         case OP_MOE_COMPACT: {
             const fe2o3_moe_compact_v1_args *a = static_cast<const fe2o3_moe_compact_v1_args *>(args);
             if (a->d_model == 0 || (a->d_model % 8)) { *status = unsupported("d_model must be a positive multiple of 8"); return 0; }
@@ -720,6 +738,13 @@ int32_t launch_prepared(fe2o3_prepared *p, cudaStream_t s) {
                 st = launch_moe_compact(s, a->x.ptr, a->permutation.ptr, a->compact_x.ptr, rows, a->d_model, a->tokens);
             if (st != FE2O3_OK) return st;
             st = gemm_tc_launch(&p->gemm[0], s);
+            if (st != FE2O3_OK) return st;
+            return gemm_tc_launch(&p->gemm[1], s);
+        }
+        case OP_MOE_FFN_COMBINE: {
+            const fe2o3_moe_expert_ffn_combine_v1_args *a = reinterpret_cast<const fe2o3_moe_expert_ffn_combine_v1_args *>(p->kernarg);
+            (void)a;   // (the first GEMM clears the output the second one adds into)
+            int32_t st = gemm_tc_launch(&p->gemm[0], s);
             if (st != FE2O3_OK) return st;
             return gemm_tc_launch(&p->gemm[1], s);
         }
@@ -1396,6 +1421,37 @@ int32_t fe2o3_moe_expert_ffn_v1_prepare(fe2o3_ctx *ctx, const fe2o3_moe_expert_f
     return FE2O3_OK;
 }
 
+int32_t fe2o3_moe_expert_ffn_combine_v1_check(const fe2o3_moe_expert_ffn_combine_v1_args *args) {
+    return check_op(OP_MOE_FFN_COMBINE, args);
+}
+int32_t fe2o3_moe_expert_ffn_combine_v1_prepare(fe2o3_ctx *ctx, const fe2o3_moe_expert_ffn_combine_v1_args *a,
+                                                fe2o3_prepared **out) {
+    int32_t st = prepare_common(ctx, OP_MOE_FFN_COMBINE, a, out);
+    if (st != FE2O3_OK) return st;
+    fe2o3_prepared *p = *out;
+    const uint32_t rows = (uint32_t)a->permutation.len;
+    const uint32_t *off = reinterpret_cast<const uint32_t *>(a->expert_offsets.ptr);
+    const uint32_t *perm = reinterpret_cast<const uint32_t *>(a->permutation.ptr);
+    // A of the first GEMM is gathered (the address given for A only makes a valid tensor map: x itself)
+    st = gemm_tc_plan(ctx, &p->gemm[0], a->x.ptr, a->w1.ptr, a->hidden.ptr, rows, a->d_ff, a->d_model,
+                      a->d_model, a->d_ff, a->d_ff, 1.f, 0.f, EPI_GELU_BF16, off, a->experts);
+    if (st == FE2O3_OK)
+        st = gemm_tc_plan(ctx, &p->gemm[1], a->hidden.ptr, a->w2.ptr, a->combined_output.ptr, rows, a->d_model, a->d_ff,
+                          a->d_ff, a->d_model, a->d_model, 1.f, 0.f, EPI_COMBINE_ADD, off, a->experts);
+    if (st != FE2O3_OK) return fail_prepare(out, st);
+    if (!gemm_tc_set_gather(&p->gemm[0], perm, reinterpret_cast<const void *>(a->x.ptr), a->tokens)) {
+        fe2o3_set_error("Unsupported{x must be 16-byte aligned with whole 64-column blocks}");
+        return fail_prepare(out, FE2O3_ERR_UNSUPPORTED_SHAPE);
+    }
+    gemm_tc_set_combine(&p->gemm[1], perm, reinterpret_cast<const float *>(a->route_weights.ptr), a->tokens);
+    // the second GEMM adds into the output, which starts from +0: cleared by the first GEMM's idle epilogue warps
+    p->gemm[0].p.zero_ptr = reinterpret_cast<uint4 *>(a->combined_output.ptr);
+    p->gemm[0].p.zero_vecs = (uint64_t)a->tokens * a->d_model / 4;
+    gemm_tc_geometry(&p->gemm[0], &p->geo);
+    p->geo.launches = 2;
+    return FE2O3_OK;
+}
+
 int32_t fe2o3_moe_compact_v1_check(const fe2o3_moe_compact_v1_args *args) { return check_op(OP_MOE_COMPACT, args); }
 int32_t fe2o3_moe_grouped_ffn_v1_check(const fe2o3_moe_grouped_ffn_v1_args *args) {
     return check_op(OP_MOE_GROUPED_FFN, args);
@@ -1630,6 +1686,7 @@ int32_t fe2o3_launch_and_wait(fe2o3_executable *exe, uint32_t kernel_id, const f
         case OP_MOE_COMPACT: st = fe2o3_moe_compact_v1_prepare(exe->ctx, (const fe2o3_moe_compact_v1_args *)kernarg, &p); break;
         case OP_MOE_GROUPED_FFN: st = fe2o3_moe_grouped_ffn_v1_prepare(exe->ctx, (const fe2o3_moe_grouped_ffn_v1_args *)kernarg, &p); break;
         case OP_MOE_EP_FFN: st = fe2o3_moe_ep_ffn_v1_prepare(exe->ctx, (const fe2o3_moe_ep_ffn_v1_args *)kernarg, &p); break;
+        case OP_MOE_FFN_COMBINE: st = fe2o3_moe_expert_ffn_combine_v1_prepare(exe->ctx, (const fe2o3_moe_expert_ffn_combine_v1_args *)kernarg, &p); break;
         default:
             st = prepare_common(exe->ctx, kernel_id, kernarg, &p);
             if (st == FE2O3_OK) st = finish_simple(p);

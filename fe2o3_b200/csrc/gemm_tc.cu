@@ -431,6 +431,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         uint32_t it = 0;
         bool ok = !dead;
         bool store_pending = false;
+        if (p.zero_ptr && !dead) {
+            const uint64_t stride = (uint64_t)gridDim.x * (kEpilogueWarps * 32);
+            for (uint64_t i = (uint64_t)blockIdx.x * (kEpilogueWarps * 32) + ew * 32 + lane; i < p.zero_vecs; i += stride)
+                p.zero_ptr[i] = make_uint4(0u, 0u, 0u, 0u);
+        }
         for (uint32_t id = blockIdx.x; ok; id += gridDim.x, ++it) {
             TileCoord t = decode_tile(id, p, n_tiles, s_off, s_pair);
             if (!t.valid) break;
@@ -451,6 +456,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     dst_row = s_peer[meta.y] + (unsigned long long)meta.x * p.N * sizeof(float);
                 else
                     kstatus_set(p.status, FE2O3_KSTATUS_SLOT_RANGE);
+            }
+            float row_weight = 0.0f;
+            if (p.epilogue == EPI_COMBINE_ADD && row_ok) {
+                // where this lane's row is added and with which weight: route id of the slot, the token's two
+                // weights checked like the separate combine does (finite, non-negative, summing to exactly 1)
+                const uint32_t route = __ldg(p.combine_perm + row);
+                if (route != 0xffffffffu && (route >> 1) < p.combine_tokens) {
+                    const float w0 = __ldg(p.combine_weights + (route & ~1u)), w1 = __ldg(p.combine_weights + (route | 1u));
+                    if (!isfinite(w0) || !isfinite(w1) || w0 < 0.f || w1 < 0.f || __fadd_rn(w0, w1) != 1.0f) {
+                        kstatus_set(p.status, FE2O3_KSTATUS_WEIGHTS);
+                    } else {
+                        dst_row = reinterpret_cast<unsigned long long>(p.c) + (unsigned long long)(route >> 1) * p.N * sizeof(float);
+                        row_weight = (route & 1u) ? w1 : w0;
+                    }
+                }
             }
             if (out_bf16) {
                 // ---- GELU, bf16 output: two chunks (64 columns) per 128-byte group
@@ -516,7 +536,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     }
                     const uint32_t col = col_base + g * 32;
                     if (col >= p.N) continue;
-                    if (p.epilogue == EPI_SCATTER_PEER) {
+                    if (p.epilogue == EPI_SCATTER_PEER || p.epilogue == EPI_COMBINE_ADD) {
                         // Every row of the tile has its own destination (the return buffer of its home
                         // rank, at its route id).  The chunk is transposed through the warp's slice of
                         // shared memory so that each store instruction writes four whole 128-byte
@@ -533,8 +553,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                             const uint32_t rr = it * 4 + (lane >> 3);
                             const uint4 v = *reinterpret_cast<const uint4 *>(slice + rr * 128 + ((piece ^ (rr & 7)) * 16));
                             const unsigned long long dst = __shfl_sync(0xffffffffu, dst_row, rr);
-                            if (dst != 0 && col + piece * 4 < p.N)
-                                *reinterpret_cast<uint4 *>(dst + (unsigned long long)(col + piece * 4) * sizeof(float)) = v;
+                            const float wgt = __shfl_sync(0xffffffffu, row_weight, rr);
+                            if (dst != 0 && col + piece * 4 < p.N) {
+                                const unsigned long long at = dst + (unsigned long long)(col + piece * 4) * sizeof(float);
+                                if (p.epilogue == EPI_COMBINE_ADD)   // weight * row (one rounding), then one addition per element
+                                    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(at),
+                                                 "f"(__fmul_rn(wgt, __uint_as_float(v.x))), "f"(__fmul_rn(wgt, __uint_as_float(v.y))),
+                                                 "f"(__fmul_rn(wgt, __uint_as_float(v.z))), "f"(__fmul_rn(wgt, __uint_as_float(v.w)))
+                                                 : "memory");
+                                else
+                                    *reinterpret_cast<uint4 *>(at) = v;
+                            }
                         }
                     } else if (bulk && p.epilogue == EPI_STORE) {
                         if (store_pending) {
@@ -714,7 +743,7 @@ int32_t gemm_tc_plan(fe2o3_ctx *ctx, GemmTcPlan *plan, uint64_t a, uint64_t b, u
     const uint32_t esize = epilogue == EPI_GELU_BF16 ? 2u : 4u;
     uint32_t bulk = 0;
     plan->tmC = plan->tmA;   // a valid map when the bulk path is off (never used then)
-    if (epilogue != EPI_ALPHA_BETA && epilogue != EPI_SCATTER_PEER && (c & 15u) == 0 && ((uint64_t)ldc * esize) % 16u == 0 &&
+    if (epilogue != EPI_ALPHA_BETA && epilogue != EPI_SCATTER_PEER && epilogue != EPI_COMBINE_ADD && (c & 15u) == 0 && ((uint64_t)ldc * esize) % 16u == 0 &&
         M > 0 && N > 0) {
         uint64_t dC[2] = {N, M}, sC[1] = {(uint64_t)ldc * esize};
         uint32_t bC[2] = {128u / esize, 32};
@@ -723,7 +752,7 @@ int32_t gemm_tc_plan(fe2o3_ctx *ctx, GemmTcPlan *plan, uint64_t a, uint64_t b, u
         bulk = 1;
     }
     plan->p = GemmParams{reinterpret_cast<void *>(c), M, N, K, ldc, alpha, beta, epilogue, expert_offsets, experts,
-                         expert_mod, bulk, ctx->status_word, ep ? *ep : GemmEp{}, nullptr, nullptr, 0u};
+                         expert_mod, bulk, ctx->status_word, ep ? *ep : GemmEp{}, nullptr, nullptr, 0u, nullptr, nullptr, 0u, nullptr, 0ull};
     const uint32_t n_tiles = (N + plan->bn - 1) / plan->bn;
     const uint64_t m_tiles = (uint64_t)(M + BM - 1) / BM + experts;  // grouped: each expert may add a ragged tile
     uint64_t tiles = m_tiles * n_tiles;
@@ -784,6 +813,14 @@ bool gemm_tc_set_gather(GemmTcPlan *plan, const uint32_t *perm, const void *src,
     return true;
 }
 
+// Makes the plan's output a weighted accumulation into token rows (see GemmParams); the plan must have been made
+// with EPI_COMBINE_ADD and c = the [tokens][N] f32 output.
+void gemm_tc_set_combine(GemmTcPlan *plan, const uint32_t *perm, const float *weights, uint32_t tokens) {
+    plan->p.combine_perm = perm;
+    plan->p.combine_weights = weights;
+    plan->p.combine_tokens = tokens;
+}
+
 void gemm_tc_geometry(const GemmTcPlan *plan, fe2o3_geometry *geo) {
     *geo = fe2o3_geometry{{plan->grid, 1, 1}, {(uint32_t)(kThreads + (plan->p.gather_perm ? kGatherThreads : 0)), 1, 1}, plan->smem, 1};
 }
@@ -793,4 +830,5 @@ static Fe2o3KernelRegistration reg_tiled("tiled_gemm_lds_slice1", reinterpret_ca
 static Fe2o3KernelRegistration reg_general("tiled_gemm_general_v1", reinterpret_cast<const void *>(gemm_tc_kernel<256, 168>));
 static Fe2o3KernelRegistration reg_ffn("moe_expert_ffn_v1", reinterpret_cast<const void *>(gemm_tc_kernel<256, 168>));
 static Fe2o3KernelRegistration reg_gffn("moe_grouped_ffn_v1", reinterpret_cast<const void *>(gemm_tc_kernel<256, 168>));
+static Fe2o3KernelRegistration reg_ffnc("moe_expert_ffn_combine_v1", reinterpret_cast<const void *>(gemm_tc_kernel<256, 128>));
 static Fe2o3KernelRegistration reg_epffn("moe_ep_ffn_v1", reinterpret_cast<const void *>(gemm_tc_kernel<256, 168>));

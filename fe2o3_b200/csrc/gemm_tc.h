@@ -2,7 +2,7 @@
 #pragma once
 #include "common.cuh"
 
-enum GemmEpilogue : uint32_t { EPI_STORE = 0, EPI_ALPHA_BETA = 1, EPI_GELU_BF16 = 2, EPI_SCATTER_PEER = 3 };
+enum GemmEpilogue : uint32_t { EPI_STORE = 0, EPI_ALPHA_BETA = 1, EPI_GELU_BF16 = 2, EPI_SCATTER_PEER = 3, EPI_COMBINE_ADD = 4 };
 
 // Expert-parallel extensions of the grouped GEMM (all zero otherwise).  The rows of A are this rank's
 // receive buffer: `experts` contiguous segments (one per local expert), each made of `world` runs, one
@@ -54,6 +54,18 @@ struct GemmParams {
     const uint32_t *gather_perm;
     const void *gather_src;
     uint32_t gather_tokens;
+    // EPI_COMBINE_ADD (second GEMM of the single-GPU expert FFN with the combine folded in): row r is the expert
+    // output of route combine_perm[r]; it is multiplied by that route's weight and added to row (route >> 1) of
+    // c ([combine_tokens][N] f32, zero before the launch).  A token has at most two routes and the sum starts
+    // from +0, so the result does not depend on which of the two arrives first.
+    const uint32_t *combine_perm;
+    const float *combine_weights;
+    uint32_t combine_tokens;
+    // A buffer this launch clears before anything else (zero_vecs 16-byte pieces): the epilogue warps, which
+    // have nothing to do while the first tile is being multiplied, write the zeros.  The first GEMM of the fused
+    // expert FFN clears the output that the second one accumulates into.
+    uint4 *zero_ptr;
+    uint64_t zero_vecs;
 };
 
 struct GemmTcPlan {
@@ -78,4 +90,5 @@ int32_t gemm_tc_plan(fe2o3_ctx *ctx, GemmTcPlan *plan, uint64_t a, uint64_t b, u
 int32_t gemm_tc_launch(const GemmTcPlan *plan, cudaStream_t s);
 int32_t gemm_tc_init_device();
 bool gemm_tc_set_gather(GemmTcPlan *plan, const uint32_t *perm, const void *src, uint32_t tokens);
+void gemm_tc_set_combine(GemmTcPlan *plan, const uint32_t *perm, const float *weights, uint32_t tokens);
 void gemm_tc_geometry(const GemmTcPlan *plan, fe2o3_geometry *geo);

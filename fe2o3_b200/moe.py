@@ -16,6 +16,8 @@ with NCCL all-to-alls instead and needs the host for its split sizes.  torch is
 used for device memory and process-group plumbing only; every arithmetic stage
 is a kernel of libfe2o3_b200.so.
 """
+import os
+
 import numpy as np
 
 from . import SCHEDULE_AUTO, Fe2o3Error, PeerRegion, prepare  # noqa: F401
@@ -164,7 +166,17 @@ class MoeTop2Layer:
             rows, ffn_in, ffn_res, ffn_off = R, self.compact_x, self.compact_out, self.offsets
         self.hidden = z(rows * f, torch.bfloat16)
         self.rows = rows
-        if world == 1:
+        # one GPU: expert FFN and combine as one operation when the row length allows it (the first GEMM gathers
+        # its rows, the second adds the weighted rows into the output); FE2O3_MOE_FUSED_COMBINE=0 keeps the
+        # reference's separate launches
+        self.fused_combine = world == 1 and d % 64 == 0 and os.environ.get("FE2O3_MOE_FUSED_COMBINE") != "0"
+        if self.fused_combine:
+            self.k_ffns = [P("moe_expert_ffn_combine_v1", x=x, w1=self.w1, w2=self.w2, permutation=self.perm,
+                             expert_offsets=self.offsets, route_weights=self.weights, hidden=self.hidden,
+                             combined_output=out, tokens=T, d_model=d, d_ff=f, experts=E)
+                           for x, out in zip(self.xs, self.outs)]
+            self.k_ffn = self.k_ffns[0]
+        elif world == 1:
             self.k_ffns = [P("moe_expert_ffn_v1", x=x, w1=self.w1, w2=self.w2, permutation=self.perm,
                              expert_offsets=self.offsets, compact_x=self.compact_x, hidden=self.hidden,
                              compact_output=self.compact_out, tokens=T, d_model=d, d_ff=f, experts=E) for x in self.xs]
@@ -330,7 +342,8 @@ class MoeTop2Layer:
             self.k_phases[io][1].launch(s)   # combine from the local return buffer, advance the pass number
         elif self.world == 1:
             self.k_ffns[io].launch(s)
-            self.k_combines[io].launch(s)
+            if not self.fused_combine:
+                self.k_combines[io].launch(s)
         else:
             self._exchange_forward(io)
             self.k_combines[io].launch(s)

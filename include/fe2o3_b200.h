@@ -310,6 +310,24 @@ typedef struct fe2o3_moe_expert_ffn_v1_args {
     uint32_t tokens, d_model, d_ff, experts;
 } fe2o3_moe_expert_ffn_v1_args;
 
+/* The expert schedule and the combine of examples/moe_expert_v1/src/kernel.rs:104-157
+ * in one operation, for callers that do not need the expert outputs by slot:
+ * the first GEMM gathers the rows of x through `permutation`, and the second
+ * one multiplies every output row by its route's weight and adds it to the
+ * token's row of combined_output (cleared by the first GEMM).  A token has
+ * at most two routes and the sum starts from +0, so the result is the same bits
+ * as moe_expert_ffn_v1 followed by moe_expert_combine_v1, whichever route's row
+ * is added first; dropped routes contribute nothing.  A token whose weights are
+ * non-finite, negative or do not sum to exactly 1.0 records
+ * FE2O3_KSTATUS_WEIGHTS and gets no contribution (its row stays zero, where
+ * the separate combine leaves it unwritten).  rows = permutation.len;
+ * hidden [rows][d_ff] bf16 is workspace.  Needs d_model a multiple of 64
+ * (otherwise Unsupported: use the separate operations). */
+typedef struct fe2o3_moe_expert_ffn_combine_v1_args {
+    fe2o3_slice x, w1, w2, permutation, expert_offsets, route_weights, hidden, combined_output;
+    uint32_t tokens, d_model, d_ff, experts;
+} fe2o3_moe_expert_ffn_combine_v1_args;
+
 /* The two halves of the expert schedule as separate launches, for the
  * expert-parallel layout where an all-to-all sits between them.
  * moe_compact_v1: compact_x[slot,:] = x[permutation[slot]/2,:], zero rows for
@@ -494,6 +512,7 @@ int32_t fe2o3_moe_expert_ffn_v1_check(const fe2o3_moe_expert_ffn_v1_args *args);
 int32_t fe2o3_moe_expert_combine_v1_check(const fe2o3_moe_expert_combine_v1_args *args);
 int32_t fe2o3_moe_compact_v1_check(const fe2o3_moe_compact_v1_args *args);
 int32_t fe2o3_moe_grouped_ffn_v1_check(const fe2o3_moe_grouped_ffn_v1_args *args);
+int32_t fe2o3_moe_expert_ffn_combine_v1_check(const fe2o3_moe_expert_ffn_combine_v1_args *args);
 int32_t fe2o3_moe_ep_exchange_v1_check(const fe2o3_moe_ep_exchange_v1_args *args);
 int32_t fe2o3_moe_ep_ffn_v1_check(const fe2o3_moe_ep_ffn_v1_args *args);
 int32_t fe2o3_masked_reduce_u32_check(const fe2o3_masked_reduce_u32_args *args);
@@ -529,6 +548,8 @@ int32_t fe2o3_moe_expert_combine_v1_prepare(fe2o3_ctx *ctx, const fe2o3_moe_expe
 int32_t fe2o3_moe_compact_v1_prepare(fe2o3_ctx *ctx, const fe2o3_moe_compact_v1_args *args, fe2o3_prepared **out);
 int32_t fe2o3_moe_grouped_ffn_v1_prepare(fe2o3_ctx *ctx, const fe2o3_moe_grouped_ffn_v1_args *args,
                                          fe2o3_prepared **out);
+int32_t fe2o3_moe_expert_ffn_combine_v1_prepare(fe2o3_ctx *ctx, const fe2o3_moe_expert_ffn_combine_v1_args *args,
+                                                fe2o3_prepared **out);
 int32_t fe2o3_moe_ep_exchange_v1_prepare(fe2o3_ctx *ctx, const fe2o3_moe_ep_exchange_v1_args *args,
                                          fe2o3_prepared **out);
 int32_t fe2o3_moe_ep_ffn_v1_prepare(fe2o3_ctx *ctx, const fe2o3_moe_ep_ffn_v1_args *args, fe2o3_prepared **out);

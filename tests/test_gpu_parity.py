@@ -655,6 +655,27 @@ def test_expert_ffn_gathered_rows_equal_compacted_rows(gpu, orc, monkeypatch):
         outs[mode] = res[0]
     accepted = int(routing["expert_offsets"][E]) * d
     assert accepted > 0 and (bits(outs["0"][:accepted]) == bits(outs["1"][:accepted])).all()
+    # ... and with the combine folded into the second GEMM (weighted rows added into the token rows): the same
+    # bits as the separate combine kernel on those expert outputs, whichever of a token's two rows lands first
+    weights = orc.moe_route_weights(logits, routing["top2_experts"], T, E)
+    WT, INV = B(weights), B(routing["inverse"])
+    SEP = fe.DeviceBuffer.from_host(stream, np.full(T * d, np.nan, np.float32))
+    fe.prepare(ctx, "moe_expert_combine_v1", compact_output=CO, inverse=INV, route_weights=WT, combined_output=SEP,
+               tokens=T, width=d).launch_and_wait(stream, 20000)
+    want = SEP.to_host_vec(stream)
+    FUSED = fe.DeviceBuffer.from_host(stream, np.full(T * d, np.nan, np.float32))   # the operation clears it itself
+    HID2 = fe.DeviceBuffer.zeroed(stream, R * f, np.uint16)
+    p = fe.prepare(ctx, "moe_expert_ffn_combine_v1", x=X, w1=W1, w2=W2, permutation=PERM, expert_offsets=OFF,
+                   route_weights=WT, hidden=HID2, combined_output=FUSED, tokens=T, d_model=d, d_ff=f, experts=E)
+    assert p.geometry.launches == 2 and p.symbol == "moe_expert_ffn_combine_v1"
+    for _ in range(3):
+        p.launch_and_wait(stream, 20000)
+        assert p.kernel_status == 0
+        assert (bits(FUSED.to_host_vec(stream)) == bits(want)).all()
+    # a row length that is not whole 64-column blocks has no fused form
+    with pytest.raises(fe.Fe2o3Error):
+        fe.prepare(ctx, "moe_expert_ffn_combine_v1", x=X, w1=W1, w2=W2, permutation=PERM, expert_offsets=OFF,
+                   route_weights=WT, hidden=HID2, combined_output=FUSED, tokens=T * d // 72, d_model=72, d_ff=f, experts=E)
 
 
 # ------------------------------------------------------------ adapter surface
