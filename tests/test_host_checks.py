@@ -110,6 +110,17 @@ def test_attention_softmax_moe_reduction_admission():
                inclusive_output=sl(8192, 64), exclusive_output=sl(12288, 64)) == "Length"
     assert err("moe_expert_combine_v1", compact_output=sl(0, 16 * 16), inverse=sl(1 << 20, 16),
                route_weights=sl(1 << 21, 16), combined_output=sl(512, 8 * 16), tokens=8, width=16) == "OutputAliasesInput"
+    # expert FFN with the combine folded in: rows = permutation.len, d_model in whole 64-column blocks
+    T, d, f, E = 8, 64, 16, 2
+    fk = dict(x=sl(0, T * d), w1=sl(1 << 20, E * d * f), w2=sl(2 << 20, E * f * d), permutation=sl(3 << 20, 2 * T),
+              expert_offsets=sl(4 << 20, E + 1), route_weights=sl(5 << 20, 2 * T), hidden=sl(6 << 20, 2 * T * f),
+              combined_output=sl(7 << 20, T * d), tokens=T, d_model=d, d_ff=f, experts=E)
+    fe.check_args("moe_expert_ffn_combine_v1", fe.make_args("moe_expert_ffn_combine_v1", **fk))
+    assert err("moe_expert_ffn_combine_v1", **{**fk, "d_model": 72, "x": sl(0, T * 72), "w1": sl(1 << 20, E * 72 * f),
+                                                "w2": sl(2 << 20, E * f * 72), "combined_output": sl(7 << 20, T * 72)}) == "UnsupportedShape"
+    assert err("moe_expert_ffn_combine_v1", **{**fk, "route_weights": sl(5 << 20, 2 * T - 1)}) == "Length"
+    assert err("moe_expert_ffn_combine_v1", **{**fk, "hidden": sl(6 << 20, 2 * T * f + 1)}) == "Length"
+    assert err("moe_expert_ffn_combine_v1", **{**fk, "combined_output": sl(64, T * d)}) == "OutputAliasesInput"
     # u64 overflow of a region is a RegionOverflow, not a wrap-around
     assert err("masked_reduce_u32", values=(BASE, 1 << 63), active=(BASE, 1 << 63), output=sl(0, 1)) == "InvalidRegion"
 
