@@ -500,14 +500,37 @@ def wl_moe(h, steps, warmup, cpu=True, exchange="auto", **shape):
     step_ms = h.max_over_ranks(float(np.mean(ms)))
     flops = T * 2 * 4.0 * d * f + 2.0 * T * d * E
     # Roofline of the dominant kernel: the two grouped FFN GEMMs of this rank on the rows the pass routed,
-    # CUDA events around the pair.  One GPU: the pair launched alone.  Several GPUs: the pair inside
-    # eager passes (its first GEMM waits in the kernel for the other ranks' rows and its second one
-    # stores rows into their memory, so it cannot run outside a pass); waiting time is included.
+    # by CUDA events.  One GPU: the pair's duration inside the timed passes, as the pass minus the same pass
+    # without the expert FFN, both replayed from CUDA graphs; beside it the pair replayed alone from a graph
+    # of its own, which is slower (its first GEMM then finds no token rows in L2 and the GPU stays at its power
+    # limit).  Several GPUs: the pair inside passes launched kernel by kernel (its first GEMM waits in the
+    # kernel for the other ranks' rows and its second one stores rows into their memory, so it cannot run
+    # outside a pass); that waiting is included.
     n_ffn = max(3, min(steps, 10))
-    if layer.exchange == "none":
-        # the layer's own prepared expert FFN (its first GEMM gathers the rows of x through the permutation of
-        # the pass just run), launched alone
+    ffn_in_pass_ms = None
+    if layer.exchange == "nccl":
         ffn_ms = float(np.mean(h.time_steps(lambda: layer.k_ffn.launch(h.stream), n_ffn, 3, flush=False)))
+    elif h.world == 1 and layer.exchange == "none" and graphed:
+        side = torch.cuda.Stream()
+        pair_graph = torch.cuda.CUDAGraph()
+        torch.cuda.synchronize()
+        with torch.cuda.graph(pair_graph, stream=side):
+            layer.k_ffn.launch(h.ctx.wrap_stream(side.cuda_stream))
+        ffn_ms = float(np.mean(h.time_steps(pair_graph.replay, n_ffn, 3, flush=False)))
+        # ... and what the pair takes inside the pass: the pass minus the same pass without the expert FFN
+        # (gate, routing, route weights), both replayed from CUDA graphs.  Inside the pass the first GEMM finds
+        # the token rows in L2 (the gate has just read them) and the GPU is not at its power limit throughout.
+        rest_graph = torch.cuda.CUDAGraph()
+        torch.cuda.synchronize()
+        with torch.cuda.graph(rest_graph, stream=side):
+            ss = h.ctx.wrap_stream(side.cuda_stream)
+            layer.k_gate.launch(ss)
+            layer.k_top2.launch(ss)
+            layer.k_weights.launch(ss)
+            if not layer.fused_combine:
+                layer.k_combine.launch(ss)
+        rest_ms = float(np.mean(h.time_steps(rest_graph.replay, n_ffn, 3, flush=False)))
+        ffn_in_pass_ms = float(np.mean(ms)) - rest_ms
     else:
         marks = [(fe.Event(h.ctx), fe.Event(h.ctx)) for _ in range(n_ffn + 3)]
         h.barrier()
@@ -516,6 +539,8 @@ def wl_moe(h, steps, warmup, cpu=True, exchange="auto", **shape):
         h.barrier()
         ffn_ms = float(np.mean([e.elapsed_time_ms_since(b) for b, e in marks[3:]]))
     ffn_rows = int(layer.ffn_rows())
+    ffn_alone_ms = ffn_ms if ffn_in_pass_ms else None
+    ffn_ms = ffn_in_pass_ms or ffn_ms   # the duration inside the timed region where it could be measured
     ffn_tf = ffn_rows * 4.0 * d * f / (ffn_ms * 1e-3) / 1e12
     sms = int(h.ctx.observe_environment().multiprocessors)
     m_tiles = -(-ffn_rows // 128) + (E // h.world)   # upper bound: one ragged tile per expert segment
@@ -525,8 +550,15 @@ def wl_moe(h, steps, warmup, cpu=True, exchange="auto", **shape):
                                    traffic=NCU_TRAFFIC.get(("moe_top2_v1", (T, d, f, E))) if h.world == 1 else None,
                                    peak_source=peaks["source"]),
                         "kernel": "gemm_tc_kernel<256>, the two grouped FFN GEMMs of the pass, combine included (two launches" +
-                                  (", timed alone)" if layer.exchange == "none" else ", timed inside eager passes, waits for other ranks included)"),
+                                  ("; duration inside the timed passes = pass minus the same pass without the expert FFN, both replayed "
+                                   "from CUDA graphs; the pair replayed alone, where the first GEMM finds no token rows in L2, is "
+                                   "given beside it)" if ffn_alone_ms else
+                                   ", timed inside passes launched kernel by kernel, waits for other ranks included)"),
                         "rows": ffn_rows, "ms_per_pair": ffn_ms,
+                        "frac_of_sustained_peak": ffn_tf / peaks["bf16_tflops_sustained"],
+                        "ms_per_pair_replayed_alone": ffn_alone_ms,
+                        "frac_replayed_alone": (ffn_rows * 4.0 * d * f / (ffn_alone_ms * 1e-3) / 1e12 / peaks["bf16_tflops"])
+                        if ffn_alone_ms else None,
                         "whole_pass": {"achieved": flops / (step_ms * 1e-3) / 1e12 / h.world,
                                        "peak": peaks["bf16_tflops_sustained"],
                                        "frac": flops / (step_ms * 1e-3) / 1e12 / h.world / peaks["bf16_tflops_sustained"],

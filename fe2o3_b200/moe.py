@@ -325,8 +325,8 @@ class MoeTop2Layer:
 
     def forward(self, stream=None, ffn_marks=None, io=0):
         """Enqueues one layer pass on `stream` (default: the layer's stream) over buffer pair `io` and returns
-        the output tensor.  `ffn_marks`: optional (begin, end) events recorded around the expert FFN of the
-        peer exchange."""
+        the output tensor.  `ffn_marks`: optional (begin, end) events recorded around the expert FFN (one GPU, or
+        the peer exchange)."""
         s = stream or self.stream
         self.k_gates[io].launch(s)
         self.k_top2.launch(s)
@@ -341,7 +341,11 @@ class MoeTop2Layer:
                 ffn_marks[1].record(s)
             self.k_phases[io][1].launch(s)   # combine from the local return buffer, advance the pass number
         elif self.world == 1:
+            if ffn_marks:
+                ffn_marks[0].record(s)
             self.k_ffns[io].launch(s)
+            if ffn_marks:
+                ffn_marks[1].record(s)
             if not self.fused_combine:
                 self.k_combines[io].launch(s)
         else:
