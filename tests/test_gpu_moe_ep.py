@@ -77,6 +77,38 @@ def test_peer_path_single_rank(gpu, orc, shape, capacity):
     assert ctx.take_kernel_status(stream) == 0 and _close(out, want)
 
 
+@pytest.mark.parametrize("shape,capacity", [((512, 128, 256, 8), None), ((700, 192, 320, 4), 260), ((300, 136, 256, 8), None)])
+def test_single_gpu_layer_fused_and_separate_schedules_agree(gpu, orc, monkeypatch, shape, capacity):
+    """One GPU: the layer runs gate, routing, route weights and the expert FFN with the combine folded in
+    (six launches); with FE2O3_MOE_FUSED_COMBINE=0, or a row length that is not whole 64-column blocks, it
+    runs the reference's schedule (compaction or gathered rows, two GEMMs, combine kernel).  Same bits, both
+    replayed from CUDA graphs over two input/output buffer pairs, and the oracle's result within tolerance."""
+    fe, ctx, stream = gpu
+    import torch
+    from fe2o3_b200.moe import MoeTop2Layer
+    T, d, f, E = shape
+    x, wg, w1, w2 = _inputs(T, d, f, E)
+    outs = {}
+    for mode in ("1", "0"):
+        monkeypatch.setenv("FE2O3_MOE_FUSED_COMBINE", mode)
+        layer = MoeTop2Layer(ctx, stream, T, d, f, E, capacity=capacity, io_sets=2)
+        assert layer.fused_combine == (mode == "1" and d % 64 == 0)
+        layer.load(x, wg, w1, w2)
+        layer.xs[1].copy_(layer.xs[0])
+        first = layer.forward().cpu().numpy().copy()
+        assert ctx.take_kernel_status(stream) == 0
+        assert layer.capture()
+        for io in (0, 1, 0):
+            layer.outs[io].fill_(float("nan"))
+            got = layer.replay(io=io).cpu().numpy()
+            torch.cuda.synchronize()
+            assert (got.view(np.uint32) == first.view(np.uint32)).all()
+        outs[mode] = first
+    assert (outs["0"].view(np.uint32) == outs["1"].view(np.uint32)).all()
+    _, want = _oracle_rank(orc, x, wg, w1, w2, T, d, f, E, T * 2 if capacity is None else capacity)
+    assert _close(outs["1"].reshape(T, d), want)
+
+
 class VirtualRanks:
     """W ranks of the peer exchange in one process on one GPU, stepped stage by stage."""
 
