@@ -297,7 +297,11 @@ typedef struct fe2o3_moe_route_weights_v1_args {
 
 /* Expert schedule of examples/moe_expert_v1/src/pipeline.rs:166-270 (compact ->
  * GEMM per expert -> compact rows) with the expert widened to
- * GELU(x*W1)*W2.  x [tokens][d_model] bf16, w1 [E][d_model][d_ff] bf16,
+ * GELU(x*W1)*W2 (GELU in its erf form; the kernel evaluates erf by Abramowitz &
+ * Stegun 7.1.26, absolute error below 1.5e-7, before the hidden activation is
+ * rounded to bf16, whose step is 4e-3 relative; the oracle uses the C library's
+ * erf: outputs agree within the stated tolerance, not bit for bit).
+ * x [tokens][d_model] bf16, w1 [E][d_model][d_ff] bf16,
  * w2 [E][d_ff][d_model] bf16, permutation/expert_offsets from routing;
  * compact_x [rows][d_model] bf16 and hidden [rows][d_ff] bf16 are
  * caller-provided workspace; compact_output [rows][d_model] f32.
