@@ -150,7 +150,6 @@ class MoeTop2Layer:
             self.k_ffn = P("moe_ep_ffn_v1", recv_x=(self._ptrs["recv_x"][me], self.max_rows * d), w1=self.w1, w2=self.w2,
                            hidden=self.hidden, recv_meta=(self._ptrs["recv_meta"][me], 2 * self.max_rows),
                            flags=(self._ptrs["flags"][me], 5 * world + 6), progress=self.progress, d_ff=f, **common)
-            self.launches_per_step = 7
             return
         self.compact_x = z(R * d, torch.bfloat16)            # local routes, expert-major
         self.compact_out = z(R * d, torch.float32)           # FFN rows back in local slot order
@@ -190,7 +189,6 @@ class MoeTop2Layer:
         self.k_combines = [P("moe_expert_combine_v1", compact_output=self.compact_out, inverse=self.inverse,
                              route_weights=self.weights, combined_output=out, tokens=T, width=d) for out in self.outs]
         self.k_combine = self.k_combines[0]
-        self.launches_per_step = 7 if world == 1 else 8
 
     # ---- peer-visible buffers ---------------------------------------------------------------
     @staticmethod
