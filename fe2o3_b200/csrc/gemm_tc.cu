@@ -404,7 +404,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 for (int i = 0; i < kRowsPerThread; ++i) {
                     const bool live = tok[i] != 0xffffffffu;
                     const uint8_t *src = live ? src_base + (uint64_t)tok[i] * p.K * 2 + col : src_base;
-                    asm volatile("cp.async.cg.shared.global.L2::256B [%0], [%1], 16, %2;" ::"r"(sa + i * (kGatherThreads / 8) * 128), "l"(src), "r"(live ? 16 : 0) : "memory");
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(sa + i * (kGatherThreads / 8) * 128), "l"(src), "r"(live ? 16 : 0) : "memory");
                 }
                 asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&full[stage])) : "memory");
                 if (++stage == kStages) { stage = 0; phase ^= 1; }
