@@ -1,6 +1,9 @@
 """Builds libfe2o3_b200.so in-tree with nvcc for sm_100a.
 
-Usage: python fe2o3_b200/build.py [--force] [--verbose]
+Usage: python fe2o3_b200/build.py [--force] [--verbose] [--trace]
+
+--trace builds a second library, libfe2o3_b200_trace.so, whose kernels record device time stamps
+(-DFE2O3_EP_TRACE -DFE2O3_ATTN_TRACE); FE2O3_B200_LIB selects it, fe2o3_b200/trace.py reads the stamps.
 """
 import os
 import subprocess
@@ -27,7 +30,14 @@ def _stale(target, deps):
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force=False, verbose=False):
+def build(force=False, verbose=False, trace=False):
+    if trace:
+        return _build(force, verbose, os.path.join(HERE, "build_trace"), os.path.join(HERE, "libfe2o3_b200_trace.so"),
+                      ["-DFE2O3_EP_TRACE", "-DFE2O3_ATTN_TRACE"])
+    return _build(force, verbose, OBJ, OUT, [])
+
+
+def _build(force, verbose, OBJ, OUT, extra):
     os.makedirs(OBJ, exist_ok=True)
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
     headers.append(os.path.join(HERE, "..", "include", "fe2o3_b200.h"))
@@ -39,7 +49,7 @@ def build(force=False, verbose=False):
 
     def compile_one(job):
         src, obj = job
-        cmd = [NVCC] + FLAGS + ["-c", os.path.join(CSRC, src), "-o", obj]
+        cmd = [NVCC] + FLAGS + extra + ["-c", os.path.join(CSRC, src), "-o", obj]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"nvcc failed for {src}:\n{r.stdout}\n{r.stderr}")
@@ -61,4 +71,4 @@ def build(force=False, verbose=False):
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, trace="--trace" in sys.argv))

@@ -111,6 +111,34 @@ __device__ __forceinline__ bool unit_at(const AttnParams &p, uint32_t i, Unit &u
     return true;
 }
 
+#ifdef FE2O3_ATTN_TRACE
+// Development aid, compiled in only with -DFE2O3_ATTN_TRACE (the library built by `build.py --trace`): SM
+// clock stamps of CTA 0's softmax warps (slot layout below) and, for every CTA, clock and wall-clock time at
+// its start and end.  Read back with fe2o3_debug_attn_trace (fe2o3_b200/trace.py prints them).
+//   [(tile*8 + block)*8 + k]          first unit, blocks 0..7: k = 0 before the S wait, 1 S here, 2 scores
+//                                     loaded, 3 maximum done, 4 exponentials done, 5 P stored, 6 arrival made
+//   [512 + (tile*8 + unit)*8 + k]     units 0..5: k = 0 begin, 1 blocks done, 2 last P*V done, 3 output done
+//   [1024 + cta*4 + k]                k = 0/1 clock64 / globaltimer at the CTA's start, 2/3 at its end
+__device__ unsigned long long g_attn_trace[2048];
+__device__ __forceinline__ void attn_stamp(uint32_t slot) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%clock64;" : "=l"(t)::"memory");
+    g_attn_trace[slot] = t;
+}
+__device__ __forceinline__ void attn_stamp_cta(uint32_t slot) {
+    unsigned long long t, ns;
+    asm volatile("mov.u64 %0, %%clock64;" : "=l"(t)::"memory");
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns)::"memory");
+    g_attn_trace[slot] = t;
+    g_attn_trace[slot + 1] = ns;
+}
+#define ATTN_STAMP(cond, slot) do { if (cond) attn_stamp(slot); } while (0)
+#define ATTN_STAMP_CTA(cond, slot) do { if (cond) attn_stamp_cta(slot); } while (0)
+#else
+#define ATTN_STAMP(cond, slot) do { } while (0)
+#define ATTN_STAMP_CTA(cond, slot) do { } while (0)
+#endif
+
 // Register re-balance between warpgroups (all four warps of a warpgroup execute it).
 template <int N>
 __device__ __forceinline__ void regs_release() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
@@ -137,6 +165,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(stagger + 1);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    ATTN_STAMP_CTA(threadIdx.x == 0 && blockIdx.x < 256, 1024 + blockIdx.x * 4);
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < Q_STAGES; ++i) {
@@ -332,6 +361,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             ++n;
             if (t >= u.nt) continue;
             const uint32_t qrow = u.q0 + t * BQ + r;   // query index inside the head
+            const bool utr = blockIdx.x == 0 && quad == 0 && lane == 0 && n <= 6;
+            const uint32_t uslot = 512 + (t * 8 + (n - 1)) * 8;
+            ATTN_STAMP(utr, uslot + 0);
             float m_ref = -INFINITY;   // exponent offset, in raw score units (identical in both halves)
             float l = 0.0f;            // this thread's share of the denominator
             bool s_early = false;      // s_full of the coming block was seen complete by the early probe
@@ -341,8 +373,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 // waits of a step are probed ahead of the long phases (S of the next block before the P
                 // store of this one, P*V of the previous block before the exponentials) and only fall
                 // back to the bounded wait when the early answer was "not yet".
+                const bool tr = blockIdx.x == 0 && ui == 0 && quad == 0 && lane == 0 && j < 8;
+                const uint32_t tslot = (t * 8 + j) * 8;
+                ATTN_STAMP(tr, tslot + 0);
                 if (!__all_sync(0xffffffffu, s_early) && !mbar_wait_warp(&s_full[t], gt & 1)) { ok = false; break; }
                 s_early = false;
+                ATTN_STAMP(tr, tslot + 1);
                 tc_fence_after();
                 // this thread's part of the score row into registers, then S is free for the next Q*K^T
                 uint32_t s[NCH][32];
@@ -352,6 +388,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&s_empty[t]);
+                ATTN_STAMP(tr, tslot + 2);
 
                 const uint32_t key0 = j * BKV;
                 const bool need_mask = (j * BKV + BKV > p.seq) || (p.causal && j * BKV + BKV - 1 > u.q0 + t * BQ);
@@ -394,6 +431,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 // the sums) is divided out with the denominator at the end.
                 const bool pv_early = j > 0 && mbar_test(&pv_done[t], (gt - 1) & 1);
                 const float mcb = mc - kTruncBiasLog2;
+                ATTN_STAMP(tr && mcb < 1e30f, tslot + 3);
                 const uint64_t c2 = pack_f32x2(c, c), nmc2 = pack_f32x2(-mcb, -mcb);
                 uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};   // four pairs of +0.0f
                 uint32_t pk[NCH][16];
@@ -446,18 +484,23 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     }
                 }
                 l = fmaf(l, factor, (sum[0] + sum[1]) + (sum[2] + sum[3]));
+                ATTN_STAMP(tr && l < 1e38f, tslot + 4);
                 if (j + 1 < u.nkv) s_early = mbar_test(&s_full[t], (gt + 1) & 1);
                 // P as packed bf16 pairs into tensor memory: 16 columns per 32 keys
 #pragma unroll
                 for (int ch = 0; ch < NCH; ++ch) tmem_st_32x32b_x16(tP + ch * 16, pk[ch]);
                 tmem_st_wait();
+                ATTN_STAMP(tr, tslot + 5);
                 // publish P and any O rescale (both TMEM stores) to the MMA issuer
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&p_ready[t]);
+                ATTN_STAMP(tr, tslot + 6);
             }
             if (!ok) break;
+            ATTN_STAMP(utr, uslot + 1);
             if (!mbar_wait_warp(&pv_done[t], (gt - 1) & 1)) { ok = false; break; }
+            ATTN_STAMP(utr, uslot + 2);
             tc_fence_after();
             const float l_row = l;
             // Output.  The unit's Q tile is dead once its last Q*K^T has completed (the s_full wait above
@@ -504,11 +547,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             // the next unit's first P*V overwrites O: order this thread's reads of O before its p_ready arrival
             tc_fence_before();
             __syncwarp();
+            ATTN_STAMP(utr, uslot + 3);
         }
         if (!ok && lane == 0) kstatus_set(p.status, FE2O3_KSTATUS_WAIT_EXPIRED);
     }
     tc_fence_before();
     __syncthreads();
+    ATTN_STAMP_CTA(threadIdx.x == 0 && blockIdx.x < 256, 1024 + blockIdx.x * 4 + 2);
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, kTmemCols);
@@ -588,5 +633,12 @@ void attention_tc_geometry(const AttnTcPlan *plan, fe2o3_geometry *geo) {
 }
 
 void attention_tc_free(AttnTcPlan *plan) { delete plan; }
+
+#ifdef FE2O3_ATTN_TRACE
+// copies the 2048 stamps of the last launches to `out` (trace builds only; not part of the ABI header)
+extern "C" int32_t fe2o3_debug_attn_trace(unsigned long long *out) {
+    return cudaMemcpyFromSymbol(out, g_attn_trace, sizeof(unsigned long long) * 2048) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 static Fe2o3KernelRegistration reg_attention("flash_attention_v1", reinterpret_cast<const void *>(attention_tc_kernel));
