@@ -2,12 +2,14 @@
 
     FE2O3_B200_LIB=fe2o3_b200/libfe2o3_b200_trace.so python -m fe2o3_b200.trace attention
     FE2O3_B200_LIB=fe2o3_b200/libfe2o3_b200_trace.so python -m fe2o3_b200.trace moe_peer
+    FE2O3_B200_LIB=$PWD/fe2o3_b200/libfe2o3_b200_trace.so python -m torch.distributed.run --nnodes=1 \
+        --nproc-per-node N --master-addr 127.0.0.1 --master-port 29713 -m fe2o3_b200.trace moe_ranks
 
 `attention`: SM-clock stamps of CTA 0's softmax warps through the phases of a key block and through its
 units, and every CTA's cycles and wall-clock time (csrc/attention_tc.cu, FE2O3_ATTN_TRACE).
 `moe_peer`: the timeline of one pass of the expert-parallel MoE kernels on one GPU, the rank being its own
-and only peer (csrc/moe_ep.cu and csrc/gemm_tc.cu, FE2O3_EP_TRACE; with several ranks every rank's flags
-region holds the same stamps at 64-bit words 256..271).
+and only peer (csrc/moe_ep.cu and csrc/gemm_tc.cu, FE2O3_EP_TRACE).  `moe_ranks`: the same timeline of every rank of an N-GPU run (one process per
+GPU), for one pass replayed from the CUDA graph.
 A development aid: the stamps cost a few global stores per block and are compiled out of the normal build.
 """
 import ctypes as C
@@ -105,11 +107,59 @@ def moe_peer(tokens=16384, d_model=2048, d_ff=4096, experts=8):
     assert ctx.take_kernel_status(s) == 0
 
 
+def moe_ranks(tokens=16384, d_model=2048, d_ff=4096, experts=8):
+    import os
+
+    import torch
+    import torch.distributed as dist
+
+    import fe2o3_b200 as fe
+    from fe2o3_b200 import synth
+    from fe2o3_b200.moe import MoeTop2Layer
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    ctx = fe.GpuContext(local)
+    s = ctx.default_stream()
+    t_local, per = tokens // world, experts // world
+    layer = MoeTop2Layer(ctx, s, tokens, d_model, d_ff, experts, rank=rank, world=world)
+    x = synth.normal_bf16(4, 1, tokens * d_model, 1.0)[rank * t_local * d_model:(rank + 1) * t_local * d_model]
+    layer.load(x, synth.normal_bf16(4, 2, d_model * experts, 0.02),
+               np.concatenate([synth.normal_bf16(4, 100 + e, d_model * d_ff, 0.02) for e in range(rank * per, (rank + 1) * per)]),
+               np.concatenate([synth.normal_bf16(4, 200 + e, d_ff * d_model, 0.02) for e in range(rank * per, (rank + 1) * per)]))
+    layer.forward()
+    torch.cuda.synchronize()
+    dist.barrier()
+    assert layer.capture()
+    for _ in range(30):
+        layer.replay()
+    torch.cuda.synchronize()
+
+    class Raw:   # the stamps live behind the flags of this rank's flags region: 64-bit words 256...
+        def __init__(self, ptr, n):
+            self.__cuda_array_interface__ = {"shape": (n,), "typestr": "<i8", "data": (ptr, False), "version": 2}
+    tr = torch.as_tensor(Raw(layer._ptrs["flags"][rank] + 2048, len(EP_STAMPS)), device="cuda").cpu().numpy()
+    rel = {n: round((int(tr[i]) - int(tr[0])) / 1000.0, 1) for i, n in enumerate(EP_STAMPS) if tr[i] > 0}
+    everyone = [None] * world
+    dist.all_gather_object(everyone, (rank, rel))
+    if rank == 0:
+        print("us after each rank's dispatch kernel started:")
+        for r, v in everyone:
+            print("rank", r, v)
+    assert ctx.take_kernel_status(s) == 0
+    dist.barrier()
+    layer.close()
+    dist.destroy_process_group()
+
+
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else ""
     if what == "attention":
         attention()
     elif what == "moe_peer":
         moe_peer()
+    elif what == "moe_ranks":
+        moe_ranks()
     else:
         raise SystemExit(__doc__)
