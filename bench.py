@@ -486,6 +486,7 @@ def wl_moe(h, steps, warmup, cpu=True, exchange="auto", **shape):
     layer = MoeTop2Layer(h.ctx, h.stream, T, d, f, E, rank=h.rank, world=h.world, io_sets=2, exchange=exchange)
     x, wg, w1, w2 = moe_inputs(h.rank, h.world, T, d, f, E)
     layer.load(x, wg, w1, w2)
+    h.barrier()      # the ranks have prepared their inputs at different speeds: start the first pass together
     l0 = fe.launch_count()
     layer.forward()  # one eager pass: first-launch set-up happens outside any capture
     h.barrier()
